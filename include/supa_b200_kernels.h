@@ -1,0 +1,267 @@
+/*
+ * supa_b200_kernels.h -- C ABI of the B200 (sm_100a) kernel library behind the
+ * torch-supa operator hot path.
+ *
+ * Every entry point is a plain `extern "C"` launcher: POD descriptors, raw device
+ * pointers, sizes and a CUDA stream.  Launchers are asynchronous on the given stream,
+ * never allocate, never synchronise, never change the current device and are
+ * thread-safe.  They return 0 on success or a negative sb_status.  Errors found in the
+ * *data* on the device (an out-of-range class index) are never a trap: the kernel sets
+ * bits in a caller-supplied status word and treats the row as ignored; the host reads
+ * the word at its next natural synchronisation point.
+ *
+ * Each declaration names the reference interface it replaces; paths are relative to the
+ * torch-supa source tree.
+ */
+#ifndef SUPA_B200_KERNELS_H_
+#define SUPA_B200_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_API __attribute__((visibility("default")))
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer; NULL is the legacy
+ * default stream. */
+typedef void* sb_stream_t;
+
+typedef enum sb_status {
+  SB_OK = 0,
+  SB_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, bad enum value */
+  SB_ERR_UNSUPPORTED = -2,      /* dtype / op combination that has no kernel */
+  SB_ERR_CUDA = -3,             /* the launch itself failed (cudaGetLastError) */
+  SB_ERR_TOO_LARGE = -4,        /* a size beyond what the entry point documents */
+  SB_ERR_MISALIGNED = -5        /* pointer not aligned to its element size */
+} sb_status;
+
+/* Element types.  The numbering is private to this library (the ATen shim maps
+ * c10::ScalarType onto it). */
+typedef enum sb_dtype {
+  SB_BOOL = 0,
+  SB_U8 = 1,
+  SB_I8 = 2,
+  SB_I16 = 3,
+  SB_I32 = 4,
+  SB_I64 = 5,
+  SB_F16 = 6,
+  SB_BF16 = 7,
+  SB_F32 = 8,
+  SB_F64 = 9,
+  SB_DTYPE_COUNT = 10
+} sb_dtype;
+
+/* Bits of the device status word. */
+#define SB_STATUS_TARGET_OUT_OF_RANGE 0x1 /* a class index outside [0, classes) and != ignore_index */
+
+typedef enum sb_reduction { SB_REDUCTION_NONE = 0, SB_REDUCTION_MEAN = 1, SB_REDUCTION_SUM = 2 } sb_reduction;
+
+/* Library identification: version string and the SM architecture the kernels were built for. */
+SB_API const char* sb_version(void);
+SB_API int sb_built_for_sm(void);
+/* Human-readable text for an sb_status. */
+SB_API const char* sb_status_string(int status);
+/* sizeof one element of `dtype`, 0 if unknown. */
+SB_API size_t sb_dtype_size(int dtype);
+
+/* ------------------------------------------------------------------------------------------
+ * Cross entropy (class-index targets), forward and backward in one sweep.
+ *
+ * Replaces cross_entropy_loss_2d_kernel_supa and its kernel family
+ * (torch_supa/csrc/aten/ops/kernels/elementwise/CrossEntropyLossKernel.cu:71-195,580-749) and the
+ * backward chain nll_loss_backward -> _log_softmax_backward_data of
+ * CrossEntropyLossFastPathFunction (torch_supa/csrc/aten/ops/CrossEntropyLoss.cpp:94-135), plus the
+ * ignore_index / label_smoothing arithmetic of the upstream composite the reference falls back to
+ * (CrossEntropyLoss.cpp:50).
+ *
+ * Protocol for reduction = mean / sum on one or several GPUs (acc is two doubles on the device:
+ * acc[0] = loss sum, acc[1] = number of rows whose target != ignore_index):
+ *   1. sb_ce_count_valid      -> acc[1]            (then all-reduce acc[1] when rows are sharded)
+ *   2. sb_ce_forward_backward -> row_loss, grad    (reads acc[1] for the 1/|V| scale of `mean`)
+ *   3. sb_ce_loss_sum         -> acc[0]            (then all-reduce acc[0] when rows are sharded)
+ *   4. sb_ce_loss_finish      -> loss scalar in the logits' dtype
+ * For reduction = none only step 2 is needed and row_loss is the result.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct sb_ce_args {
+  const void* logits;      /* [rows, classes], row-major, row stride = classes elements */
+  int32_t dtype;           /* SB_F32, SB_BF16 or SB_F16 (math is fp32 for all three) */
+  int32_t reduction;       /* sb_reduction: selects the gradient scale (mean: 1/acc[1]; sum, none: 1) */
+  const int64_t* target;   /* [rows] class indices; rows equal to ignore_index contribute nothing */
+  void* grad_logits;       /* [rows, classes] same dtype as logits, or NULL for forward only.
+                              May alias `logits` (in-place gradient). */
+  float* row_loss;         /* [rows] per-row loss, 0 for ignored rows (the result for `none`) */
+  float* row_lse;          /* [rows] per-row log-sum-exp, or NULL */
+  const float* row_grad_out; /* [rows] upstream gradient per row (for `none`), or NULL for 1 */
+  const double* acc;       /* device pointer to {loss_sum, valid_count}; acc[1] is read when
+                              reduction == mean and grad_logits != NULL.  May be NULL otherwise. */
+  int64_t rows;
+  int64_t classes;
+  int64_t ignore_index;
+  float label_smoothing;   /* in [0, 1] */
+  float grad_scale;        /* extra host-side factor on the gradient (the upstream scalar, usually 1) */
+  int32_t* status;         /* device status word, OR-ed with SB_STATUS_* bits; may be NULL */
+} sb_ce_args;
+
+/* Counts rows with target != ignore_index into acc[1] (as a double) and zeroes acc[0]; flags
+ * out-of-range targets in *status.  Replaces the `counts[row]` side buffer of
+ * cross_entropy_index_mean_kernel (CrossEntropyLossKernel.cu:121-162). */
+SB_API int sb_ce_count_valid(const int64_t* target, int64_t rows, int64_t classes, int64_t ignore_index,
+                             double* acc, int32_t* status, sb_stream_t stream);
+
+/* The fused sweep (see protocol above). */
+SB_API int sb_ce_forward_backward(const sb_ce_args* args, sb_stream_t stream);
+
+/* acc[0] = sum(row_loss[0..rows)) in a fixed order (bit-reproducible; no float atomics, unlike the
+ * atomicAdd of cross_entropy_index_kernel, CrossEntropyLossKernel.cu:113). */
+SB_API int sb_ce_loss_sum(const float* row_loss, int64_t rows, double* acc, sb_stream_t stream);
+
+/* loss = acc[0] / acc[1] for mean (NaN when acc[1] == 0, as
+ * cross_entropy_finalize_mean_buffer_kernel, CrossEntropyLossKernel.cu:164-195), acc[0] for sum;
+ * written as one element of `dtype` at `out`. */
+SB_API int sb_ce_loss_finish(const double* acc, int32_t reduction, void* out, int32_t dtype, sb_stream_t stream);
+
+/* sb_ce_loss_sum followed by sb_ce_loss_finish in one launch (single-GPU case: no all-reduce between). */
+SB_API int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* acc, int32_t reduction, void* out,
+                                 int32_t dtype, sb_stream_t stream);
+
+/* grad[i, :] *= factor where factor = *scale / *applied (both device floats); *applied = *scale
+ * afterwards.  A no-op sweep is skipped on the device when the factor is exactly 1.  Used by the
+ * autograd node when the upstream gradient of a mean/sum loss is not 1. */
+SB_API int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype,
+                              float* applied, sb_stream_t stream);
+
+/* Which kernel family sb_ce_forward_backward will use for this shape: 0 = generic two-sweep rows,
+ * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
+ * of 2/4 CTAs.  For diagnostics and benchmarks. */
+SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
+
+/* ------------------------------------------------------------------------------------------
+ * log_softmax / nll_loss as separate operators.
+ *
+ * Replace the kernels behind aten::_log_softmax(.out), aten::_log_softmax_backward_data(.out),
+ * aten::nll_loss_forward(.output) and aten::nll_loss_backward(.grad_input) that the reference takes
+ * from its external native-op library (call sites: torch_supa/csrc/aten/ops/CrossEntropyLoss.cpp:76,79,127,132).
+ * The tensor is viewed as [outer, dim, inner] with the softmax taken over `dim`.
+ * ------------------------------------------------------------------------------------------ */
+SB_API int sb_log_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer,
+                                  int64_t dim, int64_t inner, sb_stream_t stream);
+/* grad_in = grad_out - exp(out) * sum_dim(grad_out) */
+SB_API int sb_log_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in,
+                                   int32_t grad_in_dtype, int64_t outer, int64_t dim, int64_t inner,
+                                   sb_stream_t stream);
+
+typedef struct sb_nll_args {
+  const void* log_probs;  /* [rows, classes] contiguous */
+  int32_t dtype;          /* SB_F32, SB_BF16, SB_F16, SB_F64 */
+  int32_t target_dtype;   /* SB_I64 or SB_U8 */
+  const void* target;     /* [rows] */
+  const void* weight;     /* [classes] in `dtype`, or NULL */
+  int64_t rows;
+  int64_t classes;
+  int64_t ignore_index;
+  int32_t reduction;
+  int32_t* status;
+} sb_nll_args;
+/* output: [rows] for none, one element otherwise; total_weight: one element (sum of the weights of
+ * the rows that count).  Both in args->dtype. */
+SB_API int sb_nll_loss_forward(const sb_nll_args* args, void* output, void* total_weight, sb_stream_t stream);
+/* grad_input[rows, classes] = 0 except [i, target_i] = -w * g (/ total_weight for mean). */
+SB_API int sb_nll_loss_backward(const sb_nll_args* args, const void* grad_output, const void* total_weight,
+                                void* grad_input, sb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * TensorIterator-style elementwise engine.
+ *
+ * Replaces gpu_kernel / gpu_kernel_impl and its launch policies
+ * (torch_supa/csrc/aten/ops/kernels/elementwise/Loops.cuh:110-134, CUDALoops.cuh:382-937) together with the
+ * functors of add (UfuncCUDA_add.cu:77-341), mul (BinaryMulKernel.cu:25-43) and the gelu / silu / glu
+ * stubs of the external native-op library.  Operand 0 is the output.  Shapes arrive already broadcast
+ * (stride 0) and coalesced, fastest dimension first, strides in ELEMENTS of the operand's own dtype.
+ * Arithmetic runs in the op-math type of `common_dtype` (fp32 for fp16/bf16) and is cast to the
+ * output dtype on store, as Loops.cuh:176-209 does.
+ * ------------------------------------------------------------------------------------------ */
+#define SB_MAX_DIMS 25
+#define SB_MAX_OPERANDS 4
+
+typedef enum sb_ew_op {
+  SB_EW_COPY = 0,          /* out = cast(in0) */
+  SB_EW_FILL = 1,          /* out = scalar */
+  SB_EW_ADD = 2,           /* out = in0 + alpha * in1      (bool: logical or) */
+  SB_EW_MUL = 3,           /* out = in0 * in1              (bool: logical and) */
+  SB_EW_SUB = 4,           /* out = in0 - alpha * in1 */
+  SB_EW_DIV = 5,           /* out = in0 / in1 (true division, floating compute types) */
+  SB_EW_GELU_ERF = 6,      /* unary */
+  SB_EW_GELU_TANH = 7,     /* unary */
+  SB_EW_SILU = 8,          /* unary */
+  SB_EW_GLU = 9,           /* out = in0 * sigmoid(in1) */
+  SB_EW_GELU_ERF_BWD = 10, /* out = in0(grad) * gelu'(in1(self)) */
+  SB_EW_GELU_TANH_BWD = 11,
+  SB_EW_SILU_BWD = 12,     /* out = in0(grad) * silu'(in1(self)) */
+  SB_EW_GLU_BWD_A = 13,    /* out = sigmoid(in1(b)) * in0(grad)                      (gradient of the first half) */
+  SB_EW_GLU_BWD_B = 14,    /* out = (1 - s) * s * in0(grad) * in2(a), s = sigmoid(in1(b)) (gradient of the second half) */
+  SB_EW_ADD_SCALAR = 15,   /* out = in0 + alpha * scalar */
+  SB_EW_MUL_SCALAR = 16,   /* out = in0 * scalar */
+  SB_EW_NEG = 17,          /* unary */
+  SB_EW_OP_COUNT = 18
+} sb_ew_op;
+
+typedef struct sb_ew_desc {
+  int32_t op;            /* sb_ew_op */
+  int32_t ndim;          /* 1..SB_MAX_DIMS (a 0-dim tensor is ndim 1, size 1) */
+  int32_t noperands;     /* outputs + inputs, 1..SB_MAX_OPERANDS; operand 0 is the output */
+  int32_t common_dtype;  /* dtype the arithmetic is defined on (result of type promotion) */
+  int64_t sizes[SB_MAX_DIMS];
+  int64_t strides[SB_MAX_OPERANDS][SB_MAX_DIMS]; /* elements; 0 = broadcast */
+  void* data[SB_MAX_OPERANDS];
+  int32_t dtype[SB_MAX_OPERANDS];
+  double alpha;          /* add/sub scale when the compute type is floating */
+  int64_t ialpha;        /* add/sub scale when the compute type is integral */
+  double scalar;         /* FILL / *_SCALAR operand (floating compute types) */
+  int64_t iscalar;       /* FILL / *_SCALAR operand (integral and bool compute types) */
+} sb_ew_desc;
+
+SB_API int sb_elementwise(const sb_ew_desc* desc, sb_stream_t stream);
+/* Which launch path the engine picks for this descriptor: 0 contiguous-vectorised, 1 row-vectorised
+ * (unit inner stride, broadcast/strided outer dims), 2 tiled 2-D transpose, 3 generic strided. */
+SB_API int sb_elementwise_path(const sb_ew_desc* desc);
+
+/* ------------------------------------------------------------------------------------------
+ * Reductions.
+ *
+ * Replaces gpu_reduce_kernel / ReduceOp / setReduceConfig
+ * (torch_supa/csrc/aten/ops/kernels/reduce/Reduce.cuh:220-224,400-476,1040-1333) for sum_kernel_cuda
+ * (ReduceSumKernel.cu:80-113), mean_kernel_cuda (ReduceMomentKernel.cu:16-55) and the amax stub of the
+ * external native-op library.  Dimensions fastest first; a reduced dimension has out_stride 0.
+ * Accumulation is fp32 for fp16/bf16/fp32 inputs, fp64 for fp64, int64 for integers; amax is exact and
+ * propagates NaN.
+ * ------------------------------------------------------------------------------------------ */
+typedef enum sb_reduce_op { SB_RED_SUM = 0, SB_RED_MEAN = 1, SB_RED_AMAX = 2, SB_RED_AMIN = 3, SB_RED_OP_COUNT = 4 } sb_reduce_op;
+
+typedef struct sb_reduce_desc {
+  int32_t op;        /* sb_reduce_op */
+  int32_t ndim;      /* 1..SB_MAX_DIMS */
+  int32_t in_dtype;
+  int32_t out_dtype;
+  int64_t sizes[SB_MAX_DIMS];
+  int64_t in_strides[SB_MAX_DIMS];  /* elements */
+  int64_t out_strides[SB_MAX_DIMS]; /* elements; 0 on reduced dimensions */
+  const void* in;
+  void* out;
+  void* scratch;        /* device scratch of at least sb_reduce_scratch_bytes(desc) bytes, or NULL if that is 0 */
+  size_t scratch_bytes;
+} sb_reduce_desc;
+
+/* Scratch the launch needs (only when one output is split over several CTAs); 0 for most shapes. */
+SB_API size_t sb_reduce_scratch_bytes(const sb_reduce_desc* desc);
+SB_API int sb_reduce(const sb_reduce_desc* desc, sb_stream_t stream);
+/* 0 = inner-contiguous rows, 1 = rows split over several CTAs (two stage), 2 = outer (column) reduce,
+ * 3 = generic. */
+SB_API int sb_reduce_path(const sb_reduce_desc* desc);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* SUPA_B200_KERNELS_H_ */

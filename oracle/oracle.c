@@ -1,0 +1,220 @@
+/*
+ * oracle.c -- CPU restatement of the operator hot path, used ONLY as the checker.
+ *
+ * TEST INFRASTRUCTURE.  Nothing under torch_supa_b200/ loads, links or calls this file; the tests,
+ * the smoke check and the benchmark's CPU-baseline leg do.
+ *
+ * Every function restates, in plain C with double accumulation, the arithmetic of one piece of the
+ * torch-supa operator path.  Paths are relative to the torch-supa source tree.  The reference's
+ * device code cannot be compiled outside its vendor toolchain, and its tests hold no stored vectors:
+ * they compare with PyTorch's CPU kernels (torch_supa/testing/common_utils.py:151-168,
+ * test/test_loss.py:235-276).  This restatement is therefore pinned against fixtures produced by
+ * those same PyTorch CPU kernels (tests/golden/).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#define ORACLE_API __attribute__((visibility("default")))
+
+enum { RED_NONE = 0, RED_MEAN = 1, RED_SUM = 2 };
+
+/* Row statistics as in cross_entropy_index_mean_kernel
+ * (torch_supa/csrc/aten/ops/kernels/elementwise/CrossEntropyLossKernel.cu:144-160): a max pass,
+ * a sum-of-exp pass, lse = log(sum) + max. */
+static double row_lse(const float* x, int64_t classes, double* sum_x) {
+  double m = -INFINITY, s = 0.0, sx = 0.0;
+  for (int64_t c = 0; c < classes; ++c)
+    if ((double)x[c] > m) m = (double)x[c];
+  for (int64_t c = 0; c < classes; ++c) {
+    s += exp((double)x[c] - m);
+    sx += (double)x[c];
+  }
+  if (sum_x) *sum_x = sx;
+  return log(s) + m;
+}
+
+/* Cross entropy with class-index targets.
+ *   forward : loss_i = lse_i - x[i, t_i] (CrossEntropyLossKernel.cu:157), rows with
+ *             t_i == ignore_index give 0 and do not count (:134-141); mean = sum / count, NaN when the
+ *             count is 0 (:164-195); label smoothing as in the upstream composite the reference defers
+ *             to (torch_supa/csrc/aten/ops/CrossEntropyLoss.cpp:50):
+ *             loss_i = (1 - eps) * (lse_i - x[i, t_i]) + eps / C * sum_c (lse_i - x[i, c]).
+ *   backward: the chain nll_loss_backward -> _log_softmax_backward_data of
+ *             CrossEntropyLoss.cpp:94-135, which is
+ *             grad[i, c] = (softmax[i, c] - (1 - eps) [c == t_i] - eps / C) * g / count (mean) or * g.
+ * `loss` holds 1 double (mean, sum) or `rows` doubles (none); `row_grad_out` is the per-row upstream
+ * gradient for none (NULL = 1); `grad` may be NULL.  Returns the number of out-of-range targets
+ * (those rows are treated as ignored). */
+ORACLE_API int64_t oracle_cross_entropy(const float* logits, const int64_t* target, int64_t rows, int64_t classes,
+                                        int64_t ignore_index, double label_smoothing, int reduction, double grad_out,
+                                        const double* row_grad_out, double* loss, double* grad) {
+  int64_t bad = 0;
+  double count = 0.0, total = 0.0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t t = target[i];
+    if (t != ignore_index && t >= 0 && t < classes) count += 1.0;
+  }
+  for (int64_t i = 0; i < rows; ++i) {
+    const float* x = logits + i * classes;
+    const int64_t t = target[i];
+    int ignored = (t == ignore_index);
+    if (!ignored && (t < 0 || t >= classes)) {
+      ++bad;
+      ignored = 1;
+    }
+    double li = 0.0;
+    if (!ignored) {
+      double sx;
+      const double lse = row_lse(x, classes, &sx);
+      li = (1.0 - label_smoothing) * (lse - (double)x[t]) + label_smoothing / (double)classes * ((double)classes * lse - sx);
+      if (grad) {
+        double scale = grad_out;
+        if (reduction == RED_MEAN) scale /= count;
+        if (reduction == RED_NONE && row_grad_out) scale *= row_grad_out[i];
+        for (int64_t c = 0; c < classes; ++c) {
+          double g = exp((double)x[c] - lse) - label_smoothing / (double)classes;
+          if (c == t) g -= 1.0 - label_smoothing;
+          grad[i * classes + c] = g * scale;
+        }
+      }
+    } else if (grad) {
+      for (int64_t c = 0; c < classes; ++c) grad[i * classes + c] = 0.0;
+    }
+    if (reduction == RED_NONE) loss[i] = li;
+    else total += li;
+  }
+  if (reduction == RED_MEAN) loss[0] = count > 0.0 ? total / count : NAN;
+  else if (reduction == RED_SUM) loss[0] = total;
+  return bad;
+}
+
+/* log_softmax over the middle dimension of [outer, dim, inner]: x - max - log(sum exp(x - max)),
+ * the operator behind at::log_softmax at CrossEntropyLoss.cpp:76. */
+ORACLE_API void oracle_log_softmax(const float* x, int64_t outer, int64_t dim, int64_t inner, double* out) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const float* p = x + o * dim * inner + i;
+      double m = -INFINITY, s = 0.0;
+      for (int64_t d = 0; d < dim; ++d)
+        if ((double)p[d * inner] > m) m = (double)p[d * inner];
+      for (int64_t d = 0; d < dim; ++d) s += exp((double)p[d * inner] - m);
+      const double lse = m + log(s);
+      for (int64_t d = 0; d < dim; ++d) out[o * dim * inner + d * inner + i] = (double)p[d * inner] - lse;
+    }
+}
+
+/* _log_softmax_backward_data (CrossEntropyLoss.cpp:132): grad_in = g - exp(y) * sum_dim(g). */
+ORACLE_API void oracle_log_softmax_backward(const float* g, const float* y, int64_t outer, int64_t dim, int64_t inner,
+                                            double* grad_in) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const int64_t base = o * dim * inner + i;
+      double s = 0.0;
+      for (int64_t d = 0; d < dim; ++d) s += (double)g[base + d * inner];
+      for (int64_t d = 0; d < dim; ++d)
+        grad_in[base + d * inner] = (double)g[base + d * inner] - exp((double)y[base + d * inner]) * s;
+    }
+}
+
+/* nll_loss_forward (CrossEntropyLoss.cpp:79): -w[t] x[i, t]; total_weight = sum of w[t] over counted rows. */
+ORACLE_API void oracle_nll_loss(const float* logp, const int64_t* target, const float* weight, int64_t rows,
+                                int64_t classes, int64_t ignore_index, int reduction, double* out, double* total_weight) {
+  double tot = 0.0, tw = 0.0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t t = target[i];
+    double v = 0.0;
+    if (t != ignore_index && t >= 0 && t < classes) {
+      const double w = weight ? (double)weight[t] : 1.0;
+      v = -w * (double)logp[i * classes + t];
+      tw += w;
+    }
+    if (reduction == RED_NONE) out[i] = v;
+    else tot += v;
+  }
+  if (reduction == RED_MEAN) out[0] = tot / tw;
+  else if (reduction == RED_SUM) out[0] = tot;
+  *total_weight = tw;
+}
+
+/* nll_loss_backward (CrossEntropyLoss.cpp:127). */
+ORACLE_API void oracle_nll_loss_backward(const double* grad_out, const int64_t* target, const float* weight, int64_t rows,
+                                         int64_t classes, int64_t ignore_index, int reduction, double total_weight,
+                                         double* grad_in) {
+  for (int64_t i = 0; i < rows * classes; ++i) grad_in[i] = 0.0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t t = target[i];
+    if (t == ignore_index || t < 0 || t >= classes) continue;
+    const double w = weight ? (double)weight[t] : 1.0;
+    double g = reduction == RED_NONE ? grad_out[i] : grad_out[0];
+    if (reduction == RED_MEAN) g /= total_weight;
+    grad_in[i * classes + t] = -w * g;
+  }
+}
+
+/* Row reductions with a wide accumulator (sum_functor / MeanOps / MaxNanFunctor of
+ * torch_supa/csrc/aten/ops/kernels/reduce/ReduceSumKernel.cu:80-100, ReduceMomentKernel.cu:16-35).
+ * op: 0 sum, 1 mean, 2 amax (NaN propagates), 3 amin. */
+ORACLE_API void oracle_reduce_rows(const float* x, int64_t rows, int64_t len, int op, double* out) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* p = x + r * len;
+    if (op <= 1) {
+      double s = 0.0;
+      for (int64_t i = 0; i < len; ++i) s += (double)p[i];
+      out[r] = op == 1 ? s / (double)len : s;
+    } else {
+      double m = op == 2 ? -INFINITY : INFINITY;
+      int nan = 0;
+      for (int64_t i = 0; i < len; ++i) {
+        const double v = (double)p[i];
+        if (v != v) nan = 1;
+        if (op == 2 ? v > m : v < m) m = v;
+      }
+      out[r] = nan ? NAN : m;
+    }
+  }
+}
+
+/* Elementwise functors in double.  Codes follow the kernel library's sb_ew_op numbering.
+ * add/mul: UfuncCUDA_add.cu:13-16 (self + alpha * other), BinaryInternal.h:16-29; the activations are
+ * the formulas of the ATen kernels the reference links from its native-op library. */
+static double sigmoid_d(double x) { return 1.0 / (1.0 + exp(-x)); }
+ORACLE_API double oracle_ew_scalar(int op, double a, double b, double c, double alpha) {
+  const double kBeta = 0.79788456080286535588, kKappa = 0.044715;
+  switch (op) {
+    case 0: return a;
+    case 2: return a + alpha * b;
+    case 3: return a * b;
+    case 4: return a - alpha * b;
+    case 5: return a / b;
+    case 6: return a * 0.5 * (1.0 + erf(a * 0.70710678118654752440));
+    case 7: return 0.5 * a * (1.0 + tanh(kBeta * (a + kKappa * a * a * a)));
+    case 8: return a * sigmoid_d(a);
+    case 9: return a * sigmoid_d(b);
+    case 10: {
+      const double cdf = 0.5 * (1.0 + erf(b * 0.70710678118654752440));
+      const double pdf = exp(-0.5 * b * b) * 0.39894228040143267794;
+      return a * (cdf + b * pdf);
+    }
+    case 11: {
+      const double inner = kBeta * (b + kKappa * b * b * b);
+      const double th = tanh(inner);
+      return a * (0.5 * (1.0 + th) + 0.5 * b * (1.0 - th * th) * kBeta * (1.0 + 3.0 * kKappa * b * b));
+    }
+    case 12: {
+      const double s = sigmoid_d(b);
+      return a * s * (1.0 + b * (1.0 - s));
+    }
+    case 13: return sigmoid_d(b) * a;
+    case 14: {
+      const double s = sigmoid_d(b);
+      return (1.0 - s) * s * a * c;
+    }
+    case 17: return -a;
+    default: return NAN;
+  }
+}
+ORACLE_API void oracle_elementwise(int op, const double* a, const double* b, const double* c, double alpha, int64_t n,
+                                   double* out) {
+  for (int64_t i = 0; i < n; ++i) out[i] = oracle_ew_scalar(op, a ? a[i] : 0.0, b ? b[i] : 0.0, c ? c[i] : 0.0, alpha);
+}

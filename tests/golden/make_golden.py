@@ -1,0 +1,136 @@
+"""Generates tests/golden/hotpath_golden.npz from PyTorch's CPU ATen kernels.
+
+The reference's tests keep no stored vectors; their golden is always the CPU result of the same torch
+call (torch_supa/testing/common_utils.py:151-168).  This script freezes such CPU results for small
+seeded inputs so that the C oracle and the CUDA kernels can be checked against them anywhere.
+
+Run from the repository root:  python tests/golden/make_golden.py
+"""
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+OUT = Path(__file__).resolve().parent / "hotpath_golden.npz"
+
+
+def ce_cases():
+    """(name, rows, classes, reduction, ignore_index, n_ignored, label_smoothing)"""
+    cases = []
+    for rows, classes in ((6, 130), (1, 6), (9, 1027)):
+        for red in ("mean", "sum", "none"):
+            for ign, eps in ((0, 0.0), (2, 0.0), (0, 0.1), (2, 0.1)):
+                if rows == 1 and ign:
+                    continue
+                if classes == 1027 and (red, ign, eps) not in (("mean", 2, 0.1), ("none", 0, 0.0), ("sum", 2, 0.0)):
+                    continue
+                cases.append((f"ce_{rows}x{classes}_{red}_ign{ign}_eps{int(eps * 10)}", rows, classes, red, -100, ign, eps))
+    cases.append(("ce_4x10_mean_allignored", 4, 10, "mean", -100, 4, 0.0))
+    cases.append(("ce_5x12_mean_ignoreclass2", 5, 12, "mean", 2, 0, 0.0))
+    return cases
+
+
+def main():
+    torch.manual_seed(0)
+    torch.set_num_threads(1)
+    d = {}
+    g = torch.Generator().manual_seed(0)
+    for name, rows, classes, red, ignore_index, n_ign, eps in ce_cases():
+        x = (torch.randn(rows, classes, generator=g) * 2).requires_grad_(True)
+        t = torch.randint(0, classes, (rows,), generator=g)
+        if n_ign:
+            t[torch.randperm(rows, generator=g)[:n_ign]] = ignore_index
+        loss = F.cross_entropy(x, t, ignore_index=ignore_index, label_smoothing=eps, reduction=red)
+        go = torch.randn(loss.shape, generator=g) if red == "none" else torch.tensor(0.75)
+        (grad,) = torch.autograd.grad(loss, x, go)
+        d[name + "/logits"] = x.detach().numpy()
+        d[name + "/target"] = t.numpy()
+        d[name + "/loss"] = loss.detach().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad"] = grad.numpy()
+        d[name + "/meta"] = np.array([ignore_index, eps], dtype=np.float64)
+
+    # log_softmax forward/backward over the last and a middle dimension
+    for name, shape, dim in (("lsm_last", (7, 300), 1), ("lsm_mid", (3, 17, 5), 1), ("lsm_long", (2, 2500), 1)):
+        x = (torch.randn(*shape, generator=g) * 3).requires_grad_(True)
+        y = F.log_softmax(x, dim)
+        go = torch.randn(*shape, generator=g)
+        (gi,) = torch.autograd.grad(y, x, go)
+        d[name + "/x"] = x.detach().numpy()
+        d[name + "/y"] = y.detach().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad_in"] = gi.numpy()
+        d[name + "/dim"] = np.array([dim])
+
+    # nll_loss with and without class weights
+    for name, red, use_w in (("nll_mean", "mean", False), ("nll_sum_w", "sum", True), ("nll_none_w", "none", True),
+                             ("nll_mean_w", "mean", True)):
+        logp = F.log_softmax(torch.randn(11, 23, generator=g), 1).requires_grad_(True)
+        t = torch.randint(0, 23, (11,), generator=g)
+        t[3] = -100
+        w = torch.rand(23, generator=g) + 0.5 if use_w else None
+        out = F.nll_loss(logp, t, weight=w, reduction=red)
+        go = torch.randn(out.shape, generator=g)
+        (gi,) = torch.autograd.grad(out, logp, go)
+        d[name + "/logp"] = logp.detach().numpy()
+        d[name + "/target"] = t.numpy()
+        if use_w:
+            d[name + "/weight"] = w.numpy()
+        d[name + "/out"] = out.detach().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad_in"] = gi.numpy()
+
+    # row reductions
+    r = torch.randn(9, 777, generator=g)
+    d["red/x"] = r.numpy()
+    d["red/sum"] = r.sum(-1).numpy()
+    d["red/mean"] = r.mean(-1).numpy()
+    d["red/amax"] = r.amax(-1).numpy()
+    d["red/amin"] = r.amin(-1).numpy()
+    d["red/sum_dim0"] = r.sum(0).numpy()
+    rb = r.bfloat16()
+    d["red/bf16_sum"] = rb.sum(-1).float().numpy()
+    d["red/bf16_sum_f32"] = rb.sum(-1, dtype=torch.float32).numpy()
+    d["red/bf16_mean"] = rb.mean(-1).float().numpy()
+    d["red/bf16_amax"] = rb.amax(-1).float().numpy()
+
+    # activations forward / backward
+    a = (torch.randn(5, 14, generator=g) * 2).requires_grad_(True)
+    go = torch.randn(5, 14, generator=g)
+    for key, fn in (("gelu_erf", lambda v: F.gelu(v)), ("gelu_tanh", lambda v: F.gelu(v, approximate="tanh")),
+                    ("silu", F.silu)):
+        y = fn(a)
+        (gi,) = torch.autograd.grad(y, a, go)
+        d[f"act/{key}"] = y.detach().numpy()
+        d[f"act/{key}_bwd"] = gi.numpy()
+    y = F.glu(a, -1)
+    go_glu = torch.randn(5, 7, generator=g)
+    (gi,) = torch.autograd.grad(y, a, go_glu)
+    d["act/x"] = a.detach().numpy()
+    d["act/grad_out"] = go.numpy()
+    d["act/glu"] = y.detach().numpy()
+    d["act/glu_grad_out"] = go_glu.numpy()
+    d["act/glu_bwd"] = gi.numpy()
+
+    # binary ops with promotion and broadcasting
+    p = torch.randn(4, 1, 16, generator=g).half()
+    q = torch.randn(1, 5, 16, generator=g).half()
+    d["bin/p"] = p.numpy()
+    d["bin/q"] = q.numpy()
+    d["bin/p_plus_q"] = (p + q).numpy()
+    i32 = torch.randint(-1000, 1001, (8, 8), generator=g, dtype=torch.int32)
+    f32 = torch.randn(8, 8, generator=g)
+    d["bin/i32"] = i32.numpy()
+    d["bin/f32"] = f32.numpy()
+    d["bin/i32_plus_f32"] = (i32 + f32).numpy()
+    d["bin/add_alpha"] = torch.add(f32, f32.t(), alpha=2.5).numpy()
+    d["bin/mul_t"] = (f32.t() * f32).numpy()
+    big = torch.tensor([2**31 - 1, -2**31, 7], dtype=torch.int32)
+    d["bin/int_wrap"] = (big + torch.tensor([1, -1, 3], dtype=torch.int32)).numpy()
+    np.savez_compressed(OUT, **d)
+    print("wrote", OUT, OUT.stat().st_size, "bytes,", len(d), "arrays")
+
+
+if __name__ == "__main__":
+    main()

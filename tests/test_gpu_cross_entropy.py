@@ -1,0 +1,188 @@
+"""Fused cross entropy through the C ABI against the oracle, the fixtures and PyTorch CPU (needs a GPU)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.helpers import assert_close, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(dev, logits, target, **kw):
+    from torch_supa_b200 import functional as F2
+
+    loss, grad = F2.cross_entropy_forward_backward(logits.to(dev), target.to(dev), **kw)
+    torch.cuda.synchronize()
+    return loss.float().cpu().numpy(), (None if grad is None else grad.float().cpu().numpy())
+
+
+def _ce_names(golden):
+    return sorted({k.split("/")[0] for k in golden.files if k.startswith("ce_")})
+
+
+@pytest.mark.parametrize("idx", range(32))
+def test_golden_fixtures_fp32(golden, cuda_device, idx):
+    names = _ce_names(golden)
+    if idx >= len(names):
+        pytest.skip("no such case")
+    name = names[idx]
+    red = name.split("_")[2]
+    ignore_index, eps = golden[name + "/meta"]
+    go = golden[name + "/grad_out"]
+    kw = dict(ignore_index=int(ignore_index), label_smoothing=float(eps), reduction=red)
+    if red == "none":
+        kw["row_grad_out"] = torch.from_numpy(go).to(cuda_device)
+    else:
+        kw["grad_scale"] = float(go)
+    loss, grad = _run(cuda_device, torch.from_numpy(golden[name + "/logits"]), torch.from_numpy(golden[name + "/target"]), **kw)
+    assert_close(np.atleast_1d(loss), np.atleast_1d(golden[name + "/loss"]), 2e-6, 2e-6, name + " loss")
+    # fp32: rtol 1.3e-6 is the reference's; the absolute floor is scaled to these O(1) gradients
+    assert_close(grad, golden[name + "/grad"], 1e-5, 3e-7, name + " grad")
+
+
+SHAPES = [(16, 1000), (1, 1000), (512, 1024), (512, 1027), (33, 4099), (7, 32000), (3, 50257), (64, 31), (130, 64),
+          (5, 1), (2, 128256)]
+
+
+@pytest.mark.parametrize("rows,classes", SHAPES)
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_against_oracle(cuda_device, rows, classes, reduction, dtype):
+    g = torch.Generator().manual_seed(rows * 1000003 + classes)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    if rows > 4:
+        target[torch.randperm(rows, generator=g)[: rows // 5]] = -100
+    eps = 0.1 if (rows + classes) % 2 else 0.0
+    target_before = target.clone()
+    loss, grad = _run(cuda_device, logits, target, label_smoothing=eps, reduction=reduction)
+    assert torch.equal(target, target_before)
+    eloss, egrad, bad = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, eps, reduction)
+    assert bad == 0
+    if dtype == torch.float32:
+        assert_close(np.atleast_1d(loss), eloss, 2e-6, 2e-6, "loss")
+        scale = max(1.0, float((target != -100).sum())) if reduction == "mean" else 1.0
+        assert_close(grad * scale, egrad * scale, 1e-5, 3e-7, "grad (scaled to per-row magnitude)")
+    else:
+        # 16-bit: the oracle result cast to the dtype, rtol 1.6e-2 (bf16) / 1e-3 (fp16) plus rounding of the cast
+        rtol = 1.6e-2 if dtype == torch.bfloat16 else 2e-3
+        if reduction == "none":
+            assert_close(loss, eloss, 2e-6, 2e-6, "row loss (fp32 output)")
+        else:
+            assert rel_err(loss, eloss[0]) <= 1e-2
+        scale = max(1.0, float((target != -100).sum())) if reduction == "mean" else 1.0
+        assert_close(grad * scale, egrad * scale, rtol, 1e-4 if dtype == torch.bfloat16 else 2e-5, "grad")
+    ignored = (target == -100).numpy()
+    assert np.all(grad[ignored] == 0), "ignored rows must have an exactly zero gradient"
+
+
+def test_matches_pytorch_cpu_fp32_config1_slice(cuda_device):
+    """A 256-row slice of the fp32 [4096, 32000] configuration against F.cross_entropy on the CPU."""
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(256, 32000, generator=g) * 2
+    target = torch.randint(0, 32000, (256,), generator=g)
+    loss, grad = _run(cuda_device, logits, target)
+    ref_loss, ref_grad = oracle.aten_cross_entropy(logits, target)
+    assert rel_err(loss, ref_loss) <= 1e-5
+    assert_close(grad * 256, ref_grad.numpy() * 256, 1e-5, 3e-7, "grad")
+
+
+def test_all_rows_ignored(cuda_device):
+    logits = torch.randn(4, 10)
+    target = torch.full((4,), -100)
+    loss, grad = _run(cuda_device, logits, target, reduction="mean")
+    assert np.isnan(loss)
+    assert np.all(grad == 0)
+    loss, _ = _run(cuda_device, logits, target, reduction="sum")
+    assert loss == 0
+    loss, _ = _run(cuda_device, logits, target, reduction="none")
+    assert np.all(loss == 0)
+
+
+def test_ignore_index_may_be_a_valid_class(cuda_device):
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(9, 12, generator=g)
+    target = torch.randint(0, 12, (9,), generator=g)
+    target[:3] = 2
+    loss, grad = _run(cuda_device, logits, target, ignore_index=2)
+    eloss, egrad, _ = oracle.c_cross_entropy(logits.numpy(), target.numpy(), 2, 0.0, "mean")
+    assert_close(np.atleast_1d(loss), eloss, 2e-6, 2e-6, "loss")
+    assert np.all(grad[:3] == 0)
+
+
+def test_out_of_range_target_sets_status_and_does_not_trap(cuda_device):
+    from torch_supa_b200 import capi, functional as F2
+
+    logits = torch.randn(6, 8).to(cuda_device)
+    target = torch.tensor([1, 2, 8, 3, -7, 0]).to(cuda_device)
+    ws = F2.CrossEntropyWorkspace(6, cuda_device)
+    loss, grad = F2.cross_entropy_forward_backward(logits, target, reduction="sum", workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) & capi.STATUS_TARGET_OUT_OF_RANGE
+    assert torch.all(grad[2] == 0) and torch.all(grad[4] == 0)
+    eloss, _, bad = oracle.c_cross_entropy(logits.cpu().numpy(), target.cpu().numpy(), -100, 0.0, "sum")
+    assert bad == 2
+    assert rel_err(loss.item(), eloss[0]) <= 2e-6
+    # the context is still healthy
+    assert torch.isfinite(torch.ones(4, device=cuda_device).sum()).item()
+
+
+def test_forward_only_and_in_place_gradient(cuda_device):
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(40, 3000, generator=g) * 2).to(cuda_device)
+    target = torch.randint(0, 3000, (40,), generator=g).to(cuda_device)
+    loss_a, none = F2.cross_entropy_forward_backward(logits, target, want_grad=False)
+    assert none is None
+    loss_b, grad = F2.cross_entropy_forward_backward(logits, target)
+    buf = logits.clone()
+    loss_c, grad_inplace = F2.cross_entropy_forward_backward(buf, target, grad=buf)
+    torch.cuda.synchronize()
+    assert loss_a.item() == loss_b.item() == loss_c.item()
+    assert torch.equal(grad, grad_inplace)
+
+
+def test_results_are_bit_reproducible(cuda_device):
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(300, 5000, generator=g) * 2).bfloat16().to(cuda_device)
+    target = torch.randint(0, 5000, (300,), generator=g).to(cuda_device)
+    l1, g1 = F2.cross_entropy_forward_backward(logits, target, label_smoothing=0.1)
+    l2, g2 = F2.cross_entropy_forward_backward(logits, target, label_smoothing=0.1)
+    torch.cuda.synchronize()
+    assert l1.item() == l2.item() and torch.equal(g1, g2)
+
+
+def test_rescale_grad(cuda_device):
+    from torch_supa_b200 import capi
+
+    grad = torch.randn(1000, device=cuda_device)
+    ref = grad.clone()
+    applied = torch.ones(1, device=cuda_device)
+    for s in (1.0, 0.25, 0.25, 2.0):
+        scale = torch.tensor(s, device=cuda_device)
+        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, applied)
+        torch.cuda.synchronize()
+        assert_close(grad.cpu().numpy(), (ref * s).cpu().numpy(), 2e-7, 0, f"scale {s}")
+        assert applied.item() == s
+
+
+def test_linearity_property_full_vocab(cuda_device):
+    """Size-independent checks at the large-vocabulary row length: gradient rows sum to ~0 (softmax sums to 1,
+    the smoothed one-hot sums to 1) and the loss of row-permuted inputs is unchanged."""
+    from torch_supa_b200 import functional as F2
+
+    rows, classes = 64, 128256
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = (torch.randn(rows, classes, device=cuda_device, generator=g) * 2).bfloat16()
+    target = torch.randint(0, classes, (rows,), device=cuda_device, generator=g)
+    loss, grad = F2.cross_entropy_forward_backward(logits.float(), target, label_smoothing=0.1, reduction="sum")
+    row_sums = grad.double().sum(1)
+    assert float(row_sums.abs().max()) < 1e-4
+    perm = torch.randperm(rows, device=cuda_device)
+    loss_p, _ = F2.cross_entropy_forward_backward(logits.float()[perm].contiguous(), target[perm].contiguous(),
+                                                  label_smoothing=0.1, reduction="sum")
+    assert rel_err(loss_p.item(), loss.item()) <= 1e-6

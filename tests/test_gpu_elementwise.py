@@ -1,0 +1,235 @@
+"""Elementwise engine through the C ABI against fixtures, oracle and PyTorch CPU (needs a GPU)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: (1.3e-6, 1e-5), torch.bfloat16: (1.6e-2, 1e-5), torch.float16: (1e-3, 1e-5),
+       torch.float64: (1e-12, 1e-12)}
+SHAPES = [(16,), (1024, 512), (1023, 511), (1025, 513), (128, 2135), (3, 5, 7)]
+
+
+def _ew(dev, op, out_shape, out_dtype, *inputs, **kw):
+    from torch_supa_b200 import functional as F2
+
+    out = torch.empty(out_shape, dtype=out_dtype, device=dev)
+    F2.elementwise(op, out, *[i.to(dev) if i.device.type == "cpu" else i for i in inputs], **kw)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def _cmp(out, ref, dtype, what, loosen=1.0):
+    rtol, atol = TOL[dtype]
+    assert out.dtype == ref.dtype
+    assert_close(out.double().numpy(), ref.double().numpy(), rtol * loosen, atol * loosen, what)
+
+
+def test_fixtures(golden, cuda_device):
+    from torch_supa_b200 import capi
+
+    x = torch.from_numpy(golden["act/x"])
+    go = torch.from_numpy(golden["act/grad_out"])
+    for key, fwd, bwd in (("gelu_erf", capi.EW_GELU_ERF, capi.EW_GELU_ERF_BWD),
+                          ("gelu_tanh", capi.EW_GELU_TANH, capi.EW_GELU_TANH_BWD), ("silu", capi.EW_SILU, capi.EW_SILU_BWD)):
+        assert_close(_ew(cuda_device, fwd, x.shape, torch.float32, x).numpy(), golden[f"act/{key}"], 2e-6, 2e-6, key)
+        assert_close(_ew(cuda_device, bwd, x.shape, torch.float32, go, x).numpy(), golden[f"act/{key}_bwd"], 4e-6, 2e-6,
+                     key + " backward")
+    a, b = x[:, :7], x[:, 7:]
+    assert_close(_ew(cuda_device, capi.EW_GLU, (5, 7), torch.float32, a, b).numpy(), golden["act/glu"], 2e-6, 2e-6, "glu")
+    p, q = torch.from_numpy(golden["bin/p"]), torch.from_numpy(golden["bin/q"])
+    out = _ew(cuda_device, capi.EW_ADD, (4, 5, 16), torch.float16, p, q)
+    assert np.array_equal(out.numpy(), golden["bin/p_plus_q"]), "fp16 add is exactly rounded"
+    i32, f32 = torch.from_numpy(golden["bin/i32"]), torch.from_numpy(golden["bin/f32"])
+    out = _ew(cuda_device, capi.EW_ADD, (8, 8), torch.float32, i32, f32, common_dtype=torch.float32)
+    assert np.array_equal(out.numpy(), golden["bin/i32_plus_f32"]), "int32 + fp32 is exactly rounded"
+    out = _ew(cuda_device, capi.EW_ADD, (8, 8), torch.float32, f32, f32.t(), alpha=2.5)
+    assert_close(out.numpy(), golden["bin/add_alpha"], 1.3e-6, 1e-6, "add with alpha, transposed operand")
+    out = _ew(cuda_device, capi.EW_MUL, (8, 8), torch.float32, f32.t(), f32)
+    assert np.array_equal(out.numpy(), golden["bin/mul_t"])
+    big = torch.tensor([2**31 - 1, -2**31, 7], dtype=torch.int32)
+    out = _ew(cuda_device, capi.EW_ADD, (3,), torch.int32, big, torch.tensor([1, -1, 3], dtype=torch.int32))
+    assert np.array_equal(out.numpy(), golden["bin/int_wrap"]), "int32 overflow wraps"
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+def test_activations_forward_backward(cuda_device, shape, dtype):
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g) * 2).to(dtype)
+    go = torch.randn(*shape, generator=g).to(dtype)
+    xr = x.double().requires_grad_(True)
+    cases = [("gelu", capi.EW_GELU_ERF, capi.EW_GELU_ERF_BWD, lambda v: F.gelu(v)),
+             ("gelu_tanh", capi.EW_GELU_TANH, capi.EW_GELU_TANH_BWD, lambda v: F.gelu(v, approximate="tanh")),
+             ("silu", capi.EW_SILU, capi.EW_SILU_BWD, F.silu)]
+    for name, fwd, bwd, fn in cases:
+        y = fn(xr)
+        (gi,) = torch.autograd.grad(y, xr, go.double())
+        _cmp(_ew(cuda_device, fwd, shape, dtype, x), y.detach().to(dtype), dtype, name, loosen=2 if dtype != torch.float64 else 1e3)
+        _cmp(_ew(cuda_device, bwd, shape, dtype, go, x), gi.to(dtype), dtype, name + " backward",
+             loosen=3 if dtype != torch.float64 else 1e3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1024, 512), (1023, 510), (16, 22016)])
+def test_glu_on_strided_halves(cuda_device, shape, dtype):
+    """glu reads the two halves of the last dimension as strided views, as the SwiGLU configuration does."""
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(shape[1])
+    x = torch.randn(*shape, generator=g).to(dtype)
+    h = shape[1] // 2
+    xd = x.to(cuda_device)
+    a, b = xd[:, :h], xd[:, h:]
+    ref = F.glu(x.double(), -1)
+    _cmp(_ew(cuda_device, capi.EW_GLU, (shape[0], h), dtype, a, b), ref.to(dtype), dtype, "glu", loosen=2)
+    # silu(a) * b, the SwiGLU chain as two separately dispatched operators
+    s = _ew(cuda_device, capi.EW_SILU, (shape[0], h), dtype, a)
+    out = _ew(cuda_device, capi.EW_MUL, (shape[0], h), dtype, s, b)
+    ref2 = (F.silu(x[:, :h].float()).to(dtype).float() * x[:, h:].float()).to(dtype)
+    _cmp(out, ref2, dtype, "silu(a) * b", loosen=2)
+    go = torch.randn(shape[0], h, generator=g).to(dtype)
+    ga = _ew(cuda_device, capi.EW_GLU_BWD_A, (shape[0], h), dtype, go, b)
+    gb = _ew(cuda_device, capi.EW_GLU_BWD_B, (shape[0], h), dtype, go, b, a)
+    xr = x.double().requires_grad_(True)
+    (gi,) = torch.autograd.grad(F.glu(xr, -1), xr, go.double())
+    _cmp(torch.cat([ga, gb], 1), gi.to(dtype), dtype, "glu backward", loosen=3)
+
+
+def test_broadcast_add_fp16(cuda_device):
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(0)
+    p = torch.randn(16, 1, 4096, generator=g).half()
+    q = torch.randn(1, 64, 4096, generator=g).half()
+    out = _ew(cuda_device, capi.EW_ADD, (16, 64, 4096), torch.float16, p, q)
+    assert torch.equal(out, p + q)
+    # in-place with a broadcast `other`
+    from torch_supa_b200 import functional as F2
+
+    acc = (p + q).to(cuda_device)
+    F2.elementwise(capi.EW_ADD, acc, acc, q.to(cuda_device), alpha=2.0)
+    assert_close(acc.cpu().float().numpy(), torch.add(p + q, q, alpha=2.0).float().numpy(), 1e-3, 1e-3, "in place")
+
+
+def test_transposed_operand_mul_both_orders(cuda_device):
+    from torch_supa_b200 import capi, functional as F2
+
+    g = torch.Generator().manual_seed(1)
+    m = torch.randn(512, 256, generator=g)
+    n = torch.randn(256, 512, generator=g)
+    md, nd = m.to(cuda_device).t(), n.to(cuda_device)
+    out_rm = torch.empty(256, 512, device=cuda_device)
+    F2.elementwise(capi.EW_MUL, out_rm, nd, md)
+    assert torch.equal(out_rm.cpu(), n * m.t())
+    out_cm = torch.empty(512, 256, device=cuda_device).t()  # column-major output, as m.t() * n produces
+    F2.elementwise(capi.EW_MUL, out_cm, md, nd)
+    assert torch.equal(out_cm.cpu(), m.t() * n)
+    # as_strided operand of the reference's add test: [1, 1024, 512] with strides [524288, 1, 1024]
+    base = torch.randn(512 * 1024, generator=g)
+    v = base.as_strided((1, 1024, 512), (524288, 1, 1024))
+    w = torch.randn(1, 1024, 512, generator=g)
+    out = _ew(cuda_device, capi.EW_ADD, (1, 1024, 512), torch.float32, base.to(cuda_device).as_strided((1, 1024, 512), (524288, 1, 1024)), w)
+    assert torch.equal(out, v + w)
+
+
+@pytest.mark.parametrize("pair", [(torch.int32, torch.float32), (torch.bfloat16, torch.float32), (torch.float32, torch.float16),
+                                  (torch.int8, torch.int32), (torch.uint8, torch.int64), (torch.bool, torch.float32),
+                                  (torch.int64, torch.float64), (torch.int16, torch.bfloat16)])
+@pytest.mark.parametrize("op", ["add", "mul"])
+def test_type_promotion(cuda_device, pair, op):
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(4)
+
+    def make(dt):
+        if dt == torch.bool:
+            return torch.rand(131, 128, generator=g) > 0.5
+        if dt.is_floating_point:
+            return torch.randn(131, 128, generator=g).to(dt)
+        return torch.randint(-100 if dt != torch.uint8 else 0, 100, (131, 128), generator=g).to(dt)
+
+    a, b = make(pair[0]), make(pair[1])
+    ref = a + b if op == "add" else a * b
+    out = _ew(cuda_device, capi.EW_ADD if op == "add" else capi.EW_MUL, ref.shape, ref.dtype, a, b, common_dtype=ref.dtype)
+    assert out.dtype == ref.dtype
+    if ref.dtype.is_floating_point:
+        assert torch.equal(out, ref), "a single correctly rounded operation must match bit for bit"
+    else:
+        assert torch.equal(out, ref)
+
+
+def test_bool_and_integer_semantics(cuda_device):
+    from torch_supa_b200 import capi
+
+    a = torch.tensor([True, True, False, False])
+    b = torch.tensor([True, False, True, False])
+    assert torch.equal(_ew(cuda_device, capi.EW_ADD, (4,), torch.bool, a, b), a + b)
+    assert torch.equal(_ew(cuda_device, capi.EW_MUL, (4,), torch.bool, a, b), a * b)
+    i = torch.arange(-50, 50, dtype=torch.int16)
+    assert torch.equal(_ew(cuda_device, capi.EW_ADD, (100,), torch.int16, i, i, alpha=3), torch.add(i, i, alpha=3))
+    u = torch.arange(0, 256, dtype=torch.int32).to(torch.uint8)
+    assert torch.equal(_ew(cuda_device, capi.EW_MUL, (256,), torch.uint8, u, u), u * u)
+
+
+@pytest.mark.parametrize("src", [torch.float32, torch.float64, torch.bfloat16, torch.float16, torch.int32, torch.int64,
+                                 torch.uint8, torch.int8, torch.int16, torch.bool])
+@pytest.mark.parametrize("dst", [torch.float32, torch.float64, torch.bfloat16, torch.float16, torch.int32, torch.int64,
+                                 torch.uint8, torch.int8, torch.int16, torch.bool])
+def test_cast_copy_is_bit_exact(cuda_device, src, dst):
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(9)
+    if src == torch.bool:
+        x = torch.rand(1000, generator=g) > 0.5
+    elif src.is_floating_point:
+        x = (torch.rand(1000, generator=g) * 100).to(src)  # non-negative, in range of every target type
+    else:
+        x = torch.randint(0, 100, (1000,), generator=g).to(src)
+    out = _ew(cuda_device, capi.EW_COPY, (1000,), dst, x, common_dtype=src)
+    assert torch.equal(out, x.to(dst))
+
+
+def test_fill_and_scalar_ops(cuda_device):
+    from torch_supa_b200 import capi
+
+    out = _ew(cuda_device, capi.EW_FILL, (7, 9), torch.bfloat16, scalar=1.5, common_dtype=torch.bfloat16)
+    assert torch.equal(out, torch.full((7, 9), 1.5, dtype=torch.bfloat16))
+    out = _ew(cuda_device, capi.EW_FILL, (5,), torch.int64, scalar=-3, common_dtype=torch.int64)
+    assert torch.equal(out, torch.full((5,), -3))
+    x = torch.randn(33, 65)
+    assert torch.equal(_ew(cuda_device, capi.EW_MUL_SCALAR, x.shape, torch.float32, x, scalar=0.25), x * 0.25)
+    assert torch.equal(_ew(cuda_device, capi.EW_ADD_SCALAR, x.shape, torch.float32, x, scalar=2.0, alpha=3.0), x + 6.0)
+    assert torch.equal(_ew(cuda_device, capi.EW_NEG, x.shape, torch.float32, x), -x)
+    assert torch.equal(_ew(cuda_device, capi.EW_DIV, x.shape, torch.float32, x, x + 3), x / (x + 3))
+    assert torch.equal(_ew(cuda_device, capi.EW_SUB, x.shape, torch.float32, x, x.flip(0), alpha=0.5), torch.sub(x, x.flip(0), alpha=0.5))
+
+
+def test_many_dims_generic_path(cuda_device):
+    from torch_supa_b200 import capi, functional as F2
+
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(2, 3, 2, 3, 2, 3, 2, 3, generator=g)
+    y = torch.randn(3, 2, 3, 2, 3, 2, 3, 2, generator=g)
+    xd = x.to(cuda_device).permute(7, 6, 5, 4, 3, 2, 1, 0)
+    yd = y.to(cuda_device)
+    out = torch.empty(3, 2, 3, 2, 3, 2, 3, 2, device=cuda_device)
+    desc = capi.make_ew_desc(capi.EW_ADD, out, [xd, yd], coalesce=False)
+    assert desc.ndim == 8
+    capi.elementwise(desc)
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), x.permute(7, 6, 5, 4, 3, 2, 1, 0) + y)
+    F2.elementwise(capi.EW_MUL, out, xd, yd)
+    assert torch.equal(out.cpu(), x.permute(7, 6, 5, 4, 3, 2, 1, 0) * y)
+
+
+def test_zero_numel_is_a_no_op(cuda_device):
+    from torch_supa_b200 import capi
+
+    out = _ew(cuda_device, capi.EW_ADD, (0, 5), torch.float32, torch.empty(0, 5), torch.empty(0, 5))
+    assert out.shape == (0, 5)

@@ -1,0 +1,107 @@
+"""log_softmax and nll_loss kernels through the C ABI against fixtures, oracle and PyTorch CPU (needs a GPU)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["lsm_last", "lsm_mid", "lsm_long"])
+def test_log_softmax_fixtures(golden, cuda_device, name):
+    from torch_supa_b200 import functional as F2
+
+    dim = int(golden[name + "/dim"][0])
+    x = torch.from_numpy(golden[name + "/x"]).to(cuda_device)
+    y = F2.log_softmax(x, dim)
+    assert_close(y.cpu().numpy(), golden[name + "/y"], 2e-6, 2e-6, name)
+    gi = F2.log_softmax_backward(torch.from_numpy(golden[name + "/grad_out"]).to(cuda_device), y, dim)
+    assert_close(gi.cpu().numpy(), golden[name + "/grad_in"], 1e-5, 2e-6, name + " backward")
+
+
+@pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), -1), ((1025, 513), 0),
+                                       ((128, 2135), -1), ((6, 32000), -1), ((4, 5, 6, 7), 2), ((3, 40000), -1),
+                                       ((2, 1027), -1), ((5, 4100), -1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+def test_log_softmax_forward_backward(cuda_device, shape, dim, dtype):
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(len(shape) * 17 + shape[0])
+    x = (torch.randn(*shape, generator=g) * 3).to(dtype)
+    go = torch.randn(*shape, generator=g).to(dtype)
+    y = F2.log_softmax(x.to(cuda_device), dim)
+    ref = F.log_softmax(x.double(), dim)
+    tol = {torch.float32: (2e-6, 4e-6), torch.float64: (1e-12, 1e-12), torch.bfloat16: (1.6e-2, 1e-2),
+           torch.float16: (2e-3, 2e-3)}[dtype]
+    assert_close(y.double().cpu().numpy(), ref.numpy(), tol[0], tol[1], "forward")
+    gi = F2.log_softmax_backward(go.to(cuda_device), y, dim)
+    sumg = go.double().sum(dim, keepdim=True)
+    ref_gi = go.double() - torch.exp(y.double().cpu()) * sumg
+    mag = float(sumg.abs().max()) + 1.0
+    atol = {torch.float32: 4e-6, torch.float64: 1e-11, torch.bfloat16: 2e-2, torch.float16: 3e-3}[dtype] * mag
+    assert_close(gi.double().cpu().numpy(), ref_gi.numpy(), tol[0], atol, "backward")
+
+
+def test_log_softmax_half_to_float(cuda_device):
+    from torch_supa_b200 import functional as F2
+
+    x = torch.randn(33, 700).bfloat16()
+    y = F2.log_softmax(x.to(cuda_device), -1, out_dtype=torch.float32)
+    assert y.dtype == torch.float32
+    assert_close(y.cpu().numpy(), F.log_softmax(x.float(), -1).numpy(), 2e-6, 4e-6, "bf16 -> fp32")
+    go = torch.randn(33, 700)
+    gi = F2.log_softmax_backward(go.to(cuda_device), y, -1, input_dtype=torch.bfloat16)
+    assert gi.dtype == torch.bfloat16
+    ref = go - torch.exp(y.cpu()) * go.sum(-1, keepdim=True)
+    assert_close(gi.float().cpu().numpy(), ref.numpy(), 1.6e-2, 0.3, "backward to bf16")
+
+
+@pytest.mark.parametrize("name", ["nll_mean", "nll_sum_w", "nll_none_w", "nll_mean_w"])
+def test_nll_fixtures(golden, cuda_device, name):
+    from torch_supa_b200 import functional as F2
+
+    red = name.split("_")[1]
+    w = torch.from_numpy(golden[name + "/weight"]).to(cuda_device) if name.endswith("_w") else None
+    logp = torch.from_numpy(golden[name + "/logp"]).to(cuda_device)
+    t = torch.from_numpy(golden[name + "/target"]).to(cuda_device)
+    out, tw = F2.nll_loss_forward(logp, t, w, -100, red)
+    assert_close(np.atleast_1d(out.cpu().numpy()), np.atleast_1d(golden[name + "/out"]), 2e-6, 2e-6, name)
+    go = torch.from_numpy(np.atleast_1d(golden[name + "/grad_out"])).to(cuda_device)
+    gi = F2.nll_loss_backward(go, logp, t, w, -100, red, tw)
+    assert_close(gi.cpu().numpy(), golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
+
+
+@pytest.mark.parametrize("rows,classes", [(16, 10), (1000, 2000), (20000, 100), (100, 20000)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
+def test_nll_against_oracle(cuda_device, rows, classes, reduction, dtype):
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(rows + classes)
+    logp = F.log_softmax(torch.randn(rows, classes, generator=g), 1).to(dtype)
+    t = torch.randint(0, classes, (rows,), generator=g)
+    t[::7] = -100
+    out, tw = F2.nll_loss_forward(logp.to(cuda_device), t.to(cuda_device), None, -100, reduction)
+    eout, etw = oracle.c_nll_loss(logp.float().numpy(), t.numpy(), None, -100, reduction)
+    rtol = {torch.float32: 2e-6, torch.float64: 1e-6, torch.bfloat16: 1e-2}[dtype]
+    assert_close(np.atleast_1d(out.double().cpu().numpy()), eout, rtol, rtol, "forward")
+    if reduction != "none":
+        assert abs(float(tw) - etw) <= (0 if dtype != torch.bfloat16 else 1e-2 * etw)
+    go = torch.randn(rows if reduction == "none" else 1, generator=g).to(dtype)
+    gi = F2.nll_loss_backward(go.to(cuda_device), logp.to(cuda_device), t.to(cuda_device), None, -100, reduction, tw)
+    egi = oracle.c_nll_loss_backward(go.double().numpy(), t.numpy(), classes, None, -100, reduction, float(tw))
+    assert_close(gi.double().cpu().numpy(), egi, rtol, 0, "backward")
+    assert int((gi != 0).sum()) <= rows
+
+
+def test_nll_uint8_targets(cuda_device):
+    from torch_supa_b200 import functional as F2
+
+    logp = F.log_softmax(torch.randn(50, 200), 1)
+    t = torch.randint(0, 200, (50,), dtype=torch.uint8)
+    out, _ = F2.nll_loss_forward(logp.to(cuda_device), t.to(cuda_device), None, -100, "sum")
+    eout, _ = oracle.c_nll_loss(logp.numpy(), t.numpy().astype(np.int64), None, -100, "sum")
+    assert_close(np.atleast_1d(out.cpu().numpy()), eout, 2e-6, 2e-6, "uint8 targets")

@@ -1,0 +1,96 @@
+"""The plain-C oracle against the frozen PyTorch-CPU fixtures (CPU only)."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.helpers import assert_close
+
+
+def _ce_names(golden):
+    return sorted({k.split("/")[0] for k in golden.files if k.startswith("ce_")})
+
+
+def test_ce_cases_present(golden):
+    assert len(_ce_names(golden)) >= 20
+
+
+@pytest.mark.parametrize("idx", range(32))
+def test_cross_entropy_matches_golden(golden, idx):
+    names = _ce_names(golden)
+    if idx >= len(names):
+        pytest.skip("no such case")
+    name = names[idx]
+    red = name.split("_")[2]
+    ignore_index, eps = golden[name + "/meta"]
+    go = golden[name + "/grad_out"]
+    loss, grad, bad = oracle.c_cross_entropy(
+        golden[name + "/logits"], golden[name + "/target"], int(ignore_index), float(eps), red,
+        grad_out=1.0 if red == "none" else float(go), row_grad_out=go if red == "none" else None)
+    assert bad == 0
+    expect = np.atleast_1d(golden[name + "/loss"])
+    assert_close(loss, expect, 2e-6, 2e-6, name + " loss")
+    assert_close(grad, golden[name + "/grad"], 1e-5, 2e-7, name + " grad")
+
+
+def test_all_ignored_mean_is_nan(golden):
+    loss, grad, _ = oracle.c_cross_entropy(golden["ce_4x10_mean_allignored/logits"], golden["ce_4x10_mean_allignored/target"])
+    assert np.isnan(loss[0]) and np.isnan(golden["ce_4x10_mean_allignored/loss"])
+    assert np.all(grad == 0)
+
+
+def test_out_of_range_target_is_counted_not_fatal():
+    x = np.zeros((3, 4), dtype=np.float32)
+    loss, grad, bad = oracle.c_cross_entropy(x, np.array([1, 9, -3]), reduction="sum")
+    assert bad == 2
+    assert_close(loss, [np.log(4.0)], 1e-12, 0, "loss")
+    assert np.all(grad[1:] == 0)
+
+
+@pytest.mark.parametrize("name", ["lsm_last", "lsm_mid", "lsm_long"])
+def test_log_softmax(golden, name):
+    dim = int(golden[name + "/dim"][0])
+    y = oracle.c_log_softmax(golden[name + "/x"], dim)
+    assert_close(y, golden[name + "/y"], 2e-6, 2e-6, name)
+    gi = oracle.c_log_softmax_backward(golden[name + "/grad_out"], golden[name + "/y"], dim)
+    assert_close(gi, golden[name + "/grad_in"], 1e-5, 2e-6, name + " backward")
+
+
+@pytest.mark.parametrize("name", ["nll_mean", "nll_sum_w", "nll_none_w", "nll_mean_w"])
+def test_nll_loss(golden, name):
+    red = name.split("_")[1]
+    w = golden[name + "/weight"] if name.endswith("_w") else None
+    out, tw = oracle.c_nll_loss(golden[name + "/logp"], golden[name + "/target"], w, -100, red)
+    assert_close(out, np.atleast_1d(golden[name + "/out"]), 2e-6, 2e-6, name)
+    gi = oracle.c_nll_loss_backward(golden[name + "/grad_out"], golden[name + "/target"], 23, w, -100, red, tw)
+    assert_close(gi, golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
+
+
+def test_row_reductions(golden):
+    x = golden["red/x"]
+    assert_close(oracle.c_reduce_rows(x, "sum"), golden["red/sum"], 1e-5, 1e-5, "sum")
+    assert_close(oracle.c_reduce_rows(x, "mean"), golden["red/mean"], 1e-5, 1e-6, "mean")
+    assert np.array_equal(oracle.c_reduce_rows(x, "amax"), golden["red/amax"].astype(np.float64))
+    assert np.array_equal(oracle.c_reduce_rows(x, "amin"), golden["red/amin"].astype(np.float64))
+    xn = x.copy()
+    xn[2, 5] = np.nan
+    assert np.isnan(oracle.c_reduce_rows(xn, "amax")[2])
+
+
+def test_activations(golden):
+    x = golden["act/x"].astype(np.float64)
+    go = golden["act/grad_out"].astype(np.float64)
+    for key, fwd, bwd in (("gelu_erf", 6, 10), ("gelu_tanh", 7, 11), ("silu", 8, 12)):
+        assert_close(oracle.c_elementwise(fwd, x), golden[f"act/{key}"], 2e-6, 2e-6, key)
+        assert_close(oracle.c_elementwise(bwd, go, x), golden[f"act/{key}_bwd"], 4e-6, 2e-6, key + " backward")
+    a, b = x[:, :7], x[:, 7:]
+    assert_close(oracle.c_elementwise(9, a, b), golden["act/glu"], 2e-6, 2e-6, "glu")
+    g = golden["act/glu_grad_out"].astype(np.float64)
+    ga = oracle.c_elementwise(13, g, b)
+    gb = oracle.c_elementwise(14, g, b, a)
+    assert_close(np.concatenate([ga, gb], axis=1), golden["act/glu_bwd"], 4e-6, 2e-6, "glu backward")
+
+
+def test_binary(golden):
+    f = golden["bin/f32"].astype(np.float64)
+    assert_close(oracle.c_elementwise(2, f, f.T.copy(), alpha=2.5), golden["bin/add_alpha"], 2e-6, 2e-6, "add alpha")
+    assert_close(oracle.c_elementwise(3, f.T.copy(), f), golden["bin/mul_t"], 2e-6, 2e-6, "mul")

@@ -1,0 +1,59 @@
+// Parameter block and row arithmetic shared by the cross-entropy kernel variants.
+#pragma once
+
+#include "common.cuh"
+
+namespace sb {
+
+struct CEParams {
+  const void* logits;
+  void* grad;                // nullable
+  const int64_t* target;
+  float* row_loss;
+  float* row_lse;            // nullable
+  const float* row_grad_out; // nullable
+  const double* acc;         // {loss_sum, valid_count}
+  int64_t rows;
+  int64_t classes;
+  int64_t ignore_index;
+  float label_smoothing;
+  float grad_scale;
+  int reduction;
+  int dtype;
+  int32_t* status;           // nullable
+};
+
+// loss of one non-ignored row; sum_x is the plain sum of the row's logits.
+__device__ __forceinline__ float ce_row_loss(float lse, float x_target, float sum_x, float eps, float eps_over_c) {
+  if (eps == 0.f) return lse - x_target;  // logf(row_sum) + row_max - row_input[target]
+  return lse - (1.f - eps) * x_target - eps_over_c * sum_x;
+}
+
+// Factor applied to (softmax - smoothed one-hot) of a row.
+__device__ __forceinline__ float ce_row_scale(const CEParams& p, int64_t row) {
+  float scale = p.grad_scale;
+  if (p.reduction == SB_REDUCTION_MEAN) scale = static_cast<float>(static_cast<double>(scale) / p.acc[1]);
+  if (p.row_grad_out) scale *= p.row_grad_out[row];
+  return scale;
+}
+
+__device__ __forceinline__ void ce_store_loss(double loss_sum, double count, int reduction, void* out, int dtype) {
+  double v = loss_sum;
+  if (reduction == SB_REDUCTION_MEAN) v = count > 0.0 ? loss_sum / count : CUDART_NAN;
+  switch (dtype) {
+    case SB_F32: *static_cast<float*>(out) = static_cast<float>(v); break;
+    case SB_BF16: *static_cast<__nv_bfloat16*>(out) = __float2bfloat16_rn(static_cast<float>(v)); break;
+    case SB_F16: *static_cast<__half*>(out) = __float2half_rn(static_cast<float>(v)); break;
+    case SB_F64: *static_cast<double*>(out) = v; break;
+    default: break;
+  }
+}
+
+// Kernel families (defined in cross_entropy.cu and cross_entropy_tma.cu).
+int ce_launch_generic(const CEParams& p, cudaStream_t st);
+int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant);
+// Chooses the family for a shape: 0 generic, 1/2/4 = resident in shared memory of a 1/2/4-CTA cluster.
+int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logits, const void* grad);
+int ce_dispatch(const CEParams& p, cudaStream_t st);
+
+}  // namespace sb

@@ -1,0 +1,440 @@
+// Fused cross entropy forward + backward for class-index targets: generic row kernels and the
+// small bookkeeping kernels (valid-row count, deterministic loss sum, finish, gradient rescale).
+//
+// Row math (the same as cross_entropy_index_mean_kernel of the reference,
+// torch_supa/csrc/aten/ops/kernels/elementwise/CrossEntropyLossKernel.cu:121-162, extended with label
+// smoothing and the gradient): with lse = max + log(sum exp(x - max)),
+//   loss_i = lse - (1 - eps) * x[t_i] - (eps / C) * sum_c x_c            (0 when t_i == ignore_index)
+//   grad_ic = (exp(x_c - lse) - (1 - eps) * [c == t_i] - eps / C) * scale  (0 when t_i == ignore_index)
+// where scale = upstream / |V| for `mean` (|V| = rows that are not ignored), upstream otherwise.
+//
+// Kernels in this file read each row twice (statistics sweep, gradient sweep); the second read is
+// served by L1/L2 because a CTA (or warp) re-reads the row it has just streamed.  The variant that keeps
+// the row in shared memory lives in cross_entropy_tma.cu; ce_dispatch() chooses between them.
+#include "ce_common.cuh"
+
+namespace sb {
+
+// ---------------------------------------------------------------------------------------------
+// One CTA per row, grid-stride over rows.  VEC elements per 16-byte access when the row pitch and
+// the base pointers allow it, else VEC = 1.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS) ce_rows_cta_kernel(CEParams p) {
+  constexpr bool kAccurate = sizeof(T) == 4;
+  __shared__ float s_m[THREADS / 32];
+  __shared__ float s_s[THREADS / 32];
+  __shared__ float s_x[THREADS / 32];
+  __shared__ float s_out[3];
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int64_t C = p.classes;
+  const int64_t nvec = C / VEC;  // VEC > 1 only when C % VEC == 0
+  const float eps = p.label_smoothing;
+  const float eps_c = eps / static_cast<float>(C);
+
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* x = static_cast<const T*>(p.logits) + row * C;
+    T* g = p.grad ? static_cast<T*>(p.grad) + row * C : nullptr;
+    const int64_t t = p.target[row];
+    bool ignored = (t == p.ignore_index);
+    if (!ignored && (t < 0 || t >= C)) {
+      if (tid == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+      ignored = true;
+    }
+    if (ignored) {  // uniform over the CTA
+      if (tid == 0) {
+        p.row_loss[row] = 0.f;
+        if (p.row_lse) p.row_lse[row] = 0.f;
+      }
+      if (g) {
+        Vec<T, VEC> z;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) z.v[k] = from_float<T>(0.f);
+        for (int64_t i = tid; i < nvec; i += THREADS) store_vec<T, VEC>(g + i * VEC, z);
+      }
+      continue;
+    }
+
+    // ---- sweep 1: online (max, sum exp) and sum x ------------------------------------------
+    float m = -CUDART_INF_F, s = 0.f, sx = 0.f;
+    for (int64_t i = tid; i < nvec; i += THREADS) {
+      Vec<T, VEC> v = load_vec<T, VEC>(x + i * VEC);
+      float f[VEC];
+      float vmax = -CUDART_INF_F;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        f[k] = to_float(v.v[k]);
+        vmax = fmaxf(vmax, f[k]);
+      }
+      if (vmax > m) {
+        s *= kAccurate ? exp_accurate(m - vmax) : exp_fast(m - vmax);  // m = -inf: s is 0, exp(-inf) = 0
+        m = vmax;
+      }
+      const float mm = (m == -CUDART_INF_F) ? 0.f : m;  // keep exp(-inf - -inf) out of the sum
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        s += kAccurate ? exp_accurate(f[k] - mm) : exp_fast(f[k] - mm);
+        sx += f[k];
+      }
+    }
+    MaxSum ms = warp_merge(MaxSum{m, s});
+    sx = warp_sum(sx);
+    if (lane == 0) {
+      s_m[warp] = ms.m;
+      s_s[warp] = ms.s;
+      s_x[warp] = sx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      MaxSum a{lane < THREADS / 32 ? s_m[lane] : -CUDART_INF_F, lane < THREADS / 32 ? s_s[lane] : 0.f};
+      float b = lane < THREADS / 32 ? s_x[lane] : 0.f;
+      a = warp_merge(a);
+      b = warp_sum(b);
+      if (lane == 0) {
+        const float lse = a.m + logf(a.s);
+        const float xt = to_float(x[t]);
+        s_out[0] = lse;
+        s_out[1] = ce_row_loss(lse, xt, b, eps, eps_c);
+      }
+    }
+    __syncthreads();
+    const float lse = s_out[0];
+    if (tid == 0) {
+      p.row_loss[row] = s_out[1];
+      if (p.row_lse) p.row_lse[row] = lse;
+    }
+
+    // ---- sweep 2: gradient ---------------------------------------------------------------------
+    if (g) {
+      const float scale = ce_row_scale(p, row);
+      const float sub_all = eps_c * scale;
+      const float sub_t = (1.f - eps) * scale;
+      for (int64_t i = tid; i < nvec; i += THREADS) {
+        Vec<T, VEC> v = load_vec<T, VEC>(x + i * VEC);
+        Vec<T, VEC> o;
+        const int64_t c0 = i * VEC;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const float d = to_float(v.v[k]) - lse;
+          const float pr = kAccurate ? exp_accurate(d) : exp_fast(d);
+          float gv = fmaf(pr, scale, -sub_all);
+          if (c0 + k == t) gv -= sub_t;
+          o.v[k] = from_float<T>(gv);
+        }
+        store_vec<T, VEC>(g + c0, o);
+      }
+    }
+    __syncthreads();  // s_out is rewritten by the next row
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per row for short rows (classes <= 1024): the reference keeps a family of special
+// kernels for C <= 64 (CrossEntropyLossKernel.cu:228-530); one warp-per-row kernel covers them.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) ce_rows_warp_kernel(CEParams p) {
+  constexpr bool kAccurate = sizeof(T) == 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_per_grid = static_cast<int64_t>(gridDim.x) * (THREADS / 32);
+  const int64_t C = p.classes;
+  const float eps = p.label_smoothing;
+  const float eps_c = eps / static_cast<float>(C);
+
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5); row < p.rows;
+       row += warps_per_grid) {
+    const T* x = static_cast<const T*>(p.logits) + row * C;
+    T* g = p.grad ? static_cast<T*>(p.grad) + row * C : nullptr;
+    const int64_t t = p.target[row];
+    bool ignored = (t == p.ignore_index);
+    if (!ignored && (t < 0 || t >= C)) {
+      if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+      ignored = true;
+    }
+    if (ignored) {
+      if (lane == 0) {
+        p.row_loss[row] = 0.f;
+        if (p.row_lse) p.row_lse[row] = 0.f;
+      }
+      if (g)
+        for (int64_t c = lane; c < C; c += 32) g[c] = from_float<T>(0.f);
+      continue;
+    }
+    float m = -CUDART_INF_F, sx = 0.f;
+    for (int64_t c = lane; c < C; c += 32) {
+      const float f = to_float(x[c]);
+      m = fmaxf(m, f);
+      sx += f;
+    }
+    m = warp_max(m);
+    sx = warp_sum(sx);
+    const float mm = (m == -CUDART_INF_F) ? 0.f : m;
+    float s = 0.f;
+    for (int64_t c = lane; c < C; c += 32) {
+      const float d = to_float(x[c]) - mm;
+      s += kAccurate ? exp_accurate(d) : exp_fast(d);
+    }
+    s = warp_sum(s);
+    const float lse = m + logf(s);
+    if (lane == 0) {
+      p.row_loss[row] = ce_row_loss(lse, to_float(x[t]), sx, eps, eps_c);
+      if (p.row_lse) p.row_lse[row] = lse;
+    }
+    if (g) {
+      __syncwarp();  // x[t] has been read before an in-place gradient overwrites it
+      const float scale = ce_row_scale(p, row);
+      const float sub_all = eps_c * scale;
+      const float sub_t = (1.f - eps) * scale;
+      for (int64_t c = lane; c < C; c += 32) {
+        const float d = to_float(x[c]) - lse;
+        const float pr = kAccurate ? exp_accurate(d) : exp_fast(d);
+        float gv = fmaf(pr, scale, -sub_all);
+        if (c == t) gv -= sub_t;
+        g[c] = from_float<T>(gv);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bookkeeping kernels.
+// ---------------------------------------------------------------------------------------------
+// acc[1] += number of rows in this CTA's slice whose target is not ignore_index.  The sum of
+// integer-valued doubles below 2^53 is exact, so the atomic order does not change the result.
+__global__ void __launch_bounds__(256) ce_count_valid_kernel(const int64_t* __restrict__ target, int64_t rows,
+                                                             int64_t classes, int64_t ignore_index, double* acc,
+                                                             int32_t* status) {
+  __shared__ unsigned int s_cnt[8];
+  unsigned int cnt = 0;
+  bool bad = false;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < rows;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t t = target[i];
+    if (t != ignore_index) {
+      if (t < 0 || t >= classes) bad = true;
+      else ++cnt;
+    }
+  }
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  const bool any_bad = __any_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) {
+    s_cnt[threadIdx.x >> 5] = cnt;
+    if (any_bad && status) atomicOr(status, SB_STATUS_TARGET_OUT_OF_RANGE);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int total = 0;
+    for (int w = 0; w < 8; ++w) total += s_cnt[w];
+    if (total) atomicAdd(acc + 1, static_cast<double>(total));
+  }
+}
+
+// Fixed-order sum of row_loss in double: thread k adds elements k, k+1024, ... then a tree.
+template <bool FINISH>
+__global__ void __launch_bounds__(1024) ce_loss_sum_kernel(const float* __restrict__ row_loss, int64_t rows, double* acc,
+                                                           int reduction, void* out, int out_dtype) {
+  __shared__ double s_part[32];
+  double a = 0.0;
+  for (int64_t i = threadIdx.x; i < rows; i += 1024) a += static_cast<double>(row_loss[i]);
+  a = warp_sum(a);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    double b = warp_sum(s_part[threadIdx.x]);
+    if (threadIdx.x == 0) {
+      acc[0] = b;
+      if (FINISH) ce_store_loss(b, acc[1], reduction, out, out_dtype);
+    }
+  }
+}
+
+__global__ void ce_loss_finish_kernel(const double* acc, int reduction, void* out, int out_dtype) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) ce_store_loss(acc[0], acc[1], reduction, out, out_dtype);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_scalar_as_float(const void* p) {
+  return to_float(*static_cast<const T*>(p));
+}
+
+// grad *= (*scale / *applied), skipped when that factor is exactly 1.  `applied` is updated by a
+// trailing single-thread kernel so that every CTA of the sweep sees the old value.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) ce_rescale_kernel(T* grad, int64_t numel, const void* scale, int scale_dtype,
+                                                         const float* applied) {
+  float sc;
+  switch (scale_dtype) {
+    case SB_F32: sc = load_scalar_as_float<float>(scale); break;
+    case SB_BF16: sc = load_scalar_as_float<__nv_bfloat16>(scale); break;
+    case SB_F16: sc = load_scalar_as_float<__half>(scale); break;
+    default: sc = load_scalar_as_float<double>(scale); break;
+  }
+  const float factor = sc / *applied;
+  if (factor == 1.f) return;
+  const int64_t nvec = numel / VEC;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    Vec<T, VEC> v = load_vec<T, VEC>(grad + i * VEC);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v.v[k] = from_float<T>(to_float(v.v[k]) * factor);
+    store_vec<T, VEC>(grad + i * VEC, v);
+  }
+  if (blockIdx.x == 0)
+    for (int64_t i = nvec * VEC + threadIdx.x; i < numel; i += 256) grad[i] = from_float<T>(to_float(grad[i]) * factor);
+}
+__global__ void ce_rescale_commit_kernel(const void* scale, int scale_dtype, float* applied) {
+  float sc;
+  switch (scale_dtype) {
+    case SB_F32: sc = load_scalar_as_float<float>(scale); break;
+    case SB_BF16: sc = load_scalar_as_float<__nv_bfloat16>(scale); break;
+    case SB_F16: sc = load_scalar_as_float<__half>(scale); break;
+    default: sc = load_scalar_as_float<double>(scale); break;
+  }
+  *applied = sc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+static int launch_generic(const CEParams& p, cudaStream_t st) {
+  constexpr int kVec = 16 / sizeof(T);
+  const int sms = sm_count();
+  if (p.classes <= 1024) {
+    constexpr int kThreads = 256;
+    const int64_t ctas = (p.rows + kThreads / 32 - 1) / (kThreads / 32);
+    const int grid = static_cast<int>(ctas < static_cast<int64_t>(sms) * 8 ? ctas : static_cast<int64_t>(sms) * 8);
+    ce_rows_warp_kernel<T, kThreads><<<grid, kThreads, 0, st>>>(p);
+    return launch_status();
+  }
+  constexpr int kThreads = 512;
+  const int64_t max_grid = static_cast<int64_t>(sms) * 4;
+  const int grid = static_cast<int>(p.rows < max_grid ? p.rows : max_grid);
+  const bool aligned = (p.classes % kVec == 0) && (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0) &&
+                       (p.grad == nullptr || reinterpret_cast<uintptr_t>(p.grad) % 16 == 0);
+  if (aligned)
+    ce_rows_cta_kernel<T, kVec, kThreads><<<grid, kThreads, 0, st>>>(p);
+  else
+    ce_rows_cta_kernel<T, 1, kThreads><<<grid, kThreads, 0, st>>>(p);
+  return launch_status();
+}
+
+int ce_launch_generic(const CEParams& p, cudaStream_t st) {
+  switch (p.dtype) {
+    case SB_F32: return launch_generic<float>(p, st);
+    case SB_BF16: return launch_generic<__nv_bfloat16>(p, st);
+    case SB_F16: return launch_generic<__half>(p, st);
+    default: return SB_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int sb_ce_count_valid(const int64_t* target, int64_t rows, int64_t classes, int64_t ignore_index, double* acc,
+                      int32_t* status, sb_stream_t stream) {
+  if (rows < 0 || classes < 0 || !acc || (rows > 0 && !target)) return SB_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(acc, 0, 2 * sizeof(double), st) != cudaSuccess) return SB_ERR_CUDA;
+  if (rows == 0) return SB_OK;
+  const int64_t ctas = (rows + 255) / 256;
+  const int grid = static_cast<int>(ctas < 4 * sm_count() ? ctas : 4 * sm_count());
+  ce_count_valid_kernel<<<grid, 256, 0, st>>>(target, rows, classes, ignore_index, acc, status);
+  return launch_status();
+}
+
+int sb_ce_forward_backward(const sb_ce_args* a, sb_stream_t stream) {
+  if (!a) return SB_ERR_INVALID_ARGUMENT;
+  if (a->rows < 0 || a->classes < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (a->rows == 0) return SB_OK;
+  if (a->classes == 0) return SB_ERR_INVALID_ARGUMENT;
+  if (!a->logits || !a->target || !a->row_loss) return SB_ERR_INVALID_ARGUMENT;
+  if (a->dtype != SB_F32 && a->dtype != SB_BF16 && a->dtype != SB_F16) return SB_ERR_UNSUPPORTED;
+  if (a->reduction < SB_REDUCTION_NONE || a->reduction > SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  if (!(a->label_smoothing >= 0.f && a->label_smoothing <= 1.f)) return SB_ERR_INVALID_ARGUMENT;
+  if (a->grad_logits && a->reduction == SB_REDUCTION_MEAN && !a->acc) return SB_ERR_INVALID_ARGUMENT;
+  const size_t es = dtype_size(a->dtype);
+  if (reinterpret_cast<uintptr_t>(a->logits) % es || reinterpret_cast<uintptr_t>(a->grad_logits) % es)
+    return SB_ERR_MISALIGNED;
+  CEParams p;
+  p.logits = a->logits;
+  p.grad = a->grad_logits;
+  p.target = a->target;
+  p.row_loss = a->row_loss;
+  p.row_lse = a->row_lse;
+  p.row_grad_out = a->row_grad_out;
+  p.acc = a->acc;
+  p.rows = a->rows;
+  p.classes = a->classes;
+  p.ignore_index = a->ignore_index;
+  p.label_smoothing = a->label_smoothing;
+  p.grad_scale = a->grad_scale;
+  p.reduction = a->reduction;
+  p.dtype = a->dtype;
+  p.status = a->status;
+  return ce_dispatch(p, as_stream(stream));
+}
+
+int sb_ce_loss_sum(const float* row_loss, int64_t rows, double* acc, sb_stream_t stream) {
+  if (rows < 0 || !acc || (rows > 0 && !row_loss)) return SB_ERR_INVALID_ARGUMENT;
+  ce_loss_sum_kernel<false><<<1, 1024, 0, as_stream(stream)>>>(row_loss, rows, acc, 0, nullptr, 0);
+  return launch_status();
+}
+
+static bool loss_dtype_ok(int dt) { return dt == SB_F32 || dt == SB_BF16 || dt == SB_F16 || dt == SB_F64; }
+
+int sb_ce_loss_finish(const double* acc, int32_t reduction, void* out, int32_t dtype, sb_stream_t stream) {
+  if (!acc || !out) return SB_ERR_INVALID_ARGUMENT;
+  if (!loss_dtype_ok(dtype)) return SB_ERR_UNSUPPORTED;
+  if (reduction != SB_REDUCTION_MEAN && reduction != SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  ce_loss_finish_kernel<<<1, 32, 0, as_stream(stream)>>>(acc, reduction, out, dtype);
+  return launch_status();
+}
+
+int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* acc, int32_t reduction, void* out, int32_t dtype,
+                          sb_stream_t stream) {
+  if (rows < 0 || !acc || !out || (rows > 0 && !row_loss)) return SB_ERR_INVALID_ARGUMENT;
+  if (!loss_dtype_ok(dtype)) return SB_ERR_UNSUPPORTED;
+  if (reduction != SB_REDUCTION_MEAN && reduction != SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  ce_loss_sum_kernel<true><<<1, 1024, 0, as_stream(stream)>>>(row_loss, rows, acc, reduction, out, dtype);
+  return launch_status();
+}
+
+int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype, float* applied,
+                       sb_stream_t stream) {
+  if (numel < 0 || !scale || !applied || (numel > 0 && !grad)) return SB_ERR_INVALID_ARGUMENT;
+  if (!loss_dtype_ok(scale_dtype)) return SB_ERR_UNSUPPORTED;
+  cudaStream_t st = as_stream(stream);
+  if (numel > 0) {
+    const int64_t want = (numel / 8 + 255) / 256 + 1;
+    const int grid = static_cast<int>(want < 8LL * sm_count() ? want : 8LL * sm_count());
+    const bool al = reinterpret_cast<uintptr_t>(grad) % 16 == 0;
+    switch (dtype) {
+      case SB_F32:
+        if (al) ce_rescale_kernel<float, 4><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied);
+        else ce_rescale_kernel<float, 1><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied);
+        break;
+      case SB_BF16:
+        if (al) ce_rescale_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied);
+        else ce_rescale_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied);
+        break;
+      case SB_F16:
+        if (al) ce_rescale_kernel<__half, 8><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied);
+        else ce_rescale_kernel<__half, 1><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied);
+        break;
+      default: return SB_ERR_UNSUPPORTED;
+    }
+    int rc = launch_status();
+    if (rc != SB_OK) return rc;
+  }
+  ce_rescale_commit_kernel<<<1, 1, 0, st>>>(scale, scale_dtype, applied);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,31 @@
+// Elementwise launchers whose arithmetic runs in fp32 (fp32, bf16 and fp16 common dtypes).
+#include "elementwise.cuh"
+
+namespace sb {
+
+namespace {
+template <int OP>
+int launch_op(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
+  switch (plan.static_dtype) {
+    case SB_F32: return ew_launch_vector<OP, float, false, StaticIO<float>>(d, plan, st);
+    case SB_BF16: return ew_launch_vector<OP, float, true, StaticIO<__nv_bfloat16>>(d, plan, st);
+    case SB_F16: return ew_launch_vector<OP, float, false, StaticIO<__half>>(d, plan, st);
+    default: return ew_launch_vector<OP, float, false, DynamicIO>(d, plan, st);
+  }
+}
+}  // namespace
+
+int ew_launch_f32(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
+  if (plan.path >= 2) return ew_launch_scalar_paths<float>(d, plan, st);
+  switch (d->op) {
+#define SB_CASE(OPCODE) case OPCODE: return launch_op<OPCODE>(d, plan, st);
+    SB_CASE(SB_EW_COPY) SB_CASE(SB_EW_FILL) SB_CASE(SB_EW_ADD) SB_CASE(SB_EW_MUL) SB_CASE(SB_EW_SUB) SB_CASE(SB_EW_DIV)
+    SB_CASE(SB_EW_GELU_ERF) SB_CASE(SB_EW_GELU_TANH) SB_CASE(SB_EW_SILU) SB_CASE(SB_EW_GLU) SB_CASE(SB_EW_GELU_ERF_BWD)
+    SB_CASE(SB_EW_GELU_TANH_BWD) SB_CASE(SB_EW_SILU_BWD) SB_CASE(SB_EW_GLU_BWD_A) SB_CASE(SB_EW_GLU_BWD_B)
+    SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG)
+#undef SB_CASE
+    default: return SB_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace sb

@@ -1,0 +1,192 @@
+// nll_loss forward / backward for [rows, classes] log-probabilities and class-index targets.
+//
+// forward:  out_i = -w[t_i] * x[i, t_i] (0 when t_i == ignore_index); `none` stores out_i, `sum` and
+//           `mean` reduce it in a fixed order (one CTA, per-thread strided partial sums then a tree, so
+//           the result is bit-reproducible); total_weight = sum of w[t_i] over rows that count.
+// backward: grad_input is zero except [i, t_i] = -w[t_i] * g, with g = grad_output_i for `none`,
+//           grad_output for `sum`, grad_output / total_weight for `mean`.
+// An index outside [0, classes) that is not ignore_index sets SB_STATUS_TARGET_OUT_OF_RANGE and the row
+// is skipped; nothing traps.
+#include "io.cuh"
+
+namespace sb {
+
+namespace {
+
+struct NllParams {
+  const void* x;
+  const void* target;
+  const void* weight;
+  int64_t rows, classes, ignore_index;
+  int reduction;
+  int target_dtype;
+  int32_t* status;
+};
+
+__device__ __forceinline__ int64_t load_target(const NllParams& p, int64_t i) {
+  return p.target_dtype == SB_U8 ? static_cast<int64_t>(static_cast<const uint8_t*>(p.target)[i])
+                                 : static_cast<const int64_t*>(p.target)[i];
+}
+
+// Returns true when row i counts; fills t.
+__device__ __forceinline__ bool row_counts(const NllParams& p, int64_t i, int64_t& t) {
+  t = load_target(p, i);
+  if (t == p.ignore_index) return false;
+  if (t < 0 || t >= p.classes) {
+    if (p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+    return false;
+  }
+  return true;
+}
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) nll_fwd_none_kernel(NllParams p, T* __restrict__ out) {
+  const T* x = static_cast<const T*>(p.x);
+  const T* w = static_cast<const T*>(p.weight);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < p.rows;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t t;
+    A v = 0;
+    if (row_counts(p, i, t)) {
+      const A wt = w ? convert<A, T>(w[t]) : A(1);
+      v = -wt * convert<A, T>(x[i * p.classes + t]);
+    }
+    out[i] = convert<T, A>(v);
+  }
+}
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(1024) nll_fwd_reduce_kernel(NllParams p, T* __restrict__ out, T* __restrict__ total_weight) {
+  __shared__ double s_v[32];
+  __shared__ double s_w[32];
+  const T* x = static_cast<const T*>(p.x);
+  const T* w = static_cast<const T*>(p.weight);
+  double av = 0.0, aw = 0.0;
+  for (int64_t i = threadIdx.x; i < p.rows; i += 1024) {
+    int64_t t;
+    if (row_counts(p, i, t)) {
+      const double wt = w ? static_cast<double>(convert<A, T>(w[t])) : 1.0;
+      av -= wt * static_cast<double>(convert<A, T>(x[i * p.classes + t]));
+      aw += wt;
+    }
+  }
+  av = warp_sum(av);
+  aw = warp_sum(aw);
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = av;
+    s_w[threadIdx.x >> 5] = aw;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    av = warp_sum(s_v[threadIdx.x]);
+    aw = warp_sum(s_w[threadIdx.x]);
+    if (threadIdx.x == 0) {
+      double r = av;
+      if (p.reduction == SB_REDUCTION_MEAN) r = av / aw;  // 0/0 = NaN when every row is ignored
+      *out = convert<T, A>(static_cast<A>(r));
+      *total_weight = convert<T, A>(static_cast<A>(aw));
+    }
+  }
+}
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) nll_bwd_scatter_kernel(NllParams p, const T* __restrict__ grad_output,
+                                                              const T* __restrict__ total_weight, T* __restrict__ grad_input) {
+  const T* w = static_cast<const T*>(p.weight);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < p.rows;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t t;
+    if (!row_counts(p, i, t)) continue;
+    const A wt = w ? convert<A, T>(w[t]) : A(1);
+    A g = convert<A, T>(p.reduction == SB_REDUCTION_NONE ? grad_output[i] : grad_output[0]);
+    if (p.reduction == SB_REDUCTION_MEAN) g = g / convert<A, T>(*total_weight);
+    grad_input[i * p.classes + t] = convert<T, A>(-wt * g);
+  }
+}
+
+NllParams to_params(const sb_nll_args* a) {
+  NllParams p;
+  p.x = a->log_probs;
+  p.target = a->target;
+  p.weight = a->weight;
+  p.rows = a->rows;
+  p.classes = a->classes;
+  p.ignore_index = a->ignore_index;
+  p.reduction = a->reduction;
+  p.target_dtype = a->target_dtype;
+  p.status = a->status;
+  return p;
+}
+
+int validate(const sb_nll_args* a) {
+  if (!a || a->rows < 0 || a->classes < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (a->reduction < SB_REDUCTION_NONE || a->reduction > SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  if (a->target_dtype != SB_I64 && a->target_dtype != SB_U8) return SB_ERR_UNSUPPORTED;
+  if (a->dtype != SB_F32 && a->dtype != SB_BF16 && a->dtype != SB_F16 && a->dtype != SB_F64) return SB_ERR_UNSUPPORTED;
+  if (a->rows > 0 && (!a->log_probs || !a->target)) return SB_ERR_INVALID_ARGUMENT;
+  return SB_OK;
+}
+
+template <typename T, typename A>
+int launch_fwd(const sb_nll_args* a, void* output, void* total_weight, cudaStream_t st) {
+  NllParams p = to_params(a);
+  if (a->reduction == SB_REDUCTION_NONE) {
+    if (a->rows == 0) return SB_OK;
+    const int64_t ctas = (a->rows + 255) / 256;
+    const int grid = static_cast<int>(ctas < 8LL * sm_count() ? ctas : 8LL * sm_count());
+    nll_fwd_none_kernel<T, A><<<grid, 256, 0, st>>>(p, static_cast<T*>(output));
+    return launch_status();
+  }
+  nll_fwd_reduce_kernel<T, A><<<1, 1024, 0, st>>>(p, static_cast<T*>(output), static_cast<T*>(total_weight));
+  return launch_status();
+}
+
+template <typename T, typename A>
+int launch_bwd(const sb_nll_args* a, const void* grad_output, const void* total_weight, void* grad_input, cudaStream_t st) {
+  NllParams p = to_params(a);
+  const size_t bytes = static_cast<size_t>(a->rows) * static_cast<size_t>(a->classes) * sizeof(T);
+  if (bytes == 0) return SB_OK;
+  if (cudaMemsetAsync(grad_input, 0, bytes, st) != cudaSuccess) return SB_ERR_CUDA;
+  const int64_t ctas = (a->rows + 255) / 256;
+  const int grid = static_cast<int>(ctas < 8LL * sm_count() ? ctas : 8LL * sm_count());
+  nll_bwd_scatter_kernel<T, A><<<grid, 256, 0, st>>>(p, static_cast<const T*>(grad_output),
+                                                     static_cast<const T*>(total_weight), static_cast<T*>(grad_input));
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int sb_nll_loss_forward(const sb_nll_args* a, void* output, void* total_weight, sb_stream_t stream) {
+  int rc = validate(a);
+  if (rc != SB_OK) return rc;
+  if (!output || (a->reduction != SB_REDUCTION_NONE && !total_weight)) return SB_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = as_stream(stream);
+  switch (a->dtype) {
+    case SB_F32: return launch_fwd<float, float>(a, output, total_weight, st);
+    case SB_BF16: return launch_fwd<__nv_bfloat16, float>(a, output, total_weight, st);
+    case SB_F16: return launch_fwd<__half, float>(a, output, total_weight, st);
+    default: return launch_fwd<double, double>(a, output, total_weight, st);
+  }
+}
+
+int sb_nll_loss_backward(const sb_nll_args* a, const void* grad_output, const void* total_weight, void* grad_input,
+                         sb_stream_t stream) {
+  int rc = validate(a);
+  if (rc != SB_OK) return rc;
+  if (a->rows > 0 && a->classes > 0 && (!grad_output || !grad_input)) return SB_ERR_INVALID_ARGUMENT;
+  if (a->reduction == SB_REDUCTION_MEAN && !total_weight) return SB_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = as_stream(stream);
+  switch (a->dtype) {
+    case SB_F32: return launch_bwd<float, float>(a, grad_output, total_weight, grad_input, st);
+    case SB_BF16: return launch_bwd<__nv_bfloat16, float>(a, grad_output, total_weight, grad_input, st);
+    case SB_F16: return launch_bwd<__half, float>(a, grad_output, total_weight, grad_input, st);
+    default: return launch_bwd<double, double>(a, grad_output, total_weight, grad_input, st);
+  }
+}
+
+}  // extern "C"

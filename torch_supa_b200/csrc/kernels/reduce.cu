@@ -1,0 +1,551 @@
+// Reductions sum / mean / amax / amin over any set of dimensions.
+//
+// Path 0  rows       the reduced run is contiguous (unit input stride on dimension 0) and every other
+//                    dimension is kept: one CTA (long rows) or one warp (short rows) per output,
+//                    16-byte loads, 8 independent accumulators per thread, shuffle + shared-memory tree.
+// Path 1  split rows same layout but too few outputs to fill the GPU: each row is cut into segments,
+//                    one CTA per segment writes a partial into caller-provided scratch, a second
+//                    kernel folds the partials in a fixed order (no atomics: bit-reproducible).
+// Path 2  columns    dimension 0 is kept with unit strides and dimension 1 is reduced: threads run along
+//                    the kept dimension so that loads stay coalesced.
+// Path 3  generic    one thread per output walking the reduced index space.
+//
+// Accumulation type: fp32 for fp32/bf16/fp16, fp64 for fp64, int64 for integer and bool inputs.
+#include <type_traits>
+
+#include "io.cuh"
+
+namespace sb {
+
+namespace {
+
+constexpr int kRedKeep = 3;  // kept (non-reduced) dimensions handled by paths 0-2
+
+struct RedParams {
+  const void* in;
+  void* out;
+  int in_dtype, out_dtype;
+  int64_t L;                 // reduced run length (paths 0-2)
+  int64_t red_stride;        // input stride of the reduced dimension (path 2)
+  int64_t noutputs;
+  uint32_t keep_sizes[kRedKeep];
+  int64_t keep_in_strides[kRedKeep];
+  int64_t keep_out_strides[kRedKeep];
+  double scale;              // 1/count for mean, 1 otherwise
+  int splits;                // path 1
+  int64_t seg;               // path 1: elements per segment (multiple of the vector width)
+  void* scratch;
+};
+
+struct RedGenericParams {
+  const void* in;
+  void* out;
+  int in_dtype, out_dtype;
+  int nkeep, nred;
+  uint32_t keep_sizes[SB_MAX_DIMS];
+  int64_t keep_in_strides[SB_MAX_DIMS];
+  int64_t keep_out_strides[SB_MAX_DIMS];
+  uint32_t red_sizes[SB_MAX_DIMS];
+  int64_t red_in_strides[SB_MAX_DIMS];
+  int64_t noutputs, nreduce;
+  double scale;
+};
+
+// ---- functors -----------------------------------------------------------------------------------------------
+template <typename A> struct SumOp {
+  __device__ static __forceinline__ A identity() { return A(0); }
+  __device__ static __forceinline__ A combine(A a, A b) { return a + b; }
+};
+template <typename A> struct MaxOp {
+  __device__ static __forceinline__ A identity() {
+    if constexpr (std::is_same<A, float>::value) return -CUDART_INF_F;
+    else if constexpr (std::is_same<A, double>::value) return -CUDART_INF;
+    else return INT64_MIN;
+  }
+  __device__ static __forceinline__ A combine(A a, A b) {
+    if constexpr (std::is_floating_point<A>::value) return (b > a || b != b) ? b : a;  // NaN propagates
+    else return b > a ? b : a;
+  }
+};
+template <typename A> struct MinOp {
+  __device__ static __forceinline__ A identity() {
+    if constexpr (std::is_same<A, float>::value) return CUDART_INF_F;
+    else if constexpr (std::is_same<A, double>::value) return CUDART_INF;
+    else return INT64_MAX;
+  }
+  __device__ static __forceinline__ A combine(A a, A b) {
+    if constexpr (std::is_floating_point<A>::value) return (b < a || b != b) ? b : a;
+    else return b < a ? b : a;
+  }
+};
+
+template <typename A> __device__ __forceinline__ A shfl_down_t(A v, int o) { return __shfl_down_sync(0xffffffffu, v, o); }
+template <> __device__ __forceinline__ int64_t shfl_down_t<int64_t>(int64_t v, int o) {
+  return static_cast<int64_t>(__shfl_down_sync(0xffffffffu, static_cast<long long>(v), o));
+}
+
+template <class F, typename A> __device__ __forceinline__ A warp_reduce(A v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = F::combine(v, shfl_down_t<A>(v, o));
+  return v;  // valid in lane 0
+}
+
+template <class F, typename A, int THREADS> __device__ __forceinline__ A block_reduce(A v, A* sm) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_reduce<F, A>(v);
+  if (lane == 0) sm[warp] = v;
+  __syncthreads();
+  A r = F::identity();
+  if (warp == 0) {
+    r = lane < THREADS / 32 ? sm[lane] : F::identity();
+    r = warp_reduce<F, A>(r);
+  }
+  __syncthreads();
+  return r;  // valid in thread 0
+}
+
+template <typename A> __device__ __forceinline__ A apply_scale(A v, double scale) {
+  if constexpr (std::is_floating_point<A>::value) return static_cast<A>(v * static_cast<A>(scale));
+  else return v;
+}
+
+// Offsets of output number `o` (kept dims, fastest first).
+__device__ __forceinline__ void keep_offsets(const RedParams& p, int64_t o, int64_t& in_off, int64_t& out_off) {
+  uint64_t r = static_cast<uint64_t>(o);
+  in_off = 0;
+  out_off = 0;
+#pragma unroll
+  for (int d = 0; d < kRedKeep; ++d) {
+    const uint64_t i = r % p.keep_sizes[d];
+    r /= p.keep_sizes[d];
+    in_off += static_cast<int64_t>(i) * p.keep_in_strides[d];
+    out_off += static_cast<int64_t>(i) * p.keep_out_strides[d];
+  }
+}
+
+// Reduces elements [begin, end) of a contiguous run starting at element offset `base`; the vector body
+// covers the 16-byte-aligned middle, the ragged ends are scalar.
+template <class IO, class F, typename A, int VEC, int THREADS>
+__device__ __forceinline__ A thread_reduce_run(const void* in, int dtype, int64_t base, int64_t n) {
+  A acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = F::identity();
+  const int64_t nvec = n / VEC;
+  constexpr int kUnroll = 4;
+  for (int64_t i = threadIdx.x; i < nvec; i += THREADS * kUnroll) {
+    A f[kUnroll][VEC];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t v = i + static_cast<int64_t>(u) * THREADS;
+      if (v < nvec) IO::template load<A, VEC>(in, base + v * VEC, dtype, f[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t v = i + static_cast<int64_t>(u) * THREADS;
+      if (v < nvec) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], f[u][k]);
+      }
+    }
+  }
+  for (int64_t e = nvec * VEC + threadIdx.x; e < n; e += THREADS) {
+    A one[1];
+    IO::template load<A, 1>(in, base + e, dtype, one);
+    acc[0] = F::combine(acc[0], one[0]);
+  }
+  A r = acc[0];
+#pragma unroll
+  for (int k = 1; k < VEC; ++k) r = F::combine(r, acc[k]);
+  return r;
+}
+
+// ---- path 0 ------------------------------------------------------------------------------------------------
+template <class IO, class F, typename A, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS) red_rows_cta_kernel(RedParams p) {
+  __shared__ A sm[32];
+  for (int64_t o = blockIdx.x; o < p.noutputs; o += gridDim.x) {
+    int64_t in_off, out_off;
+    keep_offsets(p, o, in_off, out_off);
+    A v = thread_reduce_run<IO, F, A, VEC, THREADS>(p.in, p.in_dtype, in_off, p.L);
+    v = block_reduce<F, A, THREADS>(v, sm);
+    if (threadIdx.x == 0) {
+      A r[1] = {apply_scale<A>(v, p.scale)};
+      DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+    }
+  }
+}
+
+template <class IO, class F, typename A, int THREADS>
+__global__ void __launch_bounds__(THREADS) red_rows_warp_kernel(RedParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * (THREADS / 32);
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5); o < p.noutputs; o += stride) {
+    int64_t in_off, out_off;
+    keep_offsets(p, o, in_off, out_off);
+    A v = F::identity();
+    for (int64_t e = lane; e < p.L; e += 32) {
+      A one[1];
+      IO::template load<A, 1>(p.in, in_off + e, p.in_dtype, one);
+      v = F::combine(v, one[0]);
+    }
+    v = warp_reduce<F, A>(v);
+    if (lane == 0) {
+      A r[1] = {apply_scale<A>(v, p.scale)};
+      DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+    }
+  }
+}
+
+// ---- path 1 ------------------------------------------------------------------------------------------------
+template <class IO, class F, typename A, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS) red_split_partial_kernel(RedParams p) {
+  __shared__ A sm[32];
+  const int64_t o = blockIdx.y;
+  const int s = blockIdx.x;
+  int64_t in_off, out_off;
+  keep_offsets(p, o, in_off, out_off);
+  const int64_t begin = static_cast<int64_t>(s) * p.seg;
+  int64_t n = p.L - begin;
+  if (n > p.seg) n = p.seg;
+  A v = F::identity();
+  if (n > 0) v = thread_reduce_run<IO, F, A, VEC, THREADS>(p.in, p.in_dtype, in_off + begin, n);
+  v = block_reduce<F, A, THREADS>(v, sm);
+  if (threadIdx.x == 0) static_cast<A*>(p.scratch)[o * p.splits + s] = v;
+}
+
+template <class F, typename A>
+__global__ void __launch_bounds__(256) red_split_final_kernel(RedParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); o < p.noutputs; o += stride) {
+    int64_t in_off, out_off;
+    keep_offsets(p, o, in_off, out_off);
+    const A* part = static_cast<const A*>(p.scratch) + o * p.splits;
+    A v = F::identity();
+    for (int s = lane; s < p.splits; s += 32) v = F::combine(v, part[s]);
+    v = warp_reduce<F, A>(v);
+    if (lane == 0) {
+      A r[1] = {apply_scale<A>(v, p.scale)};
+      DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+    }
+  }
+}
+
+// ---- path 2 ------------------------------------------------------------------------------------------------
+// keep_sizes[0] = kept dimension 0 (unit strides), keep_sizes[1..2] = outer kept dims; L rows of stride
+// red_stride are reduced.  Block = 32 columns x 8 row lanes.
+template <class IO, class F, typename A>
+__global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
+  __shared__ A sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const uint32_t col = blockIdx.x * 32 + tx;
+  uint64_t r = blockIdx.y;
+  const uint64_t i1 = r % p.keep_sizes[1];
+  const uint64_t i2 = r / p.keep_sizes[1];
+  const int64_t in_base = static_cast<int64_t>(i1) * p.keep_in_strides[1] + static_cast<int64_t>(i2) * p.keep_in_strides[2];
+  const int64_t out_base = static_cast<int64_t>(i1) * p.keep_out_strides[1] + static_cast<int64_t>(i2) * p.keep_out_strides[2];
+  A v = F::identity();
+  if (col < p.keep_sizes[0]) {
+    for (int64_t j = ty; j < p.L; j += 8) {
+      A one[1];
+      IO::template load<A, 1>(p.in, in_base + col * p.keep_in_strides[0] + j * p.red_stride, p.in_dtype, one);
+      v = F::combine(v, one[0]);
+    }
+  }
+  sm[ty][tx] = v;
+  __syncthreads();
+  if (ty == 0 && col < p.keep_sizes[0]) {
+    A a = sm[0][tx];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) a = F::combine(a, sm[k][tx]);
+    A o[1] = {apply_scale<A>(a, p.scale)};
+    DynamicIO::store<A, 1>(p.out, out_base + col * p.keep_out_strides[0], p.out_dtype, o);
+  }
+}
+
+// ---- path 3 ------------------------------------------------------------------------------------------------
+template <class F, typename A>
+__global__ void __launch_bounds__(256) red_generic_kernel(RedGenericParams p) {
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; o < p.noutputs;
+       o += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t in_off = 0, out_off = 0;
+    uint64_t r = static_cast<uint64_t>(o);
+    for (int d = 0; d < p.nkeep; ++d) {
+      const uint64_t i = r % p.keep_sizes[d];
+      r /= p.keep_sizes[d];
+      in_off += static_cast<int64_t>(i) * p.keep_in_strides[d];
+      out_off += static_cast<int64_t>(i) * p.keep_out_strides[d];
+    }
+    A v = F::identity();
+    for (int64_t j = 0; j < p.nreduce; ++j) {
+      uint64_t q = static_cast<uint64_t>(j);
+      int64_t off = in_off;
+      for (int d = 0; d < p.nred; ++d) {
+        const uint64_t i = q % p.red_sizes[d];
+        q /= p.red_sizes[d];
+        off += static_cast<int64_t>(i) * p.red_in_strides[d];
+      }
+      A one[1];
+      DynamicIO::load<A, 1>(p.in, off, p.in_dtype, one);
+      v = F::combine(v, one[0]);
+    }
+    A res[1] = {apply_scale<A>(v, p.scale)};
+    DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, res);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------
+struct Dim {
+  int64_t size, in_stride, out_stride;
+  bool reduced;
+};
+
+struct Plan {
+  int path;
+  int acc;  // 0 float, 1 double, 2 int64
+  RedParams p;
+  RedGenericParams g;
+  bool vec_ok;
+  size_t scratch_bytes;
+};
+
+int acc_of(int dtype) {
+  switch (dtype) {
+    case SB_F16: case SB_BF16: case SB_F32: return 0;
+    case SB_F64: return 1;
+    case SB_BOOL: case SB_U8: case SB_I8: case SB_I16: case SB_I32: case SB_I64: return 2;
+    default: return -1;
+  }
+}
+
+int make_plan(const sb_reduce_desc* d, Plan* plan) {
+  if (!d) return SB_ERR_INVALID_ARGUMENT;
+  if (d->op < 0 || d->op >= SB_RED_OP_COUNT) return SB_ERR_INVALID_ARGUMENT;
+  if (d->ndim < 1 || d->ndim > SB_MAX_DIMS) return SB_ERR_INVALID_ARGUMENT;
+  if (d->in_dtype < 0 || d->in_dtype >= SB_DTYPE_COUNT || d->out_dtype < 0 || d->out_dtype >= SB_DTYPE_COUNT)
+    return SB_ERR_UNSUPPORTED;
+  plan->acc = acc_of(d->in_dtype);
+  if (plan->acc < 0) return SB_ERR_UNSUPPORTED;
+  if (d->op == SB_RED_MEAN && plan->acc == 2) return SB_ERR_UNSUPPORTED;  // mean is defined on floating types
+  if ((d->op == SB_RED_AMAX || d->op == SB_RED_AMIN) && d->in_dtype == SB_BOOL) plan->acc = 2;
+
+  // split, drop size-1 dims, coalesce
+  Dim dims[SB_MAX_DIMS];
+  int n = 0;
+  int64_t noutputs = 1, nreduce = 1;
+  for (int i = 0; i < d->ndim; ++i) {
+    if (d->sizes[i] < 0) return SB_ERR_INVALID_ARGUMENT;
+    if (d->sizes[i] > 0xffffffffLL && d->ndim > 1) return SB_ERR_TOO_LARGE;
+    const bool red = d->out_strides[i] == 0;
+    if (red) nreduce *= d->sizes[i];
+    else noutputs *= d->sizes[i];
+    if (d->sizes[i] == 1) continue;
+    Dim cur{d->sizes[i], d->in_strides[i], d->out_strides[i], red};
+    if (n > 0) {
+      Dim& prev = dims[n - 1];
+      if (prev.reduced == cur.reduced && cur.in_stride == prev.in_stride * prev.size &&
+          (cur.reduced || cur.out_stride == prev.out_stride * prev.size)) {
+        prev.size *= cur.size;
+        continue;
+      }
+    }
+    dims[n++] = cur;
+  }
+  if (n == 0) {
+    dims[0] = Dim{1, 1, 0, true};
+    n = 1;
+  }
+  if (noutputs > 0 && nreduce > 0 && (!d->in || !d->out)) return SB_ERR_INVALID_ARGUMENT;
+  if (noutputs > 0 && !d->out) return SB_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(d->in) % dtype_size(d->in_dtype) || reinterpret_cast<uintptr_t>(d->out) % dtype_size(d->out_dtype))
+    return SB_ERR_MISALIGNED;
+
+  const double scale = d->op == SB_RED_MEAN ? 1.0 / static_cast<double>(nreduce) : 1.0;
+  plan->scratch_bytes = 0;
+  plan->vec_ok = false;
+
+  // generic parameters are always filled (path 3 fallback)
+  RedGenericParams& g = plan->g;
+  g.in = d->in;
+  g.out = d->out;
+  g.in_dtype = d->in_dtype;
+  g.out_dtype = d->out_dtype;
+  g.nkeep = g.nred = 0;
+  for (int i = 0; i < n; ++i) {
+    if (dims[i].reduced) {
+      g.red_sizes[g.nred] = static_cast<uint32_t>(dims[i].size);
+      g.red_in_strides[g.nred++] = dims[i].in_stride;
+    } else {
+      g.keep_sizes[g.nkeep] = static_cast<uint32_t>(dims[i].size);
+      g.keep_in_strides[g.nkeep] = dims[i].in_stride;
+      g.keep_out_strides[g.nkeep++] = dims[i].out_stride;
+    }
+  }
+  g.noutputs = noutputs;
+  g.nreduce = nreduce;
+  g.scale = scale;
+  plan->path = 3;
+
+  int nred = g.nred, nkeep = g.nkeep;
+  RedParams& p = plan->p;
+  p.in = d->in;
+  p.out = d->out;
+  p.in_dtype = d->in_dtype;
+  p.out_dtype = d->out_dtype;
+  p.scale = scale;
+  p.noutputs = noutputs;
+  p.splits = 1;
+  p.seg = 0;
+  p.scratch = d->scratch;
+  p.red_stride = 1;
+  for (int k = 0; k < kRedKeep; ++k) {
+    p.keep_sizes[k] = 1;
+    p.keep_in_strides[k] = 0;
+    p.keep_out_strides[k] = 0;
+  }
+  if (noutputs == 0 || nreduce == 0) return SB_OK;  // nothing to launch (empty reduce handled by the caller)
+
+  const size_t es = dtype_size(d->in_dtype);
+  const size_t valign = es * 8 >= 16 ? 16 : es * 8;
+  if (nred == 1 && nkeep <= kRedKeep && dims[0].reduced && dims[0].in_stride == 1) {
+    // paths 0 / 1
+    p.L = dims[0].size;
+    bool vec_ok = reinterpret_cast<uintptr_t>(d->in) % valign == 0;
+    for (int k = 0; k < nkeep; ++k) {
+      p.keep_sizes[k] = g.keep_sizes[k];
+      p.keep_in_strides[k] = g.keep_in_strides[k];
+      p.keep_out_strides[k] = g.keep_out_strides[k];
+      const uint64_t s = static_cast<uint64_t>(g.keep_in_strides[k] < 0 ? -g.keep_in_strides[k] : g.keep_in_strides[k]);
+      vec_ok = vec_ok && (s * es) % valign == 0;
+    }
+    plan->vec_ok = vec_ok;
+    plan->path = 0;
+    const int sms = sm_count();
+    // Too few rows to occupy the GPU and rows long enough to be worth cutting.
+    if (noutputs < 2LL * sms && p.L >= 32768 && noutputs <= 65535) {
+      int64_t want = (4LL * sms + noutputs - 1) / noutputs;
+      const int64_t max_by_len = p.L / 8192;
+      if (want > max_by_len) want = max_by_len;
+      if (want > 1024) want = 1024;
+      if (want >= 2) {
+        int64_t seg = (p.L + want - 1) / want;
+        seg = (seg + 63) / 64 * 64;  // keeps every segment start 16-byte aligned for all dtypes
+        p.seg = seg;
+        p.splits = static_cast<int>((p.L + seg - 1) / seg);
+        plan->path = 1;
+        const size_t acc_size = 8;  // sized for the widest accumulator (fp64 / int64)
+        plan->scratch_bytes = static_cast<size_t>(noutputs) * p.splits * acc_size;
+      }
+    }
+    return SB_OK;
+  }
+  if (nred == 1 && nkeep >= 1 && nkeep <= kRedKeep && !dims[0].reduced && dims[0].in_stride == 1) {
+    // path 2: find the reduced dim
+    uint64_t outer = 1;
+    for (int k = 0; k < nkeep; ++k) {
+      p.keep_sizes[k] = g.keep_sizes[k];
+      p.keep_in_strides[k] = g.keep_in_strides[k];
+      p.keep_out_strides[k] = g.keep_out_strides[k];
+      if (k >= 1) outer *= g.keep_sizes[k];
+    }
+    p.L = g.red_sizes[0];
+    p.red_stride = g.red_in_strides[0];
+    if (outer <= 65535) {
+      plan->path = 2;
+      return SB_OK;
+    }
+  }
+  return SB_OK;
+}
+
+template <class IO, class F, typename A>
+int launch_paths(const Plan& plan, cudaStream_t st) {
+  const RedParams& p = plan.p;
+  const int sms = sm_count();
+  if (plan.path == 0) {
+    if (p.L <= 1024) {
+      const int64_t ctas = (p.noutputs + 7) / 8;
+      const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
+      red_rows_warp_kernel<IO, F, A, 256><<<grid, 256, 0, st>>>(p);
+    } else {
+      const int grid = static_cast<int>(p.noutputs < 8LL * sms ? p.noutputs : 8LL * sms);
+      if (plan.vec_ok) red_rows_cta_kernel<IO, F, A, 8, 256><<<grid, 256, 0, st>>>(p);
+      else red_rows_cta_kernel<IO, F, A, 1, 256><<<grid, 256, 0, st>>>(p);
+    }
+    return launch_status();
+  }
+  if (plan.path == 1) {
+    dim3 grid(p.splits, static_cast<unsigned>(p.noutputs));
+    if (plan.vec_ok) red_split_partial_kernel<IO, F, A, 8, 256><<<grid, 256, 0, st>>>(p);
+    else red_split_partial_kernel<IO, F, A, 1, 256><<<grid, 256, 0, st>>>(p);
+    int rc = launch_status();
+    if (rc != SB_OK) return rc;
+    const int64_t ctas = (p.noutputs + 7) / 8;
+    red_split_final_kernel<F, A><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p);
+    return launch_status();
+  }
+  if (plan.path == 2) {
+    uint64_t outer = static_cast<uint64_t>(p.keep_sizes[1]) * p.keep_sizes[2];
+    dim3 grid((p.keep_sizes[0] + 31) / 32, static_cast<unsigned>(outer));
+    red_cols_kernel<IO, F, A><<<grid, 256, 0, st>>>(p);
+    return launch_status();
+  }
+  int64_t ctas = (plan.g.noutputs + 255) / 256;
+  if (ctas > 32LL * sms) ctas = 32LL * sms;
+  red_generic_kernel<F, A><<<static_cast<unsigned>(ctas), 256, 0, st>>>(plan.g);
+  return launch_status();
+}
+
+template <class IO, typename A>
+int launch_op(int op, const Plan& plan, cudaStream_t st) {
+  switch (op) {
+    case SB_RED_SUM: case SB_RED_MEAN: return launch_paths<IO, SumOp<A>, A>(plan, st);
+    case SB_RED_AMAX: return launch_paths<IO, MaxOp<A>, A>(plan, st);
+    case SB_RED_AMIN: return launch_paths<IO, MinOp<A>, A>(plan, st);
+    default: return SB_ERR_INVALID_ARGUMENT;
+  }
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+size_t sb_reduce_scratch_bytes(const sb_reduce_desc* d) {
+  Plan plan;
+  if (make_plan(d, &plan) != SB_OK) return 0;
+  return plan.scratch_bytes;
+}
+
+int sb_reduce_path(const sb_reduce_desc* d) {
+  Plan plan;
+  int rc = make_plan(d, &plan);
+  return rc != SB_OK ? rc : plan.path;
+}
+
+int sb_reduce(const sb_reduce_desc* d, sb_stream_t stream) {
+  Plan plan;
+  int rc = make_plan(d, &plan);
+  if (rc != SB_OK) return rc;
+  if (plan.g.noutputs == 0) return SB_OK;
+  if (plan.g.nreduce == 0) return SB_ERR_INVALID_ARGUMENT;  // the caller fills identities for empty reductions
+  if (plan.path == 1) {
+    if (!d->scratch || d->scratch_bytes < plan.scratch_bytes) return SB_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(d->scratch) % 8) return SB_ERR_MISALIGNED;
+  }
+  cudaStream_t st = as_stream(stream);
+  switch (plan.acc) {
+    case 0:
+      switch (d->in_dtype) {
+        case SB_F32: return launch_op<StaticIO<float>, float>(d->op, plan, st);
+        case SB_BF16: return launch_op<StaticIO<__nv_bfloat16>, float>(d->op, plan, st);
+        default: return launch_op<StaticIO<__half>, float>(d->op, plan, st);
+      }
+    case 1: return launch_op<DynamicIO, double>(d->op, plan, st);
+    default: return launch_op<DynamicIO, int64_t>(d->op, plan, st);
+  }
+}
+
+}  // extern "C"

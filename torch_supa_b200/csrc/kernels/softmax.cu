@@ -1,0 +1,325 @@
+// log_softmax forward / backward over one dimension of a tensor viewed as [outer, dim, inner].
+//
+// inner == 1 (softmax over the last, contiguous dimension): one CTA per row for long rows, one warp
+// per row for short ones; the statistics sweep reads the row from HBM, the output sweep re-reads it
+// from L1/L2.  inner > 1: one thread per (outer, inner) pair walking the strided dimension, coalesced
+// across `inner`.
+//
+// Arithmetic is fp32 for fp32/bf16/fp16 storage and fp64 for fp64 storage.  Outputs may be wider than
+// inputs (the `half_to_float` form of aten::_log_softmax) and input gradients narrower than output
+// gradients (its backward).
+#include "io.cuh"
+
+namespace sb {
+
+namespace {
+
+template <typename A> __device__ __forceinline__ A acc_exp(A x);
+template <> __device__ __forceinline__ float acc_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ double acc_exp<double>(double x) { return exp(x); }
+template <typename A> __device__ __forceinline__ A acc_log(A x);
+template <> __device__ __forceinline__ float acc_log<float>(float x) { return logf(x); }
+template <> __device__ __forceinline__ double acc_log<double>(double x) { return log(x); }
+template <typename A> __device__ __forceinline__ A neg_inf();
+template <> __device__ __forceinline__ float neg_inf<float>() { return -CUDART_INF_F; }
+template <> __device__ __forceinline__ double neg_inf<double>() { return -CUDART_INF; }
+
+template <typename A> __device__ __forceinline__ A shfl_xor(A v, int o) { return __shfl_xor_sync(0xffffffffu, v, o); }
+
+template <typename A> __device__ __forceinline__ A warp_sum_t(A v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += shfl_xor(v, o);
+  return v;
+}
+template <typename A> __device__ __forceinline__ A warp_max_t(A v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    A w = shfl_xor(v, o);
+    v = (w > v || w != w) ? w : v;  // NaN wins, as in a max that propagates NaN
+  }
+  return v;
+}
+
+// (max, sum exp) merge with -inf partials kept neutral.
+template <typename A> __device__ __forceinline__ void merge_ms(A& m, A& s, A m2, A s2) {
+  const A mm = (m2 > m || m2 != m2) ? m2 : m;
+  const A a = (m == neg_inf<A>()) ? A(0) : s * acc_exp<A>(m - mm);
+  const A b = (m2 == neg_inf<A>()) ? A(0) : s2 * acc_exp<A>(m2 - mm);
+  m = mm;
+  s = a + b;
+}
+
+// Block-wide (max, sum exp) -> every thread; THREADS multiple of 32.
+template <typename A, int THREADS>
+__device__ __forceinline__ void block_merge_ms(A& m, A& s, A* sm_m, A* sm_s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) merge_ms(m, s, shfl_xor(m, o), shfl_xor(s, o));
+  if (lane == 0) {
+    sm_m[warp] = m;
+    sm_s[warp] = s;
+  }
+  __syncthreads();
+  A mm = lane < THREADS / 32 ? sm_m[lane] : neg_inf<A>();
+  A ss = lane < THREADS / 32 ? sm_s[lane] : A(0);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) merge_ms(mm, ss, shfl_xor(mm, o), shfl_xor(ss, o));
+  m = mm;
+  s = ss;
+  __syncthreads();
+}
+template <typename A, int THREADS>
+__device__ __forceinline__ A block_sum(A v, A* sm) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum_t(v);
+  if (lane == 0) sm[warp] = v;
+  __syncthreads();
+  A r = lane < THREADS / 32 ? sm[lane] : A(0);
+  r = warp_sum_t(r);
+  __syncthreads();
+  return r;
+}
+
+// ---- forward, rows -----------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, typename A, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS) lsm_fwd_cta_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
+                                                              int64_t rows, int64_t C) {
+  __shared__ A sm_m[32];
+  __shared__ A sm_s[32];
+  const int64_t nvec = C / VEC;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const Tin* x = in + row * C;
+    Tout* y = out + row * C;
+    A m = neg_inf<A>(), s = 0;
+    for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
+      A f[VEC];
+      load_as<A, Tin, VEC>(x + i * VEC, f);
+      A vmax = f[0];
+#pragma unroll
+      for (int k = 1; k < VEC; ++k) vmax = (f[k] > vmax || f[k] != f[k]) ? f[k] : vmax;
+      if (vmax > m || vmax != vmax) {
+        s *= acc_exp<A>(m - vmax);
+        m = vmax;
+      }
+      const A mm = (m == neg_inf<A>()) ? A(0) : m;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) s += acc_exp<A>(f[k] - mm);
+    }
+    block_merge_ms<A, THREADS>(m, s, sm_m, sm_s);
+    const A lse = m + acc_log<A>(s);
+    for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
+      A f[VEC];
+      load_as<A, Tin, VEC>(x + i * VEC, f);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) f[k] -= lse;
+      store_as<A, Tout, VEC>(y + i * VEC, f);
+    }
+  }
+}
+
+template <typename Tin, typename Tout, typename A, int THREADS>
+__global__ void __launch_bounds__(THREADS) lsm_fwd_warp_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
+                                                               int64_t rows, int64_t C) {
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * (THREADS / 32);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5); row < rows; row += stride) {
+    const Tin* x = in + row * C;
+    Tout* y = out + row * C;
+    A m = neg_inf<A>();
+    for (int64_t c = lane; c < C; c += 32) {
+      const A f = convert<A, Tin>(x[c]);
+      m = (f > m || f != f) ? f : m;
+    }
+    m = warp_max_t(m);
+    const A mm = (m == neg_inf<A>()) ? A(0) : m;
+    A s = 0;
+    for (int64_t c = lane; c < C; c += 32) s += acc_exp<A>(convert<A, Tin>(x[c]) - mm);
+    s = warp_sum_t(s);
+    const A lse = m + acc_log<A>(s);
+    for (int64_t c = lane; c < C; c += 32) y[c] = convert<Tout, A>(convert<A, Tin>(x[c]) - lse);
+  }
+}
+
+// ---- forward, strided dimension --------------------------------------------------------------------------
+template <typename Tin, typename Tout, typename A>
+__global__ void __launch_bounds__(256) lsm_fwd_strided_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
+                                                              int64_t outer, int64_t D, int64_t inner) {
+  const int64_t total = outer * inner;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t o = idx / inner, i = idx - o * inner;
+    const Tin* x = in + o * D * inner + i;
+    Tout* y = out + o * D * inner + i;
+    A m = neg_inf<A>();
+    for (int64_t d = 0; d < D; ++d) {
+      const A f = convert<A, Tin>(x[d * inner]);
+      m = (f > m || f != f) ? f : m;
+    }
+    const A mm = (m == neg_inf<A>()) ? A(0) : m;
+    A s = 0;
+    for (int64_t d = 0; d < D; ++d) s += acc_exp<A>(convert<A, Tin>(x[d * inner]) - mm);
+    const A lse = m + acc_log<A>(s);
+    for (int64_t d = 0; d < D; ++d) y[d * inner] = convert<Tout, A>(convert<A, Tin>(x[d * inner]) - lse);
+  }
+}
+
+// ---- backward: grad_in = g - exp(y) * sum(g) ------------------------------------------------------------
+template <typename T, typename Tgi, typename A, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
+                                                              Tgi* __restrict__ gin, int64_t rows, int64_t C) {
+  __shared__ A sm[32];
+  const int64_t nvec = C / VEC;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* g = gout + row * C;
+    const T* y = yout + row * C;
+    Tgi* o = gin + row * C;
+    A acc = 0;
+    for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
+      A f[VEC];
+      load_as<A, T, VEC>(g + i * VEC, f);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc += f[k];
+    }
+    const A sum = block_sum<A, THREADS>(acc, sm);
+    for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
+      A f[VEC], yy[VEC];
+      load_as<A, T, VEC>(g + i * VEC, f);
+      load_as<A, T, VEC>(y + i * VEC, yy);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) f[k] -= acc_exp<A>(yy[k]) * sum;
+      store_as<A, Tgi, VEC>(o + i * VEC, f);
+    }
+  }
+}
+
+template <typename T, typename Tgi, typename A>
+__global__ void __launch_bounds__(256) lsm_bwd_strided_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
+                                                              Tgi* __restrict__ gin, int64_t outer, int64_t D,
+                                                              int64_t inner, bool warp_rows) {
+  if (warp_rows) {  // inner == 1 and short rows: one warp per row
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < outer; row += stride) {
+      const T* g = gout + row * D;
+      const T* y = yout + row * D;
+      Tgi* o = gin + row * D;
+      A acc = 0;
+      for (int64_t c = lane; c < D; c += 32) acc += convert<A, T>(g[c]);
+      acc = warp_sum_t(acc);
+      for (int64_t c = lane; c < D; c += 32)
+        o[c] = convert<Tgi, A>(convert<A, T>(g[c]) - acc_exp<A>(convert<A, T>(y[c])) * acc);
+    }
+    return;
+  }
+  const int64_t total = outer * inner;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t o_ = idx / inner, i = idx - o_ * inner;
+    const int64_t base = o_ * D * inner + i;
+    A acc = 0;
+    for (int64_t d = 0; d < D; ++d) acc += convert<A, T>(gout[base + d * inner]);
+    for (int64_t d = 0; d < D; ++d)
+      gin[base + d * inner] =
+          convert<Tgi, A>(convert<A, T>(gout[base + d * inner]) - acc_exp<A>(convert<A, T>(yout[base + d * inner])) * acc);
+  }
+}
+
+template <typename Tin, typename Tout, typename A>
+int launch_fwd(const void* in, void* out, int64_t outer, int64_t D, int64_t inner, cudaStream_t st) {
+  const Tin* x = static_cast<const Tin*>(in);
+  Tout* y = static_cast<Tout*>(out);
+  const int sms = sm_count();
+  if (inner == 1) {
+    if (D <= 1024) {
+      const int64_t ctas = (outer + 7) / 8;
+      const int grid = static_cast<int>(ctas < 8LL * sms ? ctas : 8LL * sms);
+      lsm_fwd_warp_kernel<Tin, Tout, A, 256><<<grid, 256, 0, st>>>(x, y, outer, D);
+      return launch_status();
+    }
+    constexpr int kVec = 16 / sizeof(Tin);
+    constexpr int kThreads = 512;
+    const int grid = static_cast<int>(outer < 4LL * sms ? outer : 4LL * sms);
+    const size_t out_align = sizeof(Tout) * kVec >= 16 ? 16 : sizeof(Tout) * kVec;
+    const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(out) % out_align == 0;
+    if (aligned) lsm_fwd_cta_kernel<Tin, Tout, A, kVec, kThreads><<<grid, kThreads, 0, st>>>(x, y, outer, D);
+    else lsm_fwd_cta_kernel<Tin, Tout, A, 1, kThreads><<<grid, kThreads, 0, st>>>(x, y, outer, D);
+    return launch_status();
+  }
+  const int64_t total = outer * inner;
+  const int64_t ctas = (total + 255) / 256;
+  const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
+  lsm_fwd_strided_kernel<Tin, Tout, A><<<grid, 256, 0, st>>>(x, y, outer, D, inner);
+  return launch_status();
+}
+
+template <typename T, typename Tgi, typename A>
+int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int64_t D, int64_t inner, cudaStream_t st) {
+  const T* g = static_cast<const T*>(gout);
+  const T* y = static_cast<const T*>(yout);
+  Tgi* o = static_cast<Tgi*>(gin);
+  const int sms = sm_count();
+  if (inner == 1 && D > 1024) {
+    constexpr int kVec = 16 / sizeof(T);
+    constexpr int kThreads = 512;
+    const int grid = static_cast<int>(outer < 4LL * sms ? outer : 4LL * sms);
+    const size_t gi_align = sizeof(Tgi) * kVec >= 16 ? 16 : sizeof(Tgi) * kVec;
+    const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(gout) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(yout) % 16 == 0 && reinterpret_cast<uintptr_t>(gin) % gi_align == 0;
+    if (aligned) lsm_bwd_cta_kernel<T, Tgi, A, kVec, kThreads><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
+    else lsm_bwd_cta_kernel<T, Tgi, A, 1, kThreads><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
+    return launch_status();
+  }
+  const bool warp_rows = inner == 1;
+  const int64_t total = warp_rows ? (outer + 7) / 8 : (outer * inner + 255) / 256;
+  const int grid = static_cast<int>(total < 16LL * sms ? total : 16LL * sms);
+  lsm_bwd_strided_kernel<T, Tgi, A><<<grid, 256, 0, st>>>(g, y, o, outer, D, inner, warp_rows);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int sb_log_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim,
+                           int64_t inner, sb_stream_t stream) {
+  if (outer < 0 || dim < 0 || inner < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (outer == 0 || dim == 0 || inner == 0) return SB_OK;
+  if (!in || !out) return SB_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(in) % dtype_size(in_dtype) || reinterpret_cast<uintptr_t>(out) % dtype_size(out_dtype))
+    return SB_ERR_MISALIGNED;
+  cudaStream_t st = as_stream(stream);
+  if (in_dtype == SB_F32 && out_dtype == SB_F32) return launch_fwd<float, float, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_BF16 && out_dtype == SB_BF16)
+    return launch_fwd<__nv_bfloat16, __nv_bfloat16, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F16 && out_dtype == SB_F16) return launch_fwd<__half, __half, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_BF16 && out_dtype == SB_F32) return launch_fwd<__nv_bfloat16, float, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F16 && out_dtype == SB_F32) return launch_fwd<__half, float, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F64 && out_dtype == SB_F64) return launch_fwd<double, double, double>(in, out, outer, dim, inner, st);
+  return SB_ERR_UNSUPPORTED;
+}
+
+int sb_log_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype,
+                            int64_t outer, int64_t dim, int64_t inner, sb_stream_t stream) {
+  if (outer < 0 || dim < 0 || inner < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (outer == 0 || dim == 0 || inner == 0) return SB_OK;
+  if (!grad_out || !out || !grad_in) return SB_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(grad_out) % dtype_size(dtype) || reinterpret_cast<uintptr_t>(out) % dtype_size(dtype) ||
+      reinterpret_cast<uintptr_t>(grad_in) % dtype_size(grad_in_dtype))
+    return SB_ERR_MISALIGNED;
+  cudaStream_t st = as_stream(stream);
+  if (dtype == SB_F32 && grad_in_dtype == SB_F32) return launch_bwd<float, float, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_BF16 && grad_in_dtype == SB_BF16)
+    return launch_bwd<__nv_bfloat16, __nv_bfloat16, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F16 && grad_in_dtype == SB_F16) return launch_bwd<__half, __half, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F32 && grad_in_dtype == SB_BF16)
+    return launch_bwd<float, __nv_bfloat16, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F32 && grad_in_dtype == SB_F16) return launch_bwd<float, __half, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F64 && grad_in_dtype == SB_F64) return launch_bwd<double, double, double>(grad_out, out, grad_in, outer, dim, inner, st);
+  return SB_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

@@ -1,0 +1,171 @@
+"""Functional front-end of the C ABI for tensors whose ``data_ptr()`` is a CUDA address.
+
+torch is used here for device memory and the current stream only; every computation is a call into
+``libsupa_b200_kernels.so`` through :mod:`torch_supa_b200.capi`.  The functions accept ordinary
+``device="cuda"`` tensors, which is how the parity tests and the benchmark drive the kernels at the C
+boundary; the ``"supa"`` device registered by the C++ host layer reaches the same entry points
+through the ATen dispatcher instead.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import capi
+
+_RED = {"none": capi.REDUCTION_NONE, "mean": capi.REDUCTION_MEAN, "sum": capi.REDUCTION_SUM}
+
+
+def _stream(t: torch.Tensor) -> int:
+    if t.device.type == "cuda":
+        return torch.cuda.current_stream(t.device).cuda_stream
+    return 0
+
+
+class CrossEntropyWorkspace:
+    """Device buffers one fused cross-entropy call needs besides its inputs and outputs."""
+
+    def __init__(self, rows: int, device):
+        self.row_loss = torch.empty(max(rows, 1), dtype=torch.float32, device=device)
+        self.acc = torch.zeros(2, dtype=torch.float64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_smoothing=0.0, reduction="mean",
+                                   grad=None, want_grad=True, workspace=None, grad_scale=1.0, row_grad_out=None,
+                                   row_lse=None, all_reduce=None):
+    """Fused cross entropy: returns ``(loss, grad_logits)``.
+
+    ``loss`` is a 0-d tensor in the logits' dtype for mean/sum and an fp32 ``[rows]`` tensor for none.
+    ``all_reduce``, when given, is called as ``all_reduce(acc_view)`` on a one-element float64 view of the
+    device accumulator, first for the valid-row count and then for the loss sum: this is the hook the
+    row-sharded multi-GPU path uses.
+    """
+    assert logits.dim() == 2 and target.dim() == 1 and logits.is_contiguous() and target.is_contiguous()
+    rows, classes = logits.shape
+    ws = workspace or CrossEntropyWorkspace(rows, logits.device)
+    st = _stream(logits)
+    if want_grad and grad is None:
+        grad = torch.empty_like(logits)
+    red = _RED[reduction]
+    if red != capi.REDUCTION_NONE:
+        capi.ce_count_valid(target, rows, classes, ignore_index, ws.acc, ws.status, st)
+        if all_reduce is not None:
+            all_reduce(ws.acc[1:2])
+    args = capi.CEArgs()
+    args.logits = logits.data_ptr()
+    args.dtype = capi.torch_dtype_code(logits.dtype)
+    args.reduction = red
+    args.target = target.data_ptr()
+    args.grad_logits = grad.data_ptr() if want_grad else None
+    args.row_loss = ws.row_loss.data_ptr()
+    args.row_lse = row_lse.data_ptr() if row_lse is not None else None
+    args.row_grad_out = row_grad_out.data_ptr() if row_grad_out is not None else None
+    args.acc = ws.acc.data_ptr()
+    args.rows, args.classes, args.ignore_index = rows, classes, ignore_index
+    args.label_smoothing = label_smoothing
+    args.grad_scale = grad_scale
+    args.status = ws.status.data_ptr()
+    capi.ce_forward_backward(args, st)
+    if red == capi.REDUCTION_NONE:
+        return ws.row_loss[:rows], (grad if want_grad else None)
+    loss = torch.empty((), dtype=logits.dtype, device=logits.device)
+    code = capi.torch_dtype_code(logits.dtype)
+    if all_reduce is None:
+        capi.ce_loss_sum_finish(ws.row_loss, rows, ws.acc, red, loss, code, st)
+    else:
+        capi.ce_loss_sum(ws.row_loss, rows, ws.acc, st)
+        all_reduce(ws.acc[0:1])
+        capi.ce_loss_finish(ws.acc, red, loss, code, st)
+    return loss, (grad if want_grad else None)
+
+
+def log_softmax(x, dim=-1, out_dtype=None):
+    x = x.contiguous()
+    dim %= max(x.dim(), 1)
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    shape = list(x.shape) or [1]
+    outer = 1
+    for s in shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in shape[dim + 1:]:
+        inner *= s
+    capi.log_softmax_forward(x, capi.torch_dtype_code(x.dtype), out, capi.torch_dtype_code(out.dtype), outer, shape[dim],
+                             inner, _stream(x))
+    return out
+
+
+def log_softmax_backward(grad_out, out, dim=-1, input_dtype=None):
+    grad_out, out = grad_out.contiguous(), out.contiguous()
+    dim %= max(out.dim(), 1)
+    gi = torch.empty(out.shape, dtype=input_dtype or out.dtype, device=out.device)
+    shape = list(out.shape) or [1]
+    outer = 1
+    for s in shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in shape[dim + 1:]:
+        inner *= s
+    capi.log_softmax_backward(grad_out, out, capi.torch_dtype_code(out.dtype), gi, capi.torch_dtype_code(gi.dtype), outer,
+                              shape[dim], inner, _stream(out))
+    return gi
+
+
+def _nll_args(logp, target, weight, ignore_index, reduction, status):
+    a = capi.NLLArgs()
+    a.log_probs = logp.data_ptr()
+    a.dtype = capi.torch_dtype_code(logp.dtype)
+    a.target_dtype = capi.torch_dtype_code(target.dtype)
+    a.target = target.data_ptr()
+    a.weight = weight.data_ptr() if weight is not None else None
+    a.rows, a.classes = logp.shape
+    a.ignore_index = ignore_index
+    a.reduction = _RED[reduction]
+    a.status = status.data_ptr() if status is not None else None
+    return a
+
+
+def nll_loss_forward(logp, target, weight=None, ignore_index=-100, reduction="mean", status=None):
+    logp, target = logp.contiguous(), target.contiguous()
+    rows = logp.shape[0]
+    out = torch.empty(rows if reduction == "none" else (), dtype=logp.dtype, device=logp.device)
+    total_weight = torch.zeros((), dtype=logp.dtype, device=logp.device)
+    capi.nll_loss_forward(_nll_args(logp, target, weight, ignore_index, reduction, status), out, total_weight, _stream(logp))
+    return out, total_weight
+
+
+def nll_loss_backward(grad_out, logp, target, weight=None, ignore_index=-100, reduction="mean", total_weight=None,
+                      status=None):
+    logp, target = logp.contiguous(), target.contiguous()
+    gi = torch.empty_like(logp)
+    capi.nll_loss_backward(_nll_args(logp, target, weight, ignore_index, reduction, status), grad_out.contiguous(),
+                           total_weight, gi, _stream(logp))
+    return gi
+
+
+def elementwise(op, out, *inputs, common_dtype=None, alpha=1.0, scalar=0.0):
+    """out = op(*inputs) with broadcasting to ``out.shape``; strides of every operand are honoured."""
+    desc = capi.make_ew_desc(op, out, inputs, common_dtype=common_dtype, alpha=alpha, scalar=scalar)
+    capi.elementwise(desc, _stream(out))
+    return out
+
+
+def reduce(op, inp, dims, keepdim=False, out_dtype=None):
+    """sum / mean / amax / amin of ``inp`` over ``dims`` (a list of dimensions)."""
+    nd = inp.dim()
+    dims = sorted({d % nd for d in dims}) if nd else []
+    shape = [s for d, s in enumerate(inp.shape) if d not in dims] if not keepdim else \
+        [1 if d in dims else s for d, s in enumerate(inp.shape)]
+    if out_dtype is None:
+        integral = inp.dtype in (torch.bool, torch.uint8, torch.int8, torch.int16, torch.int32, torch.int64)
+        out_dtype = torch.int64 if (integral and op == capi.RED_SUM) else inp.dtype
+    out = torch.empty(shape, dtype=out_dtype, device=inp.device)
+    desc = capi.make_reduce_desc(op, inp, out, dims)
+    need = capi.reduce_scratch_bytes(desc)
+    scratch = None
+    if need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=inp.device)
+        desc.scratch = scratch.data_ptr()
+        desc.scratch_bytes = need
+    capi.reduce(desc, _stream(inp))
+    return out
