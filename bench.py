@@ -59,7 +59,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -170,6 +170,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     capi.lib()  # fail loudly if the kernel library is missing
+    if args.force_generic:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 0))
 
     rows, classes, dtype_name, ignore_frac, eps = WORKLOADS[args.workload]
     if args.rows:
@@ -194,14 +196,19 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-
-    # ---- device-resident timing ---------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    # keep the GPU busy long enough for the clock sampler to see it under load
+    t_end = time.time() + (0.0 if args.quick else 0.6)
+    while time.time() < t_end:
+        step()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ---------------------------------------------------------------------
     kernel_events = []
     stream = torch.cuda.current_stream()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -213,7 +220,6 @@ def run_ours(args):
     stop.record(stream)
     barrier()
     elapsed_ms = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
 
     # dominant kernel alone (same launches, events around the fused sweep only)
     for _ in range(args.steps):
@@ -229,6 +235,7 @@ def run_ours(args):
         e1.record(stream)
         kernel_events.append((e0, e1))
     torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
     kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in kernel_events)
 
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
@@ -243,45 +250,48 @@ def run_ours(args):
 
     # ---- end to end: host buffers -> loss on the host ---------------------------------------------
     e2e = None
-    try:
-        import psutil
-
-        avail = psutil.virtual_memory().available
-    except Exception:
-        avail = 64 << 30
     nbytes = logits.numel() * esize
-    budget = int(avail * 0.4 / max(world, 1))
-    pinned_rows = rows if nbytes <= budget else max(1, int(budget // (classes * esize)))
-    host_logits = torch.empty(pinned_rows, classes, dtype=dtype).pin_memory()
-    host_logits.copy_(logits[:pinned_rows])
-    host_target = target.cpu().pin_memory()
-    host_loss = torch.empty((), dtype=dtype).pin_memory()
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    if args.quick:
+        args.no_cpu_baseline = True
+    else:
+        try:
+            import psutil
 
-    def e2e_step():
-        for r0 in range(0, rows, pinned_rows):
-            r1 = min(rows, r0 + pinned_rows)
-            logits[r0:r1].copy_(host_logits[: r1 - r0], non_blocking=True)
-        target.copy_(host_target, non_blocking=True)
-        l, _ = step()
-        host_loss.copy_(l, non_blocking=True)
+            avail = psutil.virtual_memory().available
+        except Exception:
+            avail = 64 << 30
+        budget = int(avail * 0.4 / max(world, 1))
+        pinned_rows = rows if nbytes <= budget else max(1, int(budget // (classes * esize)))
+        host_logits = torch.empty(pinned_rows, classes, dtype=dtype).pin_memory()
+        host_logits.copy_(logits[:pinned_rows])
+        host_target = target.cpu().pin_memory()
+        host_loss = torch.empty((), dtype=dtype).pin_memory()
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
 
-    e2e_step()
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record(stream)
-    for _ in range(e2e_steps):
+        def e2e_step():
+            for r0 in range(0, rows, pinned_rows):
+                r1 = min(rows, r0 + pinned_rows)
+                logits[r0:r1].copy_(host_logits[: r1 - r0], non_blocking=True)
+            target.copy_(host_target, non_blocking=True)
+            l, _ = step()
+            host_loss.copy_(l, non_blocking=True)
+
         e2e_step()
-    s1.record(stream)
-    barrier()
-    t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    e2e = {"value": total_rows / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
-           "pinned_rows": pinned_rows}
-    del host_logits
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        s1.record(stream)
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / e2e_steps
+        e2e = {"value": total_rows / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
+               "pinned_rows": pinned_rows}
+        del host_logits
 
     # ---- CPU baseline (rank 0, N = 1 only) --------------------------------------------------------
     cpu_baseline = None
@@ -340,6 +350,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="profiling mode: no clock warm loop, no e2e, no CPU baseline")
+    ap.add_argument("--force-generic", action="store_true", help="tuning: always use the generic two-sweep kernel")
     ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -56,6 +56,7 @@ typedef enum sb_dtype {
 
 /* Bits of the device status word. */
 #define SB_STATUS_TARGET_OUT_OF_RANGE 0x1 /* a class index outside [0, classes) and != ignore_index */
+#define SB_STATUS_KERNEL_TIMEOUT 0x2      /* a bounded wait inside a kernel ran out; its results are invalid */
 
 typedef enum sb_reduction { SB_REDUCTION_NONE = 0, SB_REDUCTION_MEAN = 1, SB_REDUCTION_SUM = 2 } sb_reduction;
 
@@ -137,6 +138,10 @@ SB_API int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const vo
  * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
  * of 2/4 CTAs.  For diagnostics and benchmarks. */
 SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
+
+/* Tuning hook for benchmarks and profiling (process-wide, not thread-safe against running launches):
+ * key 1 = cross-entropy kernel family (-1 automatic, 0 always the generic two-sweep kernel). */
+SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------
  * log_softmax / nll_loss as separate operators.

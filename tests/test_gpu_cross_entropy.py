@@ -186,3 +186,79 @@ def test_linearity_property_full_vocab(cuda_device):
     loss_p, _ = F2.cross_entropy_forward_backward(logits.float()[perm].contiguous(), target[perm].contiguous(),
                                                   label_smoothing=0.1, reduction="sum")
     assert rel_err(loss_p.item(), loss.item()) <= 1e-6
+
+
+@pytest.mark.parametrize("rows,classes,dtype,variant", [
+    (300, 4100, torch.float32, 1),      # 16400 B: two chunks, the second one unit shorter
+    (300, 32000, torch.float32, 1),     # the fp32 benchmark row
+    (200, 45000, torch.float32, 1),     # 180000 B: about the largest single-CTA rows
+    (200, 50000, torch.float32, 2),     # 200000 B: leaves no spare buffers in one CTA, goes to a 2-CTA cluster
+    (150, 128256, torch.bfloat16, 2),   # the bf16 benchmark row, split over a 2-CTA cluster
+    (150, 90004, torch.float32, 2),     # odd unit count: the two slices differ in length
+    (150, 100004, torch.float32, 4),    # 400016 B: odd unit count over four CTAs
+    (148, 150000, torch.float32, 4),    # 600000 B: 4-CTA cluster
+    (75, 300008, torch.float16, 4),
+    (30, 128256, torch.bfloat16, 0),    # too few rows for clusters: generic kernel
+    (64, 32002, torch.float32, 0),      # row pitch not a multiple of 16 bytes: generic kernel
+])
+def test_resident_variants(cuda_device, rows, classes, dtype, variant):
+    """The shared-memory-resident kernels (single CTA and 2/4-CTA clusters) against the oracle."""
+    from torch_supa_b200 import capi
+
+    assert capi.ce_kernel_variant(capi.torch_dtype_code(dtype), rows, classes) == variant
+    g = torch.Generator().manual_seed(classes)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::11] = -100
+    target[1] = 0
+    target[2] = classes - 1
+    for eps, red in ((0.1, "mean"), (0.0, "sum")):
+        loss, grad = _run(cuda_device, logits, target, label_smoothing=eps, reduction=red)
+        eloss, egrad, bad = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, eps, red)
+        scale = float((target != -100).sum()) if red == "mean" else 1.0
+        if dtype == torch.float32:
+            assert rel_err(loss, eloss[0]) <= 2e-6
+            assert_close(grad * scale, egrad * scale, 1e-5, 3e-7, f"grad {red}")
+        else:
+            assert rel_err(loss, eloss[0]) <= 1e-2
+            assert_close(grad * scale, egrad * scale, 1.6e-2 if dtype == torch.bfloat16 else 2e-3,
+                         1e-4 if dtype == torch.bfloat16 else 2e-5, f"grad {red}")
+        assert np.all(grad[(target == -100).numpy()] == 0)
+    # forward only and per-row losses
+    loss_n, none = _run(cuda_device, logits, target, reduction="none", want_grad=False)
+    eloss_n, _, _ = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, 0.0, "none", want_grad=False)
+    assert none is None
+    assert_close(loss_n, eloss_n, 2e-6, 2e-6, "row losses")
+
+
+def test_resident_matches_generic_bitwise_loss_order(cuda_device):
+    """Running twice gives identical bits (persistent grid, fixed row->CTA map, no atomics on floats)."""
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(2)
+    logits = (torch.randn(600, 32000, generator=g) * 2).to(cuda_device)
+    target = torch.randint(0, 32000, (600,), generator=g).to(cuda_device)
+    l1, g1 = F2.cross_entropy_forward_backward(logits, target)
+    l2, g2 = F2.cross_entropy_forward_backward(logits, target)
+    torch.cuda.synchronize()
+    assert l1.item() == l2.item() and torch.equal(g1, g2)
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(200, 32000, torch.float32), (160, 128256, torch.bfloat16), (50, 3000, torch.float32),
+                                                (64, 500, torch.float16)])
+def test_masked_logits_minus_inf(cuda_device, rows, classes, dtype):
+    """Rows where most classes are masked with -inf (and one row that is entirely -inf) behave as on the CPU."""
+    g = torch.Generator().manual_seed(7)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    logits[:, : classes // 2] = float("-inf")          # the first chunks of every row hold no finite value
+    logits[3, :] = float("-inf")
+    target = torch.randint(classes // 2, classes, (rows,), generator=g)
+    loss, grad = _run(cuda_device, logits, target, reduction="none")
+    ref_loss, ref_grad = oracle.aten_cross_entropy(logits, target, reduction="none", grad_out=torch.ones(rows))
+    ok = torch.ones(rows, dtype=torch.bool)
+    ok[3] = False
+    assert np.isnan(loss[3]) and torch.isnan(ref_loss[3])
+    assert_close(loss[ok.numpy()], ref_loss[ok].numpy(), 2e-6 if dtype == torch.float32 else 2e-6, 4e-6, "loss")
+    assert np.all(grad[ok.numpy()][:, : classes // 2] == 0)
+    tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
+    assert_close(grad[ok.numpy()], ref_grad[ok].numpy(), tol[0], tol[1], "grad")

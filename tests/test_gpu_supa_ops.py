@@ -1,0 +1,423 @@
+"""Operators through the ``supa`` device and the ATen dispatcher, golden = the same call on the CPU.
+
+These read like the reference's own op tests (test/test_add.py, test_binary_mul_kernel.py,
+test_activation_*_kernel.py, test_reduce_ops.py, test_softmax.py, test_loss.py): build the same data on CPU
+and on the device, run the operator on both, compare with the reference's tolerances."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(16,), (1024, 512), (1023, 511), (1025, 513), (128, 2135)]
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.fixture(scope="module")
+def supa():
+    import torch_supa_b200  # noqa: F401
+
+    if not torch.supa.is_available():
+        pytest.skip("no supa device")
+    return torch.device("supa", 0)
+
+
+def _pair(shape, dtype, seed=0, requires_grad=False, **kw):
+    from torch_supa_b200.testing import create_random_tensor
+
+    return create_random_tensor(shape, dtype, seed=seed, requires_grad=requires_grad, **kw)
+
+
+def _close(golden, out, dtype=None, loosen=1.0):
+    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+
+    dtype = dtype or golden.dtype
+    assert out.device.type == "supa" and out.dtype == golden.dtype and out.shape == golden.shape
+    assert_allclose(golden, out, RTOL[dtype] * loosen, ATOL[dtype] * loosen, equal_nan=True)
+
+
+# ---- runtime ---------------------------------------------------------------------------------------------------
+def test_roundtrip_and_views(supa):
+    x = torch.arange(24, dtype=torch.float32).reshape(2, 3, 4)
+    d = x.to(supa)
+    assert d.device == supa and d.is_supa
+    assert torch.equal(d.cpu(), x)
+    assert torch.equal(d.transpose(0, 2).contiguous().cpu(), x.transpose(0, 2).contiguous())
+    assert torch.equal(d[:, 1:, ::2].cpu(), x[:, 1:, ::2])
+    assert torch.equal(d.view(6, 4).t().cpu(), x.view(6, 4).t())
+    assert torch.equal(d.to(torch.int32).cpu(), x.to(torch.int32))
+    assert torch.equal(torch.ones(5, device=supa).cpu(), torch.ones(5))
+    assert torch.equal(torch.zeros(3, 2, device=supa, dtype=torch.bfloat16).cpu(), torch.zeros(3, 2, dtype=torch.bfloat16))
+    assert torch.full((4,), 7, device=supa).sum(0).item() == 28
+    e = torch.empty(0, device=supa)
+    assert e.numel() == 0 and e.cpu().numel() == 0
+    y = d.clone()
+    y.resize_(4, 6)
+    assert y.shape == (4, 6) and torch.equal(y.cpu().flatten(), x.flatten())
+    nc = torch.empty(4, 6, device=supa).t()
+    nc.copy_(x.view(6, 4))
+    assert torch.equal(nc.cpu(), x.view(6, 4))
+
+
+def test_pinned_non_blocking_copies(supa):
+    host = torch.randn(1 << 20).pin_memory()
+    d = host.to(supa, non_blocking=True)
+    back = torch.empty_like(host).pin_memory()
+    back.copy_(d, non_blocking=True)
+    torch.supa.synchronize()
+    assert torch.equal(back, host)
+
+
+def test_allocator_statistics_and_host_side_oom(supa):
+    torch.supa.synchronize()
+    base = torch.supa.memory_allocated()
+    x = torch.empty(1 << 20, device=supa)
+    assert torch.supa.memory_allocated() - base == 4 << 20
+    assert torch.supa.max_memory_allocated() >= base + (4 << 20)
+    del x
+    assert torch.supa.memory_allocated() == base
+    assert torch.supa.memory_reserved() >= 0
+    torch.supa.set_memory_limit(base + (1 << 20))
+    try:
+        with pytest.raises(torch.OutOfMemoryError):
+            torch.empty(1 << 20, device=supa)  # 4 MiB > 1 MiB cap: refused on the host, the GPU is never asked
+        small = torch.empty(1 << 10, device=supa)
+        assert small.numel() == 1 << 10
+    finally:
+        torch.supa.set_memory_limit(0)
+    assert torch.supa.memory_stats()["num_ooms"] >= 1
+    torch.supa.empty_cache()
+
+
+def test_streams_and_events(supa):
+    s = torch.Stream(device=supa)
+    start, end = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
+    x = torch.randn(1 << 22).to(supa)
+    with s:
+        start.record()
+        y = x * 2
+        y.record_stream(s) if hasattr(y, "record_stream") else None
+        end.record()
+    end.synchronize()
+    assert start.elapsed_time(end) >= 0
+    s.synchronize()
+    assert torch.equal(y.cpu(), x.cpu() * 2)
+
+
+def test_autograd_engine_runs_backward_on_device(supa):
+    a_cpu, a = _pair((64, 128), torch.float32, requires_grad=True)
+    b_cpu, b = _pair((64, 128), torch.float32, seed=1, requires_grad=True)
+    (F.silu(a) * b).sum().backward()
+    (F.silu(a_cpu) * b_cpu).sum().backward()
+    _close(a_cpu.grad, a.grad, loosen=4)
+    _close(b_cpu.grad, b.grad, loosen=4)
+
+
+# ---- add / mul ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_sub_mul_same_shape(supa, shape, dtype):
+    a_cpu, a = _pair(shape, dtype)
+    b_cpu, b = _pair(shape, dtype, seed=1)
+    _close(a_cpu + b_cpu, a + b)
+    _close(a_cpu - b_cpu, a - b)
+    _close(a_cpu * b_cpu, a * b)
+    _close(torch.add(a_cpu, b_cpu, alpha=2), torch.add(a, b, alpha=2))
+    _close(a_cpu / (b_cpu.abs() + 1), a / (b.abs() + 1) if hasattr(torch.Tensor, "_never") else (a / (b_cpu.abs() + 1).to("supa")))
+    _close(-a_cpu, -a)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_broadcast_scalar_inplace(supa, dtype):
+    a_cpu, a = _pair((128, 96), dtype)
+    one_cpu, one = _pair((1,), dtype, seed=2)
+    row_cpu, row = _pair((96,), dtype, seed=3)
+    _close(a_cpu + one_cpu, a + one)
+    _close(a_cpu * row_cpu, a * row)
+    _close(a_cpu + 2.5, a + 2.5)
+    _close(3 * a_cpu, 3 * a)
+    _close(1.5 - a_cpu, 1.5 - a)
+    _close(a_cpu * 0.5, a * 0.5)
+    c_cpu, c = a_cpu.clone(), a.clone()
+    c_cpu += row_cpu
+    c += row
+    _close(c_cpu, c)
+    c_cpu *= 2
+    c *= 2
+    _close(c_cpu, c)
+    out = torch.empty(0, device="supa", dtype=dtype)
+    torch.add(a, row, out=out)
+    _close(a_cpu + row_cpu, out)
+    out_t = torch.empty(96, 128, device="supa", dtype=dtype).t()  # out= with foreign strides
+    torch.mul(a, row, out=out_t)
+    _close(a_cpu * row_cpu, out_t)
+
+
+def test_as_strided_transposed_operand(supa):
+    """The reference's strided-add case (test/test_add.py:79-92): [1, 1024, 512] with strides [524288, 1, 1024]."""
+    base_cpu, base = _pair((524288,), torch.float32)
+    w_cpu, w = _pair((1, 1024, 512), torch.float32, seed=1)
+    v_cpu = base_cpu.as_strided((1, 1024, 512), (524288, 1, 1024))
+    v = base.as_strided((1, 1024, 512), (524288, 1, 1024))
+    _close(v_cpu + w_cpu, v + w)
+    m_cpu, m = _pair((512, 256), torch.float32, seed=2)
+    n_cpu, n = _pair((256, 512), torch.float32, seed=3)
+    r = m.t() * n
+    assert r.stride() == (m_cpu.t() * n_cpu).stride()
+    _close(m_cpu.t() * n_cpu, r)
+    _close(n_cpu * m_cpu.t(), n * m.t())
+
+
+def test_type_promotion_contract(supa):
+    """bf16 x fp32 -> fp32 (test/test_binary_mul_kernel.py:97-108), int32 + fp32 -> fp32, wrapped numbers."""
+    a_cpu, a = _pair((1024, 128), torch.bfloat16)
+    b_cpu, b = _pair((1024, 128), torch.float32, seed=1)
+    r = a * b
+    assert r.dtype == torch.float32
+    _close(a_cpu * b_cpu, r)
+    i_cpu, i = _pair((256, 256), torch.int32, min_value=-1000, max_value=1000)
+    r = i + b[:256, :].contiguous().view(-1)[: 256 * 128].repeat(2).view(256, 256) if False else None
+    f_cpu, f = _pair((256, 256), torch.float32, seed=2)
+    r = i + f
+    assert r.dtype == torch.float32
+    assert torch.equal(r.cpu(), i_cpu + f_cpu)
+    h_cpu, h = _pair((64,), torch.float16)
+    assert (h + 1.5).dtype == torch.float16 and torch.equal((h + 1.5).cpu(), h_cpu + 1.5)
+    assert (i * 1.5).dtype == torch.float32 and torch.equal((i * 1.5).cpu(), i_cpu * 1.5)
+    b1_cpu, b1 = _pair((100,), torch.bool)
+    b2_cpu, b2 = _pair((100,), torch.bool, seed=1)
+    assert torch.equal((b1 + b2).cpu(), b1_cpu + b2_cpu) and torch.equal((b1 * b2).cpu(), b1_cpu * b2_cpu)
+    big = torch.tensor([2**31 - 1, -2**31], dtype=torch.int32)
+    assert torch.equal((big.to(supa) + torch.tensor([1, -1], dtype=torch.int32).to(supa)).cpu(), big + torch.tensor([1, -1], dtype=torch.int32))
+    a4_cpu, a4 = _pair((1, 64, 24, 64), torch.bfloat16, seed=5)
+    b4_cpu, b4 = _pair((1, 64, 1, 64), torch.float32, seed=6)
+    _close(a4_cpu * b4_cpu, a4 * b4)
+
+
+# ---- activations -------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["gelu", "gelu_tanh", "silu"])
+def test_activation_forward_backward(supa, shape, dtype, act):
+    fn = {"gelu": F.gelu, "gelu_tanh": lambda v: F.gelu(v, approximate="tanh"), "silu": F.silu}[act]
+    x_cpu, x = _pair(shape, dtype, requires_grad=True)
+    g_cpu, g = _pair(shape, dtype, seed=1)
+    y = fn(x)
+    # low-precision golden: fp32 on up-cast inputs, cast down (test/test_loss.py:258-276)
+    xr = x_cpu.detach().float().requires_grad_(True)
+    yr = fn(xr)
+    _close(yr.detach().to(dtype), y.detach(), loosen=2)
+    y.backward(g)
+    yr.backward(g_cpu.float())
+    _close(xr.grad.to(dtype), x.grad, loosen=3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape,dim", [((1024, 512), -1), ((1023, 510), 1), ((64, 22016), -1), ((6, 8, 10), 1), ((512, 100), 0)])
+def test_glu_forward_backward(supa, shape, dim, dtype):
+    x_cpu, x = _pair(shape, dtype, requires_grad=True)
+    y = F.glu(x, dim)
+    xr = x_cpu.detach().float().requires_grad_(True)
+    yr = F.glu(xr, dim)
+    g_cpu, g = _pair(tuple(yr.shape), dtype, seed=1)
+    from torch_supa_b200.testing import assert_allclose
+
+    assert_allclose(yr.detach().to(dtype), y.detach(), 1.6e-2 if dtype == torch.bfloat16 else 2e-3 if dtype == torch.float16 else 3e-6,
+                    1e-2 if dtype == torch.bfloat16 else 1e-4 if dtype == torch.float16 else 1e-5)
+    y.backward(g)
+    yr.backward(g_cpu.float())
+    assert_allclose(xr.grad.to(dtype), x.grad, 1.6e-2 if dtype == torch.bfloat16 else 3e-3 if dtype == torch.float16 else 4e-6,
+                    1e-2 if dtype == torch.bfloat16 else 1e-3 if dtype == torch.float16 else 1e-5)
+
+
+def test_swiglu_chain_on_views(supa):
+    """silu(a) * b with a, b the two halves of one bf16 tensor (strided views), forward and backward."""
+    x_cpu, x = _pair((256, 22016), torch.bfloat16, requires_grad=True)
+    g_cpu, g = _pair((256, 11008), torch.bfloat16, seed=1)
+    out = F.silu(x[:, :11008]) * x[:, 11008:]
+    out.backward(g)
+    xr = x_cpu.detach().float().requires_grad_(True)
+    ref = (F.silu(xr[:, :11008]).bfloat16().float() * xr[:, 11008:])
+    ref.backward(g_cpu.float())
+    _close(ref.detach().bfloat16(), out.detach(), loosen=1)
+    from torch_supa_b200.testing import assert_allclose
+
+    assert_allclose(xr.grad.bfloat16(), x.grad, 2.4e-2, 2e-2)
+
+
+# ---- reductions ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES + [torch.float64])
+@pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), 0), ((64, 65536), -1), ((7, 9, 11), (0, 2)),
+                                       ((5, 6, 7, 8), None), ((1,), 0), ((3, 1, 5), 1)])
+def test_sum_mean_amax(supa, shape, dim, dtype):
+    from torch_supa_b200.testing import assert_allclose
+
+    x_cpu, x = _pair(shape, dtype)
+    n = x_cpu.numel() if dim is None else int(np.prod([shape[d] for d in (dim if isinstance(dim, tuple) else (dim,))]))
+    for keepdim in (False, True):
+        kw = {} if dim is None else {"dim": dim, "keepdim": keepdim}
+        for op in ("sum", "mean"):
+            out = getattr(x, op)(**kw)
+            ref = getattr(x_cpu.double(), op)(**kw)
+            assert out.dtype == dtype and out.shape == ref.shape
+            if dtype in (torch.bfloat16, torch.float16):
+                assert_allclose(ref.to(dtype).float(), out.float(), 8e-3 if dtype == torch.bfloat16 else 1e-3, 2e-2 if op == "sum" else 1e-3)
+            else:
+                k = max(1.0, 4 * (np.log2(n) - 4)) if n > 32 else 1.0
+                assert_allclose(ref.to(dtype), out, k * 1.3e-6 if dtype == torch.float32 else 1e-12,
+                                k * 1e-5 * (max(1.0, n ** 0.5 / 8) if op == "sum" else 1) if dtype == torch.float32 else 1e-10)
+        if dim is not None:
+            assert torch.equal(x.amax(**kw).cpu(), x_cpu.amax(**kw)), "amax is exact"
+            assert torch.equal(x.amin(**kw).cpu(), x_cpu.amin(**kw))
+
+
+def test_reduction_dtype_rules(supa):
+    x_cpu, x = _pair((300, 700), torch.bfloat16)
+    out = x.sum(-1, dtype=torch.float32)
+    assert out.dtype == torch.float32
+    _close(x_cpu.sum(-1, dtype=torch.float32), out, loosen=40)
+    i_cpu, i = _pair((50, 999), torch.int32, min_value=0, max_value=100)
+    assert i.sum().dtype == torch.int64 and i.sum().item() == i_cpu.sum().item()
+    assert torch.equal(i.sum(1).cpu(), i_cpu.sum(1))
+    b_cpu, b = _pair((1000,), torch.bool)
+    assert b.sum().item() == b_cpu.sum().item()
+    nan_cpu = x_cpu.float().clone()
+    nan_cpu[5, 77] = float("nan")
+    assert torch.isnan(nan_cpu.to(supa).amax(-1)[5]).item()
+    with pytest.raises((RuntimeError, IndexError)):
+        torch.empty(0, 4, device=supa).amax(0)
+    assert torch.equal(torch.empty(0, 4, device=supa).sum(0).cpu(), torch.zeros(4))
+    out = torch.empty(0, device=supa)
+    torch.sum(x.float(), 1, out=out)
+    _close(x_cpu.float().sum(1), out, loosen=40)
+
+
+# ---- softmax / nll -------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), -1), ((1025, 513), 0), ((64, 32000), -1),
+                                       ((4, 5, 6, 7), 2)])
+def test_log_softmax_forward_backward(supa, shape, dim, dtype):
+    from torch_supa_b200.testing import assert_allclose
+
+    x_cpu, x = _pair(shape, dtype, requires_grad=True)
+    g_cpu, g = _pair(shape, dtype, seed=1)
+    y = F.log_softmax(x, dim)
+    xr = x_cpu.detach().float().requires_grad_(True)
+    yr = F.log_softmax(xr, dim)
+    assert_allclose(yr.detach().to(dtype), y.detach(), 1.3e-6 if dtype == torch.float32 else 1.6e-2, 1e-5 if dtype == torch.float32 else 1e-3)
+    y.backward(g)
+    yr.backward(g_cpu.float())
+    mag = float(g_cpu.float().sum(dim, keepdim=True).abs().max()) + 1
+    assert_allclose(xr.grad.to(dtype), x.grad, 1.3e-6 if dtype == torch.float32 else 1.6e-2, (1e-5 if dtype == torch.float32 else 2e-2) * mag)
+    yf = F.log_softmax(x.detach(), dim, dtype=torch.float32)
+    assert yf.dtype == torch.float32
+    assert_allclose(F.log_softmax(x_cpu.detach().float(), dim), yf, 2e-6, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(16, 10), (1024, 512), (2000, 1000), (100, 20000)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_nll_loss_forward_backward_weight(supa, shape, reduction, dtype):
+    from torch_supa_b200.testing import assert_allclose
+
+    g = torch.Generator().manual_seed(shape[0])
+    logp_cpu = F.log_softmax(torch.randn(*shape, generator=g), 1).to(dtype).requires_grad_(True)
+    t_cpu = torch.randint(0, shape[1], (shape[0],), generator=g)
+    t_cpu[::9] = -100
+    t_before = t_cpu.clone()
+    w_cpu = (torch.rand(shape[1], generator=g) + 0.5).to(dtype)
+    for weight in (None, w_cpu):
+        x = logp_cpu.detach().to(supa).requires_grad_(True)
+        t = t_cpu.to(supa)
+        out = F.nll_loss(x, t, weight=None if weight is None else weight.to(supa), reduction=reduction)
+        xr = logp_cpu.detach().float().requires_grad_(True)
+        ref = F.nll_loss(xr, t_cpu, weight=None if weight is None else weight.float(), reduction=reduction)
+        rtol = {torch.float32: 4e-6, torch.bfloat16: 1.6e-2, torch.float16: 2e-3}[dtype]
+        assert_allclose(ref.detach().to(dtype), out.detach(), rtol, rtol)
+        go_cpu = torch.randn(ref.shape, generator=g).to(dtype)
+        out.backward(go_cpu.to(supa))
+        ref.backward(go_cpu.float())
+        assert_allclose(xr.grad.to(dtype), x.grad, rtol * 2, 1e-6 if dtype == torch.float32 else 1e-4)
+        assert torch.equal(t.cpu(), t_before), "the target tensor is not modified"
+
+
+# ---- cross entropy -------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1, 1000), (16, 1000), (1, 6), (512, 1024), (512, 1027), (64, 32000), (160, 128256)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cross_entropy_forward_backward(supa, shape, reduction, dtype):
+    """F.cross_entropy through the dispatcher (test/test_loss.py:235-276), with ignore_index and label smoothing."""
+    from torch_supa_b200.testing import assert_allclose
+
+    g = torch.Generator().manual_seed(shape[1])
+    x_cpu = (torch.randn(*shape, generator=g) * 2).to(dtype)
+    t_cpu = torch.randint(0, shape[1], (shape[0],), generator=g)
+    if shape[0] > 4:
+        t_cpu[::7] = -100
+    for eps in (0.0, 0.1):
+        x = x_cpu.to(supa).requires_grad_(True)
+        loss = F.cross_entropy(x, t_cpu.to(supa), reduction=reduction, label_smoothing=eps)
+        xr = x_cpu.float().requires_grad_(True)
+        ref = F.cross_entropy(xr, t_cpu, reduction=reduction, label_smoothing=eps)
+        assert loss.dtype == dtype and loss.shape == ref.shape
+        rtol = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
+        assert_allclose(ref.detach().to(dtype), loss.detach(), rtol, 1e-5 if dtype == torch.float32 else 1e-2)
+        go = torch.randn(ref.shape, generator=g).to(dtype) if reduction == "none" else torch.tensor(0.5, dtype=dtype)
+        loss.backward(go.to(supa))
+        ref.backward(go.float())
+        scale = float((t_cpu != -100).sum()) if reduction == "mean" else 1.0
+        grtol = {torch.float32: 1e-5, torch.bfloat16: 2.4e-2, torch.float16: 3e-3}[dtype]
+        gatol = {torch.float32: 3e-7, torch.bfloat16: 2e-4, torch.float16: 4e-5}[dtype]
+        assert x.grad.dtype == dtype
+        assert_allclose(xr.grad * scale, x.grad.float() * scale, grtol, gatol)
+
+
+def test_cross_entropy_edge_cases(supa):
+    x_cpu, x = _pair((8, 20), torch.float32)
+    all_ign = torch.full((8,), -100)
+    assert torch.isnan(F.cross_entropy(x, all_ign.to(supa))).item()
+    assert F.cross_entropy(x, all_ign.to(supa), reduction="sum").item() == 0
+    assert torch.equal(F.cross_entropy(x, all_ign.to(supa), reduction="none").cpu(), torch.zeros(8))
+    t = torch.tensor([1, 2, 2, 3, 2, 0, 5, 2])
+    _close(F.cross_entropy(x_cpu, t, ignore_index=2), F.cross_entropy(x, t.to(supa), ignore_index=2), loosen=2)
+    v_cpu, v = _pair((20,), torch.float32, seed=3)  # 1-D logits with a 0-d target
+    _close(F.cross_entropy(v_cpu, torch.tensor(4)), F.cross_entropy(v, torch.tensor(4).to(supa)), loosen=2)
+    nc = x_cpu.t().contiguous().to(supa).t()  # non-contiguous logits
+    _close(F.cross_entropy(x_cpu, t), F.cross_entropy(nc, t.to(supa)), loosen=2)
+    # no gradient requested: forward only, nothing is saved
+    with torch.no_grad():
+        _close(F.cross_entropy(x_cpu, t), F.cross_entropy(x, t.to(supa)), loosen=2)
+    # composite fallbacks: class weights, probability targets, fp64
+    w_cpu = torch.rand(20) + 0.5
+    _close(F.cross_entropy(x_cpu, t, weight=w_cpu), F.cross_entropy(x, t.to(supa), weight=w_cpu.to(supa)), loosen=4)
+    d_cpu, d = _pair((8, 20), torch.float64, seed=4)
+    _close(F.cross_entropy(d_cpu, t), F.cross_entropy(d, t.to(supa)))
+
+
+def test_cross_entropy_backward_twice_and_scaled(supa):
+    x_cpu, x = _pair((32, 5000), torch.float32, requires_grad=True)
+    t = torch.randint(0, 5000, (32,), generator=torch.Generator().manual_seed(1))
+    loss = F.cross_entropy(x, t.to(supa))
+    (loss / 4).backward(retain_graph=True)
+    g1 = x.grad.clone()
+    x.grad = None
+    loss.backward()
+    g2 = x.grad.clone()
+    ref = F.cross_entropy(x_cpu, t)
+    ref.backward()
+    from torch_supa_b200.testing import assert_allclose
+
+    assert_allclose(x_cpu.grad * 32, g2 * 32, 1e-5, 3e-7)
+    assert_allclose(x_cpu.grad * 8, g1 * 32, 1e-5, 3e-7)
+
+
+def test_out_of_range_target_raises_at_the_next_sync_and_device_survives(supa):
+    x_cpu, x = _pair((6, 8), torch.float32)
+    bad = torch.tensor([1, 2, 8, 3, 0, 1]).to(supa)
+    loss = F.cross_entropy(x, bad)  # asynchronous: nothing is raised here, nothing traps on the device
+    with pytest.raises(IndexError):
+        loss.item()
+    good = torch.tensor([1, 2, 7, 3, 0, 1])
+    _close(F.cross_entropy(x_cpu, good), F.cross_entropy(x, good.to(supa)), loosen=2)
+    torch.supa.synchronize()

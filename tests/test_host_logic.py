@@ -1,0 +1,141 @@
+"""Host-side logic that needs no GPU: registration hygiene, row sharding, the two-scalar loss protocol
+over a real 2-process gloo group."""
+import math
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_package_imports_and_registers_the_device():
+    import torch_supa_b200  # noqa: F401
+
+    assert torch._C._get_privateuse1_backend_name() == "supa"
+    assert hasattr(torch, "supa") and torch.supa.device_count() >= 0
+    assert torch.device("supa:0").type == "supa"
+
+
+def test_no_dangling_operator_registrations():
+    """Every m.impl names an existing schema (the check of test/test_dispatch_registration.py in the reference)."""
+    import torch_supa_b200  # noqa: F401
+
+    assert torch._C._dispatch_find_dangling_impls() == []
+
+
+@pytest.mark.parametrize("op", ["aten::add.Tensor", "aten::add_.Tensor", "aten::add.out", "aten::mul.Tensor", "aten::mul.out",
+                                "aten::gelu", "aten::gelu.out", "aten::gelu_backward", "aten::silu", "aten::silu_backward",
+                                "aten::glu", "aten::glu_backward", "aten::sum.dim_IntList", "aten::sum.IntList_out", "aten::mean.dim",
+                                "aten::mean.out", "aten::amax", "aten::amax.out", "aten::_log_softmax", "aten::_log_softmax.out",
+                                "aten::_log_softmax_backward_data", "aten::nll_loss_forward", "aten::nll_loss_forward.output",
+                                "aten::nll_loss_backward", "aten::nll_loss_backward.grad_input", "aten::cross_entropy_loss",
+                                "aten::empty.memory_format", "aten::empty_strided", "aten::_copy_from", "aten::as_strided",
+                                "aten::view", "aten::resize_", "aten::fill_.Scalar", "aten::zero_", "aten::_local_scalar_dense"])
+def test_operator_has_a_privateuse1_kernel(op):
+    import torch_supa_b200  # noqa: F401
+
+    table = torch._C._dispatch_dump_table(op)
+    line = [l for l in table.splitlines() if l.startswith("PrivateUse1:")]
+    assert line and "libtorch_supa_b200" in table or "registered at" in line[0], table
+
+
+def test_cross_entropy_autograd_key_falls_through():
+    import torch_supa_b200  # noqa: F401
+
+    table = torch._C._dispatch_dump_table("aten::cross_entropy_loss")
+    auto = [l for l in table.splitlines() if l.startswith("AutogradPrivateUse1:")]
+    assert auto and "fallthrough" in auto[0]
+
+
+def test_operators_fail_loudly_without_a_device():
+    import torch_supa_b200  # noqa: F401
+
+    if torch.supa.device_count() > 0:
+        pytest.skip("a device is present")
+    with pytest.raises(RuntimeError):
+        torch.empty(4, device="supa")
+
+
+def test_shard_rows_partitions_exactly():
+    from torch_supa_b200.distributed import shard_rows
+
+    for total in (0, 1, 7, 32768, 4097):
+        for world in (1, 2, 4, 8):
+            blocks = [shard_rows(total, world, r) for r in range(world)]
+            assert blocks[0][0] == 0 and blocks[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+            sizes = [e - b for b, e in blocks]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_rows(10, 2, 2)
+
+
+def test_combine_loss_rules():
+    from torch_supa_b200.distributed import combine_loss
+
+    ident = lambda v: v  # noqa: E731
+    assert combine_loss(6.0, 3.0, "mean", ident) == 2.0
+    assert combine_loss(6.0, 3.0, "sum", ident) == 6.0
+    assert math.isnan(combine_loss(0.0, 0.0, "mean", ident))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _sharded_worker(rank, world, port, out_path):
+    sys.path.insert(0, str(ROOT))
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from torch_supa_b200.distributed import combine_loss, shard_rows
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(0)
+    rows, classes = 37, 50
+    logits = torch.randn(rows, classes, generator=g) * 2
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::5] = -100
+    b, e = shard_rows(rows, world, rank)
+    local_logits = logits[b:e].clone().requires_grad_(True)
+    local_target = target[b:e]
+
+    def all_reduce_sum(values):
+        t = torch.tensor(values, dtype=torch.float64)
+        dist.all_reduce(t)
+        return t.tolist()
+
+    # step 1: valid-row count first, step 2: local sums, step 3: loss sum (the protocol of the fused kernel)
+    local_valid = float((local_target != -100).sum())
+    (global_valid,) = all_reduce_sum([local_valid])
+    local_sum = F.cross_entropy(local_logits, local_target, ignore_index=-100, label_smoothing=0.1, reduction="sum")
+    loss = combine_loss(float(local_sum), local_valid, "mean", all_reduce_sum)
+    (local_sum / global_valid).backward()
+    ref_logits = logits.clone().requires_grad_(True)
+    ref = F.cross_entropy(ref_logits, target, ignore_index=-100, label_smoothing=0.1)
+    ref.backward()
+    ok = abs(loss - float(ref)) <= 1e-6 * abs(float(ref)) and torch.allclose(local_logits.grad, ref_logits.grad[b:e], rtol=1e-5, atol=1e-8)
+    flags = torch.tensor([1.0 if ok else 0.0], dtype=torch.float64)
+    dist.all_reduce(flags)
+    if rank == 0:
+        Path(out_path).write_text(str(flags.item()))
+    dist.destroy_process_group()
+
+
+def test_two_process_gloo_sharded_loss(tmp_path):
+    """World size 2 on CPU: row blocks per rank, all-reduce of (valid count) then (loss sum), gradients scaled
+    by the global 1/|V|; equals the single-process result."""
+    out = tmp_path / "ok.txt"
+    mp.spawn(_sharded_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert float(out.read_text()) == 2.0

@@ -1,0 +1,111 @@
+// C entry points the Python package binds with ctypes (device control, memory statistics, the NCCL
+// communicator), and the all-reduce operator for supa tensors.  Errors travel as a thread-local message
+// (supa_last_error) plus a non-zero return code, since C++ exceptions cannot cross a ctypes call.
+#include <torch/library.h>
+
+#include <cstring>
+#include <string>
+
+#include "Common.h"
+#include "dist/NcclComm.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+template <class F>
+int guarded(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const c10::Error& e) {
+    g_last_error = e.what_without_backtrace();
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+  }
+  return -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+SUPA_EXPORT const char* supa_last_error() { return g_last_error.c_str(); }
+SUPA_EXPORT int supa_device_count() { return supa::device_count(); }
+SUPA_EXPORT int supa_current_device(int* out) {
+  return guarded([&] { *out = supa::current_device(); });
+}
+SUPA_EXPORT int supa_set_device(int device) {
+  return guarded([&] { supa::set_device(static_cast<c10::DeviceIndex>(device)); });
+}
+SUPA_EXPORT int supa_synchronize(int device) {
+  return guarded([&] { supa::synchronize_device(static_cast<c10::DeviceIndex>(device < 0 ? supa::current_device() : device)); });
+}
+SUPA_EXPORT int supa_current_stream(int device, void** out) {
+  return guarded([&] { *out = supa::current_cuda_stream(static_cast<c10::DeviceIndex>(device)); });
+}
+SUPA_EXPORT int supa_memory_stats(int device, int64_t* out6) {
+  return guarded([&] {
+    const supa::MemoryStats s = supa::memory_stats(static_cast<c10::DeviceIndex>(device));
+    out6[0] = s.allocated_bytes;
+    out6[1] = s.peak_allocated_bytes;
+    out6[2] = s.reserved_bytes;
+    out6[3] = s.num_allocs;
+    out6[4] = s.num_frees;
+    out6[5] = s.num_ooms;
+  });
+}
+SUPA_EXPORT int supa_reset_peak_memory_stats(int device) {
+  return guarded([&] { supa::reset_peak_memory_stats(static_cast<c10::DeviceIndex>(device)); });
+}
+SUPA_EXPORT int supa_empty_cache() {
+  return guarded([&] { supa::empty_cache(); });
+}
+SUPA_EXPORT int supa_set_memory_limit(int device, int64_t bytes) {
+  return guarded([&] { supa::set_memory_limit(static_cast<c10::DeviceIndex>(device), bytes); });
+}
+// Reads and clears the device status word after draining the current stream; a set error bit comes back
+// as a non-zero return code with the message in supa_last_error().
+SUPA_EXPORT int supa_check_status(int device) {
+  return guarded([&] {
+    const c10::DeviceIndex d = static_cast<c10::DeviceIndex>(device < 0 ? supa::current_device() : device);
+    supa::check_status_word(d, supa::current_cuda_stream(d));
+  });
+}
+
+// ---- NCCL communicator --------------------------------------------------------------------------------------
+SUPA_EXPORT int supa_nccl_unique_id(char* out128) {
+  return guarded([&] { supa::NcclComm::unique_id(out128); });
+}
+SUPA_EXPORT int supa_nccl_init(int nranks, const char* id128, int rank, int device, int64_t* handle) {
+  return guarded([&] { *handle = (new supa::NcclComm(nranks, id128, rank, device))->handle(); });
+}
+SUPA_EXPORT int supa_nccl_destroy(int64_t handle) {
+  return guarded([&] { delete supa::NcclComm::from_handle(handle); });
+}
+SUPA_EXPORT int supa_nccl_abort(int64_t handle) {
+  return guarded([&] { supa::NcclComm::from_handle(handle)->abort(); });
+}
+SUPA_EXPORT int supa_nccl_all_reduce(int64_t handle, void* data, int64_t count, int dtype, int op, void* stream) {
+  return guarded([&] { supa::NcclComm::from_handle(handle)->all_reduce(data, count, dtype, op, stream); });
+}
+
+}  // extern "C"
+
+namespace supa {
+namespace {
+
+// supa_b200::all_reduce_(Tensor(a!) self, int comm, int op) -> Tensor(a!): in place, on the current stream.
+at::Tensor& all_reduce_(at::Tensor& self, int64_t comm, int64_t op) {
+  TORCH_CHECK(is_supa(self) && self.is_contiguous(), "all_reduce_: expected a contiguous supa tensor");
+  const c10::DeviceGuard guard(self.device());
+  NcclComm::from_handle(comm)->all_reduce(self.data_ptr(), self.numel(), dtype_code(self.scalar_type()), static_cast<int>(op),
+                                          stream_of(self));
+  return self;
+}
+
+}  // namespace
+}  // namespace supa
+
+TORCH_LIBRARY_FRAGMENT(supa_b200, m) { m.def("all_reduce_(Tensor(a!) self, int comm, int op) -> Tensor(a!)"); }
+TORCH_LIBRARY_IMPL(supa_b200, PrivateUse1, m) { m.impl("all_reduce_", TORCH_FN(supa::all_reduce_)); }

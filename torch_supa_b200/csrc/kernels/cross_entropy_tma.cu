@@ -1,22 +1,761 @@
-// Cross-entropy kernel selection (and, below, the shared-memory-resident variant).
+// Cross entropy with the row resident in shared memory: one HBM read and one HBM write per logit.
+//
+// A persistent CTA (or a cluster of 2 / 4 CTAs that split the row) owns every num_clusters-th row.
+// The row slice is cut into chunks of about 8 KB.  The CTA is divided into G warp groups; group g owns
+// the chunks c = g, g + G, ... of every row together with a private ring of shared-memory buffers, and
+// runs its own little pipeline:
+//
+//   * the group's first thread streams its chunks in with 1-D bulk copies (cp.async.bulk global ->
+//     shared, completion on one mbarrier per buffer) and streams finished chunks out with bulk stores
+//     (cp.async.bulk shared -> global, bulk groups);
+//   * the group's threads sweep their chunks twice while they sit in shared memory: sweep A
+//     accumulates the online (max, sum exp) and sum x as chunks land, sweep B overwrites each chunk in
+//     place with the gradient; a group-wide named barrier (not a CTA barrier) precedes each store;
+//   * a buffer is handed back to the loader as soon as its store has finished reading it, so the
+//     loads of the next rows run under sweep B of the current row and under sweep A of the next.
+//
+// Groups meet once per row, to combine their statistics.  With a cluster the per-CTA partials
+// {max, sum, sum x, x[target]} are exchanged through distributed shared memory (st.shared::cluster into
+// every peer, then one cluster barrier per row).
+//
+// Arithmetic uses the packed fp32 pair instructions of sm_100 (fma/add .f32x2), packed bf16 maxima and
+// ex2.approx; the row statistics are in base 2 (max2 = max * log2 e).
+//
+// No TMA multicast is used anywhere: every CTA fetches its own chunks.  Every mbarrier wait is
+// bounded; a wait that runs out sets SB_STATUS_KERNEL_TIMEOUT and the kernel still terminates.
 #include "ce_common.cuh"
 
 namespace sb {
 
+namespace {
+
+int g_ce_force_variant = -1;  // tuning: -1 automatic, 0 generic, 1/2/4 resident cluster size
+
+constexpr uint32_t kMaxSpin = 1u << 22;  // try_wait attempts (each suspends up to ~1 us) before giving up
+
+struct ResidentParams {
+  CEParams p;
+  uint32_t nch;          // chunks per row slice
+  uint32_t nbuf;         // ring buffers (>= nch + 1)
+  uint32_t chunk_units;  // 16-byte units per chunk
+  uint32_t slice_units;  // 16-byte units per CTA slice (last CTA of a cluster may own fewer)
+  uint32_t row_units;    // 16-byte units per row
+  uint32_t num_clusters;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMaxSpin; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- packed fp32 pairs (sm_100) -----------------------------------------------------------------------
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// 16 bytes of T as fp32 pairs.
+template <typename T> struct Unit;
+template <> struct Unit<float> {
+  static constexpr int kPairs = 2;
+  __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[2]) {
+    f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+    f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+  }
+  __device__ static __forceinline__ uint4 pack(const float2 (&f)[2]) {
+    return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
+  }
+  __device__ static __forceinline__ float vmax(const uint4& r) {
+    return fmaxf(fmaxf(__uint_as_float(r.x), __uint_as_float(r.y)), fmaxf(__uint_as_float(r.z), __uint_as_float(r.w)));
+  }
+};
+template <> struct Unit<__nv_bfloat16> {
+  static constexpr int kPairs = 4;
+  __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[4]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  }
+  __device__ static __forceinline__ uint4 pack(const float2 (&f)[4]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[i].x, f[i].y);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  // maximum of the 8 values with packed bf16 maxima, widened once at the end
+  __device__ static __forceinline__ float vmax(const uint4& r) {
+    const __nv_bfloat162 a = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&r.x), *reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    const __nv_bfloat162 b = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&r.z), *reinterpret_cast<const __nv_bfloat162*>(&r.w));
+    const __nv_bfloat162 c = __hmax2(a, b);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&c);
+    return fmaxf(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+};
+template <> struct Unit<__half> {
+  static constexpr int kPairs = 4;
+  __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[4]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+  }
+  __device__ static __forceinline__ uint4 pack(const float2 (&f)[4]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[i].x, f[i].y);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ static __forceinline__ float vmax(const uint4& r) {
+    const __half2 a = __hmax2(*reinterpret_cast<const __half2*>(&r.x), *reinterpret_cast<const __half2*>(&r.y));
+    const __half2 b = __hmax2(*reinterpret_cast<const __half2*>(&r.z), *reinterpret_cast<const __half2*>(&r.w));
+    const float2 c = __half22float2(__hmax2(a, b));
+    return fmaxf(c.x, c.y);
+  }
+};
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kGroups = 4;          // consumer warp groups per CTA
+constexpr int kGroupThreads = 128;  // threads per group
+constexpr int kVecPerThread = 4;    // 16-byte vectors a thread handles per chunk
+constexpr int kChunkUnits = kGroupThreads * kVecPerThread;  // 512 units = 8 KB per chunk
+constexpr int kConsumers = kGroups * kGroupThreads;
+constexpr int kResidentThreads = kConsumers + 32 * kGroups;  // plus one copy-engine warp per group
+constexpr int kMaxBuffers = 32;
+
+// Shared-memory carve-up after the chunk ring.
+struct alignas(16) Tail {
+  float4 slots[2][4];        // cluster exchange: [row parity][source CTA] = {max2, sum, sum x, x[target]}
+  float red[3][32];          // per-warp partials
+  unsigned long long full[kMaxBuffers];   // loader -> consumers: chunk has landed
+  unsigned long long ready[kMaxBuffers];  // consumers -> loader: chunk holds the gradient (or may be reused)
+};
+
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// (max2, sum) merge in base 2 with empty partials (-inf, 0) kept neutral.
+__device__ __forceinline__ void merge2(float& m, float& s, float om, float os) {
+  const float nm = fmaxf(m, om);
+  const float a = (m == -CUDART_INF_F) ? 0.f : s * ex2(m - nm);
+  const float b = (om == -CUDART_INF_F) ? 0.f : os * ex2(om - nm);
+  m = nm;
+  s = a + b;
+}
+
+// Per-thread online-softmax state in base 2: two packed accumulators to shorten the dependent chains.
+struct RowStats {
+  float m2;
+  float2 s[2];
+  float2 sx[2];
+};
+
+// Folds NV vectors (already loaded) into the statistics.
+template <typename T, int NV, bool kSumX>
+__device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV]) {
+  using U = Unit<T>;
+  constexpr int P = U::kPairs;
+  float vm = U::vmax(r[0]);
+#pragma unroll
+  for (int q = 1; q < NV; ++q) vm = fmaxf(vm, U::vmax(r[q]));
+  // Logits may be -inf (masked classes): keep (-inf) - (-inf) out of the arithmetic.
+  const float nm = fmaxf(st.m2, vm * kLog2e);
+  const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);  // m2 = -inf < nm: the sums are 0, ex2(-inf) = 0
+  const float2 resc2 = make_float2(resc, resc);
+  st.s[0] = mul2(st.s[0], resc2);
+  st.s[1] = mul2(st.s[1], resc2);
+  st.m2 = nm;
+  const float mm = (nm == -CUDART_INF_F) ? 0.f : nm;
+  const float2 negm = make_float2(-mm, -mm);
+  const float2 l2e2 = make_float2(kLog2e, kLog2e);
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    float2 f[P];
+    U::unpack(r[q], f);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const float2 y = fma2(f[i], l2e2, negm);
+      st.s[i & 1] = add2(st.s[i & 1], make_float2(ex2(y.x), ex2(y.y)));
+      if (kSumX) st.sx[i & 1] = add2(st.sx[i & 1], f[i]);
+    }
+  }
+}
+
+// Gradient of one vector: (2^(x log2e - lse2)) * scale - sub.
+template <typename T>
+__device__ __forceinline__ uint4 grad_vector(const uint4& r, float2 neg_lse2, float2 scale2, float2 nsub2) {
+  using U = Unit<T>;
+  constexpr int P = U::kPairs;
+  const float2 l2e2 = make_float2(kLog2e, kLog2e);
+  float2 f[P];
+  U::unpack(r, f);
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    const float2 y = fma2(f[i], l2e2, neg_lse2);
+    f[i] = fma2(make_float2(ex2(y.x), ex2(y.y)), scale2, nsub2);
+  }
+  return U::pack(f);
+}
+
+template <typename T, int CLUSTER, bool kSumX>
+__global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(ResidentParams rp) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  using U = Unit<T>;
+  constexpr int E = 2 * U::kPairs;  // elements per 16-byte vector
+  constexpr int G = kGroups, TG = kGroupThreads, NV = kVecPerThread;
+  constexpr uint32_t kChunkBytes = kChunkUnits * 16;
+  const CEParams& p = rp.p;
+
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t cpg = rp.nch / G;   // chunks per group and row
+  const uint32_t nbg = rp.nbuf / G;  // ring buffers per group
+  Tail* tail = reinterpret_cast<Tail*>(smem + static_cast<size_t>(rp.nbuf) * kChunkBytes);
+
+  const uint32_t cta_rank = CLUSTER > 1 ? cluster_ctarank() : 0;
+  const uint32_t cluster_id = blockIdx.x / CLUSTER;
+  const int64_t nrows_local = cluster_id < p.rows ? (p.rows - cluster_id + rp.num_clusters - 1) / rp.num_clusters : 0;
+
+  // this CTA's slice of a row, in 16-byte units
+  const uint32_t slice_begin = cta_rank * rp.slice_units;
+  const uint32_t slice_end = min(slice_begin + rp.slice_units, rp.row_units);
+  const uint32_t slice_len = slice_end > slice_begin ? slice_end - slice_begin : 0;
+  const size_t row_bytes = static_cast<size_t>(rp.row_units) * 16;
+
+  if (tid == 0) {
+    for (uint32_t b = 0; b < rp.nbuf; ++b) {
+      mbar_init(smem_u32(&tail->full[b]), 1);
+      mbar_init(smem_u32(&tail->ready[b]), TG / 32);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (CLUSTER > 1) {  // peers must not write our slots before we are resident
+    cluster_arrive();
+    cluster_wait();
+  }
+
+  bool timed_out = false;
+
+  // Buffer numbering: group g owns buffers g * nbg .. g * nbg + nbg - 1; its chunks are numbered
+  // i = k * cpg + cl (local row k, cl-th chunk of the group in that row), chunk-in-row c = cl * G + g,
+  // buffer j = i % nbg, mbarrier phase parity (i / nbg) & 1.
+
+  if (warp >= kConsumers / 32) {
+    // =================== copy-engine warps: one per group; loads, stores, buffer recycling ===================
+    // Lane 0 does the work; the whole warp walks the row loop so that it can join the per-row cluster
+    // barrier (which counts every thread of every CTA) in step with the consumers.
+    const uint32_t g = warp - kConsumers / 32;
+    const int64_t per_group = nrows_local * cpg;
+    const uint32_t ring_base = smem_u32(smem) + g * nbg * kChunkBytes;
+    const uint32_t full_base = smem_u32(&tail->full[g * nbg]);
+    const uint32_t ready_base = smem_u32(&tail->ready[g * nbg]);
+    int64_t next_load = 0, ld_k = 0;
+    uint32_t ld_j = 0, ld_cl = 0;
+    bool ld_skip = false;  // the row being loaded is ignored: its logits are never read
+    int64_t ld_target = (lane == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
+    auto load_next = [&]() {  // loads the group's next chunk into the buffer its ring position names
+      if (next_load >= per_group) return;
+      const int64_t row = cluster_id + ld_k * static_cast<int64_t>(rp.num_clusters);
+      if (ld_cl == 0) {
+        const int64_t tr = ld_target;  // fetched one row ahead so that the load never waits on it
+        ld_skip = tr == p.ignore_index || tr < 0 || tr >= p.classes;  // the consumers' notion of "ignored"
+        if (ld_k + 1 < nrows_local) ld_target = p.target[row + rp.num_clusters];
+      }
+      const uint32_t u0 = (ld_cl * G + g) * kChunkUnits;
+      const uint32_t len = (!ld_skip && u0 < slice_len) ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+      const uint32_t bar = full_base + 8 * ld_j;
+      if (len) {
+        const unsigned char* src =
+            static_cast<const unsigned char*>(p.logits) + row * row_bytes + static_cast<size_t>(slice_begin + u0) * 16;
+        mbar_expect_tx(bar, len * 16);
+        bulk_g2s(ring_base + ld_j * kChunkBytes, src, len * 16, bar);
+      } else {
+        mbar_arrive(bar);
+      }
+      ++next_load;
+      if (++ld_j == nbg) ld_j = 0;
+      if (++ld_cl == cpg) {
+        ld_cl = 0;
+        ++ld_k;
+      }
+    };
+    if (lane == 0)
+      for (uint32_t j = 0; j < nbg; ++j) load_next();  // prologue: fill the ring
+    uint32_t j = 0, ph = 0;  // ring position / phase parity of the chunk being retired
+    bool pending = false;    // a committed store whose buffer has not been recycled yet
+    for (int64_t k = 0; k < nrows_local; ++k) {
+      if (CLUSTER > 1) {  // the consumers' statistics exchange of row k
+        cluster_arrive();
+        cluster_wait();
+      }
+      if (lane == 0) {
+        const int64_t row = cluster_id + k * static_cast<int64_t>(rp.num_clusters);
+        for (uint32_t cl = 0; cl < cpg; ++cl) {
+          if (!mbar_wait(ready_base + 8 * j, ph)) timed_out = true;
+          if (p.grad) {
+            const uint32_t u0 = (cl * G + g) * kChunkUnits;
+            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+            if (len) {
+              unsigned char* dst =
+                  static_cast<unsigned char*>(p.grad) + row * row_bytes + static_cast<size_t>(slice_begin + u0) * 16;
+              bulk_s2g(dst, ring_base + j * kChunkBytes, len * 16);
+            }
+            bulk_commit();
+            bulk_wait_read<1>();  // every store of this thread but the newest has finished reading shared memory
+            if (pending) load_next();
+            pending = true;
+          } else {
+            load_next();  // forward only: the buffer is free as soon as the group has read it
+          }
+          if (++j == nbg) {
+            j = 0;
+            ph ^= 1;
+          }
+        }
+      }
+      __syncwarp();
+    }
+    if (lane == 0) bulk_wait_all();
+    __syncwarp();
+    if (CLUSTER > 1) {  // the final cluster barrier
+      cluster_arrive();
+      cluster_wait();
+    }
+    if (timed_out && lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+    return;
+  }
+
+  // =================== consumer warps ===================
+  const uint32_t grp = tid / TG, gt = tid - grp * TG;
+  unsigned char* ring = smem + static_cast<size_t>(grp) * nbg * kChunkBytes;  // this group's ring
+  const uint32_t full0 = smem_u32(&tail->full[grp * nbg]);
+  const uint32_t ready0 = smem_u32(&tail->ready[grp * nbg]);
+
+  uint32_t cj = 0, cphase = 0;  // ring position and phase parity of the group's first chunk of the current row
+  const float eps = p.label_smoothing;
+  const float eps_c = eps / static_cast<float>(p.classes);
+  const int64_t elems_per_chunk = static_cast<int64_t>(kChunkUnits) * E;
+  const int64_t slice_elem0 = static_cast<int64_t>(slice_begin) * E;
+  float base_scale = p.grad_scale;  // gradient scale that does not depend on the row
+  if (p.grad && p.reduction == SB_REDUCTION_MEAN) base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
+
+  int64_t t_next = nrows_local > 0 ? p.target[cluster_id] : 0;
+  for (int64_t k = 0; k < nrows_local; ++k) {
+    const int64_t row = cluster_id + k * static_cast<int64_t>(rp.num_clusters);
+    const int64_t t = t_next;
+    if (k + 1 < nrows_local) t_next = p.target[row + rp.num_clusters];  // in flight during this row's sweeps
+    bool ignored = (t == p.ignore_index);
+    if (!ignored && (t < 0 || t >= p.classes)) {
+      if (tid == 0 && cta_rank == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+      ignored = true;
+    }
+
+    // ---- sweep A: statistics as the group's chunks land ----
+    RowStats st;
+    st.m2 = -CUDART_INF_F;
+    st.s[0] = st.s[1] = st.sx[0] = st.sx[1] = make_float2(0.f, 0.f);
+    {
+      uint32_t j = cj, ph = cphase;
+      for (uint32_t cl = 0; cl < cpg; ++cl) {
+        if (!mbar_wait(full0 + 8 * j, ph)) timed_out = true;
+        if (!ignored) {
+          const uint32_t u0 = (cl * G + grp) * kChunkUnits;
+          const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+          const uint4* buf = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
+          if (len == kChunkUnits) {
+            uint4 r[NV];
+#pragma unroll
+            for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+            stats_update<T, NV, kSumX>(st, r);
+          } else {
+            for (uint32_t v = gt; v < len; v += TG) {  // ragged last chunk of the slice
+              uint4 r[1] = {buf[v - gt]};
+              stats_update<T, 1, kSumX>(st, r);
+            }
+          }
+        }
+        if (++j == nbg) {
+          j = 0;
+          ph ^= 1;
+        }
+      }
+    }
+    float lse = 0.f, scale = 0.f, xt_all = 0.f;
+    if (!ignored) {
+      // ---- CTA reduce (consumer warps only) ----
+      float m2 = st.m2;
+      float s = (st.s[0].x + st.s[0].y) + (st.s[1].x + st.s[1].y);
+      float sx = (st.sx[0].x + st.sx[0].y) + (st.sx[1].x + st.sx[1].y);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        merge2(m2, s, __shfl_xor_sync(0xffffffffu, m2, o), __shfl_xor_sync(0xffffffffu, s, o));
+        sx += __shfl_xor_sync(0xffffffffu, sx, o);
+      }
+      if (lane == 0) {
+        tail->red[0][warp] = m2;
+        tail->red[1][warp] = s;
+        tail->red[2][warp] = sx;
+      }
+      named_barrier(1, kConsumers);
+      if (warp == 0) {
+        float wm = lane < kConsumers / 32 ? tail->red[0][lane] : -CUDART_INF_F;
+        float wsum = lane < kConsumers / 32 ? tail->red[1][lane] : 0.f;
+        float wx = lane < kConsumers / 32 ? tail->red[2][lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          merge2(wm, wsum, __shfl_xor_sync(0xffffffffu, wm, o), __shfl_xor_sync(0xffffffffu, wsum, o));
+          wx += __shfl_xor_sync(0xffffffffu, wx, o);
+        }
+        if (lane == 0) {
+          // x[target] if it lies in this CTA's slice: chunk c of the row belongs to group c % G
+          float xt = 0.f;
+          const int64_t tl = t - slice_elem0;
+          if (tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
+            const uint32_t c = static_cast<uint32_t>(tl / elems_per_chunk);
+            const uint32_t off = static_cast<uint32_t>(tl - c * elems_per_chunk);
+            const uint32_t og = c % G, ocl = c / G;
+            uint32_t oj = cj + ocl, oph = cphase;  // every group is at the same ring position
+            if (oj >= nbg) {
+              oj -= nbg;
+              oph ^= 1;
+            }
+            // already complete (the owning group passed it before the barrier above): makes the data visible here
+            if (!mbar_wait(smem_u32(&tail->full[og * nbg + oj]), oph)) timed_out = true;
+            xt = to_float(reinterpret_cast<const T*>(smem + (static_cast<size_t>(og) * nbg + oj) * kChunkBytes)[off]);
+          }
+          if (CLUSTER > 1) {
+            const uint32_t slot = smem_u32(&tail->slots[k & 1][cta_rank]);
+#pragma unroll
+            for (int jj = 0; jj < CLUSTER; ++jj) st_cluster_f4(mapa(slot, jj), wm, wsum, wx, xt);
+          } else {
+            tail->slots[0][0] = make_float4(wm, wsum, wx, xt);
+          }
+        }
+      }
+    }
+    if (CLUSTER > 1) {
+      cluster_arrive();
+      cluster_wait();
+    } else {
+      named_barrier(1, kConsumers);
+    }
+    if (!p.grad) {
+      // forward only: every read of this row's chunks (x[target] included) lies before the barrier above;
+      // hand the buffers back, one arrival per warp and chunk
+      if (lane == 0) {
+        uint32_t j = cj;
+        for (uint32_t cl = 0; cl < cpg; ++cl) {
+          mbar_arrive(ready0 + 8 * j);
+          if (++j == nbg) j = 0;
+        }
+      }
+    }
+    if (!ignored) {
+      float gm = -CUDART_INF_F, gs = 0.f, gx = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < CLUSTER; ++jj) {
+        const float4 v = tail->slots[CLUSTER > 1 ? (k & 1) : 0][jj];
+        merge2(gm, gs, v.x, v.y);
+        gx += v.z;
+        xt_all += v.w;
+      }
+      lse = (gm + log2f(gs)) * kLn2;
+      if (tid == 0 && cta_rank == 0) {
+        p.row_loss[row] = ce_row_loss(lse, xt_all, gx, eps, eps_c);
+        if (p.row_lse) p.row_lse[row] = lse;
+      }
+      scale = base_scale;
+      if (p.grad && p.row_grad_out) scale *= p.row_grad_out[row];
+    } else if (tid == 0 && cta_rank == 0) {
+      p.row_loss[row] = 0.f;
+      if (p.row_lse) p.row_lse[row] = 0.f;
+    }
+
+    // ---- sweep B: gradient in place, chunk by chunk; the copy-engine warp streams it out ----
+    if (p.grad) {
+      const float sub_all = eps_c * scale;
+      const float sub_t = (1.f - eps) * scale;
+      const float2 neg_lse2 = make_float2(-lse * kLog2e, -lse * kLog2e);
+      const float2 scale2 = make_float2(scale, scale);
+      const float2 nsub2 = make_float2(-sub_all, -sub_all);
+      // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
+      // x[target] with the same arithmetic and a single rounding.
+      const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
+      uint32_t j = cj;
+      for (uint32_t cl = 0; cl < cpg; ++cl) {
+        const uint32_t u0 = (cl * G + grp) * kChunkUnits;
+        const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+        uint4* buf = reinterpret_cast<uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
+        if (!ignored) {
+          if (len == kChunkUnits) {
+            uint4 r[NV];
+#pragma unroll
+            for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+#pragma unroll
+            for (int q = 0; q < NV; ++q) buf[q * TG] = grad_vector<T>(r[q], neg_lse2, scale2, nsub2);
+          } else {
+            for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2);
+          }
+          // position of the target inside this chunk, in elements
+          const int64_t tl = t - (slice_elem0 + static_cast<int64_t>(u0) * E);
+          if (tl >= 0 && tl < static_cast<int64_t>(len) * E && (static_cast<uint32_t>(tl) / E) % TG == gt)
+            reinterpret_cast<T*>(ring + static_cast<size_t>(j) * kChunkBytes)[tl] = from_float<T>(g_target);
+        } else {
+          for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async();  // this thread's writes become visible to the bulk-copy engine
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready0 + 8 * j);
+        if (++j == nbg) j = 0;
+      }
+    }
+
+    // advance the ring position to the next row
+    cj += cpg;
+    while (cj >= nbg) {
+      cj -= nbg;
+      cphase ^= 1;
+    }
+  }
+
+  if (timed_out && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+  if (CLUSTER > 1) {  // do not retire while a peer may still address our shared memory
+    cluster_arrive();
+    cluster_wait();
+  }
+}
+
+size_t resident_smem_bytes(uint32_t nbuf) { return static_cast<size_t>(nbuf) * kChunkUnits * 16 + sizeof(Tail); }
+
+// Geometry for a row of `row_units` 16-byte units split over `cluster` CTAs.  Returns false when the
+// slice does not fit next to at least one spare buffer per group.
+bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, ResidentParams* rp) {
+  const uint32_t slice_units = (row_units + cluster - 1) / cluster;
+  uint32_t cpg = (slice_units + kGroups * kChunkUnits - 1) / (kGroups * kChunkUnits);
+  if (cpg == 0) cpg = 1;
+  if (smem_limit <= sizeof(Tail)) return false;
+  uint32_t nbg = static_cast<uint32_t>((smem_limit - sizeof(Tail)) / (static_cast<size_t>(kChunkUnits) * 16)) / kGroups;
+  if (nbg * kGroups > kMaxBuffers) nbg = kMaxBuffers / kGroups;
+  if (nbg < cpg + 1) return false;
+  rp->nch = cpg * kGroups;
+  rp->nbuf = nbg * kGroups;
+  rp->chunk_units = kChunkUnits;
+  rp->slice_units = slice_units;
+  rp->row_units = row_units;
+  return true;
+}
+
+template <typename T, int CLUSTER, bool SUMX>
+int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
+  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX>;
+  const size_t smem = resident_smem_bytes(rp.nbuf);
+  static thread_local int configured_device = -1;  // per (instantiation, thread): attribute set for this device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_device != dev) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin()) != cudaSuccess)
+      return SB_ERR_CUDA;
+    configured_device = dev;
+  }
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = CLUSTER;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  int clusters = sm_count() / CLUSTER;
+  if (CLUSTER > 1) {
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(sm_count() / CLUSTER * CLUSTER);
+    probe.blockDim = dim3(kResidentThreads);
+    probe.dynamicSmemBytes = smem;
+    probe.attrs = &attr;
+    probe.numAttrs = 1;
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &probe) == cudaSuccess && max_clusters > 0 &&
+        max_clusters < clusters)
+      clusters = max_clusters;
+  }
+  if (clusters < 1) clusters = 1;
+  if (static_cast<int64_t>(clusters) > rp.p.rows) clusters = static_cast<int>(rp.p.rows);
+  rp.num_clusters = clusters;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * CLUSTER);
+  cfg.blockDim = dim3(kResidentThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, rp) != cudaSuccess) {
+    cudaGetLastError();
+    return SB_ERR_CUDA;
+  }
+  return SB_OK;
+}
+
+template <typename T, int CLUSTER>
+int launch_resident(const ResidentParams& rp, cudaStream_t st) {
+  const bool sumx = rp.p.label_smoothing != 0.f;
+  return sumx ? launch_resident_cfg<T, CLUSTER, true>(rp, st) : launch_resident_cfg<T, CLUSTER, false>(rp, st);
+}
+
+template <typename T>
+int launch_resident_t(const ResidentParams& rp, cudaStream_t st, int variant) {
+  switch (variant) {
+    case 1: return launch_resident<T, 1>(rp, st);
+    case 2: return launch_resident<T, 2>(rp, st);
+    case 4: return launch_resident<T, 4>(rp, st);
+    default: return SB_ERR_INVALID_ARGUMENT;
+  }
+}
+
+}  // namespace
+
 int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logits, const void* grad) {
-  (void)dtype; (void)rows; (void)classes; (void)logits; (void)grad;
+  const int64_t row_bytes = classes * dtype_size(dtype);
+  if (rows <= 0 || classes <= 0) return 0;
+  if (row_bytes % 16) return 0;  // bulk copies need 16-byte aligned row starts
+  if (reinterpret_cast<uintptr_t>(logits) % 16 || reinterpret_cast<uintptr_t>(grad) % 16) return 0;
+  if (row_bytes < 16 * 1024) return 0;  // short rows: the per-row barriers would dominate
+  if (row_bytes / 16 > 0x7fffffffLL) return 0;
+  const size_t limit = static_cast<size_t>(max_smem_optin());
+  ResidentParams rp;
+  const int candidates[3] = {1, 2, 4};
+  for (int c : candidates) {
+    if (c > 1 && rows < sm_count() / c) continue;  // too few rows to keep every SM busy with clusters
+    if (resident_geometry(static_cast<uint32_t>(row_bytes / 16), c, limit, &rp)) return c;
+  }
   return 0;
 }
 
-int ce_launch_resident(const CEParams&, cudaStream_t, int) { return SB_ERR_UNSUPPORTED; }
+int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant) {
+  ResidentParams rp;
+  rp.p = p;
+  const int64_t row_bytes = p.classes * dtype_size(p.dtype);
+  if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
+    return SB_ERR_INVALID_ARGUMENT;
+  switch (p.dtype) {
+    case SB_F32: return launch_resident_t<float>(rp, st, variant);
+    case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant);
+    case SB_F16: return launch_resident_t<__half>(rp, st, variant);
+    default: return SB_ERR_UNSUPPORTED;
+  }
+}
 
 int ce_dispatch(const CEParams& p, cudaStream_t st) {
-  const int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
-  if (variant == 0) return ce_launch_generic(p, st);
-  return ce_launch_resident(p, st, variant);
+  int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
+  if (g_ce_force_variant == 0) variant = 0;
+  if (variant != 0) {
+    const int rc = ce_launch_resident(p, st, variant);
+    if (rc == SB_OK) return rc;
+  }
+  return ce_launch_generic(p, st);
 }
 
 }  // namespace sb
+
+// Tuning hook for benchmarks: key 1 = force the kernel family (-1 automatic, 0 generic).
+extern "C" int sb_set_tuning(int32_t key, int32_t value) {
+  if (key == 1 && (value == -1 || value == 0)) {
+    sb::g_ce_force_variant = value;
+    return SB_OK;
+  }
+  return SB_ERR_INVALID_ARGUMENT;
+}
 
 extern "C" int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes) {
   return sb::ce_choose_variant(dtype, rows, classes, nullptr, nullptr);
