@@ -229,6 +229,9 @@ at::Tensor& zero_(at::Tensor& self) {
   return fill_scalar(self, 0);
 }
 
+// Tensor.record_stream: the allocator must not reuse the memory before work queued on `s` has finished.
+void record_stream_op(at::Tensor& self, c10::Stream s) { record_stream(self.storage().data_ptr(), s); }
+
 at::Scalar local_scalar_dense(const at::Tensor& self) {
   TORCH_CHECK(self.numel() == 1, "a Tensor with ", self.numel(), " elements cannot be converted to Scalar");
   at::Tensor host = at::empty({}, self.options().device(at::kCPU));
@@ -278,4 +281,5 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("fill_.Tensor", TORCH_FN(supa::fill_tensor));
   m.impl("zero_", TORCH_FN(supa::zero_));
   m.impl("_local_scalar_dense", TORCH_FN(supa::local_scalar_dense));
+  m.impl("record_stream", TORCH_FN(supa::record_stream_op));
 }

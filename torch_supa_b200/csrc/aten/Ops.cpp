@@ -62,18 +62,26 @@ void check_inplace(const at::Tensor& self, c10::IntArrayRef sizes, const at::Ten
               " should match");
 }
 
+// TensorIterator-based structured operators record the output in the iterator; plain MetaBase ones
+// (reductions) have nothing further to do.
+template <class Base>
+void forward_to_iterator(Base* self, int64_t idx, c10::IntArrayRef sizes, c10::IntArrayRef strides, at::TensorOptions options,
+                         at::DimnameList names) {
+  if constexpr (std::is_base_of<at::TensorIteratorBase, Base>::value) self->Base::set_output_raw_strided(idx, sizes, strides, options, names);
+}
+
 // ---- the three flavours of a structured operator --------------------------------------------------------------
 template <class Base, int N = 1>
 struct FunctionalOp final : public Base {
   void set_output_strided(int64_t idx, c10::IntArrayRef sizes, c10::IntArrayRef strides, at::TensorOptions options,
                           at::DimnameList names) override {
     outputs_[idx] = create_out(sizes, strides, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   void set_output_raw_strided(int64_t idx, c10::IntArrayRef sizes, c10::IntArrayRef strides, at::TensorOptions options,
                               at::DimnameList names) override {
     outputs_[idx] = create_out(sizes, strides, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   const at::Tensor& maybe_get_output(int64_t idx) override { return outputs_[idx]; }
   std::array<at::Tensor, N> outputs_;
@@ -90,12 +98,12 @@ struct OutOp final : public Base {
     // An out= tensor with other strides than the operator wants: compute into a proxy, copy back afterwards
     // (torch_supa/csrc/aten/common/native.h:80-89).
     if (out.strides() != strides) proxies_[idx] = at::empty_strided(sizes, strides, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   void set_output_raw_strided(int64_t idx, c10::IntArrayRef sizes, c10::IntArrayRef strides, at::TensorOptions options,
                               at::DimnameList names) override {
     resize_out(outputs_[idx].get(), sizes, strides, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   const at::Tensor& maybe_get_output(int64_t idx) override { return proxies_[idx].has_value() ? *proxies_[idx] : outputs_[idx].get(); }
   void finish() {
@@ -113,12 +121,12 @@ struct InplaceOp final : public Base {
                           at::DimnameList names) override {
     check_inplace(self_, sizes, options);
     if (self_.strides() != strides) proxy_ = at::empty_strided(sizes, strides, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   void set_output_raw_strided(int64_t idx, c10::IntArrayRef sizes, c10::IntArrayRef strides, at::TensorOptions options,
                               at::DimnameList names) override {
     check_inplace(self_, sizes, options);
-    Base::set_output_raw_strided(idx, sizes, strides, options, names);
+    forward_to_iterator<Base>(this, idx, sizes, strides, options, names);
   }
   const at::Tensor& maybe_get_output(int64_t) override { return proxy_.has_value() ? *proxy_ : self_; }
   void finish() {
