@@ -134,6 +134,30 @@ SB_API int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* ac
 SB_API int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype,
                               float* applied, sb_stream_t stream);
 
+/* Cross entropy (mean or sum) for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference.  The other cross-entropy launchers need two small
+ * scratch buffers from the caller (the per-row losses and the {loss sum, valid rows} accumulator).  Some
+ * callers have nowhere to get them: a host runtime that binds this C ABI from another language and owns no
+ * device allocator, a serving process whose memory is fully committed at start-up, or a section in which
+ * cudaMalloc's implicit device-wide synchronisation is not acceptable.  For them the scratch lives in a
+ * file-scope array in device memory inside the library (SB_CE_STATIC_MAX_ROWS * 4 + 256 bytes, held by every
+ * GPU that loads the library until the process exits).  The call runs the whole sequence -- valid-row
+ * count, fused sweep, loss sum and finish -- and calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ *   args      as for sb_ce_forward_backward, with reduction = mean or sum; grad_logits may be NULL.  The
+ *             fields row_loss, row_lse, row_grad_out and acc must be NULL: the library supplies them.
+ *   loss_out  one element of args->dtype in device memory.
+ *
+ * Returns SB_ERR_TOO_LARGE when args->rows exceeds SB_CE_STATIC_MAX_ROWS.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before any stream capture begins.
+ * All calls share the one array and it keeps the previous call's contents; everything a call reads from it
+ * is rewritten by that call first.  Two calls that overlap on the GPU (different streams, no dependency)
+ * race on it: serialise them. */
+#define SB_CE_STATIC_MAX_ROWS 65536
+SB_API int sb_ce_loss_static_scratch(const sb_ce_args* args, void* loss_out, sb_stream_t stream);
+
 /* Which kernel family sb_ce_forward_backward will use for this shape: 0 = generic two-sweep rows,
  * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
  * of 2/4 CTAs.  For diagnostics and benchmarks. */

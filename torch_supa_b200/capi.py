@@ -143,6 +143,14 @@ def ce_rescale_grad(grad, dtype, numel, scale, scale_dtype, applied, stream=0):
                                                          C.c_int32(scale_dtype), _p(applied), C.c_void_p(stream)))
 
 
+CE_STATIC_MAX_ROWS = 65536
+
+
+def ce_loss_static_scratch(args: CEArgs, loss_out, stream=0):
+    """Whole mean/sum cross entropy with the scratch buffers inside the library (no device allocation)."""
+    check("sb_ce_loss_static_scratch", lib().sb_ce_loss_static_scratch(C.byref(args), _p(loss_out), C.c_void_p(stream)))
+
+
 def ce_kernel_variant(dtype, rows, classes) -> int:
     return lib().sb_ce_kernel_variant(C.c_int32(dtype), C.c_int64(rows), C.c_int64(classes))
 

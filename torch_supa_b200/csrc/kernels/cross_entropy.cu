@@ -437,4 +437,52 @@ int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* sca
   return launch_status();
 }
 
+// ---- cross entropy with library-owned scratch ------------------------------------------------------------
+// Layout of the static array: bytes [0, 16) = the accumulator {loss sum, valid rows} as two doubles, bytes
+// [256, 256 + 4 * rows) = the per-row losses.  Host code cannot use the symbol as a pointer; the device
+// address is looked up once per device with cudaGetSymbolAddress while that device is current.
+static __device__ __align__(256) unsigned char g_ce_static_scratch[SB_CE_STATIC_MAX_ROWS * sizeof(float) + 256];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+void* g_ce_static_ptr[kStaticMaxDevices];  // device address of g_ce_static_scratch per device, once resolved
+
+int ce_static_scratch(unsigned char** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return SB_ERR_CUDA;
+  void* p = __atomic_load_n(&g_ce_static_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    if (cudaGetSymbolAddress(&p, g_ce_static_scratch) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return SB_ERR_CUDA;
+    }
+    __atomic_store_n(&g_ce_static_ptr[dev], p, __ATOMIC_RELEASE);  // every thread resolves the same address
+  }
+  *out = static_cast<unsigned char*>(p);
+  return SB_OK;
+}
+}  // namespace
+
+int sb_ce_loss_static_scratch(const sb_ce_args* a, void* loss_out, sb_stream_t stream) {
+  if (!a || !loss_out) return SB_ERR_INVALID_ARGUMENT;
+  if (a->reduction != SB_REDUCTION_MEAN && a->reduction != SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  if (a->row_loss || a->row_lse || a->row_grad_out || a->acc) return SB_ERR_INVALID_ARGUMENT;
+  if (a->rows < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (a->rows > SB_CE_STATIC_MAX_ROWS) return SB_ERR_TOO_LARGE;
+  unsigned char* scratch = nullptr;
+  int rc = ce_static_scratch(&scratch);
+  if (rc != SB_OK) return rc;
+  double* acc = reinterpret_cast<double*>(scratch);
+  float* row_loss = reinterpret_cast<float*>(scratch + 256);
+  // The count kernel's memset zeroes the accumulator; the sweep writes row_loss[0 .. rows) before the sum reads it.
+  rc = sb_ce_count_valid(a->target, a->rows, a->classes, a->ignore_index, acc, a->status, stream);
+  if (rc != SB_OK) return rc;
+  sb_ce_args full = *a;
+  full.row_loss = row_loss;
+  full.acc = acc;
+  rc = sb_ce_forward_backward(&full, stream);
+  if (rc != SB_OK) return rc;
+  return sb_ce_loss_sum_finish(row_loss, a->rows, acc, a->reduction, loss_out, a->dtype, stream);
+}
+
 }  // extern "C"
