@@ -101,20 +101,12 @@ def algorithmic_bytes(rows, classes, elem_size):
     return 2 * rows * classes * elem_size + rows * 8
 
 
-def make_inputs(torch, rows, classes, dtype, ignore_frac, device, seed):
-    """Seeded synthetic logits N(0,1)*2 and uniform targets with a fraction set to ignore_index=-100."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    logits = torch.empty(rows, classes, dtype=dtype, device=device)
-    block = max(1, (1 << 28) // classes)
-    for r0 in range(0, rows, block):
-        r1 = min(rows, r0 + block)
-        logits[r0:r1] = (torch.randn(r1 - r0, classes, device=device, generator=g) * 2).to(dtype)
-    target = torch.randint(0, classes, (rows,), device=device, generator=g)
-    if ignore_frac > 0:
-        n_ign = int(rows * ignore_frac)
-        perm = torch.randperm(rows, device=device, generator=torch.Generator(device=device).manual_seed(seed + 1))
-        target[perm[:n_ign]] = -100
-    return logits, target
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused-sweep launch from the ncu captures summarised under
+# profiles/ (the bf16 figure is the 4096-row capture scaled by 8: traffic is proportional to rows).
+TRAFFIC = {
+    ("ce_fp32_4096x32000", 4096): 524.4e6 + 468.3e6,
+    ("ce_bf16_32768x128256", 32768): 8 * (1.051e9 + 0.997e9),
+}
 
 
 def run_reference(args):
@@ -157,19 +149,24 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
+    import torch.nn.functional as F
 
-    from torch_supa_b200 import capi, functional as F2
+    import torch_supa_b200  # registers the "supa" device; raises if the native libraries are missing
+    from torch_supa_b200 import benchmarks, capi
+    from torch_supa_b200.distributed import LossComm, sharded_cross_entropy
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
+    if not torch.supa.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    torch.supa.set_device(local_rank)
+    torch.cuda.set_device(local_rank)  # only for the synthetic-data generator
+    device = torch.device("supa", local_rank)
+    comm = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    capi.lib()  # fail loudly if the kernel library is missing
+        dist.init_process_group("gloo")  # host-side plumbing: barrier, max over ranks, unique-id store
+        comm = LossComm.from_env(device_index=local_rank)
     if args.force_generic:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 0))
 
@@ -178,79 +175,92 @@ def run_ours(args):
         rows = args.rows
     dtype = getattr(torch, dtype_name)
     esize = torch.empty((), dtype=dtype).element_size()
-    logits, target = make_inputs(torch, rows, classes, dtype, ignore_frac, device, seed=rank)
-    grad = torch.empty_like(logits)
-    ws = F2.CrossEntropyWorkspace(rows, device)
-    all_reduce = (lambda view: dist.all_reduce(view)) if world > 1 else None
-    launches_per_step = 3  # count_valid, fused sweep, loss sum+finish (the all-reduces are NCCL's)
-    if world > 1:
-        launches_per_step = 4  # loss sum and finish are separate launches around the all-reduce
+    # seeded synthetic inputs: logits N(0,1)*2, targets uniform with a fraction set to ignore_index
+    logits = benchmarks.device_randn((rows, classes), dtype, device, seed=rank, scale=2.0)
+    tg = torch.Generator().manual_seed(1000 + rank)
+    host_target = torch.randint(0, classes, (rows,), generator=tg)
+    if ignore_frac > 0:
+        host_target[torch.randperm(rows, generator=torch.Generator().manual_seed(2000 + rank))[: int(rows * ignore_frac)]] = -100
+    target = host_target.to(device)
+    logits.requires_grad_(True)
+    nbytes = logits.numel() * esize
+    warmup = max(args.warmup, 3)
 
-    def step():
-        return F2.cross_entropy_forward_backward(logits, target, ignore_index=-100, label_smoothing=eps, reduction="mean",
-                                                 grad=grad, workspace=ws, all_reduce=all_reduce)
+    def step(x, t):
+        """One pass of the hot path through the public API: loss (global mean) and the logit gradient."""
+        x.grad = None
+        if comm is not None:
+            loss = sharded_cross_entropy(x, t, comm, ignore_index=-100, label_smoothing=eps, reduction="mean")
+        else:
+            loss = F.cross_entropy(x, t, ignore_index=-100, label_smoothing=eps, reduction="mean")
+        loss.backward()
+        return loss
+
+    # my kernels per step: count_valid, fused sweep, loss sum(+finish), fill(applied), fill(root gradient),
+    # rescale + its commit; with N > 1 the loss sum and finish are two launches
+    launches_per_step = 7 if world == 1 else 8
 
     def barrier():
-        torch.cuda.synchronize()
+        torch.supa.synchronize()
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
+    for _ in range(warmup):
+        step(logits, target)
     barrier()
-    # keep the GPU busy long enough for the clock sampler to see it under load
-    t_end = time.time() + (0.0 if args.quick else 0.6)
+    t_end = time.time() + (0.0 if args.quick else 0.6)  # keep the GPU busy so the clock sampler sees it under load
     while time.time() < t_end:
-        step()
-        torch.cuda.synchronize()
+        step(logits, target)
+        torch.supa.synchronize()
 
     # ---- device-resident timing ---------------------------------------------------------------------
-    kernel_events = []
-    stream = torch.cuda.current_stream()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    fused_args = None
+    start, stop = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
     barrier()
-    start.record(stream)
+    start.record()
     for _ in range(args.steps):
-        loss, _ = step()
-    stop.record(stream)
+        loss = step(logits, target)
+    stop.record()
     barrier()
-    elapsed_ms = start.elapsed_time(stop)
-
-    # dominant kernel alone (same launches, events around the fused sweep only)
-    for _ in range(args.steps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        capi.ce_count_valid(target, rows, classes, -100, ws.acc, ws.status, stream.cuda_stream)
-        a = capi.CEArgs()
-        a.logits, a.dtype, a.reduction, a.target = logits.data_ptr(), capi.torch_dtype_code(dtype), capi.REDUCTION_MEAN, target.data_ptr()
-        a.grad_logits, a.row_loss, a.acc = grad.data_ptr(), ws.row_loss.data_ptr(), ws.acc.data_ptr()
-        a.rows, a.classes, a.ignore_index, a.label_smoothing, a.grad_scale = rows, classes, -100, eps, 1.0
-        a.status = ws.status.data_ptr()
-        e0.record(stream)
-        capi.ce_forward_backward(a, stream.cuda_stream)
-        e1.record(stream)
-        kernel_events.append((e0, e1))
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in kernel_events)
-
-    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
-    total_rows = rows * world
-    value = total_rows / (ms_per_step * 1e-3)
+    ms_per_step = max_over_ranks(start.elapsed_time(stop)) / args.steps
     loss_value = float(loss.float().item())
-    status_word = int(ws.status.item())
+
+    # ---- the dominant kernel alone, through the C ABI on the same buffers ------------------------------
+    grad = torch.empty_like(logits)
+    ws_row_loss = torch.empty(rows, dtype=torch.float32, device=device)
+    ws_acc = torch.zeros(2, dtype=torch.float64, device=device)
+    ws_status = torch.zeros(1, dtype=torch.int32, device=device)
+    stream = torch.supa.current_stream_handle(local_rank)
+    a = capi.CEArgs()
+    a.logits, a.dtype, a.reduction, a.target = logits.data_ptr(), capi.torch_dtype_code(dtype), capi.REDUCTION_MEAN, target.data_ptr()
+    a.grad_logits, a.row_loss, a.acc = grad.data_ptr(), ws_row_loss.data_ptr(), ws_acc.data_ptr()
+    a.rows, a.classes, a.ignore_index, a.label_smoothing, a.grad_scale = rows, classes, -100, eps, 1.0
+    a.status = ws_status.data_ptr()
+    capi.ce_count_valid(target, rows, classes, -100, ws_acc, ws_status, stream)
+    kernel_times = []
+    for _ in range(args.steps):
+        e0, e1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
+        e0.record()
+        capi.ce_forward_backward(a, stream)
+        e1.record()
+        e1.synchronize()
+        kernel_times.append(e0.elapsed_time(e1))
+    kernel_ms = statistics.mean(kernel_times)
+    status_word = int(ws_status.cpu().item())
+    clocks = sampler.stop() if rank == 0 else None
+    del grad
 
     # ---- end to end: host buffers -> loss on the host ---------------------------------------------
     e2e = None
-    nbytes = logits.numel() * esize
     if args.quick:
         args.no_cpu_baseline = True
     else:
@@ -261,37 +271,39 @@ def run_ours(args):
         except Exception:
             avail = 64 << 30
         budget = int(avail * 0.4 / max(world, 1))
-        pinned_rows = rows if nbytes <= budget else max(1, int(budget // (classes * esize)))
-        host_logits = torch.empty(pinned_rows, classes, dtype=dtype).pin_memory()
-        host_logits.copy_(logits[:pinned_rows])
-        host_target = target.cpu().pin_memory()
-        host_loss = torch.empty((), dtype=dtype).pin_memory()
-        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        logits.grad = None
+        if nbytes <= budget:
+            host_logits = torch.empty(rows, classes, dtype=dtype).pin_memory()
+            host_logits.copy_(logits.detach())
+            pinned_target = host_target.pin_memory()
+            e2e_steps = max(1, min(args.steps, args.e2e_steps))
+            del logits
+            torch.supa.empty_cache()
 
-        def e2e_step():
-            for r0 in range(0, rows, pinned_rows):
-                r1 = min(rows, r0 + pinned_rows)
-                logits[r0:r1].copy_(host_logits[: r1 - r0], non_blocking=True)
-            target.copy_(host_target, non_blocking=True)
-            l, _ = step()
-            host_loss.copy_(l, non_blocking=True)
+            def e2e_step():
+                x = host_logits.to(device, non_blocking=True).requires_grad_(True)   # H2D of this step's logits
+                t = pinned_target.to(device, non_blocking=True)                        # H2D of this step's targets
+                return float(step(x, t).item())                                         # D2H of the loss (synchronises)
 
-        e2e_step()
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record(stream)
-        for _ in range(e2e_steps):
             e2e_step()
-        s1.record(stream)
-        barrier()
-        t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / e2e_steps
-        e2e = {"value": total_rows / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
-               "pinned_rows": pinned_rows}
-        del host_logits
+            barrier()
+            t0 = time.perf_counter()
+            s0, s1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
+            s0.record()
+            for _ in range(e2e_steps):
+                e2e_loss = e2e_step()
+            s1.record()
+            barrier()
+            e2e_ms = max_over_ranks(s0.elapsed_time(s1)) / e2e_steps
+            wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+            e2e = {"value": rows * world / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "wall_ms_per_step": wall_ms,
+                   "steps": e2e_steps, "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
+                   "api": "tensor.to('supa', non_blocking) from pinned memory; F.cross_entropy; backward; loss.item()",
+                   "loss": e2e_loss}
+            del host_logits
+        else:
+            e2e = {"value": None, "unit": "rows/s", "skipped": "host memory too small for a pinned copy of the logits"}
+    torch.supa.empty_cache()
 
     # ---- CPU baseline (rank 0, N = 1 only) --------------------------------------------------------
     cpu_baseline = None
@@ -309,32 +321,31 @@ def run_ours(args):
     achieved = alg / (kernel_ms * 1e-3) / 1e9
     extras = None
     if rank == 0 and world == 1 and args.extras:
-        del logits, grad
-        torch.cuda.empty_cache()
-        from torch_supa_b200 import benchmarks
-
-        extras = benchmarks.run_extras(device, peak)
+        extras = benchmarks.run_extras(device, peak, quick=args.quick, profile=args.extras == 2)
 
     if rank == 0:
         line = {
-            "metric": "cross_entropy_fwd_bwd_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "metric": "cross_entropy_fwd_bwd_rows_per_s", "value": rows * world / (ms_per_step * 1e-3), "unit": "rows/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
             "config": {"workload": args.workload, "rows_per_gpu": rows, "classes": classes, "ignore_fraction": ignore_frac,
                        "label_smoothing": eps, "reduction": "mean", "parallelism": f"rows sharded x{world}",
-                       "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs rotate below L2 size"},
+                       "api": "F.cross_entropy on the supa device + backward" if world == 1 else "sharded_cross_entropy + backward",
+                       "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs smaller than 2x L2"},
             "loss": loss_value, "status_word": status_word,
             "kernel_variant": capi.ce_kernel_variant(capi.torch_dtype_code(dtype), rows, classes),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "frac_of_8TBs_nominal": achieved / 8000.0, "kernel_ms": kernel_ms,
-                         "algorithmic_bytes": alg, "traffic": None},
-            "hbm_gbs_whole_step": alg * world / (ms_per_step * 1e-3) / 1e9,
+                         "peak_kind": peak_kind, "frac_of_8TBs_nominal": achieved / 8000.0, "kernel": "ce_resident_kernel",
+                         "kernel_ms": kernel_ms, "algorithmic_bytes": alg, "traffic": TRAFFIC.get((args.workload, rows))},
+            "hbm_gbs_whole_step": alg / (ms_per_step * 1e-3) / 1e9,
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
         if extras is not None:
             line["extras"] = extras
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -352,7 +363,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiling mode: no clock warm loop, no e2e, no CPU baseline")
     ap.add_argument("--force-generic", action="store_true", help="tuning: always use the generic two-sweep kernel")
-    ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations")
+    ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations; 2: same, one launch each (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

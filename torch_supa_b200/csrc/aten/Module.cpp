@@ -73,6 +73,18 @@ SUPA_EXPORT int supa_check_status(int device) {
   });
 }
 
+// Raw copy between any two addresses the CUDA runtime knows (device, pinned or pageable host), queued on the
+// calling thread's current stream of `device`.
+SUPA_EXPORT int supa_memcpy_async(int device, void* dst, const void* src, int64_t nbytes) {
+  return guarded([&] {
+    const c10::DeviceIndex d = static_cast<c10::DeviceIndex>(device < 0 ? supa::current_device() : device);
+    const c10::DeviceIndex prev = supa::exchange_device(d);
+    const cudaError_t err = cudaMemcpyAsync(dst, src, static_cast<size_t>(nbytes), cudaMemcpyDefault, supa::current_cuda_stream(d));
+    if (prev != d) supa::set_device(prev);
+    SUPA_CUDA_CHECK(err);
+  });
+}
+
 // ---- NCCL communicator --------------------------------------------------------------------------------------
 SUPA_EXPORT int supa_nccl_unique_id(char* out128) {
   return guarded([&] { supa::NcclComm::unique_id(out128); });

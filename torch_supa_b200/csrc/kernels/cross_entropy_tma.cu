@@ -41,6 +41,7 @@ struct ResidentParams {
   uint32_t slice_units;  // 16-byte units per CTA slice (last CTA of a cluster may own fewer)
   uint32_t row_units;    // 16-byte units per row
   uint32_t num_clusters;
+  int mode;              // 0 cross entropy, 1 log_softmax
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -291,7 +292,20 @@ __device__ __forceinline__ uint4 grad_vector(const uint4& r, float2 neg_lse2, fl
   return U::pack(f);
 }
 
-template <typename T, int CLUSTER, bool kSumX>
+// MODE 0: cross entropy (gradient out).  MODE 1: log_softmax (x - lse out; no targets, no losses).
+// log_softmax of one vector: x - lse.
+template <typename T>
+__device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
+  using U = Unit<T>;
+  constexpr int P = U::kPairs;
+  float2 f[P];
+  U::unpack(r, f);
+#pragma unroll
+  for (int i = 0; i < P; ++i) f[i] = add2(f[i], neg_lse);
+  return U::pack(f);
+}
+
+template <typename T, int CLUSTER, bool kSumX, int MODE>
 __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(ResidentParams rp) {
   extern __shared__ __align__(128) unsigned char smem[];
   using U = Unit<T>;
@@ -346,14 +360,16 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     int64_t next_load = 0, ld_k = 0;
     uint32_t ld_j = 0, ld_cl = 0;
     bool ld_skip = false;  // the row being loaded is ignored: its logits are never read
-    int64_t ld_target = (lane == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
+    int64_t ld_target = (MODE == 0 && lane == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
     auto load_next = [&]() {  // loads the group's next chunk into the buffer its ring position names
       if (next_load >= per_group) return;
       const int64_t row = cluster_id + ld_k * static_cast<int64_t>(rp.num_clusters);
       if (ld_cl == 0) {
-        const int64_t tr = ld_target;  // fetched one row ahead so that the load never waits on it
-        ld_skip = tr == p.ignore_index || tr < 0 || tr >= p.classes;  // the consumers' notion of "ignored"
-        if (ld_k + 1 < nrows_local) ld_target = p.target[row + rp.num_clusters];
+        if (MODE == 0) {
+          const int64_t tr = ld_target;  // fetched one row ahead so that the load never waits on it
+          ld_skip = tr == p.ignore_index || tr < 0 || tr >= p.classes;  // the consumers' notion of "ignored"
+          if (ld_k + 1 < nrows_local) ld_target = p.target[row + rp.num_clusters];
+        }
       }
       const uint32_t u0 = (ld_cl * G + g) * kChunkUnits;
       const uint32_t len = (!ld_skip && u0 < slice_len) ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
@@ -433,13 +449,13 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
   float base_scale = p.grad_scale;  // gradient scale that does not depend on the row
   if (p.grad && p.reduction == SB_REDUCTION_MEAN) base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
 
-  int64_t t_next = nrows_local > 0 ? p.target[cluster_id] : 0;
+  int64_t t_next = (MODE == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
   for (int64_t k = 0; k < nrows_local; ++k) {
     const int64_t row = cluster_id + k * static_cast<int64_t>(rp.num_clusters);
     const int64_t t = t_next;
-    if (k + 1 < nrows_local) t_next = p.target[row + rp.num_clusters];  // in flight during this row's sweeps
-    bool ignored = (t == p.ignore_index);
-    if (!ignored && (t < 0 || t >= p.classes)) {
+    if (MODE == 0 && k + 1 < nrows_local) t_next = p.target[row + rp.num_clusters];  // in flight during this row's sweeps
+    bool ignored = MODE == 0 && (t == p.ignore_index);
+    if (MODE == 0 && !ignored && (t < 0 || t >= p.classes)) {
       if (tid == 0 && cta_rank == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
       ignored = true;
     }
@@ -504,7 +520,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
           // x[target] if it lies in this CTA's slice: chunk c of the row belongs to group c % G
           float xt = 0.f;
           const int64_t tl = t - slice_elem0;
-          if (tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
+          if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
             const uint32_t c = static_cast<uint32_t>(tl / elems_per_chunk);
             const uint32_t off = static_cast<uint32_t>(tl - c * elems_per_chunk);
             const uint32_t og = c % G, ocl = c / G;
@@ -554,13 +570,13 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         xt_all += v.w;
       }
       lse = (gm + log2f(gs)) * kLn2;
-      if (tid == 0 && cta_rank == 0) {
+      if (MODE == 0 && tid == 0 && cta_rank == 0) {
         p.row_loss[row] = ce_row_loss(lse, xt_all, gx, eps, eps_c);
         if (p.row_lse) p.row_lse[row] = lse;
       }
       scale = base_scale;
       if (p.grad && p.row_grad_out) scale *= p.row_grad_out[row];
-    } else if (tid == 0 && cta_rank == 0) {
+    } else if (MODE == 0 && tid == 0 && cta_rank == 0) {
       p.row_loss[row] = 0.f;
       if (p.row_lse) p.row_lse[row] = 0.f;
     }
@@ -572,6 +588,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       const float2 neg_lse2 = make_float2(-lse * kLog2e, -lse * kLog2e);
       const float2 scale2 = make_float2(scale, scale);
       const float2 nsub2 = make_float2(-sub_all, -sub_all);
+      const float2 neg_lse_nat2 = make_float2(-lse, -lse);
       // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
       // x[target] with the same arithmetic and a single rounding.
       const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
@@ -586,13 +603,15 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
 #pragma unroll
             for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
 #pragma unroll
-            for (int q = 0; q < NV; ++q) buf[q * TG] = grad_vector<T>(r[q], neg_lse2, scale2, nsub2);
+            for (int q = 0; q < NV; ++q)
+              buf[q * TG] = MODE == 0 ? grad_vector<T>(r[q], neg_lse2, scale2, nsub2) : shift_vector<T>(r[q], neg_lse_nat2);
           } else {
-            for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2);
+            for (uint32_t v = gt; v < len; v += TG)
+              buf[v - gt] = MODE == 0 ? grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2) : shift_vector<T>(buf[v - gt], neg_lse_nat2);
           }
           // position of the target inside this chunk, in elements
           const int64_t tl = t - (slice_elem0 + static_cast<int64_t>(u0) * E);
-          if (tl >= 0 && tl < static_cast<int64_t>(len) * E && (static_cast<uint32_t>(tl) / E) % TG == gt)
+          if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(len) * E && (static_cast<uint32_t>(tl) / E) % TG == gt)
             reinterpret_cast<T*>(ring + static_cast<size_t>(j) * kChunkBytes)[tl] = from_float<T>(g_target);
         } else {
           for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = make_uint4(0u, 0u, 0u, 0u);
@@ -639,9 +658,9 @@ bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, Resid
   return true;
 }
 
-template <typename T, int CLUSTER, bool SUMX>
+template <typename T, int CLUSTER, bool SUMX, int MODE>
 int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
-  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX>;
+  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX, MODE>;
   const size_t smem = resident_smem_bytes(rp.nbuf);
   static thread_local int configured_device = -1;  // per (instantiation, thread): attribute set for this device
   int dev = 0;
@@ -689,8 +708,9 @@ int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
 
 template <typename T, int CLUSTER>
 int launch_resident(const ResidentParams& rp, cudaStream_t st) {
+  if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
   const bool sumx = rp.p.label_smoothing != 0.f;
-  return sumx ? launch_resident_cfg<T, CLUSTER, true>(rp, st) : launch_resident_cfg<T, CLUSTER, false>(rp, st);
+  return sumx ? launch_resident_cfg<T, CLUSTER, true, 0>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0>(rp, st);
 }
 
 template <typename T>
@@ -725,10 +745,38 @@ int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logi
 int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant) {
   ResidentParams rp;
   rp.p = p;
+  rp.mode = 0;
   const int64_t row_bytes = p.classes * dtype_size(p.dtype);
   if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
     return SB_ERR_INVALID_ARGUMENT;
   switch (p.dtype) {
+    case SB_F32: return launch_resident_t<float>(rp, st, variant);
+    case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant);
+    case SB_F16: return launch_resident_t<__half>(rp, st, variant);
+    default: return SB_ERR_UNSUPPORTED;
+  }
+}
+
+// log_softmax over the last dimension with the row resident in shared memory (same pipeline as the cross
+// entropy, MODE 1).  Returns SB_ERR_UNSUPPORTED when the shape does not qualify; the caller then uses the
+// generic kernels.
+int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, cudaStream_t st) {
+  if (g_ce_force_variant == 0) return SB_ERR_UNSUPPORTED;
+  const int variant = ce_choose_variant(dtype, rows, dim, in, out);
+  if (variant == 0) return SB_ERR_UNSUPPORTED;
+  ResidentParams rp;
+  rp.p = CEParams{};
+  rp.p.logits = in;
+  rp.p.grad = out;
+  rp.p.rows = rows;
+  rp.p.classes = dim;
+  rp.p.dtype = dtype;
+  rp.p.grad_scale = 1.f;
+  rp.mode = 1;
+  const int64_t row_bytes = dim * dtype_size(dtype);
+  if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
+    return SB_ERR_UNSUPPORTED;
+  switch (dtype) {
     case SB_F32: return launch_resident_t<float>(rp, st, variant);
     case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant);
     case SB_F16: return launch_resident_t<__half>(rp, st, variant);

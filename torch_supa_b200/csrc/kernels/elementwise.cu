@@ -61,6 +61,7 @@ int ew_make_plan(const sb_ew_desc* d, EwPlan* plan) {
     if (same) plan->static_dtype = d->common_dtype;
   }
   plan->transposed_mask = 0;
+  plan->transpose_vec = false;
   plan->path = 3;
   if (numel == 0) return SB_OK;
 
@@ -113,6 +114,21 @@ int ew_make_plan(const sb_ew_desc* d, EwPlan* plan) {
     if (ok && mask && outer <= 65535 && (d->sizes[1] + 31) / 32 <= 65535 && (d->sizes[0] + 31) / 32 <= 0x7fffffffLL) {
       plan->path = 2;
       plan->transposed_mask = mask;
+      // 4-element accesses: sizes multiples of 4 and every access 4-element aligned
+      bool vec = d->sizes[0] % 4 == 0 && d->sizes[1] % 4 == 0 && d->noperands <= 3;  // the vector kernel holds two inputs
+      for (int k = 0; k < d->noperands && vec; ++k) {
+        const size_t es = dtype_size(d->dtype[k]);
+        const size_t a = es * 4 >= 16 ? 16 : es * 4;
+        vec = reinterpret_cast<uintptr_t>(d->data[k]) % a == 0;
+        const bool transposed = k >= 1 && (mask >> (k - 1) & 1);
+        for (int i = 0; i < d->ndim && vec; ++i) {
+          const bool unit_dim = transposed ? i == 1 : i == 0;
+          if (unit_dim) continue;
+          const int64_t st = d->strides[k][i] < 0 ? -d->strides[k][i] : d->strides[k][i];
+          vec = (static_cast<uint64_t>(st) * es) % a == 0;
+        }
+      }
+      plan->transpose_vec = vec;
       return SB_OK;
     }
   }
@@ -136,6 +152,8 @@ void ew_fill_params(const sb_ew_desc* d, EwParams* p) {
       p->strides[k][i] = (k < d->noperands && i < d->ndim) ? (d->sizes[i] == 1 && i == 0 ? 1 : d->strides[k][i]) : 0;
   }
   p->row_chunks = 1;
+  p->span = 0;
+  p->bcast = 0;
   p->rows = 1;
   p->bx = kEwThreads;
   p->unroll = 1;
@@ -172,36 +190,38 @@ int ew_rows_geometry(const sb_ew_desc* d, EwParams* p, unsigned* grid) {
   const uint64_t nv0 = (n0 + kEwVec - 1) / kEwVec;
   uint64_t rows = 1;
   for (int i = 1; i < d->ndim; ++i) rows *= static_cast<uint64_t>(d->sizes[i]);
-  int bx = 1;
-  while (bx < kEwThreads && static_cast<uint64_t>(bx) < nv0) bx <<= 1;
   const int arity = ew_arity(d->op);
-  const int max_unroll = arity <= 1 ? 4 : 2;
-  int best_u = 1;
-  double best_waste = 1e30;
-  for (int u = max_unroll; u >= 1; u >>= 1) {
-    const uint64_t per = static_cast<uint64_t>(bx) * u;
-    const uint64_t chunks = (nv0 + per - 1) / per;
-    const double waste = static_cast<double>(chunks * per) / static_cast<double>(nv0);
-    if (waste <= 1.07) {
-      best_u = u;
-      best_waste = waste;
-      break;
-    }
-    if (waste < best_waste) {
-      best_waste = waste;
-      best_u = u;
-    }
-  }
-  const uint64_t per = static_cast<uint64_t>(bx) * best_u;
-  const uint64_t chunks = (nv0 + per - 1) / per;
+  const int unroll = arity <= 1 ? 4 : 2;
+  // threads along the row: each thread should walk about four passes of `unroll` vectors, so that the row
+  // decomposition it does once is amortised; short rows get fewer threads and the block takes several rows
+  int bx = 1;
+  while (bx < kEwThreads && static_cast<uint64_t>(bx) * 2 * unroll * 4 <= nv0) bx <<= 1;
+  if (static_cast<uint64_t>(bx) * unroll < nv0 && bx < 8) bx = 8;
   const uint64_t by = kEwThreads / bx;
   const uint64_t row_blocks = (rows + by - 1) / by;
+  // long rows and few of them: cut each row into chunks so that every SM gets work
+  uint64_t chunks = 1;
+  const uint64_t want_blocks = 4ull * static_cast<uint64_t>(sm_count());
+  const uint64_t per_pass = static_cast<uint64_t>(bx) * unroll;
+  if (row_blocks < want_blocks && nv0 > 4 * per_pass) {
+    chunks = (want_blocks + row_blocks - 1) / row_blocks;
+    const uint64_t max_chunks = nv0 / (2 * per_pass);
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+  }
+  uint64_t span = (nv0 + chunks - 1) / chunks;
+  span = (span + per_pass - 1) / per_pass * per_pass;
+  chunks = (nv0 + span - 1) / span;
   const uint64_t blocks = row_blocks * chunks;
   if (blocks > 0x7fffffffULL || rows > 0xffffffffULL) return SB_ERR_TOO_LARGE;
+  bool bcast = false;
+  for (int k = 1; k < d->noperands; ++k) bcast = bcast || (p->strides[k][0] == 0);
   p->bx = bx;
-  p->unroll = best_u;
+  p->unroll = unroll;
   p->row_chunks = static_cast<uint32_t>(chunks);
+  p->span = static_cast<uint32_t>(span);
   p->rows = static_cast<uint32_t>(rows);
+  p->bcast = bcast ? 1 : 0;
   *grid = static_cast<unsigned>(blocks);
   return SB_OK;
 }

@@ -27,6 +27,8 @@ struct EwParams {
   uint32_t sizes[kEwRowDims];
   int64_t numel;          // path 0
   uint32_t row_chunks;    // path 1: blocks along one row
+  uint32_t span;          // path 1: vectors of the row one block walks
+  int bcast;              // path 1: some input has stride 0 along the row
   uint32_t rows;          // path 1: product of sizes[1..]
   int bx;                 // path 1: threads along the row (power of two), by = kEwThreads / bx
   int unroll;             // path 1: vectors per thread along the row
@@ -95,9 +97,25 @@ template <bool FAST, typename CT> __device__ __forceinline__ CT tanh_t(CT x) {
   if constexpr (std::is_same<CT, double>::value) return tanh(x);
   else return tanh_f<FAST>(x);
 }
-template <typename CT> __device__ __forceinline__ CT erf_t(CT x) {
+// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7): one reciprocal, one ex2 and five FMAs; used when the
+// result is rounded to bf16.  `e` receives exp(-x^2), which the gelu derivative needs as well.
+__device__ __forceinline__ float erf_fast(float x, float& e) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  e = exp2f(-ax * ax * 1.4426950408889634f);
+  const float r = fmaf(-poly * t, e, 1.f);
+  return copysignf(r, x);
+}
+template <bool FAST, typename CT> __device__ __forceinline__ CT erf_t(CT x) {
   if constexpr (std::is_same<CT, double>::value) return erf(x);
-  else return erff(x);
+  else if constexpr (FAST) {
+    float e;
+    return erf_fast(x, e);
+  } else return erff(x);
 }
 template <typename CT> __device__ __forceinline__ CT exp_t(CT x) {
   if constexpr (std::is_same<CT, double>::value) return exp(x);
@@ -149,7 +167,7 @@ SB_DEFINE_OP(SB_EW_NEG, 1, {
 })
 // gelu(x) = x * Phi(x), exact (erf) form.
 SB_DEFINE_OP(SB_EW_GELU_ERF, 1, {
-  if constexpr (std::is_floating_point<CT>::value) return a * CT(0.5) * (CT(1) + erf_t<CT>(a * CT(0.70710678118654752440)));
+  if constexpr (std::is_floating_point<CT>::value) return a * CT(0.5) * (CT(1) + erf_t<FAST, CT>(a * CT(0.70710678118654752440)));
   else return a;
 })
 // tanh approximation: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
@@ -175,9 +193,15 @@ SB_DEFINE_OP(SB_EW_GELU_ERF_BWD, 2, {
   if constexpr (std::is_floating_point<CT>::value) {
     const CT kAlpha = CT(0.70710678118654752440);
     const CT kBeta = CT(0.39894228040143267794);  // (2/sqrt(pi)) * sqrt(1/2) * 0.5
-    const CT cdf = CT(0.5) * (CT(1) + erf_t<CT>(b * kAlpha));
-    const CT pdf = exp_t<CT>(CT(-0.5) * b * b) * kBeta;
-    return a * (cdf + b * pdf);
+    if constexpr (FAST && std::is_same<CT, float>::value) {
+      float e;  // exp(-(x / sqrt 2)^2) = exp(-x^2 / 2), shared by the cdf and the pdf
+      const float cdf = 0.5f * (1.f + erf_fast(b * kAlpha, e));
+      return a * (cdf + b * e * kBeta);
+    } else {
+      const CT cdf = CT(0.5) * (CT(1) + erf_t<false, CT>(b * kAlpha));
+      const CT pdf = exp_t<CT>(CT(-0.5) * b * b) * kBeta;
+      return a * (cdf + b * pdf);
+    }
   } else return a;
 })
 SB_DEFINE_OP(SB_EW_GELU_TANH_BWD, 2, {
@@ -291,8 +315,11 @@ __global__ void __launch_bounds__(kEwThreads) ew_contig_kernel(EwParams p) {
 }
 
 // ---- path 1: rows -------------------------------------------------------------------------------------------
-// Block = bx threads along the row x by rows.  blockIdx.x = row_block * row_chunks + chunk.
-template <class Op, typename CT, class IO, int UNROLL>
+// Block = bx threads along the row x by rows; blockIdx.x = row_block * row_chunks + chunk.  A thread
+// decomposes its row index once and then walks its share of the row, UNROLL vectors in flight, so the
+// index arithmetic is amortised over the whole row.  BCAST: some input is constant along the row
+// (stride 0 on the fastest dimension) and is fetched as one scalar.
+template <class Op, typename CT, class IO, int UNROLL, bool BCAST>
 __global__ void __launch_bounds__(kEwThreads) ew_rows_kernel(EwParams p) {
   const OpScalars<CT> sc = make_scalars<CT>(p);
   const uint32_t bx = p.bx;
@@ -303,56 +330,73 @@ __global__ void __launch_bounds__(kEwThreads) ew_rows_kernel(EwParams p) {
   const uint32_t chunk = blockIdx.x - row_block * p.row_chunks;
   const uint32_t row = row_block * by + ty;
   if (row >= p.rows) return;
-  // decompose the row index over dims 1..3
   uint32_t r = row;
   const uint32_t i1 = r % p.sizes[1];
   r /= p.sizes[1];
   const uint32_t i2 = r % p.sizes[2];
   const uint32_t i3 = r / p.sizes[2];
   int64_t off[4];
-  bool bcast[4];
+  CT bval[3];
 #pragma unroll
-  for (int k = 0; k <= Op::arity; ++k) {
-    off[k] = i1 * p.strides[k][1] + i2 * p.strides[k][2] + i3 * p.strides[k][3];
-    bcast[k] = p.strides[k][0] == 0;
-  }
-  const uint32_t n0 = p.sizes[0];
-  const uint32_t v0 = chunk * (bx * UNROLL) + tx;  // first vector of this thread
-  CT in[3][UNROLL][kEwVec];
+  for (int k = 0; k <= Op::arity; ++k) off[k] = i1 * p.strides[k][1] + i2 * p.strides[k][2] + i3 * p.strides[k][3];
+  if (BCAST) {
 #pragma unroll
-  for (int u = 0; u < UNROLL; ++u) {
-    const uint32_t e0 = (v0 + u * bx) * kEwVec;
-    if (e0 + kEwVec <= n0) {
-#pragma unroll
-      for (int k = 0; k < Op::arity; ++k) {
-        if (bcast[k + 1]) {
-          CT one[1];
-          IO::template load<CT, 1>(p.data[k + 1], off[k + 1], p.dtype[k + 1], one);
-#pragma unroll
-          for (int e = 0; e < kEwVec; ++e) in[k][u][e] = one[0];
-        } else {
-          IO::template load<CT, kEwVec>(p.data[k + 1], off[k + 1] + e0, p.dtype[k + 1], in[k][u]);
-        }
+    for (int k = 0; k < Op::arity; ++k) {
+      bval[k] = CT();
+      if (p.strides[k + 1][0] == 0) {
+        CT one[1];
+        IO::template load<CT, 1>(p.data[k + 1], off[k + 1], p.dtype[k + 1], one);
+        bval[k] = one[0];
       }
     }
   }
+  const uint32_t n0 = p.sizes[0];
+  const uint32_t nfull = n0 / kEwVec;                 // complete vectors in a row
+  const uint32_t v_begin = chunk * p.span;            // this block's share of the row, in vectors
+  const uint32_t v_end = min(v_begin + p.span, nfull);
+  // One pass = UNROLL vectors per thread.  `load_pass` / `store_pass` are instantiated with and without
+  // bounds checks: full passes issue all their loads back to back, only the last pass of a row is guarded.
+  auto do_pass = [&](uint32_t v0, auto guarded) {
+    constexpr bool kGuard = decltype(guarded)::value;
+    CT in[3][UNROLL][kEwVec];
 #pragma unroll
-  for (int u = 0; u < UNROLL; ++u) {
-    const uint32_t e0 = (v0 + u * bx) * kEwVec;
-    if (e0 + kEwVec <= n0) {
-      CT out[kEwVec];
+    for (int u = 0; u < UNROLL; ++u) {
+      const uint32_t v = v0 + u * bx;
+      if (!kGuard || v < v_end) {
 #pragma unroll
-      for (int e = 0; e < kEwVec; ++e) out[e] = Op::apply(in[0][u][e], in[1][u][e], in[2][u][e], sc);
-      IO::template store<CT, kEwVec>(p.data[0], off[0] + e0, p.dtype[0], out);
-    } else if (e0 < n0) {  // ragged end of the row
-      for (uint32_t e = e0; e < n0; ++e) {
-        CT a[3][1] = {};
+        for (int k = 0; k < Op::arity; ++k) {
+          if (BCAST && p.strides[k + 1][0] == 0) {
 #pragma unroll
-        for (int k = 0; k < Op::arity; ++k)
-          IO::template load<CT, 1>(p.data[k + 1], off[k + 1] + (bcast[k + 1] ? 0 : e), p.dtype[k + 1], a[k]);
-        CT o[1] = {Op::apply(a[0][0], a[1][0], a[2][0], sc)};
-        IO::template store<CT, 1>(p.data[0], off[0] + e, p.dtype[0], o);
+            for (int e = 0; e < kEwVec; ++e) in[k][u][e] = bval[k];
+          } else {
+            IO::template load<CT, kEwVec>(p.data[k + 1], off[k + 1] + static_cast<int64_t>(v) * kEwVec, p.dtype[k + 1], in[k][u]);
+          }
+        }
       }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const uint32_t v = v0 + u * bx;
+      if (!kGuard || v < v_end) {
+        CT out[kEwVec];
+#pragma unroll
+        for (int e = 0; e < kEwVec; ++e) out[e] = Op::apply(in[0][u][e], in[1][u][e], in[2][u][e], sc);
+        IO::template store<CT, kEwVec>(p.data[0], off[0] + static_cast<int64_t>(v) * kEwVec, p.dtype[0], out);
+      }
+    }
+  };
+  uint32_t v0 = v_begin + tx;
+  for (; v0 + (UNROLL - 1) * bx < v_end; v0 += bx * UNROLL) do_pass(v0, std::false_type{});
+  if (v0 < v_end) do_pass(v0, std::true_type{});
+  // ragged end of the row: the last chunk's first threads take one element each
+  if (chunk == p.row_chunks - 1) {
+    for (uint32_t e = nfull * kEwVec + tx; e < n0; e += bx) {
+      CT a[3][1] = {};
+#pragma unroll
+      for (int k = 0; k < Op::arity; ++k)
+        IO::template load<CT, 1>(p.data[k + 1], off[k + 1] + (p.strides[k + 1][0] == 0 ? 0 : e), p.dtype[k + 1], a[k]);
+      CT o[1] = {Op::apply(a[0][0], a[1][0], a[2][0], sc)};
+      IO::template store<CT, 1>(p.data[0], off[0] + e, p.dtype[0], o);
     }
   }
 }
@@ -413,6 +457,91 @@ __global__ void __launch_bounds__(256) ew_transpose_kernel(EwGenericParams p, ui
   }
 }
 
+// Vector form of the tile kernel: 64 x 64 tile, 4 elements per access on both sides.  Needs sizes[0] and
+// sizes[1] to be multiples of 4 and every operand 4-element aligned along its unit-stride dimension.
+// All global loads of a tile (the transposed operands and the straight ones) are issued before anything
+// waits on them; interior tiles (kGuard = false) carry no bounds checks.
+template <typename CT, bool kGuard>
+__device__ __forceinline__ void ew_transpose_tile(const EwGenericParams& p, uint32_t transposed_mask, CT (*tile)[64][65],
+                                                  const int64_t* outer, uint32_t t0, uint32_t t1) {
+  constexpr int T = 64, V = 4, PASSES = T / 16, KMAX = 2;  // at most two inputs (the classifier guarantees it)
+  const OpScalars<CT> sc = make_scalars<CT>(p);
+  const uint32_t n0 = p.sizes[0], n1 = p.sizes[1];
+  const int nin = p.noperands - 1;
+  const uint32_t lane_v = threadIdx.x % (T / V);   // vector position along the unit-stride direction
+  const uint32_t lane_r = threadIdx.x / (T / V);   // 0..15: row inside a pass
+  // Operand k as loaded: vectors along dim1 for a transposed operand, along dim0 (like the output) otherwise.
+  // Every index below is a compile-time constant after unrolling, so the arrays stay in registers.
+  CT held[KMAX][PASSES][V];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    if (k >= nin) continue;
+    const bool tr = transposed_mask >> k & 1;
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+      const uint32_t ia = lane_r + 16 * pass, ib = lane_v * V;
+      const uint32_t i0 = t0 + (tr ? ia : ib), i1 = t1 + (tr ? ib : ia);
+      if (!kGuard || (i0 < n0 && i1 < n1)) {
+        if (!tr && p.strides[k + 1][0] == 0) {
+          CT one[1];
+          DynamicIO::load<CT, 1>(p.data[k + 1], outer[k + 1] + static_cast<int64_t>(i1) * p.strides[k + 1][1], p.dtype[k + 1], one);
+#pragma unroll
+          for (int j = 0; j < V; ++j) held[k][pass][j] = one[0];
+        } else {
+          const int64_t off = tr ? static_cast<int64_t>(i0) * p.strides[k + 1][0] + i1 : i0 + static_cast<int64_t>(i1) * p.strides[k + 1][1];
+          DynamicIO::load<CT, V>(p.data[k + 1], outer[k + 1] + off, p.dtype[k + 1], held[k][pass]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    if (k >= nin || !(transposed_mask >> k & 1)) continue;
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) tile[k][lane_v * V + j][lane_r + 16 * pass] = held[k][pass][j];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int pass = 0; pass < PASSES; ++pass) {
+    const uint32_t l1 = lane_r + 16 * pass;
+    const uint32_t i1 = t1 + l1, i0 = t0 + lane_v * V;
+    if (!kGuard || (i0 < n0 && i1 < n1)) {
+      CT a[KMAX][V];
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) a[k][j] = (k < nin && (transposed_mask >> k & 1)) ? tile[k][l1][lane_v * V + j] : held[k][pass][j];
+      }
+      CT o[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = ew_apply_runtime<CT>(p.op, a[0][j], a[1][j], a[1][j], sc);
+      DynamicIO::store<CT, V>(p.data[0], outer[0] + i0 + static_cast<int64_t>(i1) * p.strides[0][1], p.dtype[0], o);
+    }
+  }
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(256) ew_transpose_vec_kernel(EwGenericParams p, uint32_t transposed_mask) {
+  constexpr int T = 64;
+  __shared__ CT tile[2][T][T + 1];
+  const uint32_t t0 = blockIdx.x * T, t1 = blockIdx.y * T;
+  int64_t outer[SB_MAX_OPERANDS] = {0, 0, 0, 0};
+  {
+    uint32_t r = blockIdx.z;
+    for (int d = 2; d < p.ndim; ++d) {
+      const uint32_t i = r % p.sizes[d];
+      r /= p.sizes[d];
+#pragma unroll
+      for (int k = 0; k < 3; ++k) outer[k] += i * p.strides[k][d];  // strides of absent operands are zero
+    }
+  }
+  if (t0 + T <= p.sizes[0] && t1 + T <= p.sizes[1]) ew_transpose_tile<CT, false>(p, transposed_mask, tile, outer, t0, t1);
+  else ew_transpose_tile<CT, true>(p, transposed_mask, tile, outer, t0, t1);
+}
+
 // ---- path 3: generic ------------------------------------------------------------------------------------------
 template <typename CT>
 __global__ void __launch_bounds__(256) ew_generic_kernel(EwGenericParams p) {
@@ -454,6 +583,7 @@ struct EwPlan {
   bool fast;            // single-MUFU approximations allowed (bf16 result)
   int static_dtype;     // dtype code when every operand shares a dtype with a typed kernel, else -1
   uint32_t transposed_mask;
+  bool transpose_vec;   // path 2: every operand allows 4-element accesses
 };
 
 int ew_make_plan(const sb_ew_desc* d, EwPlan* plan);
@@ -488,9 +618,13 @@ int ew_launch_vector(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
   unsigned grid = 0;
   int rc = ew_rows_geometry(d, &p, &grid);
   if (rc != SB_OK) return rc;
-  if (p.unroll == 4) ew_rows_kernel<Op, CT, IO, 4><<<grid, kEwThreads, 0, st>>>(p);
-  else if (p.unroll == 2) ew_rows_kernel<Op, CT, IO, 2><<<grid, kEwThreads, 0, st>>>(p);
-  else ew_rows_kernel<Op, CT, IO, 1><<<grid, kEwThreads, 0, st>>>(p);
+  if (p.bcast) {
+    if (p.unroll == 4) ew_rows_kernel<Op, CT, IO, 4, true><<<grid, kEwThreads, 0, st>>>(p);
+    else ew_rows_kernel<Op, CT, IO, 2, true><<<grid, kEwThreads, 0, st>>>(p);
+  } else {
+    if (p.unroll == 4) ew_rows_kernel<Op, CT, IO, 4, false><<<grid, kEwThreads, 0, st>>>(p);
+    else ew_rows_kernel<Op, CT, IO, 2, false><<<grid, kEwThreads, 0, st>>>(p);
+  }
   return launch_status();
 }
 
@@ -502,8 +636,17 @@ int ew_launch_scalar_paths(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t
     uint64_t outer = 1;
     for (int i = 2; i < d->ndim; ++i) outer *= static_cast<uint64_t>(d->sizes[i]);
     if (outer > 65535) return SB_ERR_TOO_LARGE;  // the classifier never selects path 2 in that case
-    dim3 grid((g.sizes[0] + 31) / 32, (g.sizes[1] + 31) / 32, static_cast<unsigned>(outer));
-    ew_transpose_kernel<CT><<<grid, 256, 0, st>>>(g, plan.transposed_mask);
+    if constexpr (sizeof(CT) <= 4) {
+      if (plan.transpose_vec) {
+        dim3 grid((g.sizes[0] + 63) / 64, (g.sizes[1] + 63) / 64, static_cast<unsigned>(outer));
+        ew_transpose_vec_kernel<CT><<<grid, 256, 0, st>>>(g, plan.transposed_mask);
+        return launch_status();
+      }
+    }
+    {
+      dim3 grid((g.sizes[0] + 31) / 32, (g.sizes[1] + 31) / 32, static_cast<unsigned>(outer));
+      ew_transpose_kernel<CT><<<grid, 256, 0, st>>>(g, plan.transposed_mask);
+    }
     return launch_status();
   }
   int64_t blocks = (g.numel + 255) / 256;

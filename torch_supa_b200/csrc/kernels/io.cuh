@@ -3,6 +3,8 @@
 // instruction the element size allows (16 bytes per piece).
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace sb {
@@ -62,6 +64,38 @@ template <> struct RawPiece<4> { using type = uint32_t; };
 template <> struct RawPiece<2> { using type = uint16_t; };
 template <> struct RawPiece<1> { using type = uint8_t; };
 
+// 32-bit words of a raw piece, by value (keeps everything in registers: no pointer into a local array).
+template <int NW> struct Words { uint32_t w[NW]; };
+__device__ __forceinline__ Words<4> words_of(const uint4& r) { return Words<4>{{r.x, r.y, r.z, r.w}}; }
+__device__ __forceinline__ Words<2> words_of(const uint2& r) { return Words<2>{{r.x, r.y}}; }
+__device__ __forceinline__ Words<1> words_of(const uint32_t& r) { return Words<1>{{r}}; }
+__device__ __forceinline__ uint4 raw_of(const Words<4>& w) { return make_uint4(w.w[0], w.w[1], w.w[2], w.w[3]); }
+__device__ __forceinline__ uint2 raw_of(const Words<2>& w) { return make_uint2(w.w[0], w.w[1]); }
+__device__ __forceinline__ uint32_t raw_of(const Words<1>& w) { return w.w[0]; }
+
+template <typename S> struct Is16BitFloat { static constexpr bool value = std::is_same<S, __half>::value || std::is_same<S, __nv_bfloat16>::value; };
+
+// One 32-bit word holding two 16-bit floats <-> two fp32 values.  bf16 widens with a shift and a mask, fp16
+// with one packed conversion; both narrow with one packed round-to-nearest-even conversion.
+template <typename S> __device__ __forceinline__ float2 widen_pair(uint32_t w) {
+  if constexpr (std::is_same<S, __nv_bfloat16>::value) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    __half2 h;
+    *reinterpret_cast<uint32_t*>(&h) = w;
+    return __half22float2(h);
+  }
+}
+template <typename S> __device__ __forceinline__ uint32_t narrow_pair(float a, float b) {
+  if constexpr (std::is_same<S, __nv_bfloat16>::value) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
 // Loads VEC elements of storage type S starting at p (aligned to PieceOf::kPieceBytes) and converts
 // them to CT.
 template <typename CT, typename S, int VEC>
@@ -70,13 +104,33 @@ __device__ __forceinline__ void load_as(const void* p, CT (&out)[VEC]) {
   using Raw = typename RawPiece<P::kPieceBytes>::type;
 #pragma unroll
   for (int i = 0; i < P::kPieces; ++i) {
-    union {
-      Raw raw;
-      S s[P::kPerPiece];
-    } u;
-    u.raw = static_cast<const Raw*>(p)[i];
+    const Raw raw = static_cast<const Raw*>(p)[i];
+    if constexpr (std::is_same<CT, float>::value && Is16BitFloat<S>::value && P::kPieceBytes >= 4) {
+      const auto ws = words_of(raw);
 #pragma unroll
-    for (int k = 0; k < P::kPerPiece; ++k) out[i * P::kPerPiece + k] = convert<CT, S>(u.s[k]);
+      for (int k = 0; k < P::kPieceBytes / 4; ++k) {
+        const float2 f = widen_pair<S>(ws.w[k]);
+        out[i * P::kPerPiece + 2 * k] = f.x;
+        out[i * P::kPerPiece + 2 * k + 1] = f.y;
+      }
+    } else if constexpr (sizeof(S) == 4 && P::kPieceBytes >= 4) {
+      const auto ws = words_of(raw);
+#pragma unroll
+      for (int k = 0; k < P::kPerPiece; ++k) {
+        S v;
+        static_assert(sizeof(S) == sizeof(uint32_t), "");
+        memcpy(&v, &ws.w[k], 4);
+        out[i * P::kPerPiece + k] = convert<CT, S>(v);
+      }
+    } else {
+      union {
+        Raw raw;
+        S s[P::kPerPiece];
+      } u;
+      u.raw = raw;
+#pragma unroll
+      for (int k = 0; k < P::kPerPiece; ++k) out[i * P::kPerPiece + k] = convert<CT, S>(u.s[k]);
+    }
   }
 }
 template <typename CT, int VEC>
@@ -93,13 +147,29 @@ __device__ __forceinline__ void store_as(void* p, const CT (&in)[VEC]) {
   using Raw = typename RawPiece<P::kPieceBytes>::type;
 #pragma unroll
   for (int i = 0; i < P::kPieces; ++i) {
-    union {
-      Raw raw;
-      S s[P::kPerPiece];
-    } u;
+    if constexpr (std::is_same<CT, float>::value && Is16BitFloat<S>::value && P::kPieceBytes >= 4) {
+      Words<P::kPieceBytes / 4> ws;
 #pragma unroll
-    for (int k = 0; k < P::kPerPiece; ++k) u.s[k] = convert<S, CT>(in[i * P::kPerPiece + k]);
-    static_cast<Raw*>(p)[i] = u.raw;
+      for (int k = 0; k < P::kPieceBytes / 4; ++k)
+        ws.w[k] = narrow_pair<S>(in[i * P::kPerPiece + 2 * k], in[i * P::kPerPiece + 2 * k + 1]);
+      static_cast<Raw*>(p)[i] = raw_of(ws);
+    } else if constexpr (sizeof(S) == 4 && P::kPieceBytes >= 4) {
+      Words<P::kPieceBytes / 4> ws;
+#pragma unroll
+      for (int k = 0; k < P::kPerPiece; ++k) {
+        const S v = convert<S, CT>(in[i * P::kPerPiece + k]);
+        memcpy(&ws.w[k], &v, 4);
+      }
+      static_cast<Raw*>(p)[i] = raw_of(ws);
+    } else {
+      union {
+        Raw raw;
+        S s[P::kPerPiece];
+      } u;
+#pragma unroll
+      for (int k = 0; k < P::kPerPiece; ++k) u.s[k] = convert<S, CT>(in[i * P::kPerPiece + k]);
+      static_cast<Raw*>(p)[i] = u.raw;
+    }
   }
 }
 template <typename CT, int VEC>
@@ -116,6 +186,7 @@ __device__ __forceinline__ void store_bool_as(void* p, const CT (&in)[VEC]) {
 template <typename T>
 struct StaticIO {
   static constexpr bool kDynamic = false;
+  using storage = T;
   template <typename CT, int VEC>
   __device__ static __forceinline__ void load(const void* base, int64_t elem, int /*dtype*/, CT (&out)[VEC]) {
     load_as<CT, T, VEC>(static_cast<const T*>(base) + elem, out);
@@ -128,6 +199,7 @@ struct StaticIO {
 
 struct DynamicIO {
   static constexpr bool kDynamic = true;
+  using storage = void;
   template <typename CT, int VEC>
   __device__ static __forceinline__ void load(const void* base, int64_t elem, int dtype, CT (&out)[VEC]) {
     const char* b = static_cast<const char*>(base);

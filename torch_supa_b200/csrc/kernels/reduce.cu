@@ -53,31 +53,59 @@ struct RedGenericParams {
 
 // ---- functors -----------------------------------------------------------------------------------------------
 template <typename A> struct SumOp {
+  static constexpr bool kMinMax = false;
+  static constexpr bool kIsMax = false;
   __device__ static __forceinline__ A identity() { return A(0); }
   __device__ static __forceinline__ A combine(A a, A b) { return a + b; }
 };
+// max / min propagate NaN (amax semantics).  fp32 uses the single-instruction max.NaN / min.NaN forms.
 template <typename A> struct MaxOp {
+  static constexpr bool kMinMax = true;
+  static constexpr bool kIsMax = true;
   __device__ static __forceinline__ A identity() {
     if constexpr (std::is_same<A, float>::value) return -CUDART_INF_F;
     else if constexpr (std::is_same<A, double>::value) return -CUDART_INF;
     else return INT64_MIN;
   }
   __device__ static __forceinline__ A combine(A a, A b) {
-    if constexpr (std::is_floating_point<A>::value) return (b > a || b != b) ? b : a;  // NaN propagates
-    else return b > a ? b : a;
+    if constexpr (std::is_same<A, float>::value) {
+      float r;
+      asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+      return r;
+    } else if constexpr (std::is_floating_point<A>::value) {
+      return (b > a || b != b) ? b : a;
+    } else {
+      return b > a ? b : a;
+    }
   }
 };
 template <typename A> struct MinOp {
+  static constexpr bool kMinMax = true;
+  static constexpr bool kIsMax = false;
   __device__ static __forceinline__ A identity() {
     if constexpr (std::is_same<A, float>::value) return CUDART_INF_F;
     else if constexpr (std::is_same<A, double>::value) return CUDART_INF;
     else return INT64_MAX;
   }
   __device__ static __forceinline__ A combine(A a, A b) {
-    if constexpr (std::is_floating_point<A>::value) return (b < a || b != b) ? b : a;
-    else return b < a ? b : a;
+    if constexpr (std::is_same<A, float>::value) {
+      float r;
+      asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+      return r;
+    } else if constexpr (std::is_floating_point<A>::value) {
+      return (b < a || b != b) ? b : a;
+    } else {
+      return b < a ? b : a;
+    }
   }
 };
+
+// Packed 16-bit max / min (two elements per instruction, NaN propagating); exact, since the extremum of
+// 16-bit values is itself one of them.
+template <typename T2, bool IS_MAX> __device__ __forceinline__ T2 minmax2(T2 a, T2 b) {
+  if constexpr (IS_MAX) return __hmax2_nan(a, b);
+  else return __hmin2_nan(a, b);
+}
 
 template <typename A> __device__ __forceinline__ A shfl_down_t(A v, int o) { return __shfl_down_sync(0xffffffffu, v, o); }
 template <> __device__ __forceinline__ int64_t shfl_down_t<int64_t>(int64_t v, int o) {
@@ -127,41 +155,86 @@ __device__ __forceinline__ void keep_offsets(const RedParams& p, int64_t o, int6
 // covers the 16-byte-aligned middle, the ragged ends are scalar.
 template <class IO, class F, typename A, int VEC, int THREADS>
 __device__ __forceinline__ A thread_reduce_run(const void* in, int dtype, int64_t base, int64_t n) {
-  A acc[VEC];
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) acc[k] = F::identity();
+  using S = typename IO::storage;
+  constexpr bool kPacked = F::kMinMax && VEC == 8 && std::is_same<A, float>::value &&
+                           (std::is_same<S, __half>::value || std::is_same<S, __nv_bfloat16>::value);
   const int64_t nvec = n / VEC;
   constexpr int kUnroll = 4;
-  for (int64_t i = threadIdx.x; i < nvec; i += THREADS * kUnroll) {
-    A f[kUnroll][VEC];
+  A r = F::identity();
+  if constexpr (kPacked) {
+    using S2 = typename std::conditional<std::is_same<S, __half>::value, __half2, __nv_bfloat162>::type;
+    const S* src = static_cast<const S*>(in) + base;
+    S2 acc2[4];
+    {
+      const S lim = convert<S, float>(F::identity());
+      S2 init;
+      init.x = lim;
+      init.y = lim;
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t v = i + static_cast<int64_t>(u) * THREADS;
-      if (v < nvec) IO::template load<A, VEC>(in, base + v * VEC, dtype, f[u]);
+      for (int k = 0; k < 4; ++k) acc2[k] = init;
+    }
+    int64_t i = threadIdx.x;
+    for (; i + static_cast<int64_t>(kUnroll - 1) * THREADS < nvec; i += THREADS * kUnroll) {
+      uint4 raw[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) raw[u] = *reinterpret_cast<const uint4*>(src + (i + static_cast<int64_t>(u) * THREADS) * VEC);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const S2* h = reinterpret_cast<const S2*>(&raw[u]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc2[k] = minmax2<S2, F::kIsMax>(acc2[k], h[k]);
+      }
+    }
+    for (; i < nvec; i += THREADS) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + i * VEC);
+      const S2* h = reinterpret_cast<const S2*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc2[k] = minmax2<S2, F::kIsMax>(acc2[k], h[k]);
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t v = i + static_cast<int64_t>(u) * THREADS;
-      if (v < nvec) {
+    for (int k = 0; k < 4; ++k) {
+      r = F::combine(r, convert<float, S>(acc2[k].x));
+      r = F::combine(r, convert<float, S>(acc2[k].y));
+    }
+  } else {
+    A acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = F::identity();
+    // main part: all kUnroll vectors of a pass exist, so the loads carry no guards and are issued together
+    int64_t i = threadIdx.x;
+    for (; i + static_cast<int64_t>(kUnroll - 1) * THREADS < nvec; i += THREADS * kUnroll) {
+      A f[kUnroll][VEC];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) IO::template load<A, VEC>(in, base + (i + static_cast<int64_t>(u) * THREADS) * VEC, dtype, f[u]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
         for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], f[u][k]);
       }
     }
+    for (; i < nvec; i += THREADS) {  // remainder, one vector at a time
+      A f[VEC];
+      IO::template load<A, VEC>(in, base + i * VEC, dtype, f);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], f[k]);
+    }
+    r = acc[0];
+#pragma unroll
+    for (int k = 1; k < VEC; ++k) r = F::combine(r, acc[k]);
   }
   for (int64_t e = nvec * VEC + threadIdx.x; e < n; e += THREADS) {
     A one[1];
     IO::template load<A, 1>(in, base + e, dtype, one);
-    acc[0] = F::combine(acc[0], one[0]);
+    r = F::combine(r, one[0]);
   }
-  A r = acc[0];
-#pragma unroll
-  for (int k = 1; k < VEC; ++k) r = F::combine(r, acc[k]);
   return r;
 }
 
 // ---- path 0 ------------------------------------------------------------------------------------------------
 template <class IO, class F, typename A, int VEC, int THREADS>
-__global__ void __launch_bounds__(THREADS) red_rows_cta_kernel(RedParams p) {
+__global__ void __launch_bounds__(THREADS, sizeof(A) == 4 ? 2048 / THREADS : 1) red_rows_cta_kernel(RedParams p) {
+  // fp32 accumulation: capped at 32 registers so that 2048 threads stay resident (the kernel is latency bound)
+
   __shared__ A sm[32];
   for (int64_t o = blockIdx.x; o < p.noutputs; o += gridDim.x) {
     int64_t in_off, out_off;

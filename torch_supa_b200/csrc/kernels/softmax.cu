@@ -8,6 +8,7 @@
 // Arithmetic is fp32 for fp32/bf16/fp16 storage and fp64 for fp64 storage.  Outputs may be wider than
 // inputs (the `half_to_float` form of aten::_log_softmax) and input gradients narrower than output
 // gradients (its backward).
+#include "ce_common.cuh"
 #include "io.cuh"
 
 namespace sb {
@@ -229,6 +230,11 @@ int launch_fwd(const void* in, void* out, int64_t outer, int64_t D, int64_t inne
   const Tin* x = static_cast<const Tin*>(in);
   Tout* y = static_cast<Tout*>(out);
   const int sms = sm_count();
+  if (inner == 1 && std::is_same<Tin, Tout>::value && sizeof(Tin) <= 4) {
+    // long rows: keep the row in shared memory (one HBM read, one HBM write)
+    const int rc = lsm_launch_resident(in, out, DTypeOf<Tin>::value, outer, D, st);
+    if (rc != SB_ERR_UNSUPPORTED) return rc;
+  }
   if (inner == 1) {
     if (D <= 1024) {
       const int64_t ctas = (outer + 7) / 8;

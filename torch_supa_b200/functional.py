@@ -16,6 +16,8 @@ _RED = {"none": capi.REDUCTION_NONE, "mean": capi.REDUCTION_MEAN, "sum": capi.RE
 
 
 def _stream(t: torch.Tensor) -> int:
+    if t.device.type == "supa":
+        return torch.supa.current_stream_handle(t.device.index)
     if t.device.type == "cuda":
         return torch.cuda.current_stream(t.device).cuda_stream
     return 0

@@ -133,6 +133,12 @@ def set_memory_limit(nbytes: int, device=None) -> None:
     _check(_host().supa_set_memory_limit(idx if idx >= 0 else current_device(), ctypes.c_int64(nbytes)))
 
 
+def memcpy_async(dst_ptr: int, src_ptr: int, nbytes: int, device=None) -> None:
+    """cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDefault) on the current stream: moves bytes between
+    raw addresses (used to hand data produced by other CUDA code to supa tensors without a host round trip)."""
+    _check(_host().supa_memcpy_async(_index(device), ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), ctypes.c_int64(nbytes)))
+
+
 def _is_in_bad_fork() -> bool:
     return False
 
