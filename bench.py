@@ -104,8 +104,8 @@ def algorithmic_bytes(rows, classes, elem_size):
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused-sweep launch from the ncu captures summarised under
 # profiles/ (the bf16 figure is the 4096-row capture scaled by 8: traffic is proportional to rows).
 TRAFFIC = {
-    ("ce_fp32_4096x32000", 4096): 524.4e6 + 468.3e6,
-    ("ce_bf16_32768x128256", 32768): 8 * (1.051e9 + 0.997e9),
+    ("ce_fp32_4096x32000", 4096): 524.375296e6 + 470.366464e6,
+    ("ce_bf16_32768x128256", 32768): 8 * (998.527744e6 + 996.002816e6),
 }
 
 
@@ -196,9 +196,9 @@ def run_ours(args):
         loss.backward()
         return loss
 
-    # my kernels per step: count_valid, fused sweep, loss sum(+finish), fill(applied), fill(root gradient),
-    # rescale + its commit; with N > 1 the loss sum and finish are two launches
-    launches_per_step = 7 if world == 1 else 8
+    # my kernels per step: count_valid, fused sweep, loss sum(+finish), fill(root gradient, by autograd), rescale;
+    # with N > 1 the loss sum and finish are two launches
+    launches_per_step = 5 if world == 1 else 6
 
     def barrier():
         torch.supa.synchronize()

@@ -128,11 +128,12 @@ SB_API int sb_ce_loss_finish(const double* acc, int32_t reduction, void* out, in
 SB_API int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* acc, int32_t reduction, void* out,
                                  int32_t dtype, sb_stream_t stream);
 
-/* grad[i, :] *= factor where factor = *scale / *applied (both device floats); *applied = *scale
- * afterwards.  A no-op sweep is skipped on the device when the factor is exactly 1.  Used by the
- * autograd node when the upstream gradient of a mean/sum loss is not 1. */
+/* grad[i] *= factor where factor = *scale / *applied_in (device floats; a null applied_in stands for 1, the
+ * state right after the fused sweep); *applied_out = *scale.  One launch: the sweep is skipped on the device
+ * when the factor is exactly 1, and applied_out must be a different word from applied_in (callers alternate
+ * between two).  Used by the autograd node when the upstream gradient of a mean/sum loss is not 1. */
 SB_API int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype,
-                              float* applied, sb_stream_t stream);
+                              const float* applied_in, float* applied_out, sb_stream_t stream);
 
 /* Cross entropy (mean or sum) for callers that cannot allocate device memory.
  *

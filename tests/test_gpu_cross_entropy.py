@@ -161,13 +161,19 @@ def test_rescale_grad(cuda_device):
 
     grad = torch.randn(1000, device=cuda_device)
     ref = grad.clone()
-    applied = torch.ones(1, device=cuda_device)
+    applied = torch.full((2,), float("nan"), device=cuda_device)  # two words, used alternately; none valid yet
+    slot = None
     for s in (1.0, 0.25, 0.25, 2.0):
         scale = torch.tensor(s, device=cuda_device)
-        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, applied)
+        nxt = 0 if slot is None else 1 - slot
+        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, None if slot is None else applied[slot:slot + 1],
+                             applied[nxt:nxt + 1])
+        slot = nxt
         torch.cuda.synchronize()
         assert_close(grad.cpu().numpy(), (ref * s).cpu().numpy(), 2e-7, 0, f"scale {s}")
-        assert applied.item() == s
+        assert applied[slot].item() == s
+    with pytest.raises(capi.KernelError):
+        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, applied[0:1], applied[0:1])
 
 
 def test_linearity_property_full_vocab(cuda_device):

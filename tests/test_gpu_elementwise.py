@@ -117,6 +117,32 @@ def test_broadcast_add_fp16(cuda_device):
     assert_close(acc.cpu().float().numpy(), torch.add(p + q, q, alpha=2.0).float().numpy(), 1e-3, 1e-3, "in place")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 12, 256), (5, 7, 64), (4, 4, 8), (9, 6, 1032), (3, 5, 7, 40)])
+def test_outer_broadcast_binary_ops(cuda_device, shape, dtype):
+    """a[..., :, None, :] op b[..., None, :, :]: each input constant along a different dimension; ragged tile
+    edges and non-commutative ops pin the operand order of the register-tiled kernel."""
+    from torch_supa_b200 import capi, functional as F2
+
+    g = torch.Generator().manual_seed(sum(shape))
+    lead = shape[:-3]
+    n2, n1, n0 = shape[-3:]
+    a = torch.randn(*lead, n2, 1, n0, generator=g).to(dtype)
+    b = (torch.rand(*lead, 1, n1, n0, generator=g) + 0.5).to(dtype)
+    for op, fn in ((capi.EW_ADD, torch.add), (capi.EW_SUB, torch.sub), (capi.EW_MUL, torch.mul), (capi.EW_DIV, torch.div)):
+        for x, y in ((a, b), (b, a)):
+            if op == capi.EW_DIV and y is a:
+                continue  # a has values near zero
+            desc = capi.make_ew_desc(op, torch.empty(shape, dtype=dtype, device=cuda_device), [x.to(cuda_device), y.to(cuda_device)])
+            assert capi.elementwise_path(desc) == 1
+            out = _ew(cuda_device, op, shape, dtype, x, y)
+            ref = fn(x, y)
+            if dtype == torch.float32 or op in (capi.EW_ADD, capi.EW_SUB, capi.EW_MUL):
+                assert torch.equal(out, ref), (op, x is a)
+            else:
+                _cmp(out, ref, dtype, "div")
+
+
 def test_transposed_operand_mul_both_orders(cuda_device):
     from torch_supa_b200 import capi, functional as F2
 

@@ -32,8 +32,10 @@ def device_randn(shape, dtype, device, seed, scale=1.0, low=None, high=None):
     return out
 
 
-def time_op(fn, warmup=3, iters=10):
-    """Median milliseconds of ``fn()`` measured with events on the current supa stream."""
+def time_op(fn, warmup=3, iters=10, reps=5):
+    """Median milliseconds per call of ``fn()``, measured with events on the current supa stream.  Each sample
+    brackets ``reps`` back-to-back calls with one event pair, so that the device queue stays full and the host's
+    dispatch time between an event and the launch that follows it is not counted as kernel time."""
     for _ in range(warmup):
         fn()
     torch.supa.synchronize()
@@ -41,10 +43,11 @@ def time_op(fn, warmup=3, iters=10):
     for _ in range(iters):
         e0, e1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         e1.synchronize()
-        times.append(e0.elapsed_time(e1))
+        times.append(e0.elapsed_time(e1) / reps)
     return statistics.median(times)
 
 
@@ -65,7 +68,7 @@ def run_extras(device, peak_gbs, quick=False, profile=False):
         _orig = time_op
 
         def time_op(fn, warmup=1, iters=1):  # noqa: F811
-            return _orig(fn, 1, 1)
+            return _orig(fn, 1, 1, 1)
 
     # ---- config 0: cross entropy fp32 [4096, 32000], forward + backward through autograd ----
     x = device_randn((4096, 32000), torch.float32, device, 0, 2.0).requires_grad_(True)
@@ -102,7 +105,9 @@ def run_extras(device, peak_gbs, quick=False, profile=False):
     q = device_randn((1, 2048, 4096), torch.float16, device, 6)
     out.append(_entry("add fp16 [64,1,4096] + [1,2048,4096]", 64 * 2048 * 4096 * 2 + 64 * 4096 * 2 + 2048 * 4096 * 2,
                       time_op(lambda: p + q, iters=it), peak_gbs))
-    del p, q
+    w = torch.empty((64, 2048, 4096), dtype=torch.float16, device=device)
+    out.append(_entry("fill_ fp16 [64,2048,4096] (write only)", 64 * 2048 * 4096 * 2, time_op(lambda: w.fill_(1.0), iters=it), peak_gbs))
+    del p, q, w
     m = device_randn((8192, 4096), torch.float32, device, 7).t()
     nn_ = device_randn((4096, 8192), torch.float32, device, 8)
     out.append(_entry("mul fp32 transposed view [4096,8192] * contiguous (m.t() * n)", 3 * 4096 * 8192 * 4, time_op(lambda: m * nn_, iters=it),

@@ -138,9 +138,10 @@ def ce_loss_sum_finish(row_loss, rows, acc, reduction, out, dtype, stream=0):
                                                                C.c_void_p(stream)))
 
 
-def ce_rescale_grad(grad, dtype, numel, scale, scale_dtype, applied, stream=0):
+def ce_rescale_grad(grad, dtype, numel, scale, scale_dtype, applied_in, applied_out, stream=0):
     check("sb_ce_rescale_grad", lib().sb_ce_rescale_grad(_p(grad), C.c_int32(dtype), C.c_int64(numel), _p(scale),
-                                                         C.c_int32(scale_dtype), _p(applied), C.c_void_p(stream)))
+                                                         C.c_int32(scale_dtype), _p(applied_in), _p(applied_out),
+                                                         C.c_void_p(stream)))
 
 
 CE_STATIC_MAX_ROWS = 65536

@@ -256,7 +256,7 @@ struct FusedResult {
   at::Tensor loss;      // 0-d in the logits' dtype (mean, sum) or [N] (none)
   at::Tensor grad;      // [N, C] logit gradient for an upstream gradient of 1 (mean, sum with want_grad)
   at::Tensor row_lse;   // [N] fp32 (none with want_grad)
-  at::Tensor applied;   // device float: the upstream factor currently folded into `grad`
+  at::Tensor applied;   // two device floats used alternately: the upstream factor currently folded into `grad`
 };
 
 // The launch sequence of include/supa_b200_kernels.h: count -> [all-reduce] -> fused sweep -> loss sum ->
@@ -320,8 +320,7 @@ FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, int6
                  "supa cross_entropy loss finish");
   }
   if (want_grad) {
-    r.applied = at::empty({1}, f32);
-    r.applied.fill_(1.0);
+    r.applied = at::empty({2}, f32);  // written by the first rescale; until then the factor is 1 by construction
   }
   return r;
 }
@@ -337,6 +336,7 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
     ctx->saved_data["label_smoothing"] = label_smoothing;
     if (reduction == at::Reduction::None) ctx->save_for_backward({self, target, r.row_lse});
     else ctx->save_for_backward({r.grad, r.applied});
+    ctx->saved_data["applied_slot"] = static_cast<int64_t>(-1);  // which word of `applied` is valid; -1 = none (factor 1)
     ctx->saved_data["shape_1d"] = self.dim() == 1;
     return r.loss;
   }
@@ -383,10 +383,14 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
       const at::ScalarType st = scale.scalar_type();
       if (st != at::kFloat && st != at::kBFloat16 && st != at::kHalf && st != at::kDouble) scale = scale.to(at::kFloat);
       scale = scale.contiguous();
+      const int64_t slot = ctx->saved_data["applied_slot"].toInt();
+      const int64_t next = slot < 0 ? 0 : 1 - slot;
       check_kernel(sb_ce_rescale_grad(grad_self.data_ptr(), dtype_code(grad_self.scalar_type()), grad_self.numel(),
-                                      scale.const_data_ptr(), dtype_code(scale.scalar_type()), applied.data_ptr<float>(),
+                                      scale.const_data_ptr(), dtype_code(scale.scalar_type()),
+                                      slot < 0 ? nullptr : applied.const_data_ptr<float>() + slot, applied.data_ptr<float>() + next,
                                       stream_of(grad_self)),
                    "supa cross_entropy rescale");
+      ctx->saved_data["applied_slot"] = next;
       if (ctx->saved_data["shape_1d"].toBool()) grad_self = grad_self.reshape({grad_self.size(-1)});
     }
     return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};

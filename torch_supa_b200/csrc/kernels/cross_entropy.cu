@@ -260,11 +260,11 @@ __device__ __forceinline__ float load_scalar_as_float(const void* p) {
   return to_float(*static_cast<const T*>(p));
 }
 
-// grad *= (*scale / *applied), skipped when that factor is exactly 1.  `applied` is updated by a
-// trailing single-thread kernel so that every CTA of the sweep sees the old value.
+// grad *= *scale / *applied_in (1 when applied_in is null), skipped when that factor is exactly 1; block 0
+// records *applied_out = *scale.  The two words differ, so every CTA reads the old factor whenever it runs.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) ce_rescale_kernel(T* grad, int64_t numel, const void* scale, int scale_dtype,
-                                                         const float* applied) {
+                                                         const float* applied_in, float* applied_out) {
   float sc;
   switch (scale_dtype) {
     case SB_F32: sc = load_scalar_as_float<float>(scale); break;
@@ -272,7 +272,8 @@ __global__ void __launch_bounds__(256) ce_rescale_kernel(T* grad, int64_t numel,
     case SB_F16: sc = load_scalar_as_float<__half>(scale); break;
     default: sc = load_scalar_as_float<double>(scale); break;
   }
-  const float factor = sc / *applied;
+  const float factor = applied_in ? sc / *applied_in : sc;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *applied_out = sc;
   if (factor == 1.f) return;
   const int64_t nvec = numel / VEC;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < nvec;
@@ -284,16 +285,6 @@ __global__ void __launch_bounds__(256) ce_rescale_kernel(T* grad, int64_t numel,
   }
   if (blockIdx.x == 0)
     for (int64_t i = nvec * VEC + threadIdx.x; i < numel; i += 256) grad[i] = from_float<T>(to_float(grad[i]) * factor);
-}
-__global__ void ce_rescale_commit_kernel(const void* scale, int scale_dtype, float* applied) {
-  float sc;
-  switch (scale_dtype) {
-    case SB_F32: sc = load_scalar_as_float<float>(scale); break;
-    case SB_BF16: sc = load_scalar_as_float<__nv_bfloat16>(scale); break;
-    case SB_F16: sc = load_scalar_as_float<__half>(scale); break;
-    default: sc = load_scalar_as_float<double>(scale); break;
-  }
-  *applied = sc;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -406,34 +397,29 @@ int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* acc, int3
   return launch_status();
 }
 
-int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype, float* applied,
-                       sb_stream_t stream) {
-  if (numel < 0 || !scale || !applied || (numel > 0 && !grad)) return SB_ERR_INVALID_ARGUMENT;
+int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype, const float* applied_in,
+                       float* applied_out, sb_stream_t stream) {
+  if (numel < 0 || !scale || !applied_out || applied_in == applied_out || (numel > 0 && !grad)) return SB_ERR_INVALID_ARGUMENT;
   if (!loss_dtype_ok(scale_dtype)) return SB_ERR_UNSUPPORTED;
   cudaStream_t st = as_stream(stream);
-  if (numel > 0) {
-    const int64_t want = (numel / 8 + 255) / 256 + 1;
-    const int grid = static_cast<int>(want < 8LL * sm_count() ? want : 8LL * sm_count());
-    const bool al = reinterpret_cast<uintptr_t>(grad) % 16 == 0;
-    switch (dtype) {
-      case SB_F32:
-        if (al) ce_rescale_kernel<float, 4><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied);
-        else ce_rescale_kernel<float, 1><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied);
-        break;
-      case SB_BF16:
-        if (al) ce_rescale_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied);
-        else ce_rescale_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied);
-        break;
-      case SB_F16:
-        if (al) ce_rescale_kernel<__half, 8><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied);
-        else ce_rescale_kernel<__half, 1><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied);
-        break;
-      default: return SB_ERR_UNSUPPORTED;
-    }
-    int rc = launch_status();
-    if (rc != SB_OK) return rc;
+  const int64_t want = (numel / 8 + 255) / 256 + 1;
+  const int grid = static_cast<int>(want < 8LL * sm_count() ? want : 8LL * sm_count());
+  const bool al = reinterpret_cast<uintptr_t>(grad) % 16 == 0;
+  switch (dtype) {
+    case SB_F32:
+      if (al) ce_rescale_kernel<float, 4><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      else ce_rescale_kernel<float, 1><<<grid, 256, 0, st>>>(static_cast<float*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      break;
+    case SB_BF16:
+      if (al) ce_rescale_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      else ce_rescale_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      break;
+    case SB_F16:
+      if (al) ce_rescale_kernel<__half, 8><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      else ce_rescale_kernel<__half, 1><<<grid, 256, 0, st>>>(static_cast<__half*>(grad), numel, scale, scale_dtype, applied_in, applied_out);
+      break;
+    default: return SB_ERR_UNSUPPORTED;
   }
-  ce_rescale_commit_kernel<<<1, 1, 0, st>>>(scale, scale_dtype, applied);
   return launch_status();
 }
 

@@ -62,6 +62,7 @@ int ew_make_plan(const sb_ew_desc* d, EwPlan* plan) {
   }
   plan->transposed_mask = 0;
   plan->transpose_vec = false;
+  plan->outer = 0;
   plan->path = 3;
   if (numel == 0) return SB_OK;
 
@@ -97,6 +98,12 @@ int ew_make_plan(const sb_ew_desc* d, EwPlan* plan) {
     for (int i = 1; i < d->ndim; ++i) rows *= static_cast<uint64_t>(d->sizes[i]);
     if (ok && rows <= 0xffffffffULL) {
       plan->path = 1;
+      // outer-broadcast form: two inputs, whole vectors only, each input constant along a different one of dims 1, 2
+      if (d->noperands == 3 && ew_arity(d->op) == 2 && d->ndim >= 3 && d->sizes[0] % kEwVec == 0 && d->strides[1][0] == 1 &&
+          d->strides[2][0] == 1 && d->sizes[1] >= 4 && d->sizes[2] >= 4) {
+        if (d->strides[1][1] == 0 && d->strides[2][2] == 0) plan->outer = 1;
+        else if (d->strides[2][1] == 0 && d->strides[1][2] == 0) plan->outer = 2;
+      }
       return SB_OK;
     }
   }

@@ -401,6 +401,50 @@ __global__ void __launch_bounds__(kEwThreads) ew_rows_kernel(EwParams p) {
   }
 }
 
+// ---- path 1, outer-broadcast form -----------------------------------------------------------------------------
+// Binary op whose inputs are each constant along a different one of dims 1 and 2 (out[i2][i1][:] =
+// x[i2][:] op y[i1][:], the shape of `a[:, None, :] + b[None, :, :]`).  A thread owns one vector position of
+// the row and an R2 x R1 tile of (i2, i1): it loads R2 + R1 vectors and produces R2 * R1, so each input
+// vector is fetched once per tile instead of once per output row.  KX = which input is constant along dim1.
+template <class Op, typename CT, class IO, int R1, int R2, int KX>
+__global__ void __launch_bounds__(kEwThreads) ew_outer_kernel(EwParams p, uint32_t tiles1, uint32_t tiles2) {
+  constexpr int KY = 1 - KX;
+  const OpScalars<CT> sc = make_scalars<CT>(p);
+  const uint32_t nv = p.sizes[0] / kEwVec;
+  const uint64_t item = static_cast<uint64_t>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const uint32_t v = static_cast<uint32_t>(item % nv);
+  uint64_t t = item / nv;
+  const uint32_t t1 = static_cast<uint32_t>(t % tiles1);
+  t /= tiles1;
+  const uint32_t t2 = static_cast<uint32_t>(t % tiles2);
+  const uint64_t i3 = t / tiles2;
+  if (i3 >= p.sizes[3]) return;
+  const uint32_t i1 = t1 * R1, i2 = t2 * R2;
+  const int64_t col = static_cast<int64_t>(v) * kEwVec;
+  const int64_t base_x = col + i3 * p.strides[KX + 1][3], base_y = col + i3 * p.strides[KY + 1][3];
+  CT x[R2][kEwVec], y[R1][kEwVec];
+#pragma unroll
+  for (int r = 0; r < R2; ++r)
+    if (i2 + r < p.sizes[2]) IO::template load<CT, kEwVec>(p.data[KX + 1], base_x + (i2 + r) * p.strides[KX + 1][2], p.dtype[KX + 1], x[r]);
+#pragma unroll
+  for (int r = 0; r < R1; ++r)
+    if (i1 + r < p.sizes[1]) IO::template load<CT, kEwVec>(p.data[KY + 1], base_y + (i1 + r) * p.strides[KY + 1][1], p.dtype[KY + 1], y[r]);
+  const int64_t base_o = col + i3 * p.strides[0][3];
+#pragma unroll
+  for (int r2 = 0; r2 < R2; ++r2) {
+#pragma unroll
+    for (int r1 = 0; r1 < R1; ++r1) {
+      if (i2 + r2 < p.sizes[2] && i1 + r1 < p.sizes[1]) {
+        CT o[kEwVec];
+#pragma unroll
+        for (int e = 0; e < kEwVec; ++e)
+          o[e] = KX == 0 ? Op::apply(x[r2][e], y[r1][e], y[r1][e], sc) : Op::apply(y[r1][e], x[r2][e], x[r2][e], sc);
+        IO::template store<CT, kEwVec>(p.data[0], base_o + (i2 + r2) * p.strides[0][2] + (i1 + r1) * p.strides[0][1], p.dtype[0], o);
+      }
+    }
+  }
+}
+
 // ---- path 2: tiled transpose ------------------------------------------------------------------------------
 // 32 x 32 tile over (dim0, dim1); dims 2.. are walked by blockIdx.z (flattened).  Operands whose unit
 // stride lies along dim1 are read with threads along dim1 and turned through shared memory.
@@ -461,7 +505,7 @@ __global__ void __launch_bounds__(256) ew_transpose_kernel(EwGenericParams p, ui
 // sizes[1] to be multiples of 4 and every operand 4-element aligned along its unit-stride dimension.
 // All global loads of a tile (the transposed operands and the straight ones) are issued before anything
 // waits on them; interior tiles (kGuard = false) carry no bounds checks.
-template <typename CT, bool kGuard>
+template <typename CT, class IO, bool kGuard>
 __device__ __forceinline__ void ew_transpose_tile(const EwGenericParams& p, uint32_t transposed_mask, CT (*tile)[64][65],
                                                   const int64_t* outer, uint32_t t0, uint32_t t1) {
   constexpr int T = 64, V = 4, PASSES = T / 16, KMAX = 2;  // at most two inputs (the classifier guarantees it)
@@ -484,12 +528,12 @@ __device__ __forceinline__ void ew_transpose_tile(const EwGenericParams& p, uint
       if (!kGuard || (i0 < n0 && i1 < n1)) {
         if (!tr && p.strides[k + 1][0] == 0) {
           CT one[1];
-          DynamicIO::load<CT, 1>(p.data[k + 1], outer[k + 1] + static_cast<int64_t>(i1) * p.strides[k + 1][1], p.dtype[k + 1], one);
+          IO::template load<CT, 1>(p.data[k + 1], outer[k + 1] + static_cast<int64_t>(i1) * p.strides[k + 1][1], p.dtype[k + 1], one);
 #pragma unroll
           for (int j = 0; j < V; ++j) held[k][pass][j] = one[0];
         } else {
           const int64_t off = tr ? static_cast<int64_t>(i0) * p.strides[k + 1][0] + i1 : i0 + static_cast<int64_t>(i1) * p.strides[k + 1][1];
-          DynamicIO::load<CT, V>(p.data[k + 1], outer[k + 1] + off, p.dtype[k + 1], held[k][pass]);
+          IO::template load<CT, V>(p.data[k + 1], outer[k + 1] + off, p.dtype[k + 1], held[k][pass]);
         }
       }
     }
@@ -518,15 +562,17 @@ __device__ __forceinline__ void ew_transpose_tile(const EwGenericParams& p, uint
       CT o[V];
 #pragma unroll
       for (int j = 0; j < V; ++j) o[j] = ew_apply_runtime<CT>(p.op, a[0][j], a[1][j], a[1][j], sc);
-      DynamicIO::store<CT, V>(p.data[0], outer[0] + i0 + static_cast<int64_t>(i1) * p.strides[0][1], p.dtype[0], o);
+      IO::template store<CT, V>(p.data[0], outer[0] + i0 + static_cast<int64_t>(i1) * p.strides[0][1], p.dtype[0], o);
     }
   }
 }
 
-template <typename CT>
-__global__ void __launch_bounds__(256) ew_transpose_vec_kernel(EwGenericParams p, uint32_t transposed_mask) {
+template <typename CT, class IO>
+__global__ void __launch_bounds__(256, 5) ew_transpose_vec_kernel(EwGenericParams p, uint32_t transposed_mask) {
   constexpr int T = 64;
-  __shared__ CT tile[2][T][T + 1];
+  // one [T][T + 1] slot per input (only the transposed ones are used); sized by the launch
+  extern __shared__ __align__(16) unsigned char tile_raw[];
+  CT (*tile)[T][T + 1] = reinterpret_cast<CT (*)[T][T + 1]>(tile_raw);
   const uint32_t t0 = blockIdx.x * T, t1 = blockIdx.y * T;
   int64_t outer[SB_MAX_OPERANDS] = {0, 0, 0, 0};
   {
@@ -538,8 +584,8 @@ __global__ void __launch_bounds__(256) ew_transpose_vec_kernel(EwGenericParams p
       for (int k = 0; k < 3; ++k) outer[k] += i * p.strides[k][d];  // strides of absent operands are zero
     }
   }
-  if (t0 + T <= p.sizes[0] && t1 + T <= p.sizes[1]) ew_transpose_tile<CT, false>(p, transposed_mask, tile, outer, t0, t1);
-  else ew_transpose_tile<CT, true>(p, transposed_mask, tile, outer, t0, t1);
+  if (t0 + T <= p.sizes[0] && t1 + T <= p.sizes[1]) ew_transpose_tile<CT, IO, false>(p, transposed_mask, tile, outer, t0, t1);
+  else ew_transpose_tile<CT, IO, true>(p, transposed_mask, tile, outer, t0, t1);
 }
 
 // ---- path 3: generic ------------------------------------------------------------------------------------------
@@ -584,6 +630,7 @@ struct EwPlan {
   int static_dtype;     // dtype code when every operand shares a dtype with a typed kernel, else -1
   uint32_t transposed_mask;
   bool transpose_vec;   // path 2: every operand allows 4-element accesses
+  int outer;            // path 1: 1 or 2 = input 0 / input 1 is constant along dim1 and the other along dim2, else 0
 };
 
 int ew_make_plan(const sb_ew_desc* d, EwPlan* plan);
@@ -615,6 +662,18 @@ int ew_launch_vector(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
     ew_contig_kernel<Op, CT, IO, kUnroll><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p);
     return launch_status();
   }
+  if constexpr (Op::arity == 2) {
+    if (plan.outer) {
+      constexpr int R1 = 4, R2 = 4;
+      const uint32_t tiles1 = (p.sizes[1] + R1 - 1) / R1, tiles2 = (p.sizes[2] + R2 - 1) / R2;
+      const uint64_t items = static_cast<uint64_t>(p.sizes[0] / kEwVec) * tiles1 * tiles2 * p.sizes[3];
+      const uint64_t blocks = (items + kEwThreads - 1) / kEwThreads;
+      if (blocks > 0x7fffffffULL) return SB_ERR_TOO_LARGE;
+      if (plan.outer == 1) ew_outer_kernel<Op, CT, IO, R1, R2, 0><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
+      else ew_outer_kernel<Op, CT, IO, R1, R2, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
+      return launch_status();
+    }
+  }
   unsigned grid = 0;
   int rc = ew_rows_geometry(d, &p, &grid);
   if (rc != SB_OK) return rc;
@@ -639,7 +698,18 @@ int ew_launch_scalar_paths(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t
     if constexpr (sizeof(CT) <= 4) {
       if (plan.transpose_vec) {
         dim3 grid((g.sizes[0] + 63) / 64, (g.sizes[1] + 63) / 64, static_cast<unsigned>(outer));
-        ew_transpose_vec_kernel<CT><<<grid, 256, 0, st>>>(g, plan.transposed_mask);
+        // shared memory: slots up to the last transposed input (at most two inputs reach this kernel)
+        const size_t smem = ((plan.transposed_mask & 2u) ? 2 : 1) * sizeof(CT) * 64 * 65;
+        if constexpr (std::is_same<CT, float>::value) {
+          switch (plan.static_dtype) {
+            case SB_F32: ew_transpose_vec_kernel<CT, StaticIO<float>><<<grid, 256, smem, st>>>(g, plan.transposed_mask); break;
+            case SB_BF16: ew_transpose_vec_kernel<CT, StaticIO<__nv_bfloat16>><<<grid, 256, smem, st>>>(g, plan.transposed_mask); break;
+            case SB_F16: ew_transpose_vec_kernel<CT, StaticIO<__half>><<<grid, 256, smem, st>>>(g, plan.transposed_mask); break;
+            default: ew_transpose_vec_kernel<CT, DynamicIO><<<grid, 256, smem, st>>>(g, plan.transposed_mask); break;
+          }
+        } else {
+          ew_transpose_vec_kernel<CT, DynamicIO><<<grid, 256, smem, st>>>(g, plan.transposed_mask);
+        }
         return launch_status();
       }
     }

@@ -541,7 +541,9 @@ int launch_paths(const Plan& plan, cudaStream_t st) {
       const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
       red_rows_warp_kernel<IO, F, A, 256><<<grid, 256, 0, st>>>(p);
     } else {
-      const int grid = static_cast<int>(p.noutputs < 8LL * sms ? p.noutputs : 8LL * sms);
+      // one CTA per row while that stays below a few hundred waves: a fresh CTA issues its first loads at once,
+      // which keeps more reads in flight than a persistent loop does at its row boundaries
+      const int grid = static_cast<int>(p.noutputs < 2048LL * sms ? p.noutputs : 2048LL * sms);
       if (plan.vec_ok) red_rows_cta_kernel<IO, F, A, 8, 256><<<grid, 256, 0, st>>>(p);
       else red_rows_cta_kernel<IO, F, A, 1, 256><<<grid, 256, 0, st>>>(p);
     }
