@@ -298,7 +298,7 @@ def run_ours(args):
             wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
             e2e = {"value": rows * world / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "wall_ms_per_step": wall_ms,
                    "steps": e2e_steps, "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
-                   "api": "tensor.to('supa', non_blocking) from pinned memory; F.cross_entropy; backward; loss.item()",
+                   "api": "tensor.to('supa', non_blocking) from pinned memory; " + ("sharded_cross_entropy" if comm is not None else "F.cross_entropy") + "; backward; loss.item()",
                    "loss": e2e_loss}
             del host_logits
         else:
