@@ -169,6 +169,10 @@ def run_ours(args):
         comm = LossComm.from_env(device_index=local_rank)
     if args.force_generic:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 0))
+    if args.tune_variant >= 0:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, args.tune_variant))
+    if args.tune_window >= 0:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(2, args.tune_window))
 
     rows, classes, dtype_name, ignore_frac, eps = WORKLOADS[args.workload]
     if args.rows:
@@ -363,6 +367,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiling mode: no clock warm loop, no e2e, no CPU baseline")
     ap.add_argument("--force-generic", action="store_true", help="tuning: always use the generic two-sweep kernel")
+    ap.add_argument("--tune-variant", type=int, default=-1, help="tuning: force the resident kernel's cluster size (1, 2, 4)")
+    ap.add_argument("--tune-window", type=int, default=-1, help="tuning: next-row chunks folded during the statistics exchange")
     ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations; 2: same, one launch each (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -165,7 +165,10 @@ SB_API int sb_ce_loss_static_scratch(const sb_ce_args* args, void* loss_out, sb_
 SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
 
 /* Tuning hook for benchmarks and profiling (process-wide, not thread-safe against running launches):
- * key 1 = cross-entropy kernel family (-1 automatic, 0 always the generic two-sweep kernel). */
+ * key 1 = cross-entropy kernel family (-1 automatic, 0 always the generic two-sweep kernel, 1/2/4 the
+ * resident kernel with that cluster size where the shape qualifies for a resident kernel at all);
+ * key 2 = chunks of the next row the resident kernel folds while a row's statistics are exchanged
+ * (-1 automatic, 0..64). */
 SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------

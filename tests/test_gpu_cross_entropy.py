@@ -268,3 +268,28 @@ def test_masked_logits_minus_inf(cuda_device, rows, classes, dtype):
     assert np.all(grad[ok.numpy()][:, : classes // 2] == 0)
     tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
     assert_close(grad[ok.numpy()], ref_grad[ok].numpy(), tol[0], tol[1], "grad")
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(200, 32000, torch.float32), (160, 128256, torch.bfloat16), (160, 64000, torch.float16),
+                                                (50, 3000, torch.float32), (64, 500, torch.bfloat16)])
+def test_nan_logit_poisons_its_row_only(cuda_device, rows, classes, dtype):
+    """A NaN logit makes the loss and every gradient element of its row NaN, as on the CPU; other rows are untouched.
+    Positions are chosen so that the NaN falls on each of the four 4-byte pairs of a 16-byte vector."""
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    bad = {2: 5, 7: classes - 1, 11: classes // 2 + 6, 13: 16 * 9 + 3, 17: 8 * 1001 + 7}
+    for r, c in bad.items():
+        logits[r, c % classes] = float("nan")
+    loss, grad = _run(cuda_device, logits, target, reduction="none")
+    ref_loss, ref_grad = oracle.aten_cross_entropy(logits, target, reduction="none", grad_out=torch.ones(rows))
+    ok = np.ones(rows, dtype=bool)
+    for r in bad:
+        ok[r] = False
+        assert np.isnan(loss[r]) and bool(torch.isnan(ref_loss[r]))
+        assert np.all(np.isnan(grad[r])), f"row {r}: {np.count_nonzero(~np.isnan(grad[r]))} finite gradient elements"
+        assert bool(torch.isnan(ref_grad[r].float()).all())
+    assert not np.isnan(loss[ok]).any() and not np.isnan(grad[ok]).any()
+    tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
+    assert_close(loss[ok], ref_loss[torch.from_numpy(ok)].numpy(), 2e-6, 4e-6, "loss")
+    assert_close(grad[ok], ref_grad[torch.from_numpy(ok)].numpy(), tol[0], tol[1], "grad")

@@ -30,6 +30,7 @@ namespace sb {
 namespace {
 
 int g_ce_force_variant = -1;  // tuning: -1 automatic, 0 generic, 1/2/4 resident cluster size
+int g_ce_window_chunks = -1;  // tuning: chunks of the next row a group may fold while it waits for the exchange; -1 automatic
 
 constexpr uint32_t kMaxSpin = 1u << 22;  // try_wait attempts (each suspends up to ~1 us) before giving up
 
@@ -42,6 +43,7 @@ struct ResidentParams {
   uint32_t row_units;    // 16-byte units per row
   uint32_t num_clusters;
   int mode;              // 0 cross entropy, 1 log_softmax
+  uint32_t window;       // chunks of the next row a group may fold while the row statistics are exchanged
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -61,6 +63,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -111,6 +125,13 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// NaN-propagating maximum (fmaxf drops a NaN operand; a NaN logit must poison its row as it does on the CPU).
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
 // ---- packed fp32 pairs (sm_100) -----------------------------------------------------------------------
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -133,10 +154,58 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return d;
 }
 
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// 2^y for a pair, y <= 0 (clamped at -127, where the result is 0), entirely on the FMA and integer pipes:
+// y = j + f with j the nearest integer (magic-number rounding), a minimax polynomial of degree DEG for 2^f on
+// [-0.5, 0.5], times 2^j built in the exponent field.  Relative error 7.5e-5 (DEG 3), 2.7e-6 (DEG 4), 2.4e-7 (DEG 5).  The 16-bit
+// kernels send one pair in four this way because their sweeps are bound by the special-function unit.  A NaN
+// argument does not come out as NaN here: the callers make NaN rows NaN through the other three pairs.
+template <int DEG>
+__device__ __forceinline__ float2 ex2_poly2(float2 y) {
+  y.x = fmaxf(y.x, -127.f);  // j = -127 turns the scale below into +0: arguments down to -inf give exactly 0
+  y.y = fmaxf(y.y, -127.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23: the sum's mantissa holds round(y)
+  const float2 r = add2(y, magic);
+  const float2 j = add2(r, make_float2(-12582912.f, -12582912.f));
+  const float2 f = fma2(j, make_float2(-1.f, -1.f), y);
+  float2 p;
+  if (DEG == 3) {
+    p = fma2(make_float2(0.05517163872718811f, 0.05517163872718811f), f, make_float2(0.2426111251115799f, 0.2426111251115799f));
+    p = fma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+    p = fma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  } else if (DEG == 4) {
+    p = fma2(make_float2(0.009570098482072353f, 0.009570098482072353f), f, make_float2(0.05591785907745361f, 0.05591785907745361f));
+    p = fma2(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
+    p = fma2(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+    p = fma2(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+  } else {
+    p = fma2(make_float2(0.0013276468962430954f, 0.0013276468962430954f), f, make_float2(0.009675540961325169f, 0.009675540961325169f));
+    p = fma2(p, f, make_float2(0.05550713464617729f, 0.05550713464617729f));
+    p = fma2(p, f, make_float2(0.24022120237350464f, 0.24022120237350464f));
+    p = fma2(p, f, make_float2(0.6931469440460205f, 0.6931469440460205f));
+    p = fma2(p, f, make_float2(1.0000001192092896f, 1.0000001192092896f));
+  }
+  // 2^j as a float: exponent field 127 + j (the bits of r above the integer part shift out)
+  const float2 scale = make_float2(__int_as_float((__float_as_int(r.x) << 23) + 0x3f800000),
+                                   __int_as_float((__float_as_int(r.y) << 23) + 0x3f800000));
+  return mul2(p, scale);
+}
+
 // 16 bytes of T as fp32 pairs.
 template <typename T> struct Unit;
 template <> struct Unit<float> {
   static constexpr int kPairs = 2;
+  static constexpr int kPolyDeg = 0;  // 4-byte elements: the sweeps are bound by memory, every exponential is an ex2
   __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[2]) {
     f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
     f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
@@ -145,11 +214,12 @@ template <> struct Unit<float> {
     return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
   }
   __device__ static __forceinline__ float vmax(const uint4& r) {
-    return fmaxf(fmaxf(__uint_as_float(r.x), __uint_as_float(r.y)), fmaxf(__uint_as_float(r.z), __uint_as_float(r.w)));
+    return max_nan(max_nan(__uint_as_float(r.x), __uint_as_float(r.y)), max_nan(__uint_as_float(r.z), __uint_as_float(r.w)));
   }
 };
 template <> struct Unit<__nv_bfloat16> {
   static constexpr int kPairs = 4;
+  static constexpr int kPolyDeg = 3;  // polynomial degree of the gradient sweep's offloaded pair (8-bit significand out)
   __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[4]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -166,15 +236,16 @@ template <> struct Unit<__nv_bfloat16> {
   }
   // maximum of the 8 values with packed bf16 maxima, widened once at the end
   __device__ static __forceinline__ float vmax(const uint4& r) {
-    const __nv_bfloat162 a = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&r.x), *reinterpret_cast<const __nv_bfloat162*>(&r.y));
-    const __nv_bfloat162 b = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&r.z), *reinterpret_cast<const __nv_bfloat162*>(&r.w));
-    const __nv_bfloat162 c = __hmax2(a, b);
+    const __nv_bfloat162 a = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&r.x), *reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    const __nv_bfloat162 b = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&r.z), *reinterpret_cast<const __nv_bfloat162*>(&r.w));
+    const __nv_bfloat162 c = __hmax2_nan(a, b);
     const uint32_t w = *reinterpret_cast<const uint32_t*>(&c);
-    return fmaxf(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    return max_nan(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
   }
 };
 template <> struct Unit<__half> {
   static constexpr int kPairs = 4;
+  static constexpr int kPolyDeg = 4;  // 11-bit significand out
   __device__ static __forceinline__ void unpack(const uint4& r, float2 (&f)[4]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -190,13 +261,17 @@ template <> struct Unit<__half> {
     return make_uint4(w[0], w[1], w[2], w[3]);
   }
   __device__ static __forceinline__ float vmax(const uint4& r) {
-    const __half2 a = __hmax2(*reinterpret_cast<const __half2*>(&r.x), *reinterpret_cast<const __half2*>(&r.y));
-    const __half2 b = __hmax2(*reinterpret_cast<const __half2*>(&r.z), *reinterpret_cast<const __half2*>(&r.w));
-    const float2 c = __half22float2(__hmax2(a, b));
-    return fmaxf(c.x, c.y);
+    const __half2 a = __hmax2_nan(*reinterpret_cast<const __half2*>(&r.x), *reinterpret_cast<const __half2*>(&r.y));
+    const __half2 b = __hmax2_nan(*reinterpret_cast<const __half2*>(&r.z), *reinterpret_cast<const __half2*>(&r.w));
+    const float2 c = __half22float2(__hmax2_nan(a, b));
+    return max_nan(c.x, c.y);
   }
 };
 
+#ifndef SB_CE_POLY_PAIRS
+#define SB_CE_POLY_PAIRS 1
+#endif
+constexpr int kPolyPairs = SB_CE_POLY_PAIRS;  // pairs per 16-byte vector of 16-bit logits whose exponentials avoid the special-function unit
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr int kGroups = 4;          // consumer warp groups per CTA
@@ -218,17 +293,9 @@ struct alignas(16) Tail {
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "mul.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-
 // (max2, sum) merge in base 2 with empty partials (-inf, 0) kept neutral.
 __device__ __forceinline__ void merge2(float& m, float& s, float om, float os) {
   const float nm = fmaxf(m, om);
@@ -252,9 +319,10 @@ __device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV])
   constexpr int P = U::kPairs;
   float vm = U::vmax(r[0]);
 #pragma unroll
-  for (int q = 1; q < NV; ++q) vm = fmaxf(vm, U::vmax(r[q]));
-  // Logits may be -inf (masked classes): keep (-inf) - (-inf) out of the arithmetic.
-  const float nm = fmaxf(st.m2, vm * kLog2e);
+  for (int q = 1; q < NV; ++q) vm = max_nan(vm, U::vmax(r[q]));
+  // Logits may be -inf (masked classes): keep (-inf) - (-inf) out of the arithmetic.  A NaN logit makes the
+  // maximum NaN, and with it every term below.
+  const float nm = max_nan(st.m2, vm * kLog2e);
   const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);  // m2 = -inf < nm: the sums are 0, ex2(-inf) = 0
   const float2 resc2 = make_float2(resc, resc);
   st.s[0] = mul2(st.s[0], resc2);
@@ -270,7 +338,9 @@ __device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV])
 #pragma unroll
     for (int i = 0; i < P; ++i) {
       const float2 y = fma2(f[i], l2e2, negm);
-      st.s[i & 1] = add2(st.s[i & 1], make_float2(ex2(y.x), ex2(y.y)));
+      // one pair in four of a 16-bit vector goes through the FMA pipe (degree 5: the sum feeds an fp32 loss)
+      const float2 e = (U::kPolyDeg && i >= P - kPolyPairs) ? ex2_poly2<5>(y) : make_float2(ex2(y.x), ex2(y.y));
+      st.s[i & 1] = add2(st.s[i & 1], e);
       if (kSumX) st.sx[i & 1] = add2(st.sx[i & 1], f[i]);
     }
   }
@@ -287,7 +357,8 @@ __device__ __forceinline__ uint4 grad_vector(const uint4& r, float2 neg_lse2, fl
 #pragma unroll
   for (int i = 0; i < P; ++i) {
     const float2 y = fma2(f[i], l2e2, neg_lse2);
-    f[i] = fma2(make_float2(ex2(y.x), ex2(y.y)), scale2, nsub2);
+    const float2 e = (U::kPolyDeg && i >= P - kPolyPairs) ? ex2_poly2<U::kPolyDeg ? U::kPolyDeg : 3>(y) : make_float2(ex2(y.x), ex2(y.y));
+    f[i] = fma2(e, scale2, nsub2);
   }
   return U::pack(f);
 }
@@ -449,50 +520,69 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
   float base_scale = p.grad_scale;  // gradient scale that does not depend on the row
   if (p.grad && p.reduction == SB_REDUCTION_MEAN) base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
 
+  // Folds the group's chunks [from, cpg) of the row whose first chunk sits at ring position (j0, ph0) into
+  // the statistics and returns how many chunks of the row are done.  blocking: wait for every chunk;
+  // otherwise stop at the first chunk that has not landed yet (used to fill the wait for the peers'
+  // statistics with the next row's work).
+  auto fold_chunks = [&](RowStats& st, uint32_t j0, uint32_t ph0, uint32_t from, uint32_t to, bool skip, bool blocking) -> uint32_t {
+    uint32_t j = j0 + from, ph = ph0;
+    if (j >= nbg) {  // from < cpg < nbg: one wrap at most
+      j -= nbg;
+      ph ^= 1;
+    }
+    uint32_t cl = from;
+    for (; cl < to; ++cl) {
+      const uint32_t bar = full0 + 8 * j;
+      if (blocking) {
+        if (!mbar_wait(bar, ph)) timed_out = true;
+      } else if (!__all_sync(0xffffffffu, mbar_test_wait(bar, ph))) {
+        break;
+      }
+      if (!skip) {
+        const uint32_t u0 = (cl * G + grp) * kChunkUnits;
+        const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+        const uint4* buf = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
+        if (len == kChunkUnits) {
+          uint4 r[NV];
+#pragma unroll
+          for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+          stats_update<T, NV, kSumX>(st, r);
+        } else {
+          for (uint32_t v = gt; v < len; v += TG) {  // ragged last chunk of the slice
+            uint4 r[1] = {buf[v - gt]};
+            stats_update<T, 1, kSumX>(st, r);
+          }
+        }
+      }
+      if (++j == nbg) {
+        j = 0;
+        ph ^= 1;
+      }
+    }
+    return cl;
+  };
+  auto is_ignored = [&](int64_t t) { return MODE == 0 && (t == p.ignore_index || t < 0 || t >= p.classes); };
+
+  RowStats st;  // statistics of the row in sweep A; re-initialised as soon as they have been reduced
+  st.m2 = -CUDART_INF_F;
+  st.s[0] = st.s[1] = st.sx[0] = st.sx[1] = make_float2(0.f, 0.f);
+  uint32_t a_done = 0;  // chunks of the current row already folded (during the previous row's exchange)
+  uint32_t xpar = 0;    // which pair of exchange slots the row uses; advances with every row that is not ignored
+
   int64_t t_next = (MODE == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
   for (int64_t k = 0; k < nrows_local; ++k) {
     const int64_t row = cluster_id + k * static_cast<int64_t>(rp.num_clusters);
     const int64_t t = t_next;
     if (MODE == 0 && k + 1 < nrows_local) t_next = p.target[row + rp.num_clusters];  // in flight during this row's sweeps
-    bool ignored = MODE == 0 && (t == p.ignore_index);
-    if (MODE == 0 && !ignored && (t < 0 || t >= p.classes)) {
-      if (tid == 0 && cta_rank == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
-      ignored = true;
-    }
+    const bool ignored = is_ignored(t);
+    if (MODE == 0 && ignored && t != p.ignore_index && tid == 0 && cta_rank == 0 && p.status)
+      atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
 
-    // ---- sweep A: statistics as the group's chunks land ----
-    RowStats st;
-    st.m2 = -CUDART_INF_F;
-    st.s[0] = st.s[1] = st.sx[0] = st.sx[1] = make_float2(0.f, 0.f);
-    {
-      uint32_t j = cj, ph = cphase;
-      for (uint32_t cl = 0; cl < cpg; ++cl) {
-        if (!mbar_wait(full0 + 8 * j, ph)) timed_out = true;
-        if (!ignored) {
-          const uint32_t u0 = (cl * G + grp) * kChunkUnits;
-          const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
-          const uint4* buf = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
-          if (len == kChunkUnits) {
-            uint4 r[NV];
-#pragma unroll
-            for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
-            stats_update<T, NV, kSumX>(st, r);
-          } else {
-            for (uint32_t v = gt; v < len; v += TG) {  // ragged last chunk of the slice
-              uint4 r[1] = {buf[v - gt]};
-              stats_update<T, 1, kSumX>(st, r);
-            }
-          }
-        }
-        if (++j == nbg) {
-          j = 0;
-          ph ^= 1;
-        }
-      }
-    }
-    float lse = 0.f, scale = 0.f, xt_all = 0.f;
+    // ---- sweep A: statistics as the group's chunks land (the first a_done chunks are folded already) ----
+    fold_chunks(st, cj, cphase, a_done, cpg, ignored, true);
+
+    // ---- CTA reduce; the other warps go on to the next row's chunks while warp 0 combines ----
     if (!ignored) {
-      // ---- CTA reduce (consumer warps only) ----
       float m2 = st.m2;
       float s = (st.s[0].x + st.s[0].y) + (st.s[1].x + st.s[1].y);
       float sx = (st.sx[0].x + st.sx[0].y) + (st.sx[1].x + st.sx[1].y);
@@ -506,8 +596,11 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         tail->red[1][warp] = s;
         tail->red[2][warp] = sx;
       }
-      named_barrier(1, kConsumers);
-      if (warp == 0) {
+      __syncwarp();
+      if (warp != 0) {
+        named_barrier_arrive(1, kConsumers);  // partials published; no need to wait here
+      } else {
+        named_barrier(1, kConsumers);
         float wm = lane < kConsumers / 32 ? tail->red[0][lane] : -CUDART_INF_F;
         float wsum = lane < kConsumers / 32 ? tail->red[1][lane] : 0.f;
         float wx = lane < kConsumers / 32 ? tail->red[2][lane] : 0.f;
@@ -534,21 +627,37 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
             xt = to_float(reinterpret_cast<const T*>(smem + (static_cast<size_t>(og) * nbg + oj) * kChunkBytes)[off]);
           }
           if (CLUSTER > 1) {
-            const uint32_t slot = smem_u32(&tail->slots[k & 1][cta_rank]);
+            const uint32_t slot = smem_u32(&tail->slots[xpar][cta_rank]);
 #pragma unroll
             for (int jj = 0; jj < CLUSTER; ++jj) st_cluster_f4(mapa(slot, jj), wm, wsum, wx, xt);
           } else {
-            tail->slots[0][0] = make_float4(wm, wsum, wx, xt);
+            tail->slots[xpar][0] = make_float4(wm, wsum, wx, xt);
           }
         }
+        __syncwarp();
       }
     }
+    // Everybody signals that its part of the exchange is done (the cluster barrier is the hardware's; an
+    // mbarrier-based exchange with remote arrivals measured 12 % slower), then fills the time until the others
+    // have signalled too with whatever part of the next row is already in shared memory (at most rp.window chunks).
+    if (CLUSTER > 1) cluster_arrive();  // every thread of the cluster, ignored rows included
+    st.m2 = -CUDART_INF_F;
+    st.s[0] = st.s[1] = st.sx[0] = st.sx[1] = make_float2(0.f, 0.f);
+    a_done = 0;
+    if (k + 1 < nrows_local) {
+      uint32_t nj = cj + cpg, nph = cphase;
+      if (nj >= nbg) {
+        nj -= nbg;
+        nph ^= 1;
+      }
+      a_done = fold_chunks(st, nj, nph, 0, min(cpg, rp.window), is_ignored(t_next), false);
+    }
     if (CLUSTER > 1) {
-      cluster_arrive();
       cluster_wait();
     } else {
-      named_barrier(1, kConsumers);
+      named_barrier(2, kConsumers);  // warp 0 wrote the slot before it started on the next row
     }
+    float lse = 0.f, scale = 0.f, xt_all = 0.f;
     if (!p.grad) {
       // forward only: every read of this row's chunks (x[target] included) lies before the barrier above;
       // hand the buffers back, one arrival per warp and chunk
@@ -564,7 +673,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       float gm = -CUDART_INF_F, gs = 0.f, gx = 0.f;
 #pragma unroll
       for (int jj = 0; jj < CLUSTER; ++jj) {
-        const float4 v = tail->slots[CLUSTER > 1 ? (k & 1) : 0][jj];
+        const float4 v = tail->slots[xpar][jj];
         merge2(gm, gs, v.x, v.y);
         gx += v.z;
         xt_all += v.w;
@@ -576,6 +685,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       }
       scale = base_scale;
       if (p.grad && p.row_grad_out) scale *= p.row_grad_out[row];
+      if (lse != lse) scale = lse;  // a NaN row: every gradient element is NaN, the polynomial pairs included
     } else if (MODE == 0 && tid == 0 && cta_rank == 0) {
       p.row_loss[row] = 0.f;
       if (p.row_lse) p.row_lse[row] = 0.f;
@@ -616,6 +726,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         } else {
           for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = make_uint4(0u, 0u, 0u, 0u);
         }
+        // One fence and hand-over per chunk: pairing two chunks per fence and hoisting the target's position out of
+        // this loop were both measured slower (the stores start later; more values live across the sweep).
         fence_proxy_async();  // this thread's writes become visible to the bulk-copy engine
         __syncwarp();
         if (lane == 0) mbar_arrive(ready0 + 8 * j);
@@ -623,6 +735,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       }
     }
 
+    if (!ignored) xpar ^= 1;
     // advance the ring position to the next row
     cj += cpg;
     while (cj >= nbg) {
@@ -655,6 +768,7 @@ bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, Resid
   rp->chunk_units = kChunkUnits;
   rp->slice_units = slice_units;
   rp->row_units = row_units;
+  rp->window = 0;  // set by the launcher, which knows the element type
   return true;
 }
 
@@ -707,7 +821,13 @@ int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
 }
 
 template <typename T, int CLUSTER>
-int launch_resident(const ResidentParams& rp, cudaStream_t st) {
+int launch_resident(ResidentParams rp, cudaStream_t st) {
+  // Chunks of the next row a group folds while a row's statistics are exchanged.  Measured on B200: with
+  // 4-byte elements the sweeps are short next to the memory time and filling the exchange with the next
+  // row's statistics gains 8 %; with 2-byte elements the sweeps set the pace and the same reordering only
+  // delays the gradient sweep that frees the buffers the next loads need (-5 % per chunk), so it stays off.
+  const uint32_t spare = (rp.nbuf - rp.nch) / kGroups;
+  rp.window = g_ce_window_chunks >= 0 ? static_cast<uint32_t>(g_ce_window_chunks) : (sizeof(T) == 4 && spare > 1 ? spare - 1 : 0);
   if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
   const bool sumx = rp.p.label_smoothing != 0.f;
   return sumx ? launch_resident_cfg<T, CLUSTER, true, 0>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0>(rp, st);
@@ -787,6 +907,7 @@ int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int6
 int ce_dispatch(const CEParams& p, cudaStream_t st) {
   int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
   if (g_ce_force_variant == 0) variant = 0;
+  if (g_ce_force_variant > 0 && variant != 0) variant = g_ce_force_variant;  // falls back to generic if it does not fit
   if (variant != 0) {
     const int rc = ce_launch_resident(p, st, variant);
     if (rc == SB_OK) return rc;
@@ -796,10 +917,15 @@ int ce_dispatch(const CEParams& p, cudaStream_t st) {
 
 }  // namespace sb
 
-// Tuning hook for benchmarks: key 1 = force the kernel family (-1 automatic, 0 generic).
+// Tuning hook for benchmarks: key 1 = force the kernel family (-1 automatic, 0 generic, 1/2/4 resident cluster size); key 2 = chunks of the
+// next row folded during the statistics exchange (-1 automatic).
 extern "C" int sb_set_tuning(int32_t key, int32_t value) {
-  if (key == 1 && (value == -1 || value == 0)) {
+  if (key == 1 && (value == -1 || value == 0 || value == 1 || value == 2 || value == 4)) {
     sb::g_ce_force_variant = value;
+    return SB_OK;
+  }
+  if (key == 2 && value >= -1 && value <= 64) {
+    sb::g_ce_window_chunks = value;
     return SB_OK;
   }
   return SB_ERR_INVALID_ARGUMENT;
