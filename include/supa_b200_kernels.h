@@ -205,6 +205,34 @@ SB_API int sb_nll_loss_forward(const sb_nll_args* args, void* output, void* tota
 SB_API int sb_nll_loss_backward(const sb_nll_args* args, const void* grad_output, const void* total_weight,
                                 void* grad_input, sb_stream_t stream);
 
+/* nll_loss over [outer, classes, inner] log-probabilities with [outer, inner] targets: the 4-D (N, C, H, W)
+ * form of nll_loss2d_forward / nll_loss2d_backward (inner = H * W), which the reference takes from its
+ * external native-op library (exercised by test/test_loss.py:24,150-233 with the shape (2, 19, 512, 1024));
+ * inner = 1 is the plain [rows, classes] form.  Forward mean / sum reduce in two fixed-order stages through
+ * `scratch` (sb_nll_loss_nd_scratch_bytes bytes, 16-byte aligned, caller-owned); backward writes every
+ * element of grad_input exactly once (no separate zero-fill). */
+typedef struct sb_nll_nd_args {
+  const void* log_probs;  /* [outer, classes, inner] contiguous */
+  int32_t dtype;          /* SB_F32, SB_BF16, SB_F16, SB_F64 */
+  int32_t target_dtype;   /* SB_I64 or SB_U8 */
+  const void* target;     /* [outer, inner] */
+  const void* weight;     /* [classes] in `dtype`, or NULL */
+  int64_t outer;
+  int64_t classes;
+  int64_t inner;
+  int64_t ignore_index;
+  int32_t reduction;
+  int32_t* status;
+  void* scratch;          /* forward with mean / sum only */
+  size_t scratch_bytes;
+} sb_nll_nd_args;
+SB_API size_t sb_nll_loss_nd_scratch_bytes(const sb_nll_nd_args* args);
+/* output: [outer, inner] for none, one element otherwise; total_weight: one element.  Both in args->dtype. */
+SB_API int sb_nll_loss_nd_forward(const sb_nll_nd_args* args, void* output, void* total_weight, sb_stream_t stream);
+/* grad_output: [outer, inner] for none, one element otherwise. */
+SB_API int sb_nll_loss_nd_backward(const sb_nll_nd_args* args, const void* grad_output, const void* total_weight,
+                                   void* grad_input, sb_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * TensorIterator-style elementwise engine.
  *

@@ -152,6 +152,45 @@ ORACLE_API void oracle_nll_loss_backward(const double* grad_out, const int64_t* 
   }
 }
 
+/* nll_loss2d_forward / nll_loss2d_backward: the same rule per sample (n, i) of log-probabilities laid out
+ * [outer, classes, inner] with targets [outer, inner] (inner = H * W for the 4-D form exercised by the
+ * reference's test/test_loss.py:24,150-233; the kernels themselves live in its external native-op library). */
+ORACLE_API void oracle_nll_loss_nd(const float* logp, const int64_t* target, const float* weight, int64_t outer,
+                                   int64_t classes, int64_t inner, int64_t ignore_index, int reduction, double* out,
+                                   double* total_weight) {
+  double tot = 0.0, tw = 0.0;
+  for (int64_t n = 0; n < outer; ++n)
+    for (int64_t i = 0; i < inner; ++i) {
+      const int64_t t = target[n * inner + i];
+      double v = 0.0;
+      if (t != ignore_index && t >= 0 && t < classes) {
+        const double w = weight ? (double)weight[t] : 1.0;
+        v = -w * (double)logp[(n * classes + t) * inner + i];
+        tw += w;
+      }
+      if (reduction == RED_NONE) out[n * inner + i] = v;
+      else tot += v;
+    }
+  if (reduction == RED_MEAN) out[0] = tot / tw;
+  else if (reduction == RED_SUM) out[0] = tot;
+  *total_weight = tw;
+}
+
+ORACLE_API void oracle_nll_loss_nd_backward(const double* grad_out, const int64_t* target, const float* weight, int64_t outer,
+                                            int64_t classes, int64_t inner, int64_t ignore_index, int reduction,
+                                            double total_weight, double* grad_in) {
+  for (int64_t i = 0; i < outer * classes * inner; ++i) grad_in[i] = 0.0;
+  for (int64_t n = 0; n < outer; ++n)
+    for (int64_t i = 0; i < inner; ++i) {
+      const int64_t t = target[n * inner + i];
+      if (t == ignore_index || t < 0 || t >= classes) continue;
+      const double w = weight ? (double)weight[t] : 1.0;
+      double g = reduction == RED_NONE ? grad_out[n * inner + i] : grad_out[0];
+      if (reduction == RED_MEAN) g /= total_weight;
+      grad_in[(n * classes + t) * inner + i] = -w * g;
+    }
+}
+
 /* Row reductions with a wide accumulator (sum_functor / MeanOps / MaxNanFunctor of
  * torch_supa/csrc/aten/ops/kernels/reduce/ReduceSumKernel.cu:80-100, ReduceMomentKernel.cu:16-35).
  * op: 0 sum, 1 mean, 2 amax (NaN propagates), 3 amin. */

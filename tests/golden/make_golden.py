@@ -128,6 +128,24 @@ def main():
     d["bin/mul_t"] = (f32.t() * f32).numpy()
     big = torch.tensor([2**31 - 1, -2**31, 7], dtype=torch.int32)
     d["bin/int_wrap"] = (big + torch.tensor([1, -1, 3], dtype=torch.int32)).numpy()
+    # nll_loss2d: (N, C, H, W) log-probabilities and (N, H, W) targets (drawn last: earlier cases keep their values)
+    for name, red, use_w in (("nll2d_mean", "mean", False), ("nll2d_sum_w", "sum", True), ("nll2d_none_w", "none", True),
+                             ("nll2d_mean_w", "mean", True)):
+        logp = F.log_softmax(torch.randn(2, 5, 3, 7, generator=g), 1).requires_grad_(True)
+        t = torch.randint(0, 5, (2, 3, 7), generator=g)
+        t[0, 1, 2] = -100
+        t[1, 2, 6] = -100
+        w = torch.rand(5, generator=g) + 0.5 if use_w else None
+        out = F.nll_loss(logp, t, weight=w, reduction=red)
+        go = torch.randn(out.shape, generator=g)
+        (gi,) = torch.autograd.grad(out, logp, go)
+        d[name + "/logp"] = logp.detach().numpy()
+        d[name + "/target"] = t.numpy()
+        if use_w:
+            d[name + "/weight"] = w.numpy()
+        d[name + "/out"] = out.detach().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad_in"] = gi.numpy()
     np.savez_compressed(OUT, **d)
     print("wrote", OUT, OUT.stat().st_size, "bytes,", len(d), "arrays")
 

@@ -105,3 +105,65 @@ def test_nll_uint8_targets(cuda_device):
     out, _ = F2.nll_loss_forward(logp.to(cuda_device), t.to(cuda_device), None, -100, "sum")
     eout, _ = oracle.c_nll_loss(logp.numpy(), t.numpy().astype(np.int64), None, -100, "sum")
     assert_close(np.atleast_1d(out.cpu().numpy()), eout, 2e-6, 2e-6, "uint8 targets")
+
+
+# ---- nll_loss over (N, C, d1, ...) --------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["nll2d_mean", "nll2d_sum_w", "nll2d_none_w", "nll2d_mean_w"])
+def test_nll2d_fixtures(golden, cuda_device, name):
+    from torch_supa_b200 import functional as F2
+
+    red = name.split("_")[1]
+    w = torch.from_numpy(golden[name + "/weight"]).to(cuda_device) if name.endswith("_w") else None
+    logp = torch.from_numpy(golden[name + "/logp"]).to(cuda_device)
+    t = torch.from_numpy(golden[name + "/target"]).to(cuda_device)
+    out, tw = F2.nll_loss_nd_forward(logp, t, w, -100, red)
+    assert_close(np.atleast_1d(out.cpu().numpy()), np.atleast_1d(golden[name + "/out"]), 2e-6, 2e-6, name)
+    go = torch.from_numpy(np.atleast_1d(golden[name + "/grad_out"])).to(cuda_device)
+    gi = F2.nll_loss_nd_backward(go, logp, t, w, -100, red, tw)
+    assert_close(gi.cpu().numpy(), golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
+
+
+@pytest.mark.parametrize("shape", [(2, 19, 64, 48), (3, 5, 7, 9), (1, 3, 1, 1), (4, 21, 33, 40), (5, 7, 1), (2, 1000, 8, 16)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+def test_nll_nd_against_oracle(cuda_device, shape, reduction, dtype):
+    """Vector (inner a multiple of 16 bytes) and scalar store paths, class weights, ignored samples; the gradient has at
+    most one non-zero per sample and is bit-exact (a product of two exactly representable factors, rounded once)."""
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(sum(shape))
+    classes = shape[1]
+    logp = F.log_softmax(torch.randn(*shape, generator=g), 1).to(dtype)
+    tshape = (shape[0],) + tuple(shape[2:])
+    t = torch.randint(0, classes, tshape, generator=g)
+    t.view(-1)[::5] = -100
+    w = (torch.rand(classes, generator=g) + 0.5).to(dtype)
+    for weight in (None, w):
+        wd = None if weight is None else weight.to(cuda_device)
+        wn = None if weight is None else weight.float().numpy()
+        out, tw = F2.nll_loss_nd_forward(logp.to(cuda_device), t.to(cuda_device), wd, -100, reduction)
+        eout, etw = oracle.c_nll_loss_nd(logp.float().numpy(), t.numpy(), wn, -100, reduction)
+        rtol = {torch.float32: 2e-6, torch.float64: 1e-6, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
+        assert_close(np.atleast_1d(out.double().cpu().numpy()), np.atleast_1d(eout), rtol, rtol, "forward")
+        if reduction != "none":
+            assert abs(float(tw) - etw) <= rtol * max(etw, 1.0)
+        go = torch.randn(tshape if reduction == "none" else (1,), generator=g).to(dtype)
+        gi = F2.nll_loss_nd_backward(go.to(cuda_device), logp.to(cuda_device), t.to(cuda_device), wd, -100, reduction, tw)
+        egi = oracle.c_nll_loss_nd_backward(go.double().numpy(), t.numpy(), shape, wn, -100, reduction, float(tw))
+        assert_close(gi.double().cpu().numpy(), egi, rtol, 0, "backward")
+        assert int((gi != 0).sum()) <= t.numel()
+
+
+def test_nll_nd_all_ignored_and_uint8(cuda_device):
+    from torch_supa_b200 import functional as F2
+
+    logp = F.log_softmax(torch.randn(2, 6, 4, 8), 1)
+    t = torch.full((2, 4, 8), -100)
+    out, tw = F2.nll_loss_nd_forward(logp.to(cuda_device), t.to(cuda_device), None, -100, "mean")
+    assert torch.isnan(out.cpu()) and float(tw) == 0.0, "mean over no samples is NaN, as on the CPU"
+    out, _ = F2.nll_loss_nd_forward(logp.to(cuda_device), t.to(cuda_device), None, -100, "sum")
+    assert float(out) == 0.0
+    t8 = torch.randint(0, 6, (2, 4, 8), dtype=torch.uint8)
+    out, _ = F2.nll_loss_nd_forward(logp.to(cuda_device), t8.to(cuda_device), None, -100, "sum")
+    eout, _ = oracle.c_nll_loss_nd(logp.numpy(), t8.numpy().astype(np.int64), None, -100, "sum")
+    assert_close(np.atleast_1d(out.cpu().numpy()), eout, 2e-6, 2e-6, "uint8 targets")

@@ -342,6 +342,47 @@ def test_nll_loss_forward_backward_weight(supa, shape, reduction, dtype):
         assert torch.equal(t.cpu(), t_before), "the target tensor is not modified"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 19, 64, 128), (3, 5, 7, 9), (2, 19, 512, 1024)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_nll_loss2d_and_spatial_cross_entropy(supa, shape, reduction, dtype):
+    """(N, C, H, W) inputs: F.nll_loss dispatches to nll_loss2d_forward / backward, F.cross_entropy to log_softmax over
+    dim 1 followed by them (the 4-D shape (2, 19, 512, 1024) is the reference's segmentation case)."""
+    from torch_supa_b200.testing import assert_allclose
+
+    if shape[2] >= 512 and (dtype != torch.float32 or reduction == "sum"):
+        pytest.skip("the large shape runs once per reduction family")
+    g = torch.Generator().manual_seed(shape[1])
+    x_cpu = torch.randn(*shape, generator=g).to(dtype)
+    t_cpu = torch.randint(0, shape[1], (shape[0],) + shape[2:], generator=g)
+    t_cpu.view(-1)[::11] = -100
+    w_cpu = (torch.rand(shape[1], generator=g) + 0.5).to(dtype)
+    rtol = {torch.float32: 4e-6, torch.bfloat16: 1.6e-2, torch.float16: 2e-3}[dtype]
+    for weight in (None, w_cpu):
+        # nll_loss on log-probabilities
+        logp_cpu = F.log_softmax(x_cpu.float(), 1).to(dtype)
+        x = logp_cpu.to(supa).requires_grad_(True)
+        out = F.nll_loss(x, t_cpu.to(supa), weight=None if weight is None else weight.to(supa), reduction=reduction)
+        xr = logp_cpu.float().requires_grad_(True)
+        ref = F.nll_loss(xr, t_cpu, weight=None if weight is None else weight.float(), reduction=reduction)
+        assert_allclose(ref.detach().to(dtype), out.detach(), rtol, rtol)
+        go_cpu = torch.randn(ref.shape, generator=g).to(dtype)
+        out.backward(go_cpu.to(supa))
+        ref.backward(go_cpu.float())
+        assert_allclose(xr.grad.to(dtype), x.grad, rtol * 2, 1e-6 if dtype == torch.float32 else 1e-4)
+    # cross entropy on logits
+    x = x_cpu.to(supa).requires_grad_(True)
+    loss = F.cross_entropy(x, t_cpu.to(supa), reduction=reduction)
+    xr = x_cpu.float().requires_grad_(True)
+    ref = F.cross_entropy(xr, t_cpu, reduction=reduction)
+    assert_allclose(ref.detach().to(dtype), loss.detach(), rtol * 4, rtol * 4)
+    go_cpu = torch.randn(ref.shape, generator=g).to(dtype)
+    loss.backward(go_cpu.to(supa))
+    ref.backward(go_cpu.float())
+    scale = 1.0 if reduction != "mean" else float((t_cpu != -100).sum())
+    assert_allclose(xr.grad.to(dtype) * scale, x.grad * scale, rtol * 4, 1e-5 if dtype == torch.float32 else 2e-3)
+
+
 # ---- cross entropy -------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("shape", [(1, 1000), (16, 1000), (1, 6), (512, 1024), (512, 1027), (64, 32000), (160, 128256)])
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])

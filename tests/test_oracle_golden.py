@@ -65,6 +65,17 @@ def test_nll_loss(golden, name):
     assert_close(gi, golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
 
 
+@pytest.mark.parametrize("name", ["nll2d_mean", "nll2d_sum_w", "nll2d_none_w", "nll2d_mean_w"])
+def test_nll_loss2d(golden, name):
+    red = name.split("_")[1]
+    w = golden[name + "/weight"] if name.endswith("_w") else None
+    logp = golden[name + "/logp"]
+    out, tw = oracle.c_nll_loss_nd(logp, golden[name + "/target"], w, -100, red)
+    assert_close(out, np.atleast_1d(golden[name + "/out"]), 2e-6, 2e-6, name)
+    gi = oracle.c_nll_loss_nd_backward(golden[name + "/grad_out"], golden[name + "/target"], logp.shape, w, -100, red, tw)
+    assert_close(gi, golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
+
+
 def test_row_reductions(golden):
     x = golden["red/x"]
     assert_close(oracle.c_reduce_rows(x, "sum"), golden["red/sum"], 1e-5, 1e-5, "sum")

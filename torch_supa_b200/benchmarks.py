@@ -135,6 +135,20 @@ def run_extras(device, peak_gbs, quick=False, profile=False):
                       peak_gbs))
     del sm
     torch.supa.empty_cache()
+    # ---- beyond the headline configurations: nll_loss2d on a segmentation-shaped input ----
+    n4, c4, h4, w4 = 8, 19, 1024, 2048
+    logp = device_randn((n4, c4, h4, w4), torch.float32, device, 13)
+    t4 = device_randn((n4, h4, w4), torch.int64, device, 14, low=0, high=c4 - 1)
+    samples = n4 * h4 * w4
+    out.append(_entry("nll_loss2d forward (mean) fp32 [8,19,1024,2048]: one gathered element + target per sample",
+                      samples * (4 + 8), time_op(lambda: F.nll_loss(logp, t4), iters=it), peak_gbs))
+    go = device_randn((), torch.float32, device, 15)
+    tw = torch.ones((), dtype=torch.float32, device=device)
+    out.append(_entry("nll_loss2d backward (mean) fp32 [8,19,1024,2048]: gradient written once + targets",
+                      samples * c4 * 4 + samples * 8,
+                      time_op(lambda: torch.ops.aten.nll_loss2d_backward(go, logp, t4, None, 1, -100, tw), iters=it), peak_gbs))
+    del logp, t4
+    torch.supa.empty_cache()
     if profile:
         time_op = _orig
     return out

@@ -46,6 +46,15 @@ class NLLArgs(C.Structure):
     ]
 
 
+class NLLNdArgs(C.Structure):
+    _fields_ = [
+        ("log_probs", C.c_void_p), ("dtype", C.c_int32), ("target_dtype", C.c_int32), ("target", C.c_void_p),
+        ("weight", C.c_void_p), ("outer", C.c_int64), ("classes", C.c_int64), ("inner", C.c_int64),
+        ("ignore_index", C.c_int64), ("reduction", C.c_int32), ("status", C.c_void_p), ("scratch", C.c_void_p),
+        ("scratch_bytes", C.c_size_t),
+    ]
+
+
 class EWDesc(C.Structure):
     _fields_ = [
         ("op", C.c_int32), ("ndim", C.c_int32), ("noperands", C.c_int32), ("common_dtype", C.c_int32),
@@ -87,6 +96,7 @@ def lib() -> C.CDLL:
         _lib.sb_status_string.argtypes = [C.c_int]
         _lib.sb_dtype_size.restype = C.c_size_t
         _lib.sb_reduce_scratch_bytes.restype = C.c_size_t
+        _lib.sb_nll_loss_nd_scratch_bytes.restype = C.c_size_t
     return _lib
 
 
@@ -175,6 +185,19 @@ def nll_loss_forward(args: NLLArgs, output, total_weight, stream=0):
 def nll_loss_backward(args: NLLArgs, grad_output, total_weight, grad_input, stream=0):
     check("sb_nll_loss_backward", lib().sb_nll_loss_backward(C.byref(args), _p(grad_output), _p(total_weight),
                                                              _p(grad_input), C.c_void_p(stream)))
+
+
+def nll_loss_nd_scratch_bytes(args: NLLNdArgs) -> int:
+    return int(lib().sb_nll_loss_nd_scratch_bytes(C.byref(args)))
+
+
+def nll_loss_nd_forward(args: NLLNdArgs, output, total_weight, stream=0):
+    check("sb_nll_loss_nd_forward", lib().sb_nll_loss_nd_forward(C.byref(args), _p(output), _p(total_weight), C.c_void_p(stream)))
+
+
+def nll_loss_nd_backward(args: NLLNdArgs, grad_output, total_weight, grad_input, stream=0):
+    check("sb_nll_loss_nd_backward", lib().sb_nll_loss_nd_backward(C.byref(args), _p(grad_output), _p(total_weight),
+                                                                   _p(grad_input), C.c_void_p(stream)))
 
 
 def elementwise(desc: EWDesc, stream=0):

@@ -238,6 +238,117 @@ at::Tensor& nll_loss_backward_out(const at::Tensor& grad_output, const at::Tenso
   return grad_input;
 }
 
+// ---- nll_loss2d ------------------------------------------------------------------------------------------------
+// (N, C, H, W) log-probabilities, (N, H, W) targets.  Not a structured op upstream: shapes are checked and outputs
+// resized here, with the messages of libtorch's CPU kernel.
+void check_nll2d_inputs(const at::Tensor& self, const at::Tensor& target, const at::Tensor& weight) {
+  TORCH_CHECK(target.dim() == 3, "only batches of spatial targets supported (3D tensors) but got targets of dimension: ", target.dim());
+  TORCH_CHECK(self.dim() == 4, "only batches of spatial inputs supported (4D tensors), but got input of dimension: ", self.dim());
+  TORCH_CHECK(!weight.defined() || weight.numel() == self.size(1), "weight tensor should be defined either for all or no classes");
+  TORCH_CHECK(self.size(0) == target.size(0) && self.size(2) == target.size(1) && self.size(3) == target.size(2),
+              "size mismatch (got input: ", self.sizes(), " , target: ", target.sizes());
+}
+
+sb_nll_nd_args nll2d_args(const at::Tensor& input, const at::Tensor& tgt, const at::Tensor& weight, int64_t reduction,
+                          int64_t ignore_index) {
+  sb_nll_nd_args a{};
+  a.log_probs = input.const_data_ptr();
+  a.dtype = dtype_code(input.scalar_type());
+  TORCH_CHECK(tgt.scalar_type() == at::kLong || tgt.scalar_type() == at::kByte,
+              "expected scalar type Long or Byte for target but found ", tgt.scalar_type());
+  a.target_dtype = dtype_code(tgt.scalar_type());
+  a.target = tgt.const_data_ptr();
+  a.weight = weight.defined() ? weight.const_data_ptr() : nullptr;
+  a.outer = input.size(0);
+  a.classes = input.size(1);
+  a.inner = input.size(2) * input.size(3);
+  a.ignore_index = ignore_index;
+  a.reduction = reduction_code(reduction);
+  a.status = status_word(input.device().index());
+  return a;
+}
+
+std::tuple<at::Tensor&, at::Tensor&> nll_loss2d_forward_out(const at::Tensor& self, const at::Tensor& target,
+                                                            const c10::optional<at::Tensor>& weight_opt, int64_t reduction,
+                                                            int64_t ignore_index, at::Tensor& output, at::Tensor& total_weight) {
+  const c10::DeviceGuard guard(self.device());
+  at::Tensor weight;
+  if (weight_opt.has_value() && weight_opt->defined()) weight = weight_opt->contiguous().to(self.scalar_type());
+  check_nll2d_inputs(self, target, weight);
+  const int red = reduction_code(reduction);
+  total_weight.resize_({});
+  if (red == SB_REDUCTION_NONE) output.resize_({self.size(0), self.size(2), self.size(3)});
+  else output.resize_({});
+  TORCH_CHECK(output.scalar_type() == self.scalar_type() && total_weight.scalar_type() == self.scalar_type(),
+              "nll_loss2d: outputs must have the input's dtype");
+  const at::Tensor input = self.contiguous();
+  const at::Tensor tgt = target.contiguous();
+  at::Tensor result = output.is_contiguous() ? output : at::empty(output.sizes(), output.options());
+  if (red == SB_REDUCTION_NONE) total_weight.zero_();  // not written by the kernel in this mode
+  sb_nll_nd_args a = nll2d_args(input, tgt, weight, reduction, ignore_index);
+  at::Tensor scratch;
+  const size_t need = sb_nll_loss_nd_scratch_bytes(&a);
+  if (need) {
+    scratch = at::empty({static_cast<int64_t>(need)}, input.options().dtype(at::kByte));
+    a.scratch = scratch.data_ptr();
+    a.scratch_bytes = need;
+  }
+  check_kernel(sb_nll_loss_nd_forward(&a, result.data_ptr(), total_weight.data_ptr(), stream_of(input)), "supa nll_loss2d_forward");
+  if (!result.is_same(output)) output.copy_(result);
+  return std::forward_as_tuple(output, total_weight);
+}
+
+std::tuple<at::Tensor, at::Tensor> nll_loss2d_forward(const at::Tensor& self, const at::Tensor& target,
+                                                      const c10::optional<at::Tensor>& weight, int64_t reduction,
+                                                      int64_t ignore_index) {
+  const c10::DeviceGuard guard(self.device());
+  at::Tensor output = at::empty({0}, self.options());
+  at::Tensor total_weight = at::empty({0}, self.options());
+  nll_loss2d_forward_out(self, target, weight, reduction, ignore_index, output, total_weight);
+  return std::make_tuple(std::move(output), std::move(total_weight));
+}
+
+at::Tensor& nll_loss2d_backward_out(const at::Tensor& grad_output, const at::Tensor& self, const at::Tensor& target,
+                                    const c10::optional<at::Tensor>& weight_opt, int64_t reduction, int64_t ignore_index,
+                                    const at::Tensor& total_weight, at::Tensor& grad_input) {
+  const c10::DeviceGuard guard(self.device());
+  at::Tensor weight;
+  if (weight_opt.has_value() && weight_opt->defined()) weight = weight_opt->contiguous().to(self.scalar_type());
+  check_nll2d_inputs(self, target, weight);
+  grad_input.resize_(self.sizes());
+  TORCH_CHECK(total_weight.numel() == 1, "expected total_weight to be a single element tensor, got: ", total_weight.sizes(), " (",
+              total_weight.numel(), " elements)");
+  if (self.numel() == 0) return grad_input;
+  const int red = reduction_code(reduction);
+  if (red == SB_REDUCTION_NONE) {
+    TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(0) == self.size(0) && grad_output.size(1) == self.size(2) &&
+                    grad_output.size(2) == self.size(3),
+                "grad_output must have the shape of target for reduction none, got ", grad_output.sizes());
+  } else {
+    TORCH_CHECK(grad_output.numel() == 1, "Expected a single element grad_output tensor, but got: ", grad_output.sizes());
+  }
+  const at::Tensor input = self.contiguous();
+  const at::Tensor tgt = target.contiguous();
+  at::Tensor go = grad_output.contiguous();
+  if (go.scalar_type() != input.scalar_type()) go = go.to(input.scalar_type());
+  at::Tensor tw = total_weight.scalar_type() == input.scalar_type() ? total_weight : total_weight.to(input.scalar_type());
+  at::Tensor result = grad_input.is_contiguous() ? grad_input : at::empty(grad_input.sizes(), grad_input.options());
+  const sb_nll_nd_args a = nll2d_args(input, tgt, weight, reduction, ignore_index);
+  check_kernel(sb_nll_loss_nd_backward(&a, go.const_data_ptr(), tw.const_data_ptr(), result.data_ptr(), stream_of(input)),
+               "supa nll_loss2d_backward");
+  if (!result.is_same(grad_input)) grad_input.copy_(result);
+  return grad_input;
+}
+
+at::Tensor nll_loss2d_backward(const at::Tensor& grad_output, const at::Tensor& self, const at::Tensor& target,
+                               const c10::optional<at::Tensor>& weight, int64_t reduction, int64_t ignore_index,
+                               const at::Tensor& total_weight) {
+  const c10::DeviceGuard guard(self.device());
+  at::Tensor grad_input = at::empty({0}, self.options());
+  nll_loss2d_backward_out(grad_output, self, target, weight, reduction, ignore_index, total_weight, grad_input);
+  return grad_input;
+}
+
 // ---- cross entropy ---------------------------------------------------------------------------------------------
 // Which calls take the fused kernel.  Wider than the reference's predicate (CrossEntropyLoss.cpp:23-33: 2-D
 // fp32, no smoothing): 16-bit logits, label smoothing and 1-D logits are fused too; class weights,
@@ -433,6 +544,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("nll_loss_forward.output", TORCH_FN(supa::nll_loss_forward_out));
   m.impl("nll_loss_backward", TORCH_FN(supa::nll_loss_backward));
   m.impl("nll_loss_backward.grad_input", TORCH_FN(supa::nll_loss_backward_out));
+  m.impl("nll_loss2d_forward", TORCH_FN(supa::nll_loss2d_forward));
+  m.impl("nll_loss2d_forward.output", TORCH_FN(supa::nll_loss2d_forward_out));
+  m.impl("nll_loss2d_backward", TORCH_FN(supa::nll_loss2d_backward));
+  m.impl("nll_loss2d_backward.grad_input", TORCH_FN(supa::nll_loss2d_backward_out));
   m.impl("cross_entropy_loss", TORCH_FN(supa::cross_entropy_loss));
 }
 

@@ -1,0 +1,264 @@
+// nll_loss for log-probabilities laid out [outer, classes, inner] with targets [outer, inner]: the 4-D
+// (N, C, H, W) form behind nll_loss2d (inner = H * W) and, with inner = 1, the plain [rows, classes] form.
+//
+// forward:  sample s = (n, i): out_s = -w[t_s] * x[n, t_s, i] (0 when t_s == ignore_index).  `none` stores
+//           out_s; `sum` / `mean` reduce in two fixed-order stages (per-CTA partials in caller scratch, then
+//           one CTA), so the result is bit-reproducible; total_weight = sum of w[t_s] over samples that count.
+// backward: grad_input[n, c, i] = (c == t_s) ? -w[c] * g : 0, written plane by plane so that every store is
+//           coalesced along i and the tensor is written exactly once (no zero-fill pass); g = grad_output_s
+//           for `none`, grad_output for `sum`, grad_output / total_weight for `mean`.
+// An index outside [0, classes) that is not ignore_index sets SB_STATUS_TARGET_OUT_OF_RANGE and the sample is
+// skipped; nothing traps.
+#include "io.cuh"
+
+namespace sb {
+
+namespace {
+
+constexpr int kMaxPartials = 1024;
+
+struct NdParams {
+  const void* x;
+  const void* target;
+  const void* weight;
+  int64_t outer, classes, inner, samples, ignore_index;
+  int reduction;
+  int target_dtype;
+  int32_t* status;
+};
+
+__device__ __forceinline__ int64_t nd_target(const NdParams& p, int64_t s) {
+  return p.target_dtype == SB_U8 ? static_cast<int64_t>(static_cast<const uint8_t*>(p.target)[s])
+                                 : static_cast<const int64_t*>(p.target)[s];
+}
+
+__device__ __forceinline__ bool nd_counts(const NdParams& p, int64_t s, int64_t& t) {
+  t = nd_target(p, s);
+  if (t == p.ignore_index) return false;
+  if (t < 0 || t >= p.classes) {
+    if (p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+    return false;
+  }
+  return true;
+}
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) nd_fwd_none_kernel(NdParams p, T* __restrict__ out) {
+  const T* x = static_cast<const T*>(p.x);
+  const T* w = static_cast<const T*>(p.weight);
+  for (int64_t s = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; s < p.samples; s += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t t;
+    A v = 0;
+    if (nd_counts(p, s, t)) {
+      const int64_t n = s / p.inner, i = s - n * p.inner;
+      const A wt = w ? convert<A, T>(w[t]) : A(1);
+      v = -wt * convert<A, T>(x[(n * p.classes + t) * p.inner + i]);
+    }
+    out[s] = convert<T, A>(v);
+  }
+}
+
+// Stage 1: CTA b sums the samples b * 256 + tid, + gridDim * 256, ... and writes {sum, weight} to partial[b].
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) nd_fwd_partial_kernel(NdParams p, double2* __restrict__ partial) {
+  __shared__ double s_v[8];
+  __shared__ double s_w[8];
+  const T* x = static_cast<const T*>(p.x);
+  const T* w = static_cast<const T*>(p.weight);
+  double av = 0.0, aw = 0.0;
+  for (int64_t s = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; s < p.samples; s += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t t;
+    if (nd_counts(p, s, t)) {
+      const int64_t n = s / p.inner, i = s - n * p.inner;
+      const double wt = w ? static_cast<double>(convert<A, T>(w[t])) : 1.0;
+      av -= wt * static_cast<double>(convert<A, T>(x[(n * p.classes + t) * p.inner + i]));
+      aw += wt;
+    }
+  }
+  av = warp_sum(av);
+  aw = warp_sum(aw);
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = av;
+    s_w[threadIdx.x >> 5] = aw;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double v = 0.0, ww = 0.0;
+    for (int k = 0; k < 8; ++k) {
+      v += s_v[k];
+      ww += s_w[k];
+    }
+    partial[blockIdx.x] = make_double2(v, ww);
+  }
+}
+
+// Stage 2: one CTA adds the partials in index order.
+template <typename T, typename A>
+__global__ void __launch_bounds__(32) nd_fwd_final_kernel(const double2* __restrict__ partial, int count, int reduction,
+                                                          T* __restrict__ out, T* __restrict__ total_weight) {
+  if (threadIdx.x != 0) return;
+  double v = 0.0, w = 0.0;
+  for (int k = 0; k < count; ++k) {
+    v += partial[k].x;
+    w += partial[k].y;
+  }
+  if (reduction == SB_REDUCTION_MEAN) v = v / w;  // 0/0 = NaN when every sample is ignored
+  *out = convert<T, A>(static_cast<A>(v));
+  *total_weight = convert<T, A>(static_cast<A>(w));
+}
+
+// Backward: a thread owns VEC consecutive samples of one outer row and writes their value in every class plane.
+template <typename T, typename A, int VEC>
+__global__ void __launch_bounds__(256) nd_bwd_kernel(NdParams p, const T* __restrict__ grad_output, const T* __restrict__ total_weight,
+                                                     T* __restrict__ grad_input) {
+  const T* w = static_cast<const T*>(p.weight);
+  const int64_t per_row = p.inner / VEC;  // VEC divides inner (the launcher picks VEC accordingly)
+  const int64_t items = p.outer * per_row;
+  A gscale = A(1);
+  if (p.reduction != SB_REDUCTION_NONE) {
+    gscale = convert<A, T>(grad_output[0]);
+    if (p.reduction == SB_REDUCTION_MEAN) gscale = gscale / convert<A, T>(*total_weight);
+  }
+  for (int64_t it = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; it < items; it += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t n = it / per_row, i0 = (it - n * per_row) * VEC;
+    const int64_t s0 = n * p.inner + i0;
+    int64_t t[VEC];
+    A val[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      val[k] = A(0);
+      if (!nd_counts(p, s0 + k, t[k])) {
+        t[k] = -1;
+      } else {
+        const A wt = w ? convert<A, T>(w[t[k]]) : A(1);
+        const A g = p.reduction == SB_REDUCTION_NONE ? convert<A, T>(grad_output[s0 + k]) : gscale;
+        val[k] = -wt * g;
+      }
+    }
+    T* dst = grad_input + (n * p.classes) * p.inner + i0;
+    for (int64_t c = 0; c < p.classes; ++c) {
+      A o[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) o[k] = t[k] == c ? val[k] : A(0);
+      store_as<A, T, VEC>(dst + c * p.inner, o);
+    }
+  }
+}
+
+int nd_validate(const sb_nll_nd_args* a) {
+  if (!a || a->outer < 0 || a->classes < 0 || a->inner < 0) return SB_ERR_INVALID_ARGUMENT;
+  if (a->reduction < SB_REDUCTION_NONE || a->reduction > SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
+  if (a->target_dtype != SB_I64 && a->target_dtype != SB_U8) return SB_ERR_UNSUPPORTED;
+  if (a->dtype != SB_F32 && a->dtype != SB_BF16 && a->dtype != SB_F16 && a->dtype != SB_F64) return SB_ERR_UNSUPPORTED;
+  if (a->inner != 0 && a->outer > INT64_MAX / a->inner) return SB_ERR_TOO_LARGE;
+  const int64_t samples = a->outer * a->inner;
+  if (samples > 0 && (!a->log_probs || !a->target)) return SB_ERR_INVALID_ARGUMENT;
+  return SB_OK;
+}
+
+NdParams nd_params(const sb_nll_nd_args* a) {
+  NdParams p;
+  p.x = a->log_probs;
+  p.target = a->target;
+  p.weight = a->weight;
+  p.outer = a->outer;
+  p.classes = a->classes;
+  p.inner = a->inner;
+  p.samples = a->outer * a->inner;
+  p.ignore_index = a->ignore_index;
+  p.reduction = a->reduction;
+  p.target_dtype = a->target_dtype;
+  p.status = a->status;
+  return p;
+}
+
+int nd_partial_ctas(int64_t samples) {
+  int64_t ctas = (samples + 1023) / 1024;  // at least four samples per thread
+  const int64_t cap = 4LL * sm_count() < kMaxPartials ? 4LL * sm_count() : kMaxPartials;
+  if (ctas > cap) ctas = cap;
+  if (ctas < 1) ctas = 1;
+  return static_cast<int>(ctas);
+}
+
+template <typename T, typename A>
+int nd_launch_fwd(const sb_nll_nd_args* a, void* output, void* total_weight, cudaStream_t st) {
+  NdParams p = nd_params(a);
+  if (a->reduction == SB_REDUCTION_NONE) {
+    if (p.samples == 0) return SB_OK;
+    const int64_t ctas = (p.samples + 255) / 256;
+    const int grid = static_cast<int>(ctas < 16LL * sm_count() ? ctas : 16LL * sm_count());
+    nd_fwd_none_kernel<T, A><<<grid, 256, 0, st>>>(p, static_cast<T*>(output));
+    return launch_status();
+  }
+  const int ctas = nd_partial_ctas(p.samples);
+  if (!a->scratch || a->scratch_bytes < sizeof(double2) * static_cast<size_t>(ctas)) return SB_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a->scratch) % alignof(double2)) return SB_ERR_MISALIGNED;
+  double2* partial = static_cast<double2*>(a->scratch);
+  nd_fwd_partial_kernel<T, A><<<ctas, 256, 0, st>>>(p, partial);
+  int rc = launch_status();
+  if (rc != SB_OK) return rc;
+  nd_fwd_final_kernel<T, A><<<1, 32, 0, st>>>(partial, ctas, a->reduction, static_cast<T*>(output), static_cast<T*>(total_weight));
+  return launch_status();
+}
+
+template <typename T, typename A, int VEC>
+int nd_launch_bwd_vec(const NdParams& p, const void* grad_output, const void* total_weight, void* grad_input, cudaStream_t st) {
+  const int64_t items = p.outer * (p.inner / VEC);
+  const int64_t ctas = (items + 255) / 256;
+  const int grid = static_cast<int>(ctas < 16LL * sm_count() ? ctas : 16LL * sm_count());
+  nd_bwd_kernel<T, A, VEC><<<grid, 256, 0, st>>>(p, static_cast<const T*>(grad_output), static_cast<const T*>(total_weight),
+                                                  static_cast<T*>(grad_input));
+  return launch_status();
+}
+
+template <typename T, typename A>
+int nd_launch_bwd(const sb_nll_nd_args* a, const void* grad_output, const void* total_weight, void* grad_input, cudaStream_t st) {
+  NdParams p = nd_params(a);
+  if (p.samples == 0 || p.classes == 0) return SB_OK;
+  constexpr int kVec = 16 / sizeof(T);
+  const bool vec = p.inner % kVec == 0 && reinterpret_cast<uintptr_t>(grad_input) % 16 == 0;
+  if (vec) return nd_launch_bwd_vec<T, A, kVec>(p, grad_output, total_weight, grad_input, st);
+  return nd_launch_bwd_vec<T, A, 1>(p, grad_output, total_weight, grad_input, st);
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+size_t sb_nll_loss_nd_scratch_bytes(const sb_nll_nd_args* a) {
+  if (nd_validate(a) != SB_OK || a->reduction == SB_REDUCTION_NONE) return 0;
+  return sizeof(double2) * static_cast<size_t>(nd_partial_ctas(a->outer * a->inner));
+}
+
+int sb_nll_loss_nd_forward(const sb_nll_nd_args* a, void* output, void* total_weight, sb_stream_t stream) {
+  int rc = nd_validate(a);
+  if (rc != SB_OK) return rc;
+  if (!output || (a->reduction != SB_REDUCTION_NONE && !total_weight)) return SB_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = as_stream(stream);
+  switch (a->dtype) {
+    case SB_F32: return nd_launch_fwd<float, float>(a, output, total_weight, st);
+    case SB_BF16: return nd_launch_fwd<__nv_bfloat16, float>(a, output, total_weight, st);
+    case SB_F16: return nd_launch_fwd<__half, float>(a, output, total_weight, st);
+    default: return nd_launch_fwd<double, double>(a, output, total_weight, st);
+  }
+}
+
+int sb_nll_loss_nd_backward(const sb_nll_nd_args* a, const void* grad_output, const void* total_weight, void* grad_input,
+                            sb_stream_t stream) {
+  int rc = nd_validate(a);
+  if (rc != SB_OK) return rc;
+  if (a->outer * a->inner > 0 && a->classes > 0 && (!grad_output || !grad_input)) return SB_ERR_INVALID_ARGUMENT;
+  if (a->reduction == SB_REDUCTION_MEAN && !total_weight) return SB_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = as_stream(stream);
+  switch (a->dtype) {
+    case SB_F32: return nd_launch_bwd<float, float>(a, grad_output, total_weight, grad_input, st);
+    case SB_BF16: return nd_launch_bwd<__nv_bfloat16, float>(a, grad_output, total_weight, grad_input, st);
+    case SB_F16: return nd_launch_bwd<__half, float>(a, grad_output, total_weight, grad_input, st);
+    default: return nd_launch_bwd<double, double>(a, grad_output, total_weight, grad_input, st);
+  }
+}
+
+}  // extern "C"

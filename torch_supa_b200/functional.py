@@ -145,6 +145,46 @@ def nll_loss_backward(grad_out, logp, target, weight=None, ignore_index=-100, re
     return gi
 
 
+def _nll_nd_args(logp, target, weight, ignore_index, reduction, status):
+    a = capi.NLLNdArgs()
+    a.log_probs = logp.data_ptr()
+    a.dtype = capi.torch_dtype_code(logp.dtype)
+    a.target_dtype = capi.torch_dtype_code(target.dtype)
+    a.target = target.data_ptr()
+    a.weight = weight.data_ptr() if weight is not None else None
+    a.outer, a.classes = logp.shape[0], logp.shape[1]
+    inner = 1
+    for s in logp.shape[2:]:
+        inner *= s
+    a.inner = inner
+    a.ignore_index = ignore_index
+    a.reduction = _RED[reduction]
+    a.status = status.data_ptr() if status is not None else None
+    return a
+
+
+def nll_loss_nd_forward(logp, target, weight=None, ignore_index=-100, reduction="mean", status=None):
+    """nll_loss for ``logp`` of shape (N, C, d1, ...) and ``target`` of shape (N, d1, ...)."""
+    logp, target = logp.contiguous(), target.contiguous()
+    out = torch.empty(target.shape if reduction == "none" else (), dtype=logp.dtype, device=logp.device)
+    total_weight = torch.zeros((), dtype=logp.dtype, device=logp.device)
+    a = _nll_nd_args(logp, target, weight, ignore_index, reduction, status)
+    need = capi.nll_loss_nd_scratch_bytes(a)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=logp.device)
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), need
+    capi.nll_loss_nd_forward(a, out, total_weight, _stream(logp))
+    return out, total_weight
+
+
+def nll_loss_nd_backward(grad_out, logp, target, weight=None, ignore_index=-100, reduction="mean", total_weight=None,
+                         status=None):
+    logp, target = logp.contiguous(), target.contiguous()
+    gi = torch.empty_like(logp)
+    a = _nll_nd_args(logp, target, weight, ignore_index, reduction, status)
+    capi.nll_loss_nd_backward(a, grad_out.contiguous(), total_weight, gi, _stream(logp))
+    return gi
+
+
 def elementwise(op, out, *inputs, common_dtype=None, alpha=1.0, scalar=0.0):
     """out = op(*inputs) with broadcasting to ``out.shape``; strides of every operand are honoured."""
     desc = capi.make_ew_desc(op, out, inputs, common_dtype=common_dtype, alpha=alpha, scalar=scalar)
