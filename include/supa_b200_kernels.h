@@ -233,6 +233,18 @@ SB_API int sb_nll_loss_nd_forward(const sb_nll_nd_args* args, void* output, void
 SB_API int sb_nll_loss_nd_backward(const sb_nll_nd_args* args, const void* grad_output, const void* total_weight,
                                    void* grad_input, sb_stream_t stream);
 
+/* binary_cross_entropy_with_logits with reduction mean or sum in one pass: the unreduced loss of SB_EW_BCE_LOGITS /
+ * SB_EW_BCE_LOGITS_PW (times `weight` when given) is summed without being stored, where the reference writes it and
+ * calls mean() / sum() (torch_supa/csrc/aten/ops/BinaryCrossEntropyWithLogits.cpp:39-72).  x, target and weight
+ * are contiguous arrays of `numel` elements of `dtype` (SB_F32, SB_BF16, SB_F16, SB_F64); pos_weight has pw_len
+ * elements and is indexed by (flat index % pw_len), i.e. it runs along the last dimension; weight and pos_weight may
+ * be NULL.  `out` receives one element of `dtype`.  scratch: sb_bce_logits_scratch_bytes(numel) bytes, 8-byte aligned.
+ * The summation order is fixed (bit-reproducible). */
+SB_API size_t sb_bce_logits_scratch_bytes(int64_t numel);
+SB_API int sb_bce_logits_reduce(const void* x, const void* target, const void* pos_weight, int64_t pw_len, const void* weight,
+                                int32_t dtype, int64_t numel, int32_t reduction, void* out, void* scratch, size_t scratch_bytes,
+                                sb_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * TensorIterator-style elementwise engine.
  *
@@ -266,7 +278,14 @@ typedef enum sb_ew_op {
   SB_EW_ADD_SCALAR = 15,   /* out = in0 + alpha * scalar */
   SB_EW_MUL_SCALAR = 16,   /* out = in0 * scalar */
   SB_EW_NEG = 17,          /* unary */
-  SB_EW_OP_COUNT = 18
+  /* binary_cross_entropy_with_logits (torch_supa/csrc/aten/ops/kernels/elementwise/BinaryCrossEntropyWithLogitsKernel.cu:16-113):
+   * loss = (1 - t) x + lw * softplus(-x), lw = 1 + (pw - 1) t; the result is multiplied by `alpha`. */
+  SB_EW_BCE_LOGITS = 18,        /* in0 = x, in1 = t                      (lw = 1) */
+  SB_EW_BCE_LOGITS_PW = 19,     /* in0 = x, in1 = t, in2 = pos_weight */
+  SB_EW_BCE_LOGITS_BWD = 20,    /* alpha * in2(upstream gradient) * (sigmoid(x) - t) */
+  SB_EW_BCE_LOGITS_PW_BWD = 21, /* alpha * (lw * sigmoid(x) - pw * t), in2 = pos_weight */
+  SB_EW_SIGMOID = 22,           /* unary */
+  SB_EW_OP_COUNT = 23
 } sb_ew_op;
 
 typedef struct sb_ew_desc {

@@ -191,6 +191,24 @@ ORACLE_API void oracle_nll_loss_nd_backward(const double* grad_out, const int64_
     }
 }
 
+/* binary_cross_entropy_with_logits, unreduced (torch_supa/csrc/aten/ops/kernels/elementwise/
+ * BinaryCrossEntropyWithLogitsKernel.cu:16-36): (1 - t) x + lw (max(-x, 0) + log(exp(-max) + exp(-x - max))),
+ * lw = (pw - 1) t + 1; weight multiplies the result (:53-60).  pos_weight / weight may be NULL; all arrays are
+ * already broadcast to n elements.  grad = d loss / d x = (lw sigmoid(x) - pw t) * weight. */
+ORACLE_API void oracle_bce_with_logits(const float* x, const float* t, const float* pos_weight, const float* weight, int64_t n,
+                                       double* loss, double* grad) {
+  for (int64_t i = 0; i < n; ++i) {
+    const double xi = (double)x[i], ti = (double)t[i];
+    const double pw = pos_weight ? (double)pos_weight[i] : 1.0, w = weight ? (double)weight[i] : 1.0;
+    const double max_val = xi < 0.0 ? -xi : 0.0;
+    const double lw = (pw - 1.0) * ti + 1.0;
+    const double sp = max_val + log(exp(-max_val) + exp(-xi - max_val));
+    loss[i] = ((1.0 - ti) * xi + lw * sp) * w;
+    const double sg = 1.0 / (1.0 + exp(-xi));
+    grad[i] = (lw * sg - pw * ti) * w;
+  }
+}
+
 /* Row reductions with a wide accumulator (sum_functor / MeanOps / MaxNanFunctor of
  * torch_supa/csrc/aten/ops/kernels/reduce/ReduceSumKernel.cu:80-100, ReduceMomentKernel.cu:16-35).
  * op: 0 sum, 1 mean, 2 amax (NaN propagates), 3 amin. */

@@ -146,6 +146,26 @@ def main():
         d[name + "/out"] = out.detach().numpy()
         d[name + "/grad_out"] = go.numpy()
         d[name + "/grad_in"] = gi.numpy()
+    # binary_cross_entropy_with_logits (drawn after everything above)
+    for name, shape, use_w, pw_shape in (("bce_plain", (6, 9), False, None), ("bce_w", (6, 9), True, None), ("bce_pw", (6, 9), False, (9,)),
+                                         ("bce_pw_w", (2, 3, 4), True, (3, 1))):
+        x = (torch.rand(*shape, generator=g) * 10 - 5).requires_grad_(True)
+        t = torch.rand(*shape, generator=g)
+        w = torch.rand(*shape, generator=g) * 1.9 + 0.1 if use_w else None
+        pw = torch.rand(*pw_shape, generator=g) * 2.9 + 0.1 if pw_shape else None
+        loss = F.binary_cross_entropy_with_logits(x, t, weight=w, pos_weight=pw, reduction="none")
+        go = torch.randn(*shape, generator=g)
+        (gi,) = torch.autograd.grad(loss, x, go)
+        d[name + "/x"] = x.detach().numpy()
+        d[name + "/target"] = t.numpy()
+        if use_w:
+            d[name + "/weight"] = w.numpy()
+        if pw_shape:
+            d[name + "/pos_weight"] = pw.numpy()
+        d[name + "/loss"] = loss.detach().numpy()
+        d[name + "/mean"] = loss.detach().mean().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad_in"] = gi.numpy()
     np.savez_compressed(OUT, **d)
     print("wrote", OUT, OUT.stat().st_size, "bytes,", len(d), "arrays")
 

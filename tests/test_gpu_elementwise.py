@@ -259,3 +259,75 @@ def test_zero_numel_is_a_no_op(cuda_device):
 
     out = _ew(cuda_device, capi.EW_ADD, (0, 5), torch.float32, torch.empty(0, 5), torch.empty(0, 5))
     assert out.shape == (0, 5)
+
+
+@pytest.mark.parametrize("name", ["bce_plain", "bce_pw", "bce_pw_w"])
+def test_bce_with_logits_fixtures(golden, cuda_device, name):
+    """Loss and derivative kernels of binary_cross_entropy_with_logits against the frozen PyTorch CPU results;
+    pos_weight arrives as a broadcast operand (stride 0 along the dimensions it does not have)."""
+    from torch_supa_b200 import capi
+
+    x = torch.from_numpy(golden[name + "/x"])
+    t = torch.from_numpy(golden[name + "/target"])
+    go = torch.from_numpy(golden[name + "/grad_out"])
+    has_pw = (name + "/pos_weight") in golden.files
+    w = torch.from_numpy(golden[name + "/weight"]) if (name + "/weight") in golden.files else torch.ones_like(x)
+    if has_pw:
+        pw = torch.from_numpy(golden[name + "/pos_weight"]).expand_as(x)
+        loss = _ew(cuda_device, capi.EW_BCE_LOGITS_PW, x.shape, torch.float32, x, t, pw)
+        dx = _ew(cuda_device, capi.EW_BCE_LOGITS_PW_BWD, x.shape, torch.float32, x, t, pw)
+    else:
+        loss = _ew(cuda_device, capi.EW_BCE_LOGITS, x.shape, torch.float32, x, t)
+        dx = _ew(cuda_device, capi.EW_BCE_LOGITS_BWD, x.shape, torch.float32, x, t, torch.ones_like(x))
+    assert_close((loss * w).numpy(), golden[name + "/loss"], 2e-6, 2e-6, name)
+    assert_close((dx * w * go).numpy(), golden[name + "/grad_in"], 4e-6, 2e-6, name + " backward")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", [(4,), (1024, 512), (1023, 511), (2, 3, 4)])
+def test_bce_with_logits_and_sigmoid_against_oracle(cuda_device, shape, dtype):
+    from oracle import oracle
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(len(shape) * 100 + shape[0])
+    x = (torch.rand(*shape, generator=g) * 10 - 5).to(dtype)
+    t = torch.rand(*shape, generator=g).to(dtype)
+    pw = (torch.rand(shape[-1], generator=g) * 2.9 + 0.1).to(dtype)
+    eloss, egrad = oracle.c_bce_with_logits(x.float().numpy(), t.float().numpy(), pw.float().numpy())
+    loss = _ew(cuda_device, capi.EW_BCE_LOGITS_PW, shape, dtype, x, t, pw.expand(shape), alpha=0.5)
+    dx = _ew(cuda_device, capi.EW_BCE_LOGITS_PW_BWD, shape, dtype, x, t, pw.expand(shape), alpha=0.5)
+    _cmp(loss, torch.from_numpy(eloss * 0.5).to(dtype), dtype, "loss", loosen=4)
+    _cmp(dx, torch.from_numpy(egrad * 0.5).to(dtype), dtype, "derivative", loosen=4)
+    sg = _ew(cuda_device, capi.EW_SIGMOID, shape, dtype, x)
+    _cmp(sg, torch.sigmoid(x.double()).to(dtype), dtype, "sigmoid", loosen=2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", [(4,), (1024, 512), (1023, 511), (7, 3, 1029)])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_bce_with_logits_fused_reduce(cuda_device, shape, dtype, reduction):
+    """One-pass loss + mean / sum against the oracle's unreduced loss summed in float64; two runs give the same bits."""
+    from oracle import oracle
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(shape[0] + len(shape))
+    x = (torch.rand(*shape, generator=g) * 10 - 5).to(dtype)
+    t = torch.rand(*shape, generator=g).to(dtype)
+    w = (torch.rand(*shape, generator=g) * 1.9 + 0.1).to(dtype)
+    pw = (torch.rand(shape[-1], generator=g) * 2.9 + 0.1).to(dtype)
+    for weight, pos_weight in ((None, None), (w, None), (None, pw), (w, pw)):
+        eloss, _ = oracle.c_bce_with_logits(x.float().numpy(), t.float().numpy(), None if pos_weight is None else pos_weight.float().numpy(),
+                                            None if weight is None else weight.float().numpy())
+        want = eloss.sum() if reduction == "sum" else eloss.mean()
+        args = (x.to(cuda_device), t.to(cuda_device), None if pos_weight is None else pos_weight.to(cuda_device),
+                None if weight is None else weight.to(cuda_device), reduction)
+        got = F2.bce_with_logits_reduce(*args)
+        again = F2.bce_with_logits_reduce(*args)
+        torch.cuda.synchronize()
+        assert got.dtype == dtype and torch.equal(got, again)
+        rtol = {torch.float32: 4e-6, torch.float64: 1e-9, torch.bfloat16: 8e-3, torch.float16: 1e-3}[dtype]
+        want_t = float(torch.tensor(want, dtype=torch.float64).to(dtype))  # a sum beyond the fp16 range is inf on both sides
+        if want_t == float("inf"):
+            assert float(got) == float("inf")
+        else:
+            assert abs(float(got) - want) <= rtol * abs(want) + 1e-7, (float(got), want)

@@ -383,6 +383,48 @@ def test_nll_loss2d_and_spatial_cross_entropy(supa, shape, reduction, dtype):
     assert_allclose(xr.grad.to(dtype) * scale, x.grad * scale, rtol * 4, 1e-5 if dtype == torch.float32 else 2e-3)
 
 
+@pytest.mark.parametrize("shape, dtype, reduction, with_weight, with_pos_weight, pos_weight_shape", [
+    ((4,), torch.float32, "none", False, False, None),
+    ((1024, 512), torch.float32, "sum", True, False, None),
+    ((1024, 512), torch.bfloat16, "mean", False, True, None),
+    ((1023, 511), torch.float16, "none", True, True, None),
+    ((1025, 513), torch.float16, "sum", True, True, None),
+    ((2, 3, 4), torch.float32, "mean", False, True, (3, 1)),
+    ((2048, 4096), torch.float32, "mean", False, False, None),
+])
+def test_binary_cross_entropy_with_logits_forward_backward(supa, shape, dtype, reduction, with_weight, with_pos_weight, pos_weight_shape):
+    """The parameter list of the reference's test (test/test_binary_misc_ops_kernels.py:176-245) plus the backward
+    pass, which runs our own autograd node (one fused kernel) instead of libtorch's operator chain."""
+    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+
+    g = torch.Generator().manual_seed(shape[0])
+    x_cpu = (torch.rand(*shape, generator=g) * 10 - 5).to(dtype)
+    t_cpu = torch.rand(*shape, generator=g).to(dtype)
+    w_cpu = (torch.rand(*shape, generator=g) * 1.9 + 0.1).to(dtype) if with_weight else None
+    pw_cpu = None
+    if with_pos_weight:
+        pw_cpu = (torch.rand(*(pos_weight_shape or (shape[-1],)), generator=g) * 2.9 + 0.1).to(dtype)
+    xr = x_cpu.float().detach().clone().requires_grad_(True)
+    ref = F.binary_cross_entropy_with_logits(xr, t_cpu.float(), weight=None if w_cpu is None else w_cpu.float(),
+                                             pos_weight=None if pw_cpu is None else pw_cpu.float(), reduction=reduction)
+    x = x_cpu.to(supa).requires_grad_(True)
+    out = F.binary_cross_entropy_with_logits(x, t_cpu.to(supa), weight=None if w_cpu is None else w_cpu.to(supa),
+                                             pos_weight=None if pw_cpu is None else pw_cpu.to(supa), reduction=reduction)
+    assert out.device.type == "supa" and out.dtype == dtype
+    loosen = 8 if reduction == "sum" else 2   # a sum of half a million terms rounded to 16 bits
+    assert_allclose(ref.detach().to(dtype), out.detach(), RTOL[dtype] * loosen, ATOL[dtype] * loosen)
+    go_cpu = torch.rand(ref.shape, generator=g).to(dtype)
+    out.backward(go_cpu.to(supa))
+    ref.backward(go_cpu.float())
+    scale = float(x_cpu.numel()) if reduction == "mean" else 1.0
+    assert_allclose(xr.grad.to(dtype) * scale, x.grad * scale, RTOL[dtype] * 4, ATOL[dtype] * 4)
+    # no autograd: the plain kernel path
+    with torch.no_grad():
+        out2 = F.binary_cross_entropy_with_logits(x_cpu.to(supa), t_cpu.to(supa), reduction=reduction)
+        ref2 = F.binary_cross_entropy_with_logits(x_cpu.float(), t_cpu.float(), reduction=reduction)
+    assert_allclose(ref2.to(dtype), out2, RTOL[dtype] * loosen, ATOL[dtype] * loosen)
+
+
 # ---- cross entropy -------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("shape", [(1, 1000), (16, 1000), (1, 6), (512, 1024), (512, 1027), (64, 32000), (160, 128256)])
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])

@@ -76,6 +76,16 @@ def test_nll_loss2d(golden, name):
     assert_close(gi, golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
 
 
+@pytest.mark.parametrize("name", ["bce_plain", "bce_w", "bce_pw", "bce_pw_w"])
+def test_bce_with_logits(golden, name):
+    pw = golden[name + "/pos_weight"] if (name + "/pos_weight") in golden.files else None
+    w = golden[name + "/weight"] if (name + "/weight") in golden.files else None
+    loss, grad = oracle.c_bce_with_logits(golden[name + "/x"], golden[name + "/target"], pw, w)
+    assert_close(loss, golden[name + "/loss"], 2e-6, 2e-6, name)
+    assert_close(np.atleast_1d(loss.mean()), np.atleast_1d(golden[name + "/mean"]), 2e-6, 2e-6, name + " mean")
+    assert_close(grad * golden[name + "/grad_out"], golden[name + "/grad_in"], 4e-6, 2e-6, name + " backward")
+
+
 def test_row_reductions(golden):
     x = golden["red/x"]
     assert_close(oracle.c_reduce_rows(x, "sum"), golden["red/sum"], 1e-5, 1e-5, "sum")

@@ -9,9 +9,10 @@ import torch
 import torch.nn.functional as F
 
 
-def device_randn(shape, dtype, device, seed, scale=1.0, low=None, high=None):
+def device_randn(shape, dtype, device, seed, scale=1.0, low=None, high=None, uniform=False):
     """Seeded synthetic tensor on the supa device.  The random bits come from torch's CUDA generator (plumbing)
-    and are handed over with a device-to-device copy; integer dtypes draw uniformly from [low, high]."""
+    and are handed over with a device-to-device copy; integer dtypes draw uniformly from [low, high], ``uniform``
+    draws floats from [0, scale)."""
     from . import supa as supa_mod
 
     cuda = torch.device("cuda", device.index or 0)
@@ -23,7 +24,8 @@ def device_randn(shape, dtype, device, seed, scale=1.0, low=None, high=None):
     for i0 in range(0, flat_n, block):
         n = min(block, flat_n - i0)
         if dtype.is_floating_point:
-            chunk = (torch.randn(n, device=cuda, generator=g) * scale).to(dtype)
+            draw = torch.rand if uniform else torch.randn
+            chunk = (draw(n, device=cuda, generator=g) * scale).to(dtype)
         else:
             chunk = torch.randint(low, high + 1, (n,), device=cuda, generator=g).to(dtype)
         torch.cuda.current_stream(cuda).synchronize()
@@ -148,6 +150,21 @@ def run_extras(device, peak_gbs, quick=False, profile=False):
                       samples * c4 * 4 + samples * 8,
                       time_op(lambda: torch.ops.aten.nll_loss2d_backward(go, logp, t4, None, 1, -100, tw), iters=it), peak_gbs))
     del logp, t4
+    torch.supa.empty_cache()
+    # ---- binary_cross_entropy_with_logits, fp32 [8192,8192] ----
+    bx = device_randn((8192, 8192), torch.float32, device, 16, 3.0).requires_grad_(True)
+    bt = device_randn((8192, 8192), torch.float32, device, 17, uniform=True)
+    nb2 = 8192 * 8192 * 4
+    out.append(_entry("binary_cross_entropy_with_logits mean fp32 [8192,8192] (fused loss + reduction: 2 reads)", 2 * nb2,
+                      time_op(lambda: F.binary_cross_entropy_with_logits(bx.detach(), bt), iters=it), peak_gbs))
+
+    def bce_step():
+        bx.grad = None
+        F.binary_cross_entropy_with_logits(bx, bt).backward()
+
+    out.append(_entry("binary_cross_entropy_with_logits mean fwd+bwd fp32 [8192,8192] (2 reads + 2 reads, 1 write)", 5 * nb2,
+                      time_op(bce_step, iters=it), peak_gbs))
+    del bx, bt
     torch.supa.empty_cache()
     if profile:
         time_op = _orig

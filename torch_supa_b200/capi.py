@@ -23,7 +23,8 @@ STATUS_TARGET_OUT_OF_RANGE = 0x1
 
 # sb_ew_op
 (EW_COPY, EW_FILL, EW_ADD, EW_MUL, EW_SUB, EW_DIV, EW_GELU_ERF, EW_GELU_TANH, EW_SILU, EW_GLU, EW_GELU_ERF_BWD,
- EW_GELU_TANH_BWD, EW_SILU_BWD, EW_GLU_BWD_A, EW_GLU_BWD_B, EW_ADD_SCALAR, EW_MUL_SCALAR, EW_NEG) = range(18)
+ EW_GELU_TANH_BWD, EW_SILU_BWD, EW_GLU_BWD_A, EW_GLU_BWD_B, EW_ADD_SCALAR, EW_MUL_SCALAR, EW_NEG, EW_BCE_LOGITS,
+ EW_BCE_LOGITS_PW, EW_BCE_LOGITS_BWD, EW_BCE_LOGITS_PW_BWD, EW_SIGMOID) = range(23)
 # sb_reduce_op
 RED_SUM, RED_MEAN, RED_AMAX, RED_AMIN = range(4)
 
@@ -97,6 +98,7 @@ def lib() -> C.CDLL:
         _lib.sb_dtype_size.restype = C.c_size_t
         _lib.sb_reduce_scratch_bytes.restype = C.c_size_t
         _lib.sb_nll_loss_nd_scratch_bytes.restype = C.c_size_t
+        _lib.sb_bce_logits_scratch_bytes.restype = C.c_size_t
     return _lib
 
 
@@ -198,6 +200,16 @@ def nll_loss_nd_forward(args: NLLNdArgs, output, total_weight, stream=0):
 def nll_loss_nd_backward(args: NLLNdArgs, grad_output, total_weight, grad_input, stream=0):
     check("sb_nll_loss_nd_backward", lib().sb_nll_loss_nd_backward(C.byref(args), _p(grad_output), _p(total_weight),
                                                                    _p(grad_input), C.c_void_p(stream)))
+
+
+def bce_logits_scratch_bytes(numel: int) -> int:
+    return int(lib().sb_bce_logits_scratch_bytes(C.c_int64(numel)))
+
+
+def bce_logits_reduce(x, target, pos_weight, pw_len, weight, dtype, numel, reduction, out, scratch, scratch_bytes, stream=0):
+    check("sb_bce_logits_reduce", lib().sb_bce_logits_reduce(_p(x), _p(target), _p(pos_weight), C.c_int64(pw_len), _p(weight),
+                                                             C.c_int32(dtype), C.c_int64(numel), C.c_int32(reduction), _p(out),
+                                                             _p(scratch), C.c_size_t(scratch_bytes), C.c_void_p(stream)))
 
 
 def elementwise(desc: EWDesc, stream=0):

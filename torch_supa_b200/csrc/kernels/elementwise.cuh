@@ -238,19 +238,50 @@ SB_DEFINE_OP(SB_EW_GLU_BWD_B, 3, {
     return (CT(1) - sg) * sg * a * c;
   } else return a;
 })
+// softplus(-x) = -log(sigmoid(x)) = max(-x, 0) + log1p(exp(-|x|)), the stable form.
+template <typename CT> __device__ __forceinline__ CT softplus_neg(CT x) {
+  if constexpr (std::is_same<CT, double>::value) return fmax(-x, 0.0) + log1p(exp(-fabs(x)));
+  else return fmaxf(-x, 0.f) + log1pf(expf(-fabsf(x)));
+}
+// binary cross entropy on logits: a = x, b = target [, c = pos_weight]; times alpha.
+SB_DEFINE_OP(SB_EW_BCE_LOGITS, 2, {
+  if constexpr (std::is_floating_point<CT>::value) return s.alpha * ((CT(1) - b) * a + softplus_neg<CT>(a));
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_BCE_LOGITS_PW, 3, {
+  if constexpr (std::is_floating_point<CT>::value) {
+    const CT lw = (c - CT(1)) * b + CT(1);
+    return s.alpha * ((CT(1) - b) * a + lw * softplus_neg<CT>(a));
+  } else return a;
+})
+// its derivative in x: a = x, b = target, c = upstream gradient (no pos_weight) or pos_weight.
+SB_DEFINE_OP(SB_EW_BCE_LOGITS_BWD, 3, {
+  if constexpr (std::is_floating_point<CT>::value) return s.alpha * c * (sigmoid_t<false, CT>(a) - b);
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_BCE_LOGITS_PW_BWD, 3, {
+  if constexpr (std::is_floating_point<CT>::value) {
+    const CT lw = (c - CT(1)) * b + CT(1);
+    return s.alpha * (lw * sigmoid_t<false, CT>(a) - c * b);
+  } else return a;
+})
+SB_DEFINE_OP(SB_EW_SIGMOID, 1, {
+  if constexpr (std::is_floating_point<CT>::value) return sigmoid_t<FAST, CT>(a);
+  else return a;
+})
 #undef SB_DEFINE_OP
 
 __host__ __device__ inline int ew_arity(int op) {
   switch (op) {
     case SB_EW_FILL: return 0;
     case SB_EW_COPY: case SB_EW_GELU_ERF: case SB_EW_GELU_TANH: case SB_EW_SILU: case SB_EW_ADD_SCALAR:
-    case SB_EW_MUL_SCALAR: case SB_EW_NEG: return 1;
-    case SB_EW_GLU_BWD_B: return 3;
+    case SB_EW_MUL_SCALAR: case SB_EW_NEG: case SB_EW_SIGMOID: return 1;
+    case SB_EW_GLU_BWD_B: case SB_EW_BCE_LOGITS_PW: case SB_EW_BCE_LOGITS_BWD: case SB_EW_BCE_LOGITS_PW_BWD: return 3;
     default: return 2;
   }
 }
 __host__ __device__ inline bool ew_float_only(int op) {
-  return op == SB_EW_DIV || (op >= SB_EW_GELU_ERF && op <= SB_EW_GLU_BWD_B);
+  return op == SB_EW_DIV || (op >= SB_EW_GELU_ERF && op <= SB_EW_GLU_BWD_B) || (op >= SB_EW_BCE_LOGITS && op <= SB_EW_SIGMOID);
 }
 
 // Runtime-op evaluation for paths 2 and 3 (a uniform switch per element; those paths are bound by
@@ -269,7 +300,8 @@ __device__ __forceinline__ CT ew_apply_runtime(int op, CT a, CT b, CT c, const O
 #define SB_CASE(OPCODE) case OPCODE: return EwOp<OPCODE, CT, false>::apply(a, b, c, s);
       SB_CASE(SB_EW_DIV) SB_CASE(SB_EW_GELU_ERF) SB_CASE(SB_EW_GELU_TANH) SB_CASE(SB_EW_SILU) SB_CASE(SB_EW_GLU)
       SB_CASE(SB_EW_GELU_ERF_BWD) SB_CASE(SB_EW_GELU_TANH_BWD) SB_CASE(SB_EW_SILU_BWD) SB_CASE(SB_EW_GLU_BWD_A)
-      SB_CASE(SB_EW_GLU_BWD_B)
+      SB_CASE(SB_EW_GLU_BWD_B) SB_CASE(SB_EW_BCE_LOGITS) SB_CASE(SB_EW_BCE_LOGITS_PW) SB_CASE(SB_EW_BCE_LOGITS_BWD)
+      SB_CASE(SB_EW_BCE_LOGITS_PW_BWD) SB_CASE(SB_EW_SIGMOID)
 #undef SB_CASE
       default: break;
     }

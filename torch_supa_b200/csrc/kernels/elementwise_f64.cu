@@ -11,6 +11,8 @@ int ew_launch_f64(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
     SB_CASE(SB_EW_GELU_ERF) SB_CASE(SB_EW_GELU_TANH) SB_CASE(SB_EW_SILU) SB_CASE(SB_EW_GLU) SB_CASE(SB_EW_GELU_ERF_BWD)
     SB_CASE(SB_EW_GELU_TANH_BWD) SB_CASE(SB_EW_SILU_BWD) SB_CASE(SB_EW_GLU_BWD_A) SB_CASE(SB_EW_GLU_BWD_B)
     SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG)
+    SB_CASE(SB_EW_BCE_LOGITS) SB_CASE(SB_EW_BCE_LOGITS_PW) SB_CASE(SB_EW_BCE_LOGITS_BWD) SB_CASE(SB_EW_BCE_LOGITS_PW_BWD)
+    SB_CASE(SB_EW_SIGMOID)
 #undef SB_CASE
     default: return SB_ERR_UNSUPPORTED;
   }

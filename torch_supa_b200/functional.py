@@ -185,6 +185,19 @@ def nll_loss_nd_backward(grad_out, logp, target, weight=None, ignore_index=-100,
     return gi
 
 
+def bce_with_logits_reduce(x, target, pos_weight=None, weight=None, reduction="mean"):
+    """Fused binary_cross_entropy_with_logits + mean / sum for contiguous same-dtype inputs; ``pos_weight`` runs
+    along the last dimension."""
+    x, target = x.contiguous(), target.contiguous()
+    out = torch.empty((), dtype=x.dtype, device=x.device)
+    need = capi.bce_logits_scratch_bytes(x.numel())
+    scratch = torch.empty(max(need, 8), dtype=torch.uint8, device=x.device)
+    capi.bce_logits_reduce(x, target, pos_weight, 0 if pos_weight is None else pos_weight.numel(),
+                           None if weight is None else weight.contiguous(), capi.torch_dtype_code(x.dtype), x.numel(),
+                           _RED[reduction], out, scratch, need, _stream(x))
+    return out
+
+
 def elementwise(op, out, *inputs, common_dtype=None, alpha=1.0, scalar=0.0):
     """out = op(*inputs) with broadcasting to ``out.shape``; strides of every operand are honoured."""
     desc = capi.make_ew_desc(op, out, inputs, common_dtype=common_dtype, alpha=alpha, scalar=scalar)
