@@ -104,6 +104,10 @@ typedef struct sb_ce_args {
   float label_smoothing;   /* in [0, 1] */
   float grad_scale;        /* extra host-side factor on the gradient (the upstream scalar, usually 1) */
   int32_t* status;         /* device status word, OR-ed with SB_STATUS_* bits; may be NULL */
+  const float* class_weight; /* [classes] fp32 per-class weights (the `weight` argument of cross_entropy), or NULL.
+                                Row i's loss and gradient are multiplied by class_weight[target_i]; with mean the
+                                denominator acc[1] must then be the sum of those weights (sb_ce_count_weighted).
+                                Only with label_smoothing == 0. */
 } sb_ce_args;
 
 /* Counts rows with target != ignore_index into acc[1] (as a double) and zeroes acc[0]; flags
@@ -111,6 +115,11 @@ typedef struct sb_ce_args {
  * cross_entropy_index_mean_kernel (CrossEntropyLossKernel.cu:121-162). */
 SB_API int sb_ce_count_valid(const int64_t* target, int64_t rows, int64_t classes, int64_t ignore_index,
                              double* acc, int32_t* status, sb_stream_t stream);
+
+/* The same with class weights: acc[1] = sum of class_weight[target_i] over the rows that count, added in a fixed
+ * order (bit-reproducible); acc[0] = 0. */
+SB_API int sb_ce_count_weighted(const int64_t* target, const float* class_weight, int64_t rows, int64_t classes,
+                                int64_t ignore_index, double* acc, int32_t* status, sb_stream_t stream);
 
 /* The fused sweep (see protocol above). */
 SB_API int sb_ce_forward_backward(const sb_ce_args* args, sb_stream_t stream);

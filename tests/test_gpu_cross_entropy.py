@@ -293,3 +293,31 @@ def test_nan_logit_poisons_its_row_only(cuda_device, rows, classes, dtype):
     tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
     assert_close(loss[ok], ref_loss[torch.from_numpy(ok)].numpy(), 2e-6, 4e-6, "loss")
     assert_close(grad[ok], ref_grad[torch.from_numpy(ok)].numpy(), tol[0], tol[1], "grad")
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(64, 32000, torch.float32), (160, 128256, torch.bfloat16), (37, 1000, torch.float32),
+                                                (300, 3000, torch.float16), (16, 10, torch.float32)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_class_weights(cuda_device, rows, classes, dtype, reduction):
+    """Per-class weights (no label smoothing): row i is scaled by w[target_i], mean divides by the sum of those
+    weights; resident and generic kernels against PyTorch CPU in float64."""
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(rows + classes)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::6] = -100
+    w = torch.rand(classes, generator=g) + 0.25
+    xr = logits.double().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xr, target, weight=w.double(), reduction=reduction)
+    go = torch.ones(rows) if reduction == "none" else None
+    ref.backward(go.double() if go is not None else None)
+    loss, grad = F2.cross_entropy_forward_backward(logits.to(cuda_device), target.to(cuda_device), reduction=reduction,
+                                                   class_weight=w.to(cuda_device))
+    torch.cuda.synchronize()
+    tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
+    ltol = 2e-6 if (dtype == torch.float32 or reduction == "none") else tol[0]
+    assert_close(np.atleast_1d(loss.double().cpu().numpy()), np.atleast_1d(ref.detach().numpy()), ltol, 4e-6, "loss")
+    scale = float(w[target[target >= 0]].sum()) if reduction == "mean" else 1.0
+    assert_close(grad.double().cpu().numpy() * scale, xr.grad.numpy() * scale, tol[0], tol[1], "grad")
+    assert float(grad[0].abs().max()) == 0.0, "ignored rows get a zero gradient"

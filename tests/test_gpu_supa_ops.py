@@ -458,6 +458,33 @@ def test_cross_entropy_forward_backward(supa, shape, reduction, dtype):
         assert_allclose((xr.grad * scale).float(), x.grad.float().cpu() * scale, grtol, gatol)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(16, 1000), (64, 32000), (160, 128256)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_cross_entropy_class_weights_forward_backward(supa, shape, reduction, dtype):
+    """F.cross_entropy(..., weight=w) stays on the fused kernel when there is no label smoothing (weights together with
+    smoothing go to libtorch's composite, whose mask operators are outside this path)."""
+    from torch_supa_b200.testing import assert_allclose
+
+    g = torch.Generator().manual_seed(shape[0])
+    x_cpu = (torch.randn(*shape, generator=g) * 2).to(dtype)
+    t_cpu = torch.randint(0, shape[1], (shape[0],), generator=g)
+    t_cpu[::5] = -100
+    w_cpu = (torch.rand(shape[1], generator=g) + 0.25).to(dtype)
+    rtol = {torch.float32: 1e-5, torch.bfloat16: 1.6e-2, torch.float16: 2e-3}[dtype]
+    for eps in (0.0,):
+        x = x_cpu.to(supa).requires_grad_(True)
+        out = F.cross_entropy(x, t_cpu.to(supa), weight=w_cpu.to(supa), reduction=reduction, label_smoothing=eps)
+        xr = x_cpu.float().detach().clone().requires_grad_(True)
+        ref = F.cross_entropy(xr, t_cpu, weight=w_cpu.float(), reduction=reduction, label_smoothing=eps)
+        assert_allclose(ref.detach().to(dtype), out.detach(), rtol, rtol)
+        go_cpu = (torch.rand(ref.shape, generator=g) + 0.5).to(dtype)
+        out.backward(go_cpu.to(supa))
+        ref.backward(go_cpu.float())
+        scale = float(w_cpu.float()[t_cpu[t_cpu >= 0]].sum()) if reduction == "mean" else 1.0
+        assert_allclose(xr.grad.to(dtype) * scale, x.grad * scale, rtol * 2, 1e-5 if dtype == torch.float32 else 2e-3)
+
+
 def test_cross_entropy_edge_cases(supa):
     x_cpu, x = _pair((8, 20), torch.float32)
     all_ign = torch.full((8,), -100)

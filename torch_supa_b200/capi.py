@@ -35,7 +35,7 @@ class CEArgs(C.Structure):
         ("grad_logits", C.c_void_p), ("row_loss", C.c_void_p), ("row_lse", C.c_void_p),
         ("row_grad_out", C.c_void_p), ("acc", C.c_void_p), ("rows", C.c_int64), ("classes", C.c_int64),
         ("ignore_index", C.c_int64), ("label_smoothing", C.c_float), ("grad_scale", C.c_float),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("class_weight", C.c_void_p),
     ]
 
 
@@ -129,6 +129,11 @@ def torch_dtype_code(dt) -> int:
 def ce_count_valid(target, rows, classes, ignore_index, acc, status=None, stream=0):
     check("sb_ce_count_valid", lib().sb_ce_count_valid(_p(target), C.c_int64(rows), C.c_int64(classes),
                                                        C.c_int64(ignore_index), _p(acc), _p(status), C.c_void_p(stream)))
+
+
+def ce_count_weighted(target, class_weight, rows, classes, ignore_index, acc, status=None, stream=0):
+    check("sb_ce_count_weighted", lib().sb_ce_count_weighted(_p(target), _p(class_weight), C.c_int64(rows), C.c_int64(classes),
+                                                             C.c_int64(ignore_index), _p(acc), _p(status), C.c_void_p(stream)))
 
 
 def ce_forward_backward(args: CEArgs, stream=0):

@@ -351,16 +351,26 @@ at::Tensor nll_loss2d_backward(const at::Tensor& grad_output, const at::Tensor& 
 
 // ---- cross entropy ---------------------------------------------------------------------------------------------
 // Which calls take the fused kernel.  Wider than the reference's predicate (CrossEntropyLoss.cpp:23-33: 2-D
-// fp32, no smoothing): 16-bit logits, label smoothing and 1-D logits are fused too; class weights,
-// probability targets, fp64 and K-dimensional inputs go to libtorch's composite (log_softmax + nll_loss ...),
+// fp32, no smoothing): 16-bit logits, label smoothing, 1-D logits and class weights (without smoothing) are fused
+// too; weights together with smoothing, probability targets, fp64 and K-dimensional inputs go to libtorch's composite (log_softmax + nll_loss ...),
 // whose pieces are registered above.
 bool fused_path(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, double label_smoothing) {
-  const bool has_weight = weight.has_value() && weight->defined();
+  // class weights are fused when there is no label smoothing (the smoothing term would weight every class of a row)
+  bool has_weight = weight.has_value() && weight->defined();
+  if (has_weight && label_smoothing == 0.0 && is_supa(*weight) && weight->dim() == 1 && weight->numel() == self.size(-1) &&
+      c10::isFloatingType(weight->scalar_type()))
+    has_weight = false;  // this one the kernel takes
   const at::ScalarType dt = self.scalar_type();
   const bool dtype_ok = dt == at::kFloat || dt == at::kBFloat16 || dt == at::kHalf;
   const bool shape_ok = (self.dim() == 2 && target.dim() == 1 && target.size(0) == self.size(0)) || (self.dim() == 1 && target.dim() == 0);
   return dtype_ok && shape_ok && !has_weight && target.scalar_type() == at::kLong && is_supa(target) && label_smoothing >= 0.0 &&
          label_smoothing <= 1.0 && self.size(-1) > 0;
+}
+
+// The class weights as the kernel wants them: fp32, contiguous; undefined when there are none.
+at::Tensor fused_weight(const c10::optional<at::Tensor>& weight) {
+  if (!weight.has_value() || !weight->defined()) return at::Tensor();
+  return weight->to(at::kFloat).contiguous();
 }
 
 struct FusedResult {
@@ -372,8 +382,8 @@ struct FusedResult {
 
 // The launch sequence of include/supa_b200_kernels.h: count -> [all-reduce] -> fused sweep -> loss sum ->
 // [all-reduce] -> finish.  `comm` is null on a single GPU.
-FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, int64_t reduction, int64_t ignore_index,
-                          double label_smoothing, bool want_grad, NcclComm* comm) {
+FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, const at::Tensor& class_weight, int64_t reduction,
+                          int64_t ignore_index, double label_smoothing, bool want_grad, NcclComm* comm) {
   const c10::DeviceGuard guard(self.device());
   const at::Tensor logits = self.contiguous();
   const at::Tensor tgt = target.contiguous();
@@ -399,6 +409,7 @@ FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, int6
   a.label_smoothing = static_cast<float>(label_smoothing);
   a.grad_scale = 1.f;
   a.status = status_word(logits.device().index());
+  a.class_weight = class_weight.defined() ? class_weight.const_data_ptr<float>() : nullptr;  // fp32, contiguous (see fused_weight)
 
   if (red == SB_REDUCTION_NONE) {
     if (want_grad) {
@@ -411,8 +422,13 @@ FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, int6
     return r;
   }
 
-  check_kernel(sb_ce_count_valid(tgt.const_data_ptr<int64_t>(), rows, classes, ignore_index, acc.data_ptr<double>(), a.status, stream),
-               "supa cross_entropy count");
+  if (a.class_weight)
+    check_kernel(sb_ce_count_weighted(tgt.const_data_ptr<int64_t>(), a.class_weight, rows, classes, ignore_index, acc.data_ptr<double>(),
+                                      a.status, stream),
+                 "supa cross_entropy weight sum");
+  else
+    check_kernel(sb_ce_count_valid(tgt.const_data_ptr<int64_t>(), rows, classes, ignore_index, acc.data_ptr<double>(), a.status, stream),
+                 "supa cross_entropy count");
   if (comm) comm->all_reduce_sum_f64(acc.data_ptr<double>() + 1, 1, stream);
   if (want_grad) {
     r.grad = at::empty_like(logits);
@@ -438,14 +454,16 @@ FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, int6
 
 class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFunction> {
  public:
-  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& self, const at::Tensor& target, int64_t reduction,
-                            int64_t ignore_index, double label_smoothing, int64_t comm_handle) {
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& self, const at::Tensor& target,
+                            const c10::optional<at::Tensor>& weight, int64_t reduction, int64_t ignore_index, double label_smoothing,
+                            int64_t comm_handle) {
     NcclComm* comm = comm_handle ? NcclComm::from_handle(comm_handle) : nullptr;
-    FusedResult r = fused_forward(self, target, reduction, ignore_index, label_smoothing, /*want_grad=*/true, comm);
+    const at::Tensor class_weight = fused_weight(weight);
+    FusedResult r = fused_forward(self, target, class_weight, reduction, ignore_index, label_smoothing, /*want_grad=*/true, comm);
     ctx->saved_data["reduction"] = reduction;
     ctx->saved_data["ignore_index"] = ignore_index;
     ctx->saved_data["label_smoothing"] = label_smoothing;
-    if (reduction == at::Reduction::None) ctx->save_for_backward({self, target, r.row_lse});
+    if (reduction == at::Reduction::None) ctx->save_for_backward({self, target, r.row_lse, class_weight});
     else ctx->save_for_backward({r.grad, r.applied});
     ctx->saved_data["applied_slot"] = static_cast<int64_t>(-1);  // which word of `applied` is valid; -1 = none (factor 1)
     ctx->saved_data["shape_1d"] = self.dim() == 1;
@@ -457,7 +475,7 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
     const int64_t reduction = ctx->saved_data["reduction"].toInt();
     const at::Tensor& go = grad_outputs[0];
     at::Tensor grad_self;
-    if (!go.defined()) return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+    if (!go.defined()) return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
     if (reduction == at::Reduction::None) {
       // per-row upstream gradients: one more fused sweep with the saved logits (1 read + 1 write)
       const at::Tensor logits = saved[0].contiguous();
@@ -481,6 +499,7 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
       a.label_smoothing = static_cast<float>(ctx->saved_data["label_smoothing"].toDouble());
       a.grad_scale = 1.f;
       a.status = status_word(logits.device().index());
+      a.class_weight = saved[3].defined() ? saved[3].const_data_ptr<float>() : nullptr;
       check_kernel(sb_ce_forward_backward(&a, stream_of(logits)), "supa cross_entropy backward");
       grad_self = grad_self.view(saved[0].sizes());
     } else {
@@ -504,23 +523,25 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
       ctx->saved_data["applied_slot"] = next;
       if (ctx->saved_data["shape_1d"].toBool()) grad_self = grad_self.reshape({grad_self.size(-1)});
     }
-    return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+    return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
 
-at::Tensor cross_entropy_fused(const at::Tensor& self, const at::Tensor& target, int64_t reduction, int64_t ignore_index,
-                               double label_smoothing, int64_t comm_handle) {
+at::Tensor cross_entropy_fused(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight,
+                               int64_t reduction, int64_t ignore_index, double label_smoothing, int64_t comm_handle) {
+  const bool has_weight = weight.has_value() && weight->defined();
   if (at::GradMode::is_enabled() && self.requires_grad())
-    return CrossEntropyFunction::apply(self, target, reduction, ignore_index, label_smoothing, comm_handle);
+    return CrossEntropyFunction::apply(self, target, has_weight ? weight : c10::nullopt, reduction, ignore_index, label_smoothing,
+                                       comm_handle);
   NcclComm* comm = comm_handle ? NcclComm::from_handle(comm_handle) : nullptr;
-  return fused_forward(self, target, reduction, ignore_index, label_smoothing, /*want_grad=*/false, comm).loss;
+  return fused_forward(self, target, fused_weight(weight), reduction, ignore_index, label_smoothing, /*want_grad=*/false, comm).loss;
 }
 
 at::Tensor cross_entropy_loss(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight,
                               int64_t reduction, int64_t ignore_index, double label_smoothing) {
   if (!fused_path(self, target, weight, label_smoothing))
     return at::native::cross_entropy_loss_symint(self, target, weight, reduction, c10::SymInt(ignore_index), label_smoothing);
-  return cross_entropy_fused(self, target, reduction, ignore_index, label_smoothing, 0);
+  return cross_entropy_fused(self, target, weight, reduction, ignore_index, label_smoothing, 0);
 }
 
 // supa_b200::sharded_cross_entropy: the same fused path with the two scalar all-reduces of the row-sharded
@@ -529,7 +550,7 @@ at::Tensor sharded_cross_entropy(const at::Tensor& self, const at::Tensor& targe
                                  double label_smoothing, int64_t comm) {
   TORCH_CHECK(fused_path(self, target, c10::nullopt, label_smoothing),
               "sharded_cross_entropy: expected [rows, classes] fp32/bf16/fp16 logits and int64 class targets on a supa device");
-  return cross_entropy_fused(self, target, reduction, ignore_index, label_smoothing, reduction == at::Reduction::None ? 0 : comm);
+  return cross_entropy_fused(self, target, c10::nullopt, reduction, ignore_index, label_smoothing, reduction == at::Reduction::None ? 0 : comm);
 }
 
 }  // namespace

@@ -23,9 +23,14 @@ struct BceParams {
   int64_t pw_len;
 };
 
+// fp32: softplus(-x) = max(-x, 0) + ln2 * lg2(1 + 2^(-|x| log2 e)) with the hardware ex2 / lg2 (absolute error of the
+// logarithm term about 1e-7, far below what a sum of these terms resolves); keeps the pass bound by memory.
 __device__ __forceinline__ float bce_term(float x, float t, float lw) {
-  const float sp = fmaxf(-x, 0.f) + log1pf(expf(-fabsf(x)));
-  return (1.f - t) * x + lw * sp;
+  float e, l;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-fabsf(x) * 1.4426950408889634f));
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(1.f + e));
+  const float sp = fmaf(l, 0.6931471805599453f, fmaxf(-x, 0.f));
+  return fmaf(1.f - t, x, lw * sp);
 }
 __device__ __forceinline__ double bce_term(double x, double t, double lw) {
   const double sp = fmax(-x, 0.0) + log1p(exp(-fabs(x)));

@@ -21,6 +21,7 @@ struct CEParams {
   int reduction;
   int dtype;
   int32_t* status;           // nullable
+  const float* class_weight; // nullable: fp32 [classes]; multiplies the loss and the gradient of a row by w[target]
 };
 
 // loss of one non-ignored row; sum_x is the plain sum of the row's logits.
@@ -30,10 +31,11 @@ __device__ __forceinline__ float ce_row_loss(float lse, float x_target, float su
 }
 
 // Factor applied to (softmax - smoothed one-hot) of a row.
-__device__ __forceinline__ float ce_row_scale(const CEParams& p, int64_t row) {
+__device__ __forceinline__ float ce_row_scale(const CEParams& p, int64_t row, int64_t target) {
   float scale = p.grad_scale;
   if (p.reduction == SB_REDUCTION_MEAN) scale = static_cast<float>(static_cast<double>(scale) / p.acc[1]);
   if (p.row_grad_out) scale *= p.row_grad_out[row];
+  if (p.class_weight) scale *= p.class_weight[target];
   return scale;
 }
 

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(THREADS) ce_rows_cta_kernel(CEParams p) {
         const float lse = a.m + logf(a.s);
         const float xt = to_float(x[t]);
         s_out[0] = lse;
-        s_out[1] = ce_row_loss(lse, xt, b, eps, eps_c);
+        s_out[1] = ce_row_loss(lse, xt, b, eps, eps_c) * (p.class_weight ? p.class_weight[t] : 1.f);
       }
     }
     __syncthreads();
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(THREADS) ce_rows_cta_kernel(CEParams p) {
 
     // ---- sweep 2: gradient ---------------------------------------------------------------------
     if (g) {
-      const float scale = ce_row_scale(p, row);
+      const float scale = ce_row_scale(p, row, t);
       const float sub_all = eps_c * scale;
       const float sub_t = (1.f - eps) * scale;
       for (int64_t i = tid; i < nvec; i += THREADS) {
@@ -180,12 +180,12 @@ __global__ void __launch_bounds__(THREADS) ce_rows_warp_kernel(CEParams p) {
     s = warp_sum(s);
     const float lse = m + logf(s);
     if (lane == 0) {
-      p.row_loss[row] = ce_row_loss(lse, to_float(x[t]), sx, eps, eps_c);
+      p.row_loss[row] = ce_row_loss(lse, to_float(x[t]), sx, eps, eps_c) * (p.class_weight ? p.class_weight[t] : 1.f);
       if (p.row_lse) p.row_lse[row] = lse;
     }
     if (g) {
       __syncwarp();  // x[t] has been read before an in-place gradient overwrites it
-      const float scale = ce_row_scale(p, row);
+      const float scale = ce_row_scale(p, row, t);
       const float sub_all = eps_c * scale;
       const float sub_t = (1.f - eps) * scale;
       for (int64_t c = lane; c < C; c += 32) {
@@ -229,6 +229,33 @@ __global__ void __launch_bounds__(256) ce_count_valid_kernel(const int64_t* __re
     unsigned int total = 0;
     for (int w = 0; w < 8; ++w) total += s_cnt[w];
     if (total) atomicAdd(acc + 1, static_cast<double>(total));
+  }
+}
+
+// acc[1] = sum of w[target] over the rows that count, in a fixed order (one CTA: thread k adds rows k, k+1024, ... then a tree).
+__global__ void __launch_bounds__(1024) ce_count_weighted_kernel(const int64_t* __restrict__ target, const float* __restrict__ w,
+                                                                 int64_t rows, int64_t classes, int64_t ignore_index, double* acc,
+                                                                 int32_t* status) {
+  __shared__ double s_part[32];
+  double a = 0.0;
+  bool bad = false;
+  for (int64_t i = threadIdx.x; i < rows; i += 1024) {
+    const int64_t t = target[i];
+    if (t != ignore_index) {
+      if (t < 0 || t >= classes) bad = true;
+      else a += static_cast<double>(w[t]);
+    }
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0 && status) atomicOr(status, SB_STATUS_TARGET_OUT_OF_RANGE);
+  a = warp_sum(a);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const double b = warp_sum(s_part[threadIdx.x]);
+    if (threadIdx.x == 0) {
+      acc[0] = 0.0;
+      acc[1] = b;
+    }
   }
 }
 
@@ -340,6 +367,13 @@ int sb_ce_count_valid(const int64_t* target, int64_t rows, int64_t classes, int6
   return launch_status();
 }
 
+int sb_ce_count_weighted(const int64_t* target, const float* class_weight, int64_t rows, int64_t classes, int64_t ignore_index,
+                         double* acc, int32_t* status, sb_stream_t stream) {
+  if (rows < 0 || classes < 0 || !acc || !class_weight || (rows > 0 && !target)) return SB_ERR_INVALID_ARGUMENT;
+  ce_count_weighted_kernel<<<1, 1024, 0, as_stream(stream)>>>(target, class_weight, rows, classes, ignore_index, acc, status);
+  return launch_status();
+}
+
 int sb_ce_forward_backward(const sb_ce_args* a, sb_stream_t stream) {
   if (!a) return SB_ERR_INVALID_ARGUMENT;
   if (a->rows < 0 || a->classes < 0) return SB_ERR_INVALID_ARGUMENT;
@@ -349,6 +383,7 @@ int sb_ce_forward_backward(const sb_ce_args* a, sb_stream_t stream) {
   if (a->dtype != SB_F32 && a->dtype != SB_BF16 && a->dtype != SB_F16) return SB_ERR_UNSUPPORTED;
   if (a->reduction < SB_REDUCTION_NONE || a->reduction > SB_REDUCTION_SUM) return SB_ERR_INVALID_ARGUMENT;
   if (!(a->label_smoothing >= 0.f && a->label_smoothing <= 1.f)) return SB_ERR_INVALID_ARGUMENT;
+  if (a->class_weight && a->label_smoothing != 0.f) return SB_ERR_UNSUPPORTED;  // the smoothing term weights every class
   if (a->grad_logits && a->reduction == SB_REDUCTION_MEAN && !a->acc) return SB_ERR_INVALID_ARGUMENT;
   const size_t es = dtype_size(a->dtype);
   if (reinterpret_cast<uintptr_t>(a->logits) % es || reinterpret_cast<uintptr_t>(a->grad_logits) % es)
@@ -369,6 +404,7 @@ int sb_ce_forward_backward(const sb_ce_args* a, sb_stream_t stream) {
   p.reduction = a->reduction;
   p.dtype = a->dtype;
   p.status = a->status;
+  p.class_weight = a->class_weight;
   return ce_dispatch(p, as_stream(stream));
 }
 
@@ -461,7 +497,8 @@ int sb_ce_loss_static_scratch(const sb_ce_args* a, void* loss_out, sb_stream_t s
   double* acc = reinterpret_cast<double*>(scratch);
   float* row_loss = reinterpret_cast<float*>(scratch + 256);
   // The count kernel's memset zeroes the accumulator; the sweep writes row_loss[0 .. rows) before the sum reads it.
-  rc = sb_ce_count_valid(a->target, a->rows, a->classes, a->ignore_index, acc, a->status, stream);
+  rc = a->class_weight ? sb_ce_count_weighted(a->target, a->class_weight, a->rows, a->classes, a->ignore_index, acc, a->status, stream)
+                       : sb_ce_count_valid(a->target, a->rows, a->classes, a->ignore_index, acc, a->status, stream);
   if (rc != SB_OK) return rc;
   sb_ce_args full = *a;
   full.row_loss = row_loss;

@@ -679,11 +679,12 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         xt_all += v.w;
       }
       lse = (gm + log2f(gs)) * kLn2;
+      const float wt = (MODE == 0 && p.class_weight) ? p.class_weight[t] : 1.f;
       if (MODE == 0 && tid == 0 && cta_rank == 0) {
-        p.row_loss[row] = ce_row_loss(lse, xt_all, gx, eps, eps_c);
+        p.row_loss[row] = ce_row_loss(lse, xt_all, gx, eps, eps_c) * wt;
         if (p.row_lse) p.row_lse[row] = lse;
       }
-      scale = base_scale;
+      scale = base_scale * wt;
       if (p.grad && p.row_grad_out) scale *= p.row_grad_out[row];
       if (lse != lse) scale = lse;  // a NaN row: every gradient element is NaN, the polynomial pairs included
     } else if (MODE == 0 && tid == 0 && cta_rank == 0) {

@@ -255,14 +255,25 @@ SB_DEFINE_OP(SB_EW_BCE_LOGITS_PW, 3, {
   } else return a;
 })
 // its derivative in x: a = x, b = target, c = upstream gradient (no pos_weight) or pos_weight.
+// sigmoid for the derivative below: fp32 through ex2 and the approximate reciprocal (relative error about 5e-7 where the
+// value is not tiny), so that the kernel stays bound by its three streams.
+template <typename CT> __device__ __forceinline__ CT sigmoid_bce(CT x) {
+  if constexpr (std::is_same<CT, double>::value) return sigmoid_d(x);
+  else {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+    return r;
+  }
+}
 SB_DEFINE_OP(SB_EW_BCE_LOGITS_BWD, 3, {
-  if constexpr (std::is_floating_point<CT>::value) return s.alpha * c * (sigmoid_t<false, CT>(a) - b);
+  if constexpr (std::is_floating_point<CT>::value) return s.alpha * c * (sigmoid_bce<CT>(a) - b);
   else return a;
 })
 SB_DEFINE_OP(SB_EW_BCE_LOGITS_PW_BWD, 3, {
   if constexpr (std::is_floating_point<CT>::value) {
     const CT lw = (c - CT(1)) * b + CT(1);
-    return s.alpha * (lw * sigmoid_t<false, CT>(a) - c * b);
+    return s.alpha * (lw * sigmoid_bce<CT>(a) - c * b);
   } else return a;
 })
 SB_DEFINE_OP(SB_EW_SIGMOID, 1, {

@@ -15,7 +15,7 @@ namespace sb {
 
 namespace {
 
-constexpr int kMaxPartials = 1024;
+constexpr int kMaxPartials = 2048;
 
 struct NdParams {
   const void* x;
@@ -66,13 +66,33 @@ __global__ void __launch_bounds__(256) nd_fwd_partial_kernel(NdParams p, double2
   const T* x = static_cast<const T*>(p.x);
   const T* w = static_cast<const T*>(p.weight);
   double av = 0.0, aw = 0.0;
-  for (int64_t s = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; s < p.samples; s += static_cast<int64_t>(gridDim.x) * 256) {
-    int64_t t;
-    if (nd_counts(p, s, t)) {
-      const int64_t n = s / p.inner, i = s - n * p.inner;
-      const double wt = w ? static_cast<double>(convert<A, T>(w[t])) : 1.0;
-      av -= wt * static_cast<double>(convert<A, T>(x[(n * p.classes + t) * p.inner + i]));
-      aw += wt;
+  // four samples per thread and pass: the targets, then the four gathers they name, are in flight together
+  constexpr int kU = 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+  for (int64_t s0 = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; s0 < p.samples; s0 += stride * kU) {
+    int64_t t[kU];
+    bool ok[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t s = s0 + u * stride;
+      ok[u] = s < p.samples && nd_counts(p, s, t[u]);
+    }
+    A xv[kU], wv[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      xv[u] = A(0);
+      wv[u] = A(0);
+      if (ok[u]) {
+        const int64_t s = s0 + u * stride;
+        const int64_t n = s / p.inner, i = s - n * p.inner;
+        wv[u] = w ? convert<A, T>(w[t[u]]) : A(1);
+        xv[u] = convert<A, T>(x[(n * p.classes + t[u]) * p.inner + i]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      av -= static_cast<double>(wv[u]) * static_cast<double>(xv[u]);
+      aw += static_cast<double>(wv[u]);
     }
   }
   av = warp_sum(av);
@@ -174,7 +194,7 @@ NdParams nd_params(const sb_nll_nd_args* a) {
 
 int nd_partial_ctas(int64_t samples) {
   int64_t ctas = (samples + 1023) / 1024;  // at least four samples per thread
-  const int64_t cap = 4LL * sm_count() < kMaxPartials ? 4LL * sm_count() : kMaxPartials;
+  const int64_t cap = 8LL * sm_count() < kMaxPartials ? 8LL * sm_count() : kMaxPartials;
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   return static_cast<int>(ctas);

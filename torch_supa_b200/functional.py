@@ -34,13 +34,15 @@ class CrossEntropyWorkspace:
 
 def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_smoothing=0.0, reduction="mean",
                                    grad=None, want_grad=True, workspace=None, grad_scale=1.0, row_grad_out=None,
-                                   row_lse=None, all_reduce=None):
+                                   row_lse=None, all_reduce=None, class_weight=None):
     """Fused cross entropy: returns ``(loss, grad_logits)``.
 
     ``loss`` is a 0-d tensor in the logits' dtype for mean/sum and an fp32 ``[rows]`` tensor for none.
     ``all_reduce``, when given, is called as ``all_reduce(acc_view)`` on a one-element float64 view of the
     device accumulator, first for the valid-row count and then for the loss sum: this is the hook the
-    row-sharded multi-GPU path uses.
+    row-sharded multi-GPU path uses.  ``class_weight`` (fp32 ``[classes]``, only without label smoothing)
+    multiplies each row's loss and gradient by the weight of its target; ``mean`` then divides by the sum of
+    those weights.
     """
     assert logits.dim() == 2 and target.dim() == 1 and logits.is_contiguous() and target.is_contiguous()
     rows, classes = logits.shape
@@ -49,8 +51,13 @@ def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_s
     if want_grad and grad is None:
         grad = torch.empty_like(logits)
     red = _RED[reduction]
+    if class_weight is not None:
+        assert class_weight.dtype == torch.float32 and class_weight.is_contiguous() and class_weight.numel() == classes
     if red != capi.REDUCTION_NONE:
-        capi.ce_count_valid(target, rows, classes, ignore_index, ws.acc, ws.status, st)
+        if class_weight is not None:
+            capi.ce_count_weighted(target, class_weight, rows, classes, ignore_index, ws.acc, ws.status, st)
+        else:
+            capi.ce_count_valid(target, rows, classes, ignore_index, ws.acc, ws.status, st)
         if all_reduce is not None:
             all_reduce(ws.acc[1:2])
     args = capi.CEArgs()
@@ -67,6 +74,7 @@ def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_s
     args.label_smoothing = label_smoothing
     args.grad_scale = grad_scale
     args.status = ws.status.data_ptr()
+    args.class_weight = class_weight.data_ptr() if class_weight is not None else None
     capi.ce_forward_backward(args, st)
     if red == capi.REDUCTION_NONE:
         return ws.row_loss[:rows], (grad if want_grad else None)
