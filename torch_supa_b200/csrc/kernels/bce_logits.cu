@@ -46,21 +46,36 @@ __global__ void __launch_bounds__(kBceThreads) bce_partial_kernel(BceParams p, d
   const T* w = static_cast<const T*>(p.w);
   const int64_t nvec = p.numel / VEC;
   double acc = 0.0;
-  for (int64_t v = static_cast<int64_t>(blockIdx.x) * kBceThreads + threadIdx.x; v < nvec; v += static_cast<int64_t>(gridDim.x) * kBceThreads) {
-    A xv[VEC], tv[VEC], wv[VEC];
-    load_as<A, T, VEC>(x + v * VEC, xv);
-    load_as<A, T, VEC>(t + v * VEC, tv);
-    if (w) load_as<A, T, VEC>(w + v * VEC, wv);
-    A part = A(0);
+  // kU vectors of every input per thread and pass, all loads issued before the arithmetic
+  constexpr int kU = 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kBceThreads;
+  for (int64_t v0 = static_cast<int64_t>(blockIdx.x) * kBceThreads + threadIdx.x; v0 < nvec; v0 += stride * kU) {
+    A xv[kU][VEC], tv[kU][VEC], wv[kU][VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      A lw = A(1);
-      if (pw) lw = (convert<A, T>(pw[(v * VEC + k) % p.pw_len]) - A(1)) * tv[k] + A(1);
-      A term = bce_term(xv[k], tv[k], lw);
-      if (w) term *= wv[k];
-      part += term;
+    for (int u = 0; u < kU; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v < nvec) {
+        load_as<A, T, VEC>(x + v * VEC, xv[u]);
+        load_as<A, T, VEC>(t + v * VEC, tv[u]);
+        if (w) load_as<A, T, VEC>(w + v * VEC, wv[u]);
+      }
     }
-    acc += static_cast<double>(part);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v < nvec) {
+        A part = A(0);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          A lw = A(1);
+          if (pw) lw = (convert<A, T>(pw[(v * VEC + k) % p.pw_len]) - A(1)) * tv[u][k] + A(1);
+          A term = bce_term(xv[u][k], tv[u][k], lw);
+          if (w) term *= wv[u][k];
+          part += term;
+        }
+        acc += static_cast<double>(part);
+      }
+    }
   }
   // scalar tail, taken by the first threads of the first CTA
   if (blockIdx.x == 0) {
@@ -83,19 +98,27 @@ __global__ void __launch_bounds__(kBceThreads) bce_partial_kernel(BceParams p, d
   }
 }
 
+// Stage 2: one CTA; thread k adds the partials k, k + 256, ..., then a fixed tree (the order never depends on timing).
 template <typename T, typename A>
-__global__ void __launch_bounds__(32) bce_final_kernel(const double* __restrict__ partial, int count, int64_t numel, int reduction,
-                                                       T* __restrict__ out) {
-  if (threadIdx.x != 0) return;
+__global__ void __launch_bounds__(256) bce_final_kernel(const double* __restrict__ partial, int count, int64_t numel, int reduction,
+                                                        T* __restrict__ out) {
+  __shared__ double s_v[8];
   double v = 0.0;
-  for (int k = 0; k < count; ++k) v += partial[k];
-  if (reduction == SB_REDUCTION_MEAN) v = v / static_cast<double>(numel);  // 0/0 = NaN for an empty input, as mean() gives
-  *out = convert<T, A>(static_cast<A>(v));
+  for (int k = threadIdx.x; k < count; k += 256) v += partial[k];
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) s_v[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double r = 0.0;
+    for (int k = 0; k < 8; ++k) r += s_v[k];
+    if (reduction == SB_REDUCTION_MEAN) r = r / static_cast<double>(numel);  // 0/0 = NaN for an empty input, as mean() gives
+    *out = convert<T, A>(static_cast<A>(r));
+  }
 }
 
 int bce_ctas(int64_t numel) {
   int64_t ctas = (numel + 8LL * kBceThreads * 4 - 1) / (8LL * kBceThreads * 4);  // about four vectors per thread at least
-  const int64_t cap = 8LL * sm_count() < kBceMaxPartials ? 8LL * sm_count() : kBceMaxPartials;
+  const int64_t cap = 12LL * sm_count() < kBceMaxPartials ? 12LL * sm_count() : kBceMaxPartials;
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   return static_cast<int>(ctas);
@@ -112,7 +135,7 @@ int bce_launch(const BceParams& p, int reduction, void* out, void* scratch, cuda
   else bce_partial_kernel<T, A, 1><<<ctas, kBceThreads, 0, st>>>(p, partial);
   int rc = launch_status();
   if (rc != SB_OK) return rc;
-  bce_final_kernel<T, A><<<1, 32, 0, st>>>(partial, ctas, p.numel, reduction, static_cast<T*>(out));
+  bce_final_kernel<T, A><<<1, 256, 0, st>>>(partial, ctas, p.numel, reduction, static_cast<T*>(out));
   return launch_status();
 }
 

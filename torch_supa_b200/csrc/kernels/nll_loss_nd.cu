@@ -42,6 +42,20 @@ __device__ __forceinline__ bool nd_counts(const NdParams& p, int64_t s, int64_t&
   return true;
 }
 
+// sample index -> (outer row, position inside it); 32-bit division whenever the sample count allows it (a 64-bit
+// division costs more than the gather it addresses)
+__device__ __forceinline__ void nd_split(const NdParams& p, int64_t s, int64_t& n, int64_t& i) {
+  if (p.samples <= 0xffffffffLL) {
+    const uint32_t s32 = static_cast<uint32_t>(s), in32 = static_cast<uint32_t>(p.inner);
+    const uint32_t n32 = s32 / in32;
+    n = n32;
+    i = s32 - n32 * in32;
+  } else {
+    n = s / p.inner;
+    i = s - n * p.inner;
+  }
+}
+
 template <typename T, typename A>
 __global__ void __launch_bounds__(256) nd_fwd_none_kernel(NdParams p, T* __restrict__ out) {
   const T* x = static_cast<const T*>(p.x);
@@ -50,7 +64,8 @@ __global__ void __launch_bounds__(256) nd_fwd_none_kernel(NdParams p, T* __restr
     int64_t t;
     A v = 0;
     if (nd_counts(p, s, t)) {
-      const int64_t n = s / p.inner, i = s - n * p.inner;
+      int64_t n, i;
+      nd_split(p, s, n, i);
       const A wt = w ? convert<A, T>(w[t]) : A(1);
       v = -wt * convert<A, T>(x[(n * p.classes + t) * p.inner + i]);
     }
@@ -83,8 +98,8 @@ __global__ void __launch_bounds__(256) nd_fwd_partial_kernel(NdParams p, double2
       xv[u] = A(0);
       wv[u] = A(0);
       if (ok[u]) {
-        const int64_t s = s0 + u * stride;
-        const int64_t n = s / p.inner, i = s - n * p.inner;
+        int64_t n, i;
+        nd_split(p, s0 + u * stride, n, i);
         wv[u] = w ? convert<A, T>(w[t[u]]) : A(1);
         xv[u] = convert<A, T>(x[(n * p.classes + t[u]) * p.inner + i]);
       }
@@ -112,19 +127,34 @@ __global__ void __launch_bounds__(256) nd_fwd_partial_kernel(NdParams p, double2
   }
 }
 
-// Stage 2: one CTA adds the partials in index order.
+// Stage 2: one CTA; thread k adds the partials k, k + 256, ..., then a fixed tree (the order never depends on timing).
 template <typename T, typename A>
-__global__ void __launch_bounds__(32) nd_fwd_final_kernel(const double2* __restrict__ partial, int count, int reduction,
-                                                          T* __restrict__ out, T* __restrict__ total_weight) {
-  if (threadIdx.x != 0) return;
+__global__ void __launch_bounds__(256) nd_fwd_final_kernel(const double2* __restrict__ partial, int count, int reduction,
+                                                           T* __restrict__ out, T* __restrict__ total_weight) {
+  __shared__ double s_v[8];
+  __shared__ double s_w[8];
   double v = 0.0, w = 0.0;
-  for (int k = 0; k < count; ++k) {
+  for (int k = threadIdx.x; k < count; k += 256) {
     v += partial[k].x;
     w += partial[k].y;
   }
-  if (reduction == SB_REDUCTION_MEAN) v = v / w;  // 0/0 = NaN when every sample is ignored
-  *out = convert<T, A>(static_cast<A>(v));
-  *total_weight = convert<T, A>(static_cast<A>(w));
+  v = warp_sum(v);
+  w = warp_sum(w);
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = v;
+    s_w[threadIdx.x >> 5] = w;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double rv = 0.0, rw = 0.0;
+    for (int k = 0; k < 8; ++k) {
+      rv += s_v[k];
+      rw += s_w[k];
+    }
+    if (reduction == SB_REDUCTION_MEAN) rv = rv / rw;  // 0/0 = NaN when every sample is ignored
+    *out = convert<T, A>(static_cast<A>(rv));
+    *total_weight = convert<T, A>(static_cast<A>(rw));
+  }
 }
 
 // Backward: a thread owns VEC consecutive samples of one outer row and writes their value in every class plane.
@@ -140,7 +170,15 @@ __global__ void __launch_bounds__(256) nd_bwd_kernel(NdParams p, const T* __rest
     if (p.reduction == SB_REDUCTION_MEAN) gscale = gscale / convert<A, T>(*total_weight);
   }
   for (int64_t it = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; it < items; it += static_cast<int64_t>(gridDim.x) * 256) {
-    const int64_t n = it / per_row, i0 = (it - n * per_row) * VEC;
+    int64_t n, i0;
+    if (items <= 0xffffffffLL) {
+      const uint32_t n32 = static_cast<uint32_t>(it) / static_cast<uint32_t>(per_row);
+      n = n32;
+      i0 = static_cast<int64_t>(static_cast<uint32_t>(it) - n32 * static_cast<uint32_t>(per_row)) * VEC;
+    } else {
+      n = it / per_row;
+      i0 = (it - n * per_row) * VEC;
+    }
     const int64_t s0 = n * p.inner + i0;
     int64_t t[VEC];
     A val[VEC];
@@ -217,7 +255,7 @@ int nd_launch_fwd(const sb_nll_nd_args* a, void* output, void* total_weight, cud
   nd_fwd_partial_kernel<T, A><<<ctas, 256, 0, st>>>(p, partial);
   int rc = launch_status();
   if (rc != SB_OK) return rc;
-  nd_fwd_final_kernel<T, A><<<1, 32, 0, st>>>(partial, ctas, a->reduction, static_cast<T*>(output), static_cast<T*>(total_weight));
+  nd_fwd_final_kernel<T, A><<<1, 256, 0, st>>>(partial, ctas, a->reduction, static_cast<T*>(output), static_cast<T*>(total_weight));
   return launch_status();
 }
 
