@@ -195,6 +195,14 @@ SB_API int sb_log_softmax_backward(const void* grad_out, const void* out, int32_
                                    int32_t grad_in_dtype, int64_t outer, int64_t dim, int64_t inner,
                                    sb_stream_t stream);
 
+/* softmax (not log) with the same layout and dtype pairs: out = exp(x - logsumexp);
+ * backward: grad_in = out * (grad_out - sum(grad_out * out)).  One of the neighbouring operators of the
+ * external native-op library (reference tests: test/test_softmax.py, test/test_persistent_softmax.py). */
+SB_API int sb_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim,
+                              int64_t inner, sb_stream_t stream);
+SB_API int sb_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype,
+                               int64_t outer, int64_t dim, int64_t inner, sb_stream_t stream);
+
 typedef struct sb_nll_args {
   const void* log_probs;  /* [rows, classes] contiguous */
   int32_t dtype;          /* SB_F32, SB_BF16, SB_F16, SB_F64 */

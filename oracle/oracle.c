@@ -117,6 +117,31 @@ ORACLE_API void oracle_log_softmax_backward(const float* g, const float* y, int6
     }
 }
 
+/* softmax and its backward over the middle dimension of [outer, dim, inner] (exercised by the reference's
+ * test/test_softmax.py and test/test_persistent_softmax.py; the kernels live in its external native-op library):
+ * y = exp(x - max) / sum exp(x - max);  grad_in = y * (g - sum_dim(g * y)). */
+ORACLE_API void oracle_softmax(const float* x, int64_t outer, int64_t dim, int64_t inner, double* out) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const float* p = x + o * dim * inner + i;
+      double m = -INFINITY, s = 0.0;
+      for (int64_t d = 0; d < dim; ++d)
+        if ((double)p[d * inner] > m) m = (double)p[d * inner];
+      for (int64_t d = 0; d < dim; ++d) s += exp((double)p[d * inner] - m);
+      for (int64_t d = 0; d < dim; ++d) out[o * dim * inner + d * inner + i] = exp((double)p[d * inner] - m) / s;
+    }
+}
+
+ORACLE_API void oracle_softmax_backward(const float* g, const float* y, int64_t outer, int64_t dim, int64_t inner, double* grad_in) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const int64_t base = o * dim * inner + i;
+      double s = 0.0;
+      for (int64_t d = 0; d < dim; ++d) s += (double)g[base + d * inner] * (double)y[base + d * inner];
+      for (int64_t d = 0; d < dim; ++d) grad_in[base + d * inner] = (double)y[base + d * inner] * ((double)g[base + d * inner] - s);
+    }
+}
+
 /* nll_loss_forward (CrossEntropyLoss.cpp:79): -w[t] x[i, t]; total_weight = sum of w[t] over counted rows. */
 ORACLE_API void oracle_nll_loss(const float* logp, const int64_t* target, const float* weight, int64_t rows,
                                 int64_t classes, int64_t ignore_index, int reduction, double* out, double* total_weight) {

@@ -166,6 +166,17 @@ def main():
         d[name + "/mean"] = loss.detach().mean().numpy()
         d[name + "/grad_out"] = go.numpy()
         d[name + "/grad_in"] = gi.numpy()
+    # softmax (not log), drawn after everything above
+    for name, shape, dim in (("sm_last", (7, 300), 1), ("sm_mid", (3, 17, 5), 1)):
+        x = (torch.randn(*shape, generator=g) * 3).requires_grad_(True)
+        y = F.softmax(x, dim)
+        go = torch.randn(*shape, generator=g)
+        (gi,) = torch.autograd.grad(y, x, go)
+        d[name + "/x"] = x.detach().numpy()
+        d[name + "/y"] = y.detach().numpy()
+        d[name + "/grad_out"] = go.numpy()
+        d[name + "/grad_in"] = gi.numpy()
+        d[name + "/dim"] = np.array([dim])
     np.savez_compressed(OUT, **d)
     print("wrote", OUT, OUT.stat().st_size, "bytes,", len(d), "arrays")
 

@@ -321,3 +321,45 @@ def test_class_weights(cuda_device, rows, classes, dtype, reduction):
     scale = float(w[target[target >= 0]].sum()) if reduction == "mean" else 1.0
     assert_close(grad.double().cpu().numpy() * scale, xr.grad.numpy() * scale, tol[0], tol[1], "grad")
     assert float(grad[0].abs().max()) == 0.0, "ignored rows get a zero gradient"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_chunks_with_in_place_gradient_equal_one_call(cuda_device, dtype):
+    """The protocol a producer of logits uses to avoid holding [rows, classes] twice: count the valid targets once, then
+    hand over row blocks as they are produced, each overwritten by its gradient (grad_logits aliases logits), and sum
+    the per-row losses at the end.  Same loss and gradients as one call over all rows."""
+    from torch_supa_b200 import capi
+    from torch_supa_b200 import functional as F2
+
+    rows, classes, chunk = 1200, 32000, 400
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype).to(cuda_device)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::13] = -100
+    target = target.to(cuda_device)
+    loss_ref, grad_ref = F2.cross_entropy_forward_backward(logits, target, label_smoothing=0.1)
+
+    work = logits.clone()
+    row_loss = torch.empty(rows, dtype=torch.float32, device=cuda_device)
+    acc = torch.zeros(2, dtype=torch.float64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    capi.ce_count_valid(target, rows, classes, -100, acc, status, stream)
+    esize = work.element_size()
+    for r0 in range(0, rows, chunk):
+        a = capi.CEArgs()
+        a.logits = work.data_ptr() + r0 * classes * esize
+        a.grad_logits = a.logits                         # in place
+        a.dtype, a.reduction = capi.torch_dtype_code(dtype), capi.REDUCTION_MEAN
+        a.target = target.data_ptr() + r0 * 8
+        a.row_loss = row_loss.data_ptr() + r0 * 4
+        a.acc = acc.data_ptr()
+        a.rows, a.classes, a.ignore_index, a.label_smoothing, a.grad_scale = min(chunk, rows - r0), classes, -100, 0.1, 1.0
+        a.status = status.data_ptr()
+        capi.ce_forward_backward(a, stream)
+    loss = torch.empty((), dtype=dtype, device=cuda_device)
+    capi.ce_loss_sum_finish(row_loss, rows, acc, capi.REDUCTION_MEAN, loss, capi.torch_dtype_code(dtype), stream)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert float(loss) == float(loss_ref), "per-row losses do not depend on how the rows are grouped"
+    assert torch.equal(work, grad_ref)

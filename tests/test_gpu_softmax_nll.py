@@ -45,6 +45,46 @@ def test_log_softmax_forward_backward(cuda_device, shape, dim, dtype):
     assert_close(gi.double().cpu().numpy(), ref_gi.numpy(), tol[0], atol, "backward")
 
 
+@pytest.mark.parametrize("name", ["sm_last", "sm_mid"])
+def test_softmax_fixtures(golden, cuda_device, name):
+    from torch_supa_b200 import functional as F2
+
+    dim = int(golden[name + "/dim"][0])
+    x = torch.from_numpy(golden[name + "/x"]).to(cuda_device)
+    y = F2.softmax(x, dim)
+    assert_close(y.cpu().numpy(), golden[name + "/y"], 2e-6, 1e-8, name)
+    gi = F2.softmax_backward(torch.from_numpy(golden[name + "/grad_out"]).to(cuda_device), y, dim)
+    assert_close(gi.cpu().numpy(), golden[name + "/grad_in"], 2e-5, 1e-7, name + " backward")
+
+
+@pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), -1), ((1025, 513), 0), ((128, 2135), -1),
+                                       ((200, 32000), -1), ((4, 5, 6, 7), 2), ((3, 40000), -1), ((160, 128256), -1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+def test_softmax_forward_backward(cuda_device, shape, dim, dtype):
+    """softmax (not log): generic kernels and, for long last-dimension rows, the shared-memory-resident pipeline;
+    rows sum to 1; backward y * (g - sum(g * y))."""
+    from torch_supa_b200 import functional as F2
+
+    if shape[-1] > 100000 and dtype == torch.float64:
+        pytest.skip("no fp64 case at this size")
+    g = torch.Generator().manual_seed(len(shape) * 19 + shape[0])
+    x = (torch.randn(*shape, generator=g) * 3).to(dtype)
+    go = torch.randn(*shape, generator=g).to(dtype)
+    y = F2.softmax(x.to(cuda_device), dim)
+    ref = F.softmax(x.double(), dim)
+    tol = {torch.float32: (4e-6, 1e-9), torch.float64: (1e-12, 1e-15), torch.bfloat16: (1.6e-2, 1e-6),
+           torch.float16: (2e-3, 1e-7)}[dtype]
+    assert_close(y.double().cpu().numpy(), ref.numpy(), tol[0], tol[1], "forward")
+    sums = y.double().sum(dim).cpu()
+    assert float((sums - 1).abs().max()) < {torch.float32: 1e-5, torch.float64: 1e-12, torch.bfloat16: 2e-2, torch.float16: 3e-3}[dtype]
+    gi = F2.softmax_backward(go.to(cuda_device), y, dim)
+    yd = y.double().cpu()
+    ref_gi = yd * (go.double() - (go.double() * yd).sum(dim, keepdim=True))
+    # y * (g - sum) cancels where g is close to the sum: the floor scales with the operands, not with the result
+    atol = {torch.float32: 1e-6, torch.float64: 1e-13, torch.bfloat16: 2e-3, torch.float16: 2e-4}[dtype]
+    assert_close(gi.double().cpu().numpy(), ref_gi.numpy(), tol[0] * 4, atol, "backward")
+
+
 def test_log_softmax_half_to_float(cuda_device):
     from torch_supa_b200 import functional as F2
 

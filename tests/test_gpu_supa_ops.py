@@ -315,6 +315,26 @@ def test_log_softmax_forward_backward(supa, shape, dim, dtype):
     assert_allclose(F.log_softmax(x_cpu.detach().float(), dim), yf, 2e-6, 1e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), 0), ((64, 32000), -1), ((4, 5, 6, 7), 2)])
+def test_softmax_forward_backward(supa, shape, dim, dtype):
+    """F.softmax dispatches to _softmax / _softmax_backward_data on the device (autograd wiring from libtorch)."""
+    from torch_supa_b200.testing import assert_allclose
+
+    x_cpu, x = _pair(shape, dtype, requires_grad=True)
+    g_cpu, g = _pair(shape, dtype, seed=1)
+    y = F.softmax(x, dim)
+    xr = x_cpu.detach().float().requires_grad_(True)
+    yr = F.softmax(xr, dim)
+    assert_allclose(yr.detach().to(dtype), y.detach(), 4e-6 if dtype == torch.float32 else 1.6e-2, 1e-7 if dtype == torch.float32 else 1e-5)
+    y.backward(g)
+    yr.backward(g_cpu.float())
+    assert_allclose(xr.grad.to(dtype), x.grad, 2e-5 if dtype == torch.float32 else 3e-2, 1e-6 if dtype == torch.float32 else 2e-3)
+    yf = F.softmax(x.detach(), dim, dtype=torch.float32)
+    assert yf.dtype == torch.float32
+    assert_allclose(F.softmax(x_cpu.detach().float(), dim), yf, 4e-6, 1e-7)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(16, 10), (1024, 512), (2000, 1000), (100, 20000)])
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])

@@ -55,6 +55,15 @@ def test_log_softmax(golden, name):
     assert_close(gi, golden[name + "/grad_in"], 1e-5, 2e-6, name + " backward")
 
 
+@pytest.mark.parametrize("name", ["sm_last", "sm_mid"])
+def test_softmax(golden, name):
+    dim = int(golden[name + "/dim"][0])
+    y = oracle.c_softmax(golden[name + "/x"], dim)
+    assert_close(y, golden[name + "/y"], 2e-6, 1e-8, name)
+    gi = oracle.c_softmax_backward(golden[name + "/grad_out"], golden[name + "/y"], dim)
+    assert_close(gi, golden[name + "/grad_in"], 2e-5, 1e-7, name + " backward")
+
+
 @pytest.mark.parametrize("name", ["nll_mean", "nll_sum_w", "nll_none_w", "nll_mean_w"])
 def test_nll_loss(golden, name):
     red = name.split("_")[1]

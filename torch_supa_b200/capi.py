@@ -185,6 +185,16 @@ def log_softmax_backward(grad_out, out, dtype, grad_in, grad_in_dtype, outer, di
                                                                    C.c_int64(dim), C.c_int64(inner), C.c_void_p(stream)))
 
 
+def softmax_forward(inp, in_dtype, out, out_dtype, outer, dim, inner, stream=0):
+    check("sb_softmax_forward", lib().sb_softmax_forward(_p(inp), C.c_int32(in_dtype), _p(out), C.c_int32(out_dtype), C.c_int64(outer),
+                                                         C.c_int64(dim), C.c_int64(inner), C.c_void_p(stream)))
+
+
+def softmax_backward(grad_out, out, dtype, grad_in, grad_in_dtype, outer, dim, inner, stream=0):
+    check("sb_softmax_backward", lib().sb_softmax_backward(_p(grad_out), _p(out), C.c_int32(dtype), _p(grad_in), C.c_int32(grad_in_dtype),
+                                                           C.c_int64(outer), C.c_int64(dim), C.c_int64(inner), C.c_void_p(stream)))
+
+
 def nll_loss_forward(args: NLLArgs, output, total_weight, stream=0):
     check("sb_nll_loss_forward", lib().sb_nll_loss_forward(C.byref(args), _p(output), _p(total_weight), C.c_void_p(stream)))
 

@@ -46,7 +46,7 @@ void split_dims(const at::Tensor& t, int64_t dim, int64_t& outer, int64_t& size,
   for (int64_t i = dim + 1; i < t.dim(); ++i) inner *= t.size(i);
 }
 
-void log_softmax_impl(const at::Tensor& self, int64_t dim, bool half_to_float, const at::Tensor& out) {
+void log_softmax_impl(const at::Tensor& self, int64_t dim, bool half_to_float, const at::Tensor& out, bool log = true) {
   if (half_to_float)
     TORCH_CHECK(self.scalar_type() == at::kHalf || self.scalar_type() == at::kBFloat16,
                 "conversion is supported for Half and BFloat16 type only");
@@ -56,14 +56,15 @@ void log_softmax_impl(const at::Tensor& self, int64_t dim, bool half_to_float, c
   at::Tensor result = out.is_contiguous() ? out : at::empty(out.sizes(), out.options());
   int64_t outer, size, inner;
   split_dims(input, wdim, outer, size, inner);
-  check_kernel(sb_log_softmax_forward(input.const_data_ptr(), dtype_code(input.scalar_type()), result.data_ptr(),
-                                      dtype_code(result.scalar_type()), outer, size, inner, stream_of(input)),
-               "supa log_softmax");
+  check_kernel((log ? sb_log_softmax_forward : sb_softmax_forward)(input.const_data_ptr(), dtype_code(input.scalar_type()),
+                                                                  result.data_ptr(), dtype_code(result.scalar_type()), outer, size,
+                                                                  inner, stream_of(input)),
+               log ? "supa log_softmax" : "supa softmax");
   if (!result.is_same(out)) out.copy_(result);
 }
 
 void log_softmax_backward_impl(const at::Tensor& grad_output, const at::Tensor& output, int64_t dim, at::ScalarType input_dtype,
-                               const at::Tensor& grad_input) {
+                               const at::Tensor& grad_input, bool log = true) {
   if (output.numel() == 0) return;
   const int64_t wdim = at::maybe_wrap_dim(dim, output.dim());
   at::Tensor go = grad_output.contiguous();
@@ -72,9 +73,10 @@ void log_softmax_backward_impl(const at::Tensor& grad_output, const at::Tensor& 
   at::Tensor result = grad_input.is_contiguous() ? grad_input : at::empty(grad_input.sizes(), grad_input.options());
   int64_t outer, size, inner;
   split_dims(y, wdim, outer, size, inner);
-  check_kernel(sb_log_softmax_backward(go.const_data_ptr(), y.const_data_ptr(), dtype_code(y.scalar_type()), result.data_ptr(),
-                                       dtype_code(result.scalar_type()), outer, size, inner, stream_of(y)),
-               "supa log_softmax backward");
+  check_kernel((log ? sb_log_softmax_backward : sb_softmax_backward)(go.const_data_ptr(), y.const_data_ptr(), dtype_code(y.scalar_type()),
+                                                                    result.data_ptr(), dtype_code(result.scalar_type()), outer, size,
+                                                                    inner, stream_of(y)),
+               log ? "supa log_softmax backward" : "supa softmax backward");
   if (!result.is_same(grad_input)) grad_input.copy_(result);
 }
 
@@ -138,6 +140,37 @@ at::Tensor& log_softmax_backward_out(const at::Tensor& grad_output, const at::Te
   OutMeta<at::meta::structured__log_softmax_backward_data> op(out, out);
   op.meta(grad_output, output, dim, input_dtype);
   log_softmax_backward_impl(grad_output, output, dim, input_dtype, out);
+  return out;
+}
+
+// ---- softmax: the same shells around the non-log kernels ---------------------------------------------------------
+at::Tensor softmax(const at::Tensor& self, int64_t dim, bool half_to_float) {
+  const c10::DeviceGuard guard(self.device());
+  FunctionalMeta<at::meta::structured__softmax> op;
+  op.meta(self, dim, half_to_float);
+  log_softmax_impl(self, dim, half_to_float, op.outputs_[0], /*log=*/false);
+  return std::move(op.outputs_[0]);
+}
+at::Tensor& softmax_out(const at::Tensor& self, int64_t dim, bool half_to_float, at::Tensor& out) {
+  const c10::DeviceGuard guard(self.device());
+  OutMeta<at::meta::structured__softmax> op(out, out);
+  op.meta(self, dim, half_to_float);
+  log_softmax_impl(self, dim, half_to_float, out, /*log=*/false);
+  return out;
+}
+at::Tensor softmax_backward(const at::Tensor& grad_output, const at::Tensor& output, int64_t dim, at::ScalarType input_dtype) {
+  const c10::DeviceGuard guard(output.device());
+  FunctionalMeta<at::meta::structured__softmax_backward_data> op;
+  op.meta(grad_output, output, dim, input_dtype);
+  log_softmax_backward_impl(grad_output, output, dim, input_dtype, op.outputs_[0], /*log=*/false);
+  return std::move(op.outputs_[0]);
+}
+at::Tensor& softmax_backward_out(const at::Tensor& grad_output, const at::Tensor& output, int64_t dim, at::ScalarType input_dtype,
+                                 at::Tensor& out) {
+  const c10::DeviceGuard guard(output.device());
+  OutMeta<at::meta::structured__softmax_backward_data> op(out, out);
+  op.meta(grad_output, output, dim, input_dtype);
+  log_softmax_backward_impl(grad_output, output, dim, input_dtype, out, /*log=*/false);
   return out;
 }
 
@@ -561,6 +594,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("_log_softmax.out", TORCH_FN(supa::log_softmax_out));
   m.impl("_log_softmax_backward_data", TORCH_FN(supa::log_softmax_backward));
   m.impl("_log_softmax_backward_data.out", TORCH_FN(supa::log_softmax_backward_out));
+  m.impl("_softmax", TORCH_FN(supa::softmax));
+  m.impl("_softmax.out", TORCH_FN(supa::softmax_out));
+  m.impl("_softmax_backward_data", TORCH_FN(supa::softmax_backward));
+  m.impl("_softmax_backward_data.out", TORCH_FN(supa::softmax_backward_out));
   m.impl("nll_loss_forward", TORCH_FN(supa::nll_loss_forward));
   m.impl("nll_loss_forward.output", TORCH_FN(supa::nll_loss_forward_out));
   m.impl("nll_loss_backward", TORCH_FN(supa::nll_loss_backward));

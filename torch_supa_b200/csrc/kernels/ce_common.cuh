@@ -57,7 +57,8 @@ int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant);
 // Chooses the family for a shape: 0 generic, 1/2/4 = resident in shared memory of a 1/2/4-CTA cluster.
 int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logits, const void* grad);
 int ce_dispatch(const CEParams& p, cudaStream_t st);
-// log_softmax over rows of `dim` elements through the resident pipeline; SB_ERR_UNSUPPORTED if the shape does not qualify.
-int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, cudaStream_t st);
+// log_softmax (mode 1) or softmax (mode 2) over rows of `dim` elements through the resident pipeline; SB_ERR_UNSUPPORTED
+// if the shape does not qualify.
+int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, int mode, cudaStream_t st);
 
 }  // namespace sb

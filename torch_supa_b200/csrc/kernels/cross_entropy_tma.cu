@@ -42,7 +42,7 @@ struct ResidentParams {
   uint32_t slice_units;  // 16-byte units per CTA slice (last CTA of a cluster may own fewer)
   uint32_t row_units;    // 16-byte units per row
   uint32_t num_clusters;
-  int mode;              // 0 cross entropy, 1 log_softmax
+  int mode;              // 0 cross entropy, 1 log_softmax, 2 softmax
   uint32_t window;       // chunks of the next row a group may fold while the row statistics are exchanged
 };
 
@@ -363,7 +363,8 @@ __device__ __forceinline__ uint4 grad_vector(const uint4& r, float2 neg_lse2, fl
   return U::pack(f);
 }
 
-// MODE 0: cross entropy (gradient out).  MODE 1: log_softmax (x - lse out; no targets, no losses).
+// MODE 0: cross entropy (gradient out).  MODE 1: log_softmax (x - lse out; no targets, no losses).  MODE 2: softmax
+// (exp(x - lse) out: the gradient formula with scale 1 and nothing subtracted).
 // log_softmax of one vector: x - lse.
 template <typename T>
 __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
@@ -715,10 +716,10 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
             for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
 #pragma unroll
             for (int q = 0; q < NV; ++q)
-              buf[q * TG] = MODE == 0 ? grad_vector<T>(r[q], neg_lse2, scale2, nsub2) : shift_vector<T>(r[q], neg_lse_nat2);
+              buf[q * TG] = MODE != 1 ? grad_vector<T>(r[q], neg_lse2, scale2, nsub2) : shift_vector<T>(r[q], neg_lse_nat2);
           } else {
             for (uint32_t v = gt; v < len; v += TG)
-              buf[v - gt] = MODE == 0 ? grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2) : shift_vector<T>(buf[v - gt], neg_lse_nat2);
+              buf[v - gt] = MODE != 1 ? grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2) : shift_vector<T>(buf[v - gt], neg_lse_nat2);
           }
           // position of the target inside this chunk, in elements
           const int64_t tl = t - (slice_elem0 + static_cast<int64_t>(u0) * E);
@@ -830,6 +831,7 @@ int launch_resident(ResidentParams rp, cudaStream_t st) {
   const uint32_t spare = (rp.nbuf - rp.nch) / kGroups;
   rp.window = g_ce_window_chunks >= 0 ? static_cast<uint32_t>(g_ce_window_chunks) : (sizeof(T) == 4 && spare > 1 ? spare - 1 : 0);
   if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
+  if (rp.mode == 2) return launch_resident_cfg<T, CLUSTER, false, 2>(rp, st);
   const bool sumx = rp.p.label_smoothing != 0.f;
   return sumx ? launch_resident_cfg<T, CLUSTER, true, 0>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0>(rp, st);
 }
@@ -881,7 +883,7 @@ int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant) {
 // log_softmax over the last dimension with the row resident in shared memory (same pipeline as the cross
 // entropy, MODE 1).  Returns SB_ERR_UNSUPPORTED when the shape does not qualify; the caller then uses the
 // generic kernels.
-int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, cudaStream_t st) {
+int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, int mode, cudaStream_t st) {
   if (g_ce_force_variant == 0) return SB_ERR_UNSUPPORTED;
   const int variant = ce_choose_variant(dtype, rows, dim, in, out);
   if (variant == 0) return SB_ERR_UNSUPPORTED;
@@ -893,7 +895,7 @@ int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int6
   rp.p.classes = dim;
   rp.p.dtype = dtype;
   rp.p.grad_scale = 1.f;
-  rp.mode = 1;
+  rp.mode = mode;
   const int64_t row_bytes = dim * dtype_size(dtype);
   if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
     return SB_ERR_UNSUPPORTED;

@@ -82,7 +82,7 @@ __device__ __forceinline__ A block_sum(A v, A* sm) {
 }
 
 // ---- forward, rows -----------------------------------------------------------------------------------------
-template <typename Tin, typename Tout, typename A, int VEC, int THREADS>
+template <typename Tin, typename Tout, typename A, int VEC, int THREADS, bool LOG>
 __global__ void __launch_bounds__(THREADS) lsm_fwd_cta_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
                                                               int64_t rows, int64_t C) {
   __shared__ A sm_m[32];
@@ -112,13 +112,13 @@ __global__ void __launch_bounds__(THREADS) lsm_fwd_cta_kernel(const Tin* __restr
       A f[VEC];
       load_as<A, Tin, VEC>(x + i * VEC, f);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) f[k] -= lse;
+      for (int k = 0; k < VEC; ++k) f[k] = LOG ? f[k] - lse : acc_exp<A>(f[k] - lse);
       store_as<A, Tout, VEC>(y + i * VEC, f);
     }
   }
 }
 
-template <typename Tin, typename Tout, typename A, int THREADS>
+template <typename Tin, typename Tout, typename A, int THREADS, bool LOG>
 __global__ void __launch_bounds__(THREADS) lsm_fwd_warp_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
                                                                int64_t rows, int64_t C) {
   const int lane = threadIdx.x & 31;
@@ -137,12 +137,15 @@ __global__ void __launch_bounds__(THREADS) lsm_fwd_warp_kernel(const Tin* __rest
     for (int64_t c = lane; c < C; c += 32) s += acc_exp<A>(convert<A, Tin>(x[c]) - mm);
     s = warp_sum_t(s);
     const A lse = m + acc_log<A>(s);
-    for (int64_t c = lane; c < C; c += 32) y[c] = convert<Tout, A>(convert<A, Tin>(x[c]) - lse);
+    for (int64_t c = lane; c < C; c += 32) {
+      const A d = convert<A, Tin>(x[c]) - lse;
+      y[c] = convert<Tout, A>(LOG ? d : acc_exp<A>(d));
+    }
   }
 }
 
 // ---- forward, strided dimension --------------------------------------------------------------------------
-template <typename Tin, typename Tout, typename A>
+template <typename Tin, typename Tout, typename A, bool LOG>
 __global__ void __launch_bounds__(256) lsm_fwd_strided_kernel(const Tin* __restrict__ in, Tout* __restrict__ out,
                                                               int64_t outer, int64_t D, int64_t inner) {
   const int64_t total = outer * inner;
@@ -160,12 +163,15 @@ __global__ void __launch_bounds__(256) lsm_fwd_strided_kernel(const Tin* __restr
     A s = 0;
     for (int64_t d = 0; d < D; ++d) s += acc_exp<A>(convert<A, Tin>(x[d * inner]) - mm);
     const A lse = m + acc_log<A>(s);
-    for (int64_t d = 0; d < D; ++d) y[d * inner] = convert<Tout, A>(convert<A, Tin>(x[d * inner]) - lse);
+    for (int64_t d = 0; d < D; ++d) {
+      const A v = convert<A, Tin>(x[d * inner]) - lse;
+      y[d * inner] = convert<Tout, A>(LOG ? v : acc_exp<A>(v));
+    }
   }
 }
 
-// ---- backward: grad_in = g - exp(y) * sum(g) ------------------------------------------------------------
-template <typename T, typename Tgi, typename A, int VEC, int THREADS>
+// ---- backward: log_softmax: grad_in = g - exp(y) * sum(g);  softmax: grad_in = y * (g - sum(g * y)) -------
+template <typename T, typename Tgi, typename A, int VEC, int THREADS, bool LOG>
 __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
                                                               Tgi* __restrict__ gin, int64_t rows, int64_t C) {
   __shared__ A sm[32];
@@ -178,8 +184,15 @@ __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restric
     for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
       A f[VEC];
       load_as<A, T, VEC>(g + i * VEC, f);
+      if (LOG) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc += f[k];
+        for (int k = 0; k < VEC; ++k) acc += f[k];
+      } else {
+        A yy[VEC];
+        load_as<A, T, VEC>(y + i * VEC, yy);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc += f[k] * yy[k];
+      }
     }
     const A sum = block_sum<A, THREADS>(acc, sm);
     for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
@@ -187,13 +200,13 @@ __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restric
       load_as<A, T, VEC>(g + i * VEC, f);
       load_as<A, T, VEC>(y + i * VEC, yy);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) f[k] -= acc_exp<A>(yy[k]) * sum;
+      for (int k = 0; k < VEC; ++k) f[k] = LOG ? f[k] - acc_exp<A>(yy[k]) * sum : yy[k] * (f[k] - sum);
       store_as<A, Tgi, VEC>(o + i * VEC, f);
     }
   }
 }
 
-template <typename T, typename Tgi, typename A>
+template <typename T, typename Tgi, typename A, bool LOG>
 __global__ void __launch_bounds__(256) lsm_bwd_strided_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
                                                               Tgi* __restrict__ gin, int64_t outer, int64_t D,
                                                               int64_t inner, bool warp_rows) {
@@ -205,10 +218,12 @@ __global__ void __launch_bounds__(256) lsm_bwd_strided_kernel(const T* __restric
       const T* y = yout + row * D;
       Tgi* o = gin + row * D;
       A acc = 0;
-      for (int64_t c = lane; c < D; c += 32) acc += convert<A, T>(g[c]);
+      for (int64_t c = lane; c < D; c += 32) acc += LOG ? convert<A, T>(g[c]) : convert<A, T>(g[c]) * convert<A, T>(y[c]);
       acc = warp_sum_t(acc);
-      for (int64_t c = lane; c < D; c += 32)
-        o[c] = convert<Tgi, A>(convert<A, T>(g[c]) - acc_exp<A>(convert<A, T>(y[c])) * acc);
+      for (int64_t c = lane; c < D; c += 32) {
+        const A gv = convert<A, T>(g[c]), yv = convert<A, T>(y[c]);
+        o[c] = convert<Tgi, A>(LOG ? gv - acc_exp<A>(yv) * acc : yv * (gv - acc));
+      }
     }
     return;
   }
@@ -218,28 +233,30 @@ __global__ void __launch_bounds__(256) lsm_bwd_strided_kernel(const T* __restric
     const int64_t o_ = idx / inner, i = idx - o_ * inner;
     const int64_t base = o_ * D * inner + i;
     A acc = 0;
-    for (int64_t d = 0; d < D; ++d) acc += convert<A, T>(gout[base + d * inner]);
     for (int64_t d = 0; d < D; ++d)
-      gin[base + d * inner] =
-          convert<Tgi, A>(convert<A, T>(gout[base + d * inner]) - acc_exp<A>(convert<A, T>(yout[base + d * inner])) * acc);
+      acc += LOG ? convert<A, T>(gout[base + d * inner]) : convert<A, T>(gout[base + d * inner]) * convert<A, T>(yout[base + d * inner]);
+    for (int64_t d = 0; d < D; ++d) {
+      const A gv = convert<A, T>(gout[base + d * inner]), yv = convert<A, T>(yout[base + d * inner]);
+      gin[base + d * inner] = convert<Tgi, A>(LOG ? gv - acc_exp<A>(yv) * acc : yv * (gv - acc));
+    }
   }
 }
 
-template <typename Tin, typename Tout, typename A>
+template <typename Tin, typename Tout, typename A, bool LOG>
 int launch_fwd(const void* in, void* out, int64_t outer, int64_t D, int64_t inner, cudaStream_t st) {
   const Tin* x = static_cast<const Tin*>(in);
   Tout* y = static_cast<Tout*>(out);
   const int sms = sm_count();
   if (inner == 1 && std::is_same<Tin, Tout>::value && sizeof(Tin) <= 4) {
     // long rows: keep the row in shared memory (one HBM read, one HBM write)
-    const int rc = lsm_launch_resident(in, out, DTypeOf<Tin>::value, outer, D, st);
+    const int rc = lsm_launch_resident(in, out, DTypeOf<Tin>::value, outer, D, LOG ? 1 : 2, st);
     if (rc != SB_ERR_UNSUPPORTED) return rc;
   }
   if (inner == 1) {
     if (D <= 1024) {
       const int64_t ctas = (outer + 7) / 8;
       const int grid = static_cast<int>(ctas < 8LL * sms ? ctas : 8LL * sms);
-      lsm_fwd_warp_kernel<Tin, Tout, A, 256><<<grid, 256, 0, st>>>(x, y, outer, D);
+      lsm_fwd_warp_kernel<Tin, Tout, A, 256, LOG><<<grid, 256, 0, st>>>(x, y, outer, D);
       return launch_status();
     }
     constexpr int kVec = 16 / sizeof(Tin);
@@ -248,18 +265,18 @@ int launch_fwd(const void* in, void* out, int64_t outer, int64_t D, int64_t inne
     const size_t out_align = sizeof(Tout) * kVec >= 16 ? 16 : sizeof(Tout) * kVec;
     const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
                          reinterpret_cast<uintptr_t>(out) % out_align == 0;
-    if (aligned) lsm_fwd_cta_kernel<Tin, Tout, A, kVec, kThreads><<<grid, kThreads, 0, st>>>(x, y, outer, D);
-    else lsm_fwd_cta_kernel<Tin, Tout, A, 1, kThreads><<<grid, kThreads, 0, st>>>(x, y, outer, D);
+    if (aligned) lsm_fwd_cta_kernel<Tin, Tout, A, kVec, kThreads, LOG><<<grid, kThreads, 0, st>>>(x, y, outer, D);
+    else lsm_fwd_cta_kernel<Tin, Tout, A, 1, kThreads, LOG><<<grid, kThreads, 0, st>>>(x, y, outer, D);
     return launch_status();
   }
   const int64_t total = outer * inner;
   const int64_t ctas = (total + 255) / 256;
   const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
-  lsm_fwd_strided_kernel<Tin, Tout, A><<<grid, 256, 0, st>>>(x, y, outer, D, inner);
+  lsm_fwd_strided_kernel<Tin, Tout, A, LOG><<<grid, 256, 0, st>>>(x, y, outer, D, inner);
   return launch_status();
 }
 
-template <typename T, typename Tgi, typename A>
+template <typename T, typename Tgi, typename A, bool LOG>
 int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int64_t D, int64_t inner, cudaStream_t st) {
   const T* g = static_cast<const T*>(gout);
   const T* y = static_cast<const T*>(yout);
@@ -272,14 +289,14 @@ int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int
     const size_t gi_align = sizeof(Tgi) * kVec >= 16 ? 16 : sizeof(Tgi) * kVec;
     const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(gout) % 16 == 0 &&
                          reinterpret_cast<uintptr_t>(yout) % 16 == 0 && reinterpret_cast<uintptr_t>(gin) % gi_align == 0;
-    if (aligned) lsm_bwd_cta_kernel<T, Tgi, A, kVec, kThreads><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
-    else lsm_bwd_cta_kernel<T, Tgi, A, 1, kThreads><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
+    if (aligned) lsm_bwd_cta_kernel<T, Tgi, A, kVec, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
+    else lsm_bwd_cta_kernel<T, Tgi, A, 1, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
     return launch_status();
   }
   const bool warp_rows = inner == 1;
   const int64_t total = warp_rows ? (outer + 7) / 8 : (outer * inner + 255) / 256;
   const int grid = static_cast<int>(total < 16LL * sms ? total : 16LL * sms);
-  lsm_bwd_strided_kernel<T, Tgi, A><<<grid, 256, 0, st>>>(g, y, o, outer, D, inner, warp_rows);
+  lsm_bwd_strided_kernel<T, Tgi, A, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D, inner, warp_rows);
   return launch_status();
 }
 
@@ -288,28 +305,30 @@ int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int
 
 using namespace sb;
 
-extern "C" {
+namespace {
 
-int sb_log_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim,
-                           int64_t inner, sb_stream_t stream) {
+template <bool LOG>
+int softmax_forward_any(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim, int64_t inner,
+                        sb_stream_t stream) {
   if (outer < 0 || dim < 0 || inner < 0) return SB_ERR_INVALID_ARGUMENT;
   if (outer == 0 || dim == 0 || inner == 0) return SB_OK;
   if (!in || !out) return SB_ERR_INVALID_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(in) % dtype_size(in_dtype) || reinterpret_cast<uintptr_t>(out) % dtype_size(out_dtype))
     return SB_ERR_MISALIGNED;
   cudaStream_t st = as_stream(stream);
-  if (in_dtype == SB_F32 && out_dtype == SB_F32) return launch_fwd<float, float, float>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F32 && out_dtype == SB_F32) return launch_fwd<float, float, float, LOG>(in, out, outer, dim, inner, st);
   if (in_dtype == SB_BF16 && out_dtype == SB_BF16)
-    return launch_fwd<__nv_bfloat16, __nv_bfloat16, float>(in, out, outer, dim, inner, st);
-  if (in_dtype == SB_F16 && out_dtype == SB_F16) return launch_fwd<__half, __half, float>(in, out, outer, dim, inner, st);
-  if (in_dtype == SB_BF16 && out_dtype == SB_F32) return launch_fwd<__nv_bfloat16, float, float>(in, out, outer, dim, inner, st);
-  if (in_dtype == SB_F16 && out_dtype == SB_F32) return launch_fwd<__half, float, float>(in, out, outer, dim, inner, st);
-  if (in_dtype == SB_F64 && out_dtype == SB_F64) return launch_fwd<double, double, double>(in, out, outer, dim, inner, st);
+    return launch_fwd<__nv_bfloat16, __nv_bfloat16, float, LOG>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F16 && out_dtype == SB_F16) return launch_fwd<__half, __half, float, LOG>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_BF16 && out_dtype == SB_F32) return launch_fwd<__nv_bfloat16, float, float, LOG>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F16 && out_dtype == SB_F32) return launch_fwd<__half, float, float, LOG>(in, out, outer, dim, inner, st);
+  if (in_dtype == SB_F64 && out_dtype == SB_F64) return launch_fwd<double, double, double, LOG>(in, out, outer, dim, inner, st);
   return SB_ERR_UNSUPPORTED;
 }
 
-int sb_log_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype,
-                            int64_t outer, int64_t dim, int64_t inner, sb_stream_t stream) {
+template <bool LOG>
+int softmax_backward_any(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype, int64_t outer,
+                         int64_t dim, int64_t inner, sb_stream_t stream) {
   if (outer < 0 || dim < 0 || inner < 0) return SB_ERR_INVALID_ARGUMENT;
   if (outer == 0 || dim == 0 || inner == 0) return SB_OK;
   if (!grad_out || !out || !grad_in) return SB_ERR_INVALID_ARGUMENT;
@@ -317,15 +336,36 @@ int sb_log_softmax_backward(const void* grad_out, const void* out, int32_t dtype
       reinterpret_cast<uintptr_t>(grad_in) % dtype_size(grad_in_dtype))
     return SB_ERR_MISALIGNED;
   cudaStream_t st = as_stream(stream);
-  if (dtype == SB_F32 && grad_in_dtype == SB_F32) return launch_bwd<float, float, float>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F32 && grad_in_dtype == SB_F32) return launch_bwd<float, float, float, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
   if (dtype == SB_BF16 && grad_in_dtype == SB_BF16)
-    return launch_bwd<__nv_bfloat16, __nv_bfloat16, float>(grad_out, out, grad_in, outer, dim, inner, st);
-  if (dtype == SB_F16 && grad_in_dtype == SB_F16) return launch_bwd<__half, __half, float>(grad_out, out, grad_in, outer, dim, inner, st);
+    return launch_bwd<__nv_bfloat16, __nv_bfloat16, float, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F16 && grad_in_dtype == SB_F16) return launch_bwd<__half, __half, float, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
   if (dtype == SB_F32 && grad_in_dtype == SB_BF16)
-    return launch_bwd<float, __nv_bfloat16, float>(grad_out, out, grad_in, outer, dim, inner, st);
-  if (dtype == SB_F32 && grad_in_dtype == SB_F16) return launch_bwd<float, __half, float>(grad_out, out, grad_in, outer, dim, inner, st);
-  if (dtype == SB_F64 && grad_in_dtype == SB_F64) return launch_bwd<double, double, double>(grad_out, out, grad_in, outer, dim, inner, st);
+    return launch_bwd<float, __nv_bfloat16, float, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F32 && grad_in_dtype == SB_F16) return launch_bwd<float, __half, float, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
+  if (dtype == SB_F64 && grad_in_dtype == SB_F64) return launch_bwd<double, double, double, LOG>(grad_out, out, grad_in, outer, dim, inner, st);
   return SB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sb_log_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim,
+                           int64_t inner, sb_stream_t stream) {
+  return softmax_forward_any<true>(in, in_dtype, out, out_dtype, outer, dim, inner, stream);
+}
+int sb_log_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype,
+                            int64_t outer, int64_t dim, int64_t inner, sb_stream_t stream) {
+  return softmax_backward_any<true>(grad_out, out, dtype, grad_in, grad_in_dtype, outer, dim, inner, stream);
+}
+int sb_softmax_forward(const void* in, int32_t in_dtype, void* out, int32_t out_dtype, int64_t outer, int64_t dim, int64_t inner,
+                       sb_stream_t stream) {
+  return softmax_forward_any<false>(in, in_dtype, out, out_dtype, outer, dim, inner, stream);
+}
+int sb_softmax_backward(const void* grad_out, const void* out, int32_t dtype, void* grad_in, int32_t grad_in_dtype, int64_t outer,
+                        int64_t dim, int64_t inner, sb_stream_t stream) {
+  return softmax_backward_any<false>(grad_out, out, dtype, grad_in, grad_in_dtype, outer, dim, inner, stream);
 }
 
 }  // extern "C"

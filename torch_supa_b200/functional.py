@@ -121,6 +121,37 @@ def log_softmax_backward(grad_out, out, dim=-1, input_dtype=None):
     return gi
 
 
+def softmax(x, dim=-1, out_dtype=None):
+    x = x.contiguous()
+    dim %= max(x.dim(), 1)
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    shape = list(x.shape) or [1]
+    outer = 1
+    for s in shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in shape[dim + 1:]:
+        inner *= s
+    capi.softmax_forward(x, capi.torch_dtype_code(x.dtype), out, capi.torch_dtype_code(out.dtype), outer, shape[dim], inner, _stream(x))
+    return out
+
+
+def softmax_backward(grad_out, out, dim=-1, input_dtype=None):
+    grad_out, out = grad_out.contiguous(), out.contiguous()
+    dim %= max(out.dim(), 1)
+    gi = torch.empty(out.shape, dtype=input_dtype or out.dtype, device=out.device)
+    shape = list(out.shape) or [1]
+    outer = 1
+    for s in shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in shape[dim + 1:]:
+        inner *= s
+    capi.softmax_backward(grad_out, out, capi.torch_dtype_code(out.dtype), gi, capi.torch_dtype_code(gi.dtype), outer, shape[dim],
+                          inner, _stream(out))
+    return gi
+
+
 def _nll_args(logp, target, weight, ignore_index, reduction, status):
     a = capi.NLLArgs()
     a.log_probs = logp.data_ptr()
