@@ -44,22 +44,47 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs.  Reads through NVML
+    in this process (two light queries per sample; a looping nvidia-smi with its power and event queries was seen to
+    stall kernel launches for milliseconds); falls back to nvidia-smi when the NVML binding is missing.  Read-only."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
         self.gpu_index = gpu_index
+        self.period_s = period_s
         self.proc = None
         self.lines = []
         self.thread = None
+        self.samples = []       # (sm_mhz, reasons bitmask) from NVML
+        self.sm_max = None
+        self._stop = threading.Event()
+        self._nvml = None
 
     def start(self):
         try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu_index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if self.gpu_index < len(ids) and ids[self.gpu_index].isdigit():
+                    index = int(ids[self.gpu_index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self._nvml = None
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -67,11 +92,45 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
 
+    def _poll_nvml(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                try:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                except Exception:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+                self.samples.append((mhz, reasons))
+            except Exception:
+                pass
+            self._stop.wait(self.period_s)
+
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self._nvml is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            nv = self._nvml
+            names = (("hw_slowdown", getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8)),
+                     ("hw_thermal_slowdown", getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40)),
+                     ("sw_thermal_slowdown", getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20)),
+                     ("sw_power_cap", getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)))
+            reasons = set()
+            for _, mask in self.samples:
+                for name, bit in names:
+                    if mask & bit:
+                        reasons.add(name)
+            sm = [m for m, _ in self.samples]
+            try:
+                nv.nvmlShutdown()
+            except Exception:
+                pass
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.sm_max, "samples": len(sm),
+                    "reasons": sorted(reasons), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -93,7 +152,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def algorithmic_bytes(rows, classes, elem_size):
@@ -104,8 +163,8 @@ def algorithmic_bytes(rows, classes, elem_size):
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused-sweep launch from the ncu captures summarised under
 # profiles/ (the bf16 figure is the 4096-row capture scaled by 8: traffic is proportional to rows).
 TRAFFIC = {
-    ("ce_fp32_4096x32000", 4096): 524.375296e6 + 470.366464e6,
-    ("ce_bf16_32768x128256", 32768): 8 * (998.527744e6 + 996.002816e6),
+    ("ce_fp32_4096x32000", 4096): 524.488192e6 + 469.110272e6,
+    ("ce_bf16_32768x128256", 32768): 8 * (998.434048e6 + 995.995392e6),
 }
 
 
@@ -171,6 +230,8 @@ def run_ours(args):
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 0))
     if args.tune_variant >= 0:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, args.tune_variant))
+    if args.tune_keep >= 0:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(3, args.tune_keep))
     if args.tune_window >= 0:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(2, args.tune_window))
 
@@ -217,15 +278,11 @@ def run_ours(args):
         return float(t.item())
 
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.no_clocks:
         sampler.start()
     for _ in range(warmup):
         step(logits, target)
     barrier()
-    t_end = time.time() + (0.0 if args.quick else 0.6)  # keep the GPU busy so the clock sampler sees it under load
-    while time.time() < t_end:
-        step(logits, target)
-        torch.supa.synchronize()
 
     # ---- device-resident timing ---------------------------------------------------------------------
     start, stop = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
@@ -262,6 +319,29 @@ def run_ours(args):
     status_word = int(ws_status.cpu().item())
     clocks = sampler.stop() if rank == 0 else None
     del grad
+
+    # ---- the same step under sustained load: about half a second of back-to-back steps, the last ones timed.  At
+    # 1000 W the board caps its power and lowers the SM clock, so this is slower than the short timed region above.
+    sustained = None
+    if not args.quick:
+        sus_sampler = ClockSampler(local_rank, period_s=0.02)
+        if rank == 0 and not args.no_clocks:
+            sus_sampler.start()
+        for _ in range(20):  # a fixed count: every rank must issue the same collectives
+            for _ in range(8):
+                step(logits, target)
+            torch.supa.synchronize()
+        s0, s1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
+        barrier()
+        s0.record()
+        for _ in range(20):
+            step(logits, target)
+        s1.record()
+        barrier()
+        sus_ms = max_over_ranks(s0.elapsed_time(s1)) / 20
+        sus_clocks = sus_sampler.stop() if (rank == 0 and not args.no_clocks) else None
+        sustained = {"ms_per_step": sus_ms, "value": rows * world / (sus_ms * 1e-3), "unit": "rows/s", "after_steps_of_load": 160,
+                     "clocks": sus_clocks}
 
     # ---- end to end: host buffers -> loss on the host ---------------------------------------------
     e2e = None
@@ -341,7 +421,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "frac_of_8TBs_nominal": achieved / 8000.0, "kernel": "ce_resident_kernel",
                          "kernel_ms": kernel_ms, "algorithmic_bytes": alg, "traffic": TRAFFIC.get((args.workload, rows))},
-            "hbm_gbs_whole_step": alg / (ms_per_step * 1e-3) / 1e9,
+            "hbm_gbs_whole_step": alg / (ms_per_step * 1e-3) / 1e9, "sustained": sustained,
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
@@ -367,7 +447,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiling mode: no clock warm loop, no e2e, no CPU baseline")
     ap.add_argument("--force-generic", action="store_true", help="tuning: always use the generic two-sweep kernel")
+    ap.add_argument("--no-clocks", action="store_true", help="diagnostic: do not sample clocks during the run")
     ap.add_argument("--tune-variant", type=int, default=-1, help="tuning: force the resident kernel's cluster size (1, 2, 4)")
+    ap.add_argument("--tune-keep", type=int, default=-1, help="tuning: 0 recompute bf16 exponentials in the gradient sweep, 1 keep them")
     ap.add_argument("--tune-window", type=int, default=-1, help="tuning: next-row chunks folded during the statistics exchange")
     ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations; 2: same, one launch each (for profilers)")
     args = ap.parse_args()

@@ -177,7 +177,9 @@ SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
  * key 1 = cross-entropy kernel family (-1 automatic, 0 always the generic two-sweep kernel, 1/2/4 the
  * resident kernel with that cluster size where the shape qualifies for a resident kernel at all);
  * key 2 = chunks of the next row the resident kernel folds while a row's statistics are exchanged
- * (-1 automatic, 0..64). */
+ * (-1 automatic, 0..64);
+ * key 3 = how the resident kernel forms bf16 gradients: 1 (default) rescales the exponentials kept from the statistics
+ * sweep (one ex2 per logit, one more bf16 rounding), 0 recomputes them (two ex2 per logit). */
 SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------

@@ -30,6 +30,7 @@ namespace sb {
 namespace {
 
 int g_ce_force_variant = -1;  // tuning: -1 automatic, 0 generic, 1/2/4 resident cluster size
+int g_ce_keep = 1;  // tuning: 1 = bf16 gradients from kept exponentials (one ex2 per logit), 0 = recompute (two)
 int g_ce_window_chunks = -1;  // tuning: chunks of the next row a group may fold while it waits for the exchange; -1 automatic
 
 constexpr uint32_t kMaxSpin = 1u << 22;  // try_wait attempts (each suspends up to ~1 us) before giving up
@@ -269,9 +270,12 @@ template <> struct Unit<__half> {
 };
 
 #ifndef SB_CE_POLY_PAIRS
-#define SB_CE_POLY_PAIRS 1
+#define SB_CE_POLY_PAIRS 0
 #endif
-constexpr int kPolyPairs = SB_CE_POLY_PAIRS;  // pairs per 16-byte vector of 16-bit logits whose exponentials avoid the special-function unit
+// Pairs per 16-byte vector of 16-bit logits whose exponentials go through ex2_poly2 instead of the special-function unit.
+// Measured on B200: one pair gains 1 % for a short burst and loses 3 % under sustained load, where the 1000 W cap lowers
+// the clock as the instruction count rises; the default is therefore 0.
+constexpr int kPolyPairs = SB_CE_POLY_PAIRS;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr int kGroups = 4;          // consumer warp groups per CTA
@@ -286,6 +290,7 @@ constexpr int kMaxBuffers = 32;
 struct alignas(16) Tail {
   float4 slots[2][4];        // cluster exchange: [row parity][source CTA] = {max2, sum, sum x, x[target]}
   float red[3][32];          // per-warp partials
+  float xt_kept;             // kept-exponential mode: x[target] saved by the thread that owns it before it is overwritten
   unsigned long long full[kMaxBuffers];   // loader -> consumers: chunk has landed
   unsigned long long ready[kMaxBuffers];  // consumers -> loader: chunk holds the gradient (or may be reused)
 };
@@ -313,8 +318,9 @@ struct RowStats {
 };
 
 // Folds NV vectors (already loaded) into the statistics.
-template <typename T, int NV, bool kSumX>
-__device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV]) {
+// kKeep: also return the exponentials 2^(x log2e - m2) packed in the storage type (m2 = the maximum after this update).
+template <typename T, int NV, bool kSumX, bool kKeep = false>
+__device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV], uint4* kept = nullptr) {
   using U = Unit<T>;
   constexpr int P = U::kPairs;
   float vm = U::vmax(r[0]);
@@ -342,8 +348,22 @@ __device__ __forceinline__ void stats_update(RowStats& st, const uint4 (&r)[NV])
       const float2 e = (U::kPolyDeg && i >= P - kPolyPairs) ? ex2_poly2<5>(y) : make_float2(ex2(y.x), ex2(y.y));
       st.s[i & 1] = add2(st.s[i & 1], e);
       if (kSumX) st.sx[i & 1] = add2(st.sx[i & 1], f[i]);
+      if (kKeep) f[i] = e;
     }
+    if (kKeep) kept[q] = U::pack(f);
   }
+}
+
+// Gradient of one vector from its kept exponentials: e * factor - sub.
+template <typename T>
+__device__ __forceinline__ uint4 grad_from_kept(const uint4& r, float2 factor2, float2 nsub2) {
+  using U = Unit<T>;
+  constexpr int P = U::kPairs;
+  float2 f[P];
+  U::unpack(r, f);
+#pragma unroll
+  for (int i = 0; i < P; ++i) f[i] = fma2(f[i], factor2, nsub2);
+  return U::pack(f);
 }
 
 // Gradient of one vector: (2^(x log2e - lse2)) * scale - sub.
@@ -377,7 +397,14 @@ __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
   return U::pack(f);
 }
 
-template <typename T, int CLUSTER, bool kSumX, int MODE>
+// kKeep (cross entropy on bf16 logits, at most kKeepChunks chunks per group and row): the statistics sweep overwrites
+// each chunk with its exponentials 2^(x log2e - m), m being the thread's running maximum at that chunk, and the gradient
+// sweep only rescales them: one ex2 per logit instead of two and a third fewer instructions, which is what limits this
+// kernel on bf16 (special-function unit, issue slots and, under sustained load, the power cap).  The kept value is
+// rounded to bf16 once more than in the two-ex2 form (relative error 2^-8 instead of 2^-9 on the gradient, still far
+// inside the 1e-2 the reference allows for bf16, whose own backward starts from bf16 log-probabilities).
+constexpr int kKeepChunks = 4;
+template <typename T, int CLUSTER, bool kSumX, int MODE, bool kKeep = false>
 __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(ResidentParams rp) {
   extern __shared__ __align__(128) unsigned char smem[];
   using U = Unit<T>;
@@ -406,6 +433,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       mbar_init(smem_u32(&tail->full[b]), 1);
       mbar_init(smem_u32(&tail->ready[b]), TG / 32);
     }
+    tail->xt_kept = 0.f;
     fence_mbar_init();
   }
   __syncthreads();
@@ -580,7 +608,66 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
 
     // ---- sweep A: statistics as the group's chunks land (the first a_done chunks are folded already) ----
-    fold_chunks(st, cj, cphase, a_done, cpg, ignored, true);
+    float mref[kKeepChunks];          // kept mode: the maximum each of the group's chunks was scaled by (per thread)
+    uint32_t t_cl = 0xffffffffu, t_off = 0;  // kept mode: chunk of this group and element offset of the target, if this thread owns it
+    if constexpr (kKeep) {
+      if (!ignored) {
+        const int64_t tl = t - slice_elem0;
+        if (tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
+          const uint32_t tu = static_cast<uint32_t>(tl) / E;
+          const uint32_t c = tu / kChunkUnits, v = tu % kChunkUnits;
+          if (c % G == grp && v % TG == gt) {
+            t_cl = c / G;
+            t_off = static_cast<uint32_t>(tl) - c * (kChunkUnits * E);
+          }
+        }
+      }
+      uint32_t j = cj, ph = cphase;
+#pragma unroll
+      for (int cl = 0; cl < kKeepChunks; ++cl) {
+        mref[cl] = -CUDART_INF_F;
+        if (static_cast<uint32_t>(cl) < cpg) {
+          if (!mbar_wait(full0 + 8 * j, ph)) timed_out = true;
+          if (!ignored) {
+            const uint32_t u0 = (cl * G + grp) * kChunkUnits;
+            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+            unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
+            uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
+            // the logit of the target is needed for the loss: its owner saves it before the chunk is overwritten
+            if (static_cast<uint32_t>(cl) == t_cl) tail->xt_kept = to_float(reinterpret_cast<const T*>(chunk)[t_off]);
+            if (len == kChunkUnits) {
+              uint4 r[NV], e[NV];
+#pragma unroll
+              for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+              stats_update<T, NV, kSumX, true>(st, r, e);
+#pragma unroll
+              for (int q = 0; q < NV; ++q) buf[q * TG] = e[q];
+            } else {
+              // ragged last chunk of the slice: one maximum for all of this thread's vectors, then the exponentials
+              float vm = -CUDART_INF_F;
+              for (uint32_t v = gt; v < len; v += TG) vm = max_nan(vm, U::vmax(buf[v - gt]));
+              const float nm = max_nan(st.m2, vm * kLog2e);
+              const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);
+              st.s[0] = mul2(st.s[0], make_float2(resc, resc));
+              st.s[1] = mul2(st.s[1], make_float2(resc, resc));
+              st.m2 = nm;  // stats_update below finds its maximum already in place: no further rescaling
+              for (uint32_t v = gt; v < len; v += TG) {
+                uint4 r[1] = {buf[v - gt]}, e[1];
+                stats_update<T, 1, kSumX, true>(st, r, e);
+                buf[v - gt] = e[0];
+              }
+            }
+            mref[cl] = st.m2;
+          }
+          if (++j == nbg) {
+            j = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    } else {
+      fold_chunks(st, cj, cphase, a_done, cpg, ignored, true);
+    }
 
     // ---- CTA reduce; the other warps go on to the next row's chunks while warp 0 combines ----
     if (!ignored) {
@@ -614,7 +701,10 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
           // x[target] if it lies in this CTA's slice: chunk c of the row belongs to group c % G
           float xt = 0.f;
           const int64_t tl = t - slice_elem0;
-          if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
+          if (kKeep) {  // saved by its owner during the sweep (ordered by the barrier above); 0 when another CTA holds the target
+            xt = tail->xt_kept;
+            tail->xt_kept = 0.f;
+          } else if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
             const uint32_t c = static_cast<uint32_t>(tl / elems_per_chunk);
             const uint32_t off = static_cast<uint32_t>(tl - c * elems_per_chunk);
             const uint32_t og = c % G, ocl = c / G;
@@ -645,7 +735,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     st.m2 = -CUDART_INF_F;
     st.s[0] = st.s[1] = st.sx[0] = st.sx[1] = make_float2(0.f, 0.f);
     a_done = 0;
-    if (k + 1 < nrows_local) {
+    if (!kKeep && k + 1 < nrows_local) {
       uint32_t nj = cj + cpg, nph = cphase;
       if (nj >= nbg) {
         nj -= nbg;
@@ -704,6 +794,40 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
       // x[target] with the same arithmetic and a single rounding.
       const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
+      if constexpr (kKeep) {
+        // the chunks hold 2^(x log2e - mref): the gradient is that times 2^(mref - lse2) * scale, minus the smoothing share
+        uint32_t j = cj;
+#pragma unroll
+        for (int cl = 0; cl < kKeepChunks; ++cl) {
+          if (static_cast<uint32_t>(cl) < cpg) {
+            const uint32_t u0 = (cl * G + grp) * kChunkUnits;
+            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+            unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
+            uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
+            if (!ignored) {
+              const float mr = mref[cl] == -CUDART_INF_F ? 0.f : mref[cl];  // the sweep scaled an all -inf chunk by 2^0
+              const float factor = ex2(mr + neg_lse2.x) * scale;
+              const float2 factor2 = make_float2(factor, factor);
+              if (len == kChunkUnits) {
+                uint4 r[NV];
+#pragma unroll
+                for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+#pragma unroll
+                for (int q = 0; q < NV; ++q) buf[q * TG] = grad_from_kept<T>(r[q], factor2, nsub2);
+              } else {
+                for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_from_kept<T>(buf[v - gt], factor2, nsub2);
+              }
+              if (static_cast<uint32_t>(cl) == t_cl) reinterpret_cast<T*>(chunk)[t_off] = from_float<T>(g_target);
+            } else {
+              for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready0 + 8 * j);
+            if (++j == nbg) j = 0;
+          }
+        }
+      } else {
       uint32_t j = cj;
       for (uint32_t cl = 0; cl < cpg; ++cl) {
         const uint32_t u0 = (cl * G + grp) * kChunkUnits;
@@ -734,6 +858,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         __syncwarp();
         if (lane == 0) mbar_arrive(ready0 + 8 * j);
         if (++j == nbg) j = 0;
+      }
       }
     }
 
@@ -774,9 +899,9 @@ bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, Resid
   return true;
 }
 
-template <typename T, int CLUSTER, bool SUMX, int MODE>
+template <typename T, int CLUSTER, bool SUMX, int MODE, bool KEEP = false>
 int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
-  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX, MODE>;
+  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX, MODE, KEEP>;
   const size_t smem = resident_smem_bytes(rp.nbuf);
   static thread_local int configured_device = -1;  // per (instantiation, thread): attribute set for this device
   int dev = 0;
@@ -833,6 +958,13 @@ int launch_resident(ResidentParams rp, cudaStream_t st) {
   if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
   if (rp.mode == 2) return launch_resident_cfg<T, CLUSTER, false, 2>(rp, st);
   const bool sumx = rp.p.label_smoothing != 0.f;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    // bf16 with a gradient: keep the exponentials of the statistics sweep (see ce_resident_kernel)
+    if (g_ce_keep != 0 && rp.p.grad && rp.nch / kGroups <= static_cast<uint32_t>(kKeepChunks)) {
+      rp.window = 0;
+      return sumx ? launch_resident_cfg<T, CLUSTER, true, 0, true>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0, true>(rp, st);
+    }
+  }
   return sumx ? launch_resident_cfg<T, CLUSTER, true, 0>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0>(rp, st);
 }
 
@@ -921,10 +1053,15 @@ int ce_dispatch(const CEParams& p, cudaStream_t st) {
 }  // namespace sb
 
 // Tuning hook for benchmarks: key 1 = force the kernel family (-1 automatic, 0 generic, 1/2/4 resident cluster size); key 2 = chunks of the
-// next row folded during the statistics exchange (-1 automatic).
+// next row folded during the statistics exchange (-1 automatic); key 3 = bf16 gradients from kept exponentials (1, default) or
+// recomputed (0).
 extern "C" int sb_set_tuning(int32_t key, int32_t value) {
   if (key == 1 && (value == -1 || value == 0 || value == 1 || value == 2 || value == 4)) {
     sb::g_ce_force_variant = value;
+    return SB_OK;
+  }
+  if (key == 3 && (value == 0 || value == 1)) {
+    sb::g_ce_keep = value;
     return SB_OK;
   }
   if (key == 2 && value >= -1 && value <= 64) {
