@@ -164,7 +164,7 @@ def algorithmic_bytes(rows, classes, elem_size):
 # profiles/ (the bf16 figure is the 4096-row capture scaled by 8: traffic is proportional to rows).
 TRAFFIC = {
     ("ce_fp32_4096x32000", 4096): 524.488192e6 + 469.110272e6,
-    ("ce_bf16_32768x128256", 32768): 8 * (998.434048e6 + 995.995392e6),
+    ("ce_bf16_32768x128256", 32768): 8 * (998.447616e6 + 995.276288e6),
 }
 
 

@@ -397,7 +397,7 @@ __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
   return U::pack(f);
 }
 
-// kKeep (cross entropy on bf16 logits, at most kKeepChunks chunks per group and row): the statistics sweep overwrites
+// kKeep (cross entropy on 16-bit logits, at most kKeepChunks chunks per group and row): the statistics sweep overwrites
 // each chunk with its exponentials 2^(x log2e - m), m being the thread's running maximum at that chunk, and the gradient
 // sweep only rescales them: one ex2 per logit instead of two and a third fewer instructions, which is what limits this
 // kernel on bf16 (special-function unit, issue slots and, under sustained load, the power cap).  The kept value is
@@ -958,8 +958,9 @@ int launch_resident(ResidentParams rp, cudaStream_t st) {
   if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
   if (rp.mode == 2) return launch_resident_cfg<T, CLUSTER, false, 2>(rp, st);
   const bool sumx = rp.p.label_smoothing != 0.f;
-  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-    // bf16 with a gradient: keep the exponentials of the statistics sweep (see ce_resident_kernel)
+  if constexpr (sizeof(T) == 2) {
+    // 16-bit logits with a gradient: keep the exponentials of the statistics sweep (see ce_resident_kernel); in fp16 a kept
+    // value below 2^-14 is subnormal, an absolute error of at most 2^-25 on a probability
     if (g_ce_keep != 0 && rp.p.grad && rp.nch / kGroups <= static_cast<uint32_t>(kKeepChunks)) {
       rp.window = 0;
       return sumx ? launch_resident_cfg<T, CLUSTER, true, 0, true>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0, true>(rp, st);
