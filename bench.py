@@ -27,8 +27,8 @@ sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
     # name: (rows per GPU, classes, dtype, ignore fraction, label smoothing)
-    "ce_bf16_32768x128256": (32768, 128256, "bfloat16", 0.05, 0.1),   # BASELINE.json configs[4]
-    "ce_fp32_4096x32000": (4096, 32000, "float32", 0.0, 0.0),          # BASELINE.json configs[0]
+    "ce_bf16_32768x128256": (32768, 128256, "bfloat16", 0.05, 0.1),   # the headline configuration
+    "ce_fp32_4096x32000": (4096, 32000, "float32", 0.0, 0.0),          # the reference's own CPU-runnable case
 }
 DEFAULT_WORKLOAD = "ce_bf16_32768x128256"
 
