@@ -304,7 +304,23 @@ typedef enum sb_ew_op {
   SB_EW_BCE_LOGITS_BWD = 20,    /* alpha * in2(upstream gradient) * (sigmoid(x) - t) */
   SB_EW_BCE_LOGITS_PW_BWD = 21, /* alpha * (lw * sigmoid(x) - pw * t), in2 = pos_weight */
   SB_EW_SIGMOID = 22,           /* unary */
-  SB_EW_OP_COUNT = 23
+  /* Neighbouring TensorIterator operators of the external native-op library, served by the same engine. */
+  SB_EW_TANH = 23,              /* unary */
+  SB_EW_EXP = 24,               /* unary */
+  SB_EW_LOG = 25,               /* unary */
+  SB_EW_SIGMOID_BWD = 26,       /* in0(grad) * y * (1 - y), in1 = y = sigmoid output */
+  SB_EW_TANH_BWD = 27,          /* in0(grad) * (1 - y * y), in1 = y = tanh output */
+  SB_EW_MAXIMUM = 28,           /* NaN propagates */
+  SB_EW_MINIMUM = 29,
+  SB_EW_EQ = 30,                /* comparisons: 1 or 0 in the compute type, stored as the output dtype (bool) */
+  SB_EW_NE = 31,
+  SB_EW_LT = 32,
+  SB_EW_LE = 33,
+  SB_EW_GT = 34,
+  SB_EW_GE = 35,
+  SB_EW_WHERE = 36,             /* in0(condition) ? in1 : in2 */
+  SB_EW_MASKED_FILL = 37,       /* in1(mask) ? scalar : in0 */
+  SB_EW_OP_COUNT = 38
 } sb_ew_op;
 
 typedef struct sb_ew_desc {

@@ -293,6 +293,76 @@ def test_reduction_dtype_rules(supa):
     _close(x_cpu.float().sum(1), out, loosen=40)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(16,), (1024, 512), (1023, 511), (3, 5, 7)])
+def test_neighbouring_unary_ops_forward_backward(supa, shape, dtype):
+    """sigmoid / tanh / exp / log and their autograd formulas (sigmoid_backward, tanh_backward, mul, div) on the device."""
+    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+
+    for name, fn, positive in (("sigmoid", torch.sigmoid, False), ("tanh", torch.tanh, False), ("exp", torch.exp, False),
+                               ("log", torch.log, True)):
+        x_cpu, x = _pair(shape, dtype, seed=len(name), requires_grad=True)
+        if positive:
+            x_cpu = (x_cpu.detach().abs() + 0.5).requires_grad_(True)
+            x = x_cpu.detach().to(supa).requires_grad_(True)
+        g_cpu, g = _pair(shape, dtype, seed=9)
+        y = fn(x)
+        # the CPU golden runs in the same dtype: the backward formulas start from the rounded forward result on both sides
+        xr = x_cpu.detach().clone().requires_grad_(True)
+        yr = fn(xr)
+        assert_allclose(yr.detach(), y.detach(), RTOL[dtype] * 4, ATOL[dtype] * 4)
+        y.backward(g)
+        yr.backward(g_cpu)
+        assert_allclose(xr.grad, x.grad, RTOL[dtype] * 8, max(ATOL[dtype] * 8, 2e-2 if dtype != torch.float32 else 0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32, torch.int64])
+def test_comparisons_extrema_where_masked_fill(supa, dtype):
+    g = torch.Generator().manual_seed(4)
+    if dtype.is_floating_point:
+        a_cpu = torch.randn(37, 129, generator=g).to(dtype)
+        b_cpu = torch.randn(37, 129, generator=g).to(dtype)
+        b_cpu[::3] = a_cpu[::3]
+    else:
+        a_cpu = torch.randint(-5, 6, (37, 129), generator=g, dtype=dtype)
+        b_cpu = torch.randint(-5, 6, (37, 129), generator=g, dtype=dtype)
+    a, b = a_cpu.to(supa), b_cpu.to(supa)
+    for op in (torch.eq, torch.ne, torch.lt, torch.le, torch.gt, torch.ge):
+        out = op(a, b)
+        assert out.dtype == torch.bool and torch.equal(out.cpu(), op(a_cpu, b_cpu)), op.__name__
+        out = op(a, 1)
+        assert torch.equal(out.cpu(), op(a_cpu, 1)), op.__name__ + " scalar"
+        out = op(a, b[0])                                     # broadcast row
+        assert torch.equal(out.cpu(), op(a_cpu, b_cpu[0])), op.__name__ + " broadcast"
+    assert torch.equal(torch.maximum(a, b).cpu(), torch.maximum(a_cpu, b_cpu))
+    assert torch.equal(torch.minimum(a, b).cpu(), torch.minimum(a_cpu, b_cpu))
+    cond_cpu = a_cpu > b_cpu
+    cond = cond_cpu.to(supa)
+    assert torch.equal(torch.where(cond, a, b).cpu(), torch.where(cond_cpu, a_cpu, b_cpu))
+    assert torch.equal(torch.where(cond[:, :1], a, b).cpu(), torch.where(cond_cpu[:, :1], a_cpu, b_cpu))
+    filled = a.clone().masked_fill_(cond, 3)
+    assert torch.equal(filled.cpu(), a_cpu.clone().masked_fill_(cond_cpu, 3))
+    assert torch.equal(a.masked_fill(cond[0], -2).cpu(), a_cpu.masked_fill(cond_cpu[0], -2))   # functional form, broadcast mask
+    if dtype.is_floating_point:
+        n_cpu = a_cpu.clone()
+        n_cpu[1, 2] = float("nan")
+        n = n_cpu.to(supa)
+        assert torch.equal(torch.isnan(torch.maximum(n, b).cpu()), torch.isnan(torch.maximum(n_cpu, b_cpu)))
+        assert torch.equal(torch.isnan(torch.minimum(b, n).cpu()), torch.isnan(torch.minimum(b_cpu, n_cpu)))
+        assert not bool((n == n).cpu()[1, 2]) and bool((n != n).cpu()[1, 2])
+
+
+def test_cross_entropy_weights_with_label_smoothing_is_refused_loudly(supa):
+    """Class weights together with label smoothing are not fused, and libtorch's composite for them needs operators
+    outside this path (bitwise_not, ...): the call raises and names the missing operator; nothing falls back to the CPU."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(24, 50, generator=g).to(supa)
+    t = torch.randint(0, 50, (24,), generator=g).to(supa)
+    w = (torch.rand(50, generator=g) + 0.5).to(supa)
+    with pytest.raises(NotImplementedError, match="supa"):
+        F.cross_entropy(x, t, weight=w, label_smoothing=0.1)
+
+
 # ---- softmax / nll -------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), -1), ((1025, 513), 0), ((64, 32000), -1),

@@ -24,7 +24,8 @@ STATUS_TARGET_OUT_OF_RANGE = 0x1
 # sb_ew_op
 (EW_COPY, EW_FILL, EW_ADD, EW_MUL, EW_SUB, EW_DIV, EW_GELU_ERF, EW_GELU_TANH, EW_SILU, EW_GLU, EW_GELU_ERF_BWD,
  EW_GELU_TANH_BWD, EW_SILU_BWD, EW_GLU_BWD_A, EW_GLU_BWD_B, EW_ADD_SCALAR, EW_MUL_SCALAR, EW_NEG, EW_BCE_LOGITS,
- EW_BCE_LOGITS_PW, EW_BCE_LOGITS_BWD, EW_BCE_LOGITS_PW_BWD, EW_SIGMOID) = range(23)
+ EW_BCE_LOGITS_PW, EW_BCE_LOGITS_BWD, EW_BCE_LOGITS_PW_BWD, EW_SIGMOID, EW_TANH, EW_EXP, EW_LOG, EW_SIGMOID_BWD, EW_TANH_BWD,
+ EW_MAXIMUM, EW_MINIMUM, EW_EQ, EW_NE, EW_LT, EW_LE, EW_GT, EW_GE, EW_WHERE, EW_MASKED_FILL) = range(38)
 # sb_reduce_op
 RED_SUM, RED_MEAN, RED_AMAX, RED_AMIN = range(4)
 

@@ -10,6 +10,7 @@
 #include <ATen/native/BinaryOps.h>
 #include <ATen/native/DispatchStub.h>
 #include <ATen/native/ReduceOps.h>
+#include <ATen/native/TensorCompare.h>
 #include <ATen/native/TensorIterator.h>
 #include <ATen/native/UnaryOps.h>
 
@@ -175,6 +176,24 @@ void silu_backward_kernel(at::TensorIteratorBase& iter) { launch_elementwise(ite
 // glu: the iterator's inputs are the two halves of the split dimension (strided views).
 void glu_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_GLU, iter.common_dtype()); }
 
+// Neighbouring TensorIterator operators on the same engine.
+void sigmoid_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_SIGMOID, iter.common_dtype()); }
+void tanh_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_TANH, iter.common_dtype()); }
+void exp_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_EXP, iter.common_dtype()); }
+void log_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_LOG, iter.common_dtype()); }
+void sigmoid_backward_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_SIGMOID_BWD, iter.common_dtype()); }
+void tanh_backward_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_TANH_BWD, iter.common_dtype()); }
+void maximum_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_MAXIMUM, -1, false, 1.0, 1); }
+void minimum_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_MINIMUM, -1, false, 1.0, 1); }
+void eq_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_EQ, -1, false, 1.0, 1); }
+void ne_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_NE, -1, false, 1.0, 1); }
+void lt_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_LT, -1, false, 1.0, 1); }
+void le_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_LE, -1, false, 1.0, 1); }
+void gt_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_GT, -1, false, 1.0, 1); }
+void ge_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_GE, -1, false, 1.0, 1); }
+// where(condition, self, other): operand 1 is the condition; the values share a dtype (libtorch promotes them first)
+void where_kernel_supa(at::TensorIterator& iter) { launch_elementwise(iter, SB_EW_WHERE, iter.dtype(2)); }
+
 void sum_kernel(at::TensorIterator& iter) { launch_reduce(iter, SB_RED_SUM); }
 void mean_kernel(at::TensorIterator& iter) { launch_reduce(iter, SB_RED_MEAN); }
 void max_values_kernel(at::TensorIterator& iter) { launch_reduce(iter, SB_RED_AMAX); }
@@ -231,6 +250,21 @@ REGISTER_PRIVATEUSE1_DISPATCH(GeluBackwardKernel, &supa::gelu_backward_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(silu_stub, &supa::silu_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(silu_backward_stub, &supa::silu_backward_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(glu_stub, &supa::glu_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(sigmoid_stub, &supa::sigmoid_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(tanh_stub, &supa::tanh_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(exp_stub, &supa::exp_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(log_stub, &supa::log_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(sigmoid_backward_stub, &supa::sigmoid_backward_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(tanh_backward_stub, &supa::tanh_backward_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(maximum_stub, &supa::maximum_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(minimum_stub, &supa::minimum_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(eq_stub, &supa::eq_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(ne_stub, &supa::ne_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(lt_stub, &supa::lt_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(le_stub, &supa::le_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(gt_stub, &supa::gt_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(ge_stub, &supa::ge_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(where_kernel, &supa::where_kernel_supa)
 REGISTER_PRIVATEUSE1_DISPATCH(sum_stub, &supa::sum_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(mean_stub, &supa::mean_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(max_values_stub, &supa::max_values_kernel)

@@ -14,6 +14,21 @@
 #include <ATen/ops/as_strided_native.h>
 #include <ATen/ops/as_strided_ops.h>
 #include <ATen/ops/div_native.h>
+#include <ATen/ops/eq_native.h>
+#include <ATen/ops/exp_native.h>
+#include <ATen/ops/ge_native.h>
+#include <ATen/ops/gt_native.h>
+#include <ATen/ops/le_native.h>
+#include <ATen/ops/log_native.h>
+#include <ATen/ops/lt_native.h>
+#include <ATen/ops/maximum_native.h>
+#include <ATen/ops/minimum_native.h>
+#include <ATen/ops/ne_native.h>
+#include <ATen/ops/sigmoid_backward_native.h>
+#include <ATen/ops/sigmoid_native.h>
+#include <ATen/ops/tanh_backward_native.h>
+#include <ATen/ops/tanh_native.h>
+#include <ATen/ops/where_native.h>
 #include <ATen/ops/gelu_backward_meta.h>
 #include <ATen/ops/gelu_meta.h>
 #include <ATen/ops/glu_native.h>
@@ -226,6 +241,81 @@ SUPA_BINARY(div, at::native::structured_div_out)              // impl: div_true_
 SUPA_UNARY(neg, at::native::structured_neg_out)
 SUPA_UNARY(silu, at::native::structured_silu_out)
 
+// ---- neighbouring operators served by the same engine -----------------------------------------------------------
+SUPA_UNARY(sigmoid, at::native::structured_sigmoid_out)
+SUPA_UNARY(tanh, at::native::structured_tanh_out)
+SUPA_UNARY(exp, at::native::structured_exp_out)
+SUPA_UNARY(log, at::native::structured_log_out)
+SUPA_BINARY(maximum, at::native::structured_maximum_out)
+SUPA_BINARY(minimum, at::native::structured_minimum_out)
+SUPA_BINARY(sigmoid_backward, at::native::structured_sigmoid_backward_out)  // (grad_output, output)
+SUPA_BINARY(tanh_backward, at::native::structured_tanh_backward_out)
+SUPA_BINARY(eq, at::native::structured_eq_Tensor_out)
+SUPA_BINARY(ne, at::native::structured_ne_Tensor_out)
+SUPA_BINARY(lt, at::native::structured_lt_Tensor_out)
+SUPA_BINARY(le, at::native::structured_le_Tensor_out)
+SUPA_BINARY(gt, at::native::structured_gt_Tensor_out)
+SUPA_BINARY(ge, at::native::structured_ge_Tensor_out)
+
+// comparison with a Scalar: the meta step wraps the scalar into a 0-dim CPU tensor, which the stub lifts
+#define SUPA_COMPARE_SCALAR(NAME, BASE)                                                                                 \
+  at::Tensor NAME##_scalar(const at::Tensor& self, const at::Scalar& other) {                                           \
+    return run_functional<BASE>(                                                                                        \
+        self.device(), [&](auto& op) { op.meta(self, other); }, [&](auto& op, const at::Tensor& out) { op.impl(self, other, out); }); \
+  }                                                                                                                     \
+  at::Tensor& NAME##_scalar_(at::Tensor& self, const at::Scalar& other) {                                              \
+    return run_inplace<BASE>(                                                                                           \
+        self.device(), self, [&](auto& op) { op.meta(self, other); }, [&](auto& op, const at::Tensor& out) { op.impl(self, other, out); }); \
+  }                                                                                                                     \
+  at::Tensor& NAME##_scalar_out(const at::Tensor& self, const at::Scalar& other, at::Tensor& out) {                    \
+    return run_out<BASE>(                                                                                               \
+        self.device(), out, [&](auto& op) { op.meta(self, other); }, [&](auto& op, const at::Tensor& o) { op.impl(self, other, o); }); \
+  }
+SUPA_COMPARE_SCALAR(eq, at::native::structured_eq_Scalar_out)
+SUPA_COMPARE_SCALAR(ne, at::native::structured_ne_Scalar_out)
+SUPA_COMPARE_SCALAR(lt, at::native::structured_lt_Scalar_out)
+SUPA_COMPARE_SCALAR(le, at::native::structured_le_Scalar_out)
+SUPA_COMPARE_SCALAR(gt, at::native::structured_gt_Scalar_out)
+SUPA_COMPARE_SCALAR(ge, at::native::structured_ge_Scalar_out)
+
+// where: libtorch's own functions promote the values and build the iterator; the kernel comes through where_kernel
+at::Tensor where_self(const at::Tensor& condition, const at::Tensor& self, const at::Tensor& other) {
+  const c10::DeviceGuard guard(condition.device());
+  return at::native::where(condition, self, other);
+}
+at::Tensor& where_self_out(const at::Tensor& condition, const at::Tensor& self, const at::Tensor& other, at::Tensor& out) {
+  const c10::DeviceGuard guard(condition.device());
+  return at::native::where_self_out(condition, self, other, out);
+}
+
+// masked_fill_(self, mask, value): self[mask] = value; the mask broadcasts against self
+at::Tensor& masked_fill_scalar_(at::Tensor& self, const at::Tensor& mask, const at::Scalar& value) {
+  TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_fill_ only supports boolean masks, but got mask with dtype ", mask.scalar_type());
+  TORCH_CHECK(is_supa(mask) && mask.device() == self.device(), "masked_fill_: expected self and mask on the same supa device");
+  const c10::DeviceGuard guard(self.device());
+  auto iter = at::TensorIteratorConfig()
+                  .set_check_mem_overlap(false)
+                  .check_all_same_dtype(false)
+                  .resize_outputs(false)
+                  .add_output(self)
+                  .add_const_input(self)
+                  .add_const_input(mask)
+                  .build();
+  if (iter.numel() == 0) return self;
+  const at::ScalarType dt = self.scalar_type();
+  double d = 0.0;
+  int64_t i = 0;
+  if (c10::isFloatingType(dt)) d = value.to<double>();
+  else if (dt == at::kBool) i = value.to<bool>() ? 1 : 0;
+  else i = value.to<int64_t>();
+  launch_elementwise(iter, SB_EW_MASKED_FILL, dt, 1.0, 1, d, i);
+  return self;
+}
+at::Tensor& masked_fill_tensor_(at::Tensor& self, const at::Tensor& mask, const at::Tensor& value) {
+  TORCH_CHECK(value.dim() == 0, "masked_fill_ only supports a 0-dimensional value tensor, but got tensor with ", value.dim(), " dimension(s).");
+  return masked_fill_scalar_(self, mask, value.item());
+}
+
 // silu_backward(grad_output, self)
 at::Tensor silu_backward(const at::Tensor& grad_output, const at::Tensor& self) {
   return run_functional<at::native::structured_silu_backward_out>(
@@ -395,6 +485,31 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("neg", TORCH_FN(supa::neg));
   m.impl("neg_", TORCH_FN(supa::neg_));
   m.impl("neg.out", TORCH_FN(supa::neg_out));
+#define SUPA_REG_UNARY(NAME) \
+  m.impl(#NAME, TORCH_FN(supa::NAME)); m.impl(#NAME "_", TORCH_FN(supa::NAME##_)); m.impl(#NAME ".out", TORCH_FN(supa::NAME##_out));
+  SUPA_REG_UNARY(sigmoid) SUPA_REG_UNARY(tanh) SUPA_REG_UNARY(exp) SUPA_REG_UNARY(log)
+#undef SUPA_REG_UNARY
+  m.impl("maximum", TORCH_FN(supa::maximum_tensor));
+  m.impl("maximum.out", TORCH_FN(supa::maximum_out));
+  m.impl("minimum", TORCH_FN(supa::minimum_tensor));
+  m.impl("minimum.out", TORCH_FN(supa::minimum_out));
+  m.impl("sigmoid_backward", TORCH_FN(supa::sigmoid_backward_tensor));
+  m.impl("sigmoid_backward.grad_input", TORCH_FN(supa::sigmoid_backward_out));
+  m.impl("tanh_backward", TORCH_FN(supa::tanh_backward_tensor));
+  m.impl("tanh_backward.grad_input", TORCH_FN(supa::tanh_backward_out));
+#define SUPA_REG_COMPARE(NAME)                                        \
+  m.impl(#NAME ".Tensor", TORCH_FN(supa::NAME##_tensor));             \
+  m.impl(#NAME "_.Tensor", TORCH_FN(supa::NAME##_tensor_));           \
+  m.impl(#NAME ".Tensor_out", TORCH_FN(supa::NAME##_out));            \
+  m.impl(#NAME ".Scalar", TORCH_FN(supa::NAME##_scalar));             \
+  m.impl(#NAME "_.Scalar", TORCH_FN(supa::NAME##_scalar_));           \
+  m.impl(#NAME ".Scalar_out", TORCH_FN(supa::NAME##_scalar_out));
+  SUPA_REG_COMPARE(eq) SUPA_REG_COMPARE(ne) SUPA_REG_COMPARE(lt) SUPA_REG_COMPARE(le) SUPA_REG_COMPARE(gt) SUPA_REG_COMPARE(ge)
+#undef SUPA_REG_COMPARE
+  m.impl("where.self", TORCH_FN(supa::where_self));
+  m.impl("where.self_out", TORCH_FN(supa::where_self_out));
+  m.impl("masked_fill_.Scalar", TORCH_FN(supa::masked_fill_scalar_));
+  m.impl("masked_fill_.Tensor", TORCH_FN(supa::masked_fill_tensor_));
   m.impl("silu", TORCH_FN(supa::silu));
   m.impl("silu_", TORCH_FN(supa::silu_));
   m.impl("silu.out", TORCH_FN(supa::silu_out));

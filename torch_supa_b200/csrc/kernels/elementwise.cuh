@@ -280,19 +280,58 @@ SB_DEFINE_OP(SB_EW_SIGMOID, 1, {
   if constexpr (std::is_floating_point<CT>::value) return sigmoid_t<FAST, CT>(a);
   else return a;
 })
+SB_DEFINE_OP(SB_EW_TANH, 1, {
+  if constexpr (std::is_floating_point<CT>::value) return tanh_t<FAST, CT>(a);
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_EXP, 1, {
+  if constexpr (std::is_floating_point<CT>::value) return exp_t<CT>(a);
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_LOG, 1, {
+  if constexpr (std::is_same<CT, double>::value) return log(a);
+  else if constexpr (std::is_same<CT, float>::value) return logf(a);
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_SIGMOID_BWD, 2, {
+  if constexpr (std::is_floating_point<CT>::value) return a * (CT(1) - b) * b;
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_TANH_BWD, 2, {
+  if constexpr (std::is_floating_point<CT>::value) return a * (CT(1) - b * b);
+  else return a;
+})
+SB_DEFINE_OP(SB_EW_MAXIMUM, 2, {
+  if constexpr (std::is_same<CT, bool>::value) return a || b;
+  else if constexpr (std::is_floating_point<CT>::value) return (a != a) ? a : ((b != b) ? b : (a > b ? a : b));
+  else return a > b ? a : b;
+})
+SB_DEFINE_OP(SB_EW_MINIMUM, 2, {
+  if constexpr (std::is_same<CT, bool>::value) return a && b;
+  else if constexpr (std::is_floating_point<CT>::value) return (a != a) ? a : ((b != b) ? b : (a < b ? a : b));
+  else return a < b ? a : b;
+})
+SB_DEFINE_OP(SB_EW_EQ, 2, return static_cast<CT>(a == b);)
+SB_DEFINE_OP(SB_EW_NE, 2, return static_cast<CT>(a != b);)
+SB_DEFINE_OP(SB_EW_LT, 2, return static_cast<CT>(a < b);)
+SB_DEFINE_OP(SB_EW_LE, 2, return static_cast<CT>(a <= b);)
+SB_DEFINE_OP(SB_EW_GT, 2, return static_cast<CT>(a > b);)
+SB_DEFINE_OP(SB_EW_GE, 2, return static_cast<CT>(a >= b);)
+SB_DEFINE_OP(SB_EW_WHERE, 3, return a != CT(0) ? b : c;)
+SB_DEFINE_OP(SB_EW_MASKED_FILL, 2, return b != CT(0) ? s.scalar : a;)
 #undef SB_DEFINE_OP
 
 __host__ __device__ inline int ew_arity(int op) {
   switch (op) {
     case SB_EW_FILL: return 0;
     case SB_EW_COPY: case SB_EW_GELU_ERF: case SB_EW_GELU_TANH: case SB_EW_SILU: case SB_EW_ADD_SCALAR:
-    case SB_EW_MUL_SCALAR: case SB_EW_NEG: case SB_EW_SIGMOID: return 1;
-    case SB_EW_GLU_BWD_B: case SB_EW_BCE_LOGITS_PW: case SB_EW_BCE_LOGITS_BWD: case SB_EW_BCE_LOGITS_PW_BWD: return 3;
+    case SB_EW_MUL_SCALAR: case SB_EW_NEG: case SB_EW_SIGMOID: case SB_EW_TANH: case SB_EW_EXP: case SB_EW_LOG: return 1;
+    case SB_EW_GLU_BWD_B: case SB_EW_BCE_LOGITS_PW: case SB_EW_BCE_LOGITS_BWD: case SB_EW_BCE_LOGITS_PW_BWD: case SB_EW_WHERE: return 3;
     default: return 2;
   }
 }
 __host__ __device__ inline bool ew_float_only(int op) {
-  return op == SB_EW_DIV || (op >= SB_EW_GELU_ERF && op <= SB_EW_GLU_BWD_B) || (op >= SB_EW_BCE_LOGITS && op <= SB_EW_SIGMOID);
+  return op == SB_EW_DIV || (op >= SB_EW_GELU_ERF && op <= SB_EW_GLU_BWD_B) || (op >= SB_EW_BCE_LOGITS && op <= SB_EW_TANH_BWD);
 }
 
 // Runtime-op evaluation for paths 2 and 3 (a uniform switch per element; those paths are bound by
@@ -302,7 +341,9 @@ __device__ __forceinline__ CT ew_apply_runtime(int op, CT a, CT b, CT c, const O
   switch (op) {
 #define SB_CASE(OPCODE) case OPCODE: return EwOp<OPCODE, CT, false>::apply(a, b, c, s);
     SB_CASE(SB_EW_COPY) SB_CASE(SB_EW_FILL) SB_CASE(SB_EW_ADD) SB_CASE(SB_EW_MUL) SB_CASE(SB_EW_SUB)
-    SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG)
+    SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG) SB_CASE(SB_EW_MAXIMUM) SB_CASE(SB_EW_MINIMUM)
+    SB_CASE(SB_EW_EQ) SB_CASE(SB_EW_NE) SB_CASE(SB_EW_LT) SB_CASE(SB_EW_LE) SB_CASE(SB_EW_GT) SB_CASE(SB_EW_GE)
+    SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL)
 #undef SB_CASE
     default: break;
   }
@@ -312,7 +353,8 @@ __device__ __forceinline__ CT ew_apply_runtime(int op, CT a, CT b, CT c, const O
       SB_CASE(SB_EW_DIV) SB_CASE(SB_EW_GELU_ERF) SB_CASE(SB_EW_GELU_TANH) SB_CASE(SB_EW_SILU) SB_CASE(SB_EW_GLU)
       SB_CASE(SB_EW_GELU_ERF_BWD) SB_CASE(SB_EW_GELU_TANH_BWD) SB_CASE(SB_EW_SILU_BWD) SB_CASE(SB_EW_GLU_BWD_A)
       SB_CASE(SB_EW_GLU_BWD_B) SB_CASE(SB_EW_BCE_LOGITS) SB_CASE(SB_EW_BCE_LOGITS_PW) SB_CASE(SB_EW_BCE_LOGITS_BWD)
-      SB_CASE(SB_EW_BCE_LOGITS_PW_BWD) SB_CASE(SB_EW_SIGMOID)
+      SB_CASE(SB_EW_BCE_LOGITS_PW_BWD) SB_CASE(SB_EW_SIGMOID) SB_CASE(SB_EW_TANH) SB_CASE(SB_EW_EXP) SB_CASE(SB_EW_LOG)
+      SB_CASE(SB_EW_SIGMOID_BWD) SB_CASE(SB_EW_TANH_BWD)
 #undef SB_CASE
       default: break;
     }
