@@ -157,48 +157,53 @@ __global__ void __launch_bounds__(256) nd_fwd_final_kernel(const double2* __rest
   }
 }
 
-// Backward: a thread owns VEC consecutive samples of one outer row and writes their value in every class plane.
+// Backward: a CTA owns a tile of 256 * VEC * kBwdUnroll consecutive samples of one outer row; a thread owns kBwdUnroll
+// vectors of it, 256 vectors apart, and writes their values in every class plane, so that the CTA writes 16 KB (fp32)
+// of contiguous memory per plane.
+constexpr int kBwdUnroll = 4;
 template <typename T, typename A, int VEC>
 __global__ void __launch_bounds__(256) nd_bwd_kernel(NdParams p, const T* __restrict__ grad_output, const T* __restrict__ total_weight,
-                                                     T* __restrict__ grad_input) {
+                                                     T* __restrict__ grad_input, uint32_t tiles_per_row) {
   const T* w = static_cast<const T*>(p.weight);
-  const int64_t per_row = p.inner / VEC;  // VEC divides inner (the launcher picks VEC accordingly)
-  const int64_t items = p.outer * per_row;
   A gscale = A(1);
   if (p.reduction != SB_REDUCTION_NONE) {
     gscale = convert<A, T>(grad_output[0]);
     if (p.reduction == SB_REDUCTION_MEAN) gscale = gscale / convert<A, T>(*total_weight);
   }
-  for (int64_t it = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; it < items; it += static_cast<int64_t>(gridDim.x) * 256) {
-    int64_t n, i0;
-    if (items <= 0xffffffffLL) {
-      const uint32_t n32 = static_cast<uint32_t>(it) / static_cast<uint32_t>(per_row);
-      n = n32;
-      i0 = static_cast<int64_t>(static_cast<uint32_t>(it) - n32 * static_cast<uint32_t>(per_row)) * VEC;
-    } else {
-      n = it / per_row;
-      i0 = (it - n * per_row) * VEC;
-    }
-    const int64_t s0 = n * p.inner + i0;
-    int64_t t[VEC];
-    A val[VEC];
+  const int64_t n = blockIdx.x / tiles_per_row;
+  const int64_t tile0 = static_cast<int64_t>(blockIdx.x % tiles_per_row) * (256 * VEC * kBwdUnroll);
+  int64_t t[kBwdUnroll][VEC];
+  A val[kBwdUnroll][VEC];
+  int64_t i0[kBwdUnroll];
+#pragma unroll
+  for (int u = 0; u < kBwdUnroll; ++u) {
+    i0[u] = tile0 + (static_cast<int64_t>(u) * 256 + threadIdx.x) * VEC;
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
-      val[k] = A(0);
-      if (!nd_counts(p, s0 + k, t[k])) {
-        t[k] = -1;
-      } else {
-        const A wt = w ? convert<A, T>(w[t[k]]) : A(1);
-        const A g = p.reduction == SB_REDUCTION_NONE ? convert<A, T>(grad_output[s0 + k]) : gscale;
-        val[k] = -wt * g;
+      val[u][k] = A(0);
+      t[u][k] = -1;
+      if (i0[u] < p.inner) {  // inner is a multiple of VEC: a vector is inside the row or outside it as a whole
+        const int64_t s = n * p.inner + i0[u] + k;
+        if (nd_counts(p, s, t[u][k])) {
+          const A wt = w ? convert<A, T>(w[t[u][k]]) : A(1);
+          const A g = p.reduction == SB_REDUCTION_NONE ? convert<A, T>(grad_output[s]) : gscale;
+          val[u][k] = -wt * g;
+        } else {
+          t[u][k] = -1;
+        }
       }
     }
-    T* dst = grad_input + (n * p.classes) * p.inner + i0;
-    for (int64_t c = 0; c < p.classes; ++c) {
-      A o[VEC];
+  }
+  T* row = grad_input + (n * p.classes) * p.inner;
+  for (int64_t c = 0; c < p.classes; ++c) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) o[k] = t[k] == c ? val[k] : A(0);
-      store_as<A, T, VEC>(dst + c * p.inner, o);
+    for (int u = 0; u < kBwdUnroll; ++u) {
+      if (i0[u] < p.inner) {
+        A o[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = t[u][k] == c ? val[u][k] : A(0);
+        store_as<A, T, VEC>(row + c * p.inner + i0[u], o);
+      }
     }
   }
 }
@@ -261,11 +266,12 @@ int nd_launch_fwd(const sb_nll_nd_args* a, void* output, void* total_weight, cud
 
 template <typename T, typename A, int VEC>
 int nd_launch_bwd_vec(const NdParams& p, const void* grad_output, const void* total_weight, void* grad_input, cudaStream_t st) {
-  const int64_t items = p.outer * (p.inner / VEC);
-  const int64_t ctas = (items + 255) / 256;
-  const int grid = static_cast<int>(ctas < 16LL * sm_count() ? ctas : 16LL * sm_count());
-  nd_bwd_kernel<T, A, VEC><<<grid, 256, 0, st>>>(p, static_cast<const T*>(grad_output), static_cast<const T*>(total_weight),
-                                                  static_cast<T*>(grad_input));
+  const int64_t tile = 256LL * VEC * kBwdUnroll;
+  const int64_t tiles_per_row = (p.inner + tile - 1) / tile;
+  if (tiles_per_row > 0xffffffffLL || p.outer * tiles_per_row > 0x7fffffffLL) return SB_ERR_TOO_LARGE;
+  nd_bwd_kernel<T, A, VEC><<<static_cast<unsigned>(p.outer * tiles_per_row), 256, 0, st>>>(
+      p, static_cast<const T*>(grad_output), static_cast<const T*>(total_weight), static_cast<T*>(grad_input),
+      static_cast<uint32_t>(tiles_per_row));
   return launch_status();
 }
 
