@@ -363,3 +363,45 @@ def test_row_chunks_with_in_place_gradient_equal_one_call(cuda_device, dtype):
     assert int(status.item()) == 0
     assert float(loss) == float(loss_ref), "per-row losses do not depend on how the rows are grouped"
     assert torch.equal(work, grad_ref)
+
+
+def test_headline_size_properties_and_row_subset(cuda_device):
+    """The benchmark's full configuration (bf16 [32768, 128256], 5 % ignored rows, label smoothing 0.1, mean): checks that
+    do not need a CPU pass over 8.4 GB — every ignored row's gradient is exactly zero, gradient rows sum to ~0, the loss
+    equals the mean of the per-row losses — plus a seeded 256-row subset against the CPU oracle."""
+    from torch_supa_b200 import functional as F2
+
+    rows, classes, eps = 32768, 128256, 0.1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = torch.empty(rows, classes, dtype=torch.bfloat16, device=cuda_device)
+    for r0 in range(0, rows, 2048):
+        logits[r0:r0 + 2048] = (torch.randn(2048, classes, device=cuda_device, generator=g) * 2).bfloat16()
+    cg = torch.Generator().manual_seed(1)
+    target = torch.randint(0, classes, (rows,), generator=cg)
+    ignored = torch.randperm(rows, generator=cg)[:1638]
+    target[ignored] = -100
+    target_d = target.to(cuda_device)
+    ws = F2.CrossEntropyWorkspace(rows, cuda_device)
+    loss, grad = F2.cross_entropy_forward_backward(logits, target_d, label_smoothing=eps, workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) == 0
+    count = rows - 1638
+    # (1) ignored rows: exactly zero gradient and zero loss
+    assert int(grad[ignored.to(cuda_device)].ne(0).sum()) == 0
+    assert float(ws.row_loss[ignored.to(cuda_device)].abs().max()) == 0.0
+    # (2) the scalar is the mean of the per-row losses (rounded to bf16)
+    want = float(ws.row_loss.double().sum()) / count
+    assert abs(float(loss) - want) <= 4e-3 * want
+    # (3) rows of the gradient sum to zero: softmax sums to 1 and so does the smoothed one-hot (bf16 rounding noise only)
+    pick = torch.randperm(rows, generator=cg)[:256]
+    pick = pick[target[pick] != -100]
+    sub_grad = grad[pick.to(cuda_device)].double()
+    assert float(sub_grad.sum(1).abs().max()) * count < 2e-2
+    # (4) the same rows against the CPU oracle (fp32 math on the bf16 logits), gradients scaled back by the row count
+    sub_logits = logits[pick.to(cuda_device)].float().cpu()
+    eloss, egrad, bad = oracle.c_cross_entropy(sub_logits.numpy(), target[pick].numpy(), -100, eps, "none")
+    assert bad == 0
+    assert_close(ws.row_loss[pick.to(cuda_device)].cpu().numpy(), eloss, 2e-6, 4e-6, "row losses")
+    assert_close(sub_grad.cpu().numpy() * count, egrad, 1.6e-2, 1e-4, "gradient subset")
+    del logits, grad
+    torch.cuda.empty_cache()
