@@ -138,6 +138,14 @@ def run_extras(device, peak_gbs, quick=False, profile=False):
     sm = device_randn((ls_rows, 32000), torch.float32, device, 12, 3.0)
     out.append(_entry(f"log_softmax(-1) fp32 [{ls_rows},32000]", 2 * ls_rows * 32000 * 4, time_op(lambda: F.log_softmax(sm, -1), iters=3 if not quick else 3),
                       peak_gbs))
+    if ls_rows <= 16384:
+        y = F.log_softmax(sm, -1)
+        go = device_randn((ls_rows, 32000), torch.float32, device, 18)
+        out.append(_entry(f"log_softmax backward fp32 [{ls_rows},32000] (2 reads, 1 write)", 3 * ls_rows * 32000 * 4,
+                          time_op(lambda: torch.ops.aten._log_softmax_backward_data(go, y, -1, torch.float32), iters=3), peak_gbs))
+        out.append(_entry(f"softmax(-1) fp32 [{ls_rows},32000]", 2 * ls_rows * 32000 * 4, time_op(lambda: F.softmax(sm, -1), iters=3),
+                          peak_gbs))
+        del y, go
     del sm
     torch.supa.empty_cache()
     # ---- beyond the headline configurations: nll_loss2d on a segmentation-shaped input ----
