@@ -4,11 +4,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Prints ONE JSON line.  A "step" is one pass of the fused cross entropy over one batch of synthetic
-logits: valid-row count, fused forward+backward sweep, deterministic loss sum (with the two scalar
-all-reduces between them when rows are sharded over several GPUs).  `value` is rows/s over all ranks
-with inputs resident in HBM; `e2e` repeats the step with the logits and targets copied from pinned
-host memory and the loss read back, inside the timed region.  `--impl reference` times the PyTorch
-CPU ATen path (the reference's own golden and CPU route) on the host cores for the same workload.
+logits: valid-row count, fused forward+backward sweep, deterministic loss sum.  With N GPUs the rows of
+the configuration are sharded over the ranks (strong scaling: rows / N each) and the two scalars of the
+mean are exchanged inside the count and loss kernels.  `value` is rows/s of the whole job with inputs
+resident in HBM, timed after a stretch of continuous load (`burst` is the same right after the warm-up);
+`e2e` repeats the step with the logits and targets copied from pinned host memory and the loss read back,
+inside the timed region; `extras` (N = 1) are the other configurations of the path.  `--impl reference`
+times the PyTorch CPU ATen path (the reference's own golden and CPU route) on the host cores.
 """
 from __future__ import annotations
 
@@ -26,7 +28,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
-    # name: (rows per GPU, classes, dtype, ignore fraction, label smoothing)
+    # name: (rows of the whole job, classes, dtype, ignore fraction, label smoothing)
     "ce_bf16_32768x128256": (32768, 128256, "bfloat16", 0.05, 0.1),   # the headline configuration
     "ce_fp32_4096x32000": (4096, 32000, "float32", 0.0, 0.0),          # the reference's own CPU-runnable case
 }
@@ -160,16 +162,35 @@ def algorithmic_bytes(rows, classes, elem_size):
     return 2 * rows * classes * elem_size + rows * 8
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused-sweep launch from the ncu captures summarised under
-# profiles/ (the bf16 figure is the 4096-row capture scaled by 8: traffic is proportional to rows).
-TRAFFIC = {
-    ("ce_fp32_4096x32000", 4096): 524.488192e6 + 469.110272e6,
-    ("ce_bf16_32768x128256", 32768): 8 * (998.447616e6 + 995.276288e6),
+def moved_bytes(rows, classes, elem_size, ignored_rows):
+    """What the fused sweep has to move: rows whose target is ignore_index are never read (their gradient, zeros, is
+    still written)."""
+    return algorithmic_bytes(rows, classes, elem_size) - ignored_rows * classes * elem_size
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE fused-sweep launch, from the ncu captures summarised under
+# profiles/ (ce_resident_kernel_*.md name the command and the commit of each capture).  The bf16 capture holds 4096 of
+# the 32768 rows; traffic is proportional to rows, so it is scaled by rows / 4096.  Reported only for the row counts
+# it can be scaled to; None otherwise.
+NCU_TRAFFIC_PER_ROW = {
+    "ce_fp32_4096x32000": (524.488192e6 + 469.110272e6) / 4096,
+    "ce_bf16_32768x128256": (998.447616e6 + 995.276288e6) / 4096,
 }
+KERNEL_NAMES = {0: "ce_rows_cta_kernel (two sweeps)", 1: "ce_resident_kernel (1 CTA per row)", 2: "ce_resident_kernel (2-CTA cluster per row)",
+                4: "ce_resident_kernel (4-CTA cluster per row)", 8: "ce_rows_reg_kernel (row in registers)"}
+
+
+def workload_config(args, world):
+    rows_total, classes, dtype_name, ignore_frac, eps = WORKLOADS[args.workload]
+    if args.rows:
+        rows_total = args.rows
+    return {"workload": args.workload, "rows": rows_total, "classes": classes, "ignore_fraction": ignore_frac,
+            "label_smoothing": eps, "reduction": "mean", "row_shards": world}
 
 
 def run_reference(args):
-    """The PyTorch CPU ATen path on the host cores, bounded sample of the same workload."""
+    """The PyTorch CPU ATen path (the reference's test golden and its CPU route) on the host cores, each step a bounded
+    row sample of the same workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -177,6 +198,7 @@ def run_reference(args):
 
     from oracle import oracle
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     rows_full, classes, dtype_name, ignore_frac, eps = WORKLOADS[args.workload]
     dtype = getattr(torch, dtype_name)
     cores = os.cpu_count() or 1
@@ -194,11 +216,10 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "cross_entropy_fwd_bwd_rows_per_s", "value": value, "unit": "rows/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
-        "config": {"workload": args.workload, "rows_per_gpu": rows_full, "classes": classes,
-                   "ignore_fraction": ignore_frac, "label_smoothing": eps, "reduction": "mean"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+        "config": workload_config(args, world),
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"PyTorch CPU ATen F.cross_entropy fwd+bwd on {sample_rows} rows x {classes} {dtype_name}"},
+                         "sample": f"PyTorch CPU ATen F.cross_entropy fwd+bwd on {sample_rows} rows x {classes} {dtype_name} per step"},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -211,8 +232,9 @@ def run_ours(args):
     import torch.nn.functional as F
 
     import torch_supa_b200  # registers the "supa" device; raises if the native libraries are missing
-    from torch_supa_b200 import benchmarks, capi
-    from torch_supa_b200.distributed import LossComm, sharded_cross_entropy
+    import bench_extras
+    from torch_supa_b200 import capi
+    from torch_supa_b200.distributed import LossComm, shard_rows, sharded_cross_entropy
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -224,7 +246,7 @@ def run_ours(args):
     device = torch.device("supa", local_rank)
     comm = None
     if world > 1:
-        dist.init_process_group("gloo")  # host-side plumbing: barrier, max over ranks, unique-id store
+        dist.init_process_group("gloo")  # host-side plumbing: barrier, max over ranks, handle and unique-id store
         comm = LossComm.from_env(device_index=local_rank)
     if args.force_generic:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 0))
@@ -235,35 +257,13 @@ def run_ours(args):
     if args.tune_window >= 0:
         capi.check("sb_set_tuning", capi.lib().sb_set_tuning(2, args.tune_window))
 
-    rows, classes, dtype_name, ignore_frac, eps = WORKLOADS[args.workload]
-    if args.rows:
-        rows = args.rows
+    cfg = workload_config(args, world)
+    rows_total, classes, eps, ignore_frac = cfg["rows"], cfg["classes"], cfg["label_smoothing"], cfg["ignore_fraction"]
+    dtype_name = WORKLOADS[args.workload][2]
     dtype = getattr(torch, dtype_name)
     esize = torch.empty((), dtype=dtype).element_size()
-    # seeded synthetic inputs: logits N(0,1)*2, targets uniform with a fraction set to ignore_index
-    logits = benchmarks.device_randn((rows, classes), dtype, device, seed=rank, scale=2.0)
-    tg = torch.Generator().manual_seed(1000 + rank)
-    host_target = torch.randint(0, classes, (rows,), generator=tg)
-    if ignore_frac > 0:
-        host_target[torch.randperm(rows, generator=torch.Generator().manual_seed(2000 + rank))[: int(rows * ignore_frac)]] = -100
-    target = host_target.to(device)
-    logits.requires_grad_(True)
-    nbytes = logits.numel() * esize
     warmup = max(args.warmup, 3)
-
-    def step(x, t):
-        """One pass of the hot path through the public API: loss (global mean) and the logit gradient."""
-        x.grad = None
-        if comm is not None:
-            loss = sharded_cross_entropy(x, t, comm, ignore_index=-100, label_smoothing=eps, reduction="mean")
-        else:
-            loss = F.cross_entropy(x, t, ignore_index=-100, label_smoothing=eps, reduction="mean")
-        loss.backward()
-        return loss
-
-    # my kernels per step: count_valid, fused sweep, loss sum(+finish), fill(root gradient, by autograd), rescale;
-    # with N > 1 the loss sum and finish are two launches
-    launches_per_step = 5 if world == 1 else 6
+    peak, peak_kind = load_peaks()
 
     def barrier():
         torch.supa.synchronize()
@@ -277,25 +277,62 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def make_inputs(rows, seed):
+        """Seeded synthetic inputs of one rank: logits N(0,1)*2, targets uniform with a fraction set to ignore_index."""
+        x = bench_extras.device_randn((rows, classes), dtype, device, seed=seed, scale=2.0)
+        tg = torch.Generator().manual_seed(1000 + seed)
+        host_t = torch.randint(0, classes, (rows,), generator=tg)
+        if ignore_frac > 0:
+            host_t[torch.randperm(rows, generator=torch.Generator().manual_seed(2000 + seed))[: int(rows * ignore_frac)]] = -100
+        return x.requires_grad_(True), host_t
+
+    def step(x, t):
+        """One pass of the hot path through the public API: loss (global mean) and the logit gradient."""
+        x.grad = None
+        if comm is not None:
+            loss = sharded_cross_entropy(x, t, comm, ignore_index=-100, label_smoothing=eps, reduction="mean")
+        else:
+            loss = F.cross_entropy(x, t, ignore_index=-100, label_smoothing=eps, reduction="mean")
+        loss.backward()
+        return loss
+
+    def timed(x, t, steps):
+        s0, s1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
+        barrier()
+        s0.record()
+        for _ in range(steps):
+            loss = step(x, t)
+        s1.record()
+        barrier()
+        return max_over_ranks(s0.elapsed_time(s1)) / steps, loss
+
+    # ---- the workload: the rows of the configuration, sharded over the ranks (strong scaling) ----
+    b, e = shard_rows(rows_total, world, rank)
+    rows = e - b
+    logits, host_target = make_inputs(rows, seed=rank)
+    target = host_target.to(device)
+    nbytes = logits.numel() * esize
+    ignored_local = int((host_target == -100).sum())
+
     sampler = ClockSampler(local_rank)
-    if rank == 0 and not args.no_clocks:
-        sampler.start()
     for _ in range(warmup):
         step(logits, target)
     barrier()
-
-    # ---- device-resident timing ---------------------------------------------------------------------
-    start, stop = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
-    barrier()
-    start.record()
-    for _ in range(args.steps):
-        loss = step(logits, target)
-    stop.record()
-    barrier()
-    ms_per_step = max_over_ranks(start.elapsed_time(stop)) / args.steps
+    # a short burst right after the warm-up (the board has not reached its power cap yet) ...
+    burst_ms, _ = timed(logits, target, args.steps)
+    # ... then the measurement proper, after about half a second of continuous load, which is what a training loop sees:
+    # at 1000 W the board caps its power and lowers the SM clock
+    if not args.quick:
+        for _ in range(20):  # a fixed count: every rank issues the same exchanges
+            for _ in range(8):
+                step(logits, target)
+            torch.supa.synchronize()
+    if rank == 0 and not args.no_clocks:
+        sampler.start()
+    ms_per_step, loss = timed(logits, target, args.steps)
     loss_value = float(loss.float().item())
 
-    # ---- the dominant kernel alone, through the C ABI on the same buffers ------------------------------
+    # ---- the dominant kernel alone, through the C ABI on the same buffers, same thermal state ----
     grad = torch.empty_like(logits)
     ws_row_loss = torch.empty(rows, dtype=torch.float32, device=device)
     ws_acc = torch.zeros(2, dtype=torch.float64, device=device)
@@ -317,33 +354,27 @@ def run_ours(args):
         kernel_times.append(e0.elapsed_time(e1))
     kernel_ms = statistics.mean(kernel_times)
     status_word = int(ws_status.cpu().item())
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if (rank == 0 and not args.no_clocks) else None
     del grad
 
-    # ---- the same step under sustained load: about half a second of back-to-back steps, the last ones timed.  At
-    # 1000 W the board caps its power and lowers the SM clock, so this is slower than the short timed region above.
-    sustained = None
-    if not args.quick:
-        sus_sampler = ClockSampler(local_rank, period_s=0.02)
-        if rank == 0 and not args.no_clocks:
-            sus_sampler.start()
-        for _ in range(20):  # a fixed count: every rank must issue the same collectives
-            for _ in range(8):
-                step(logits, target)
-            torch.supa.synchronize()
-        s0, s1 = torch.Event(device="supa", enable_timing=True), torch.Event(device="supa", enable_timing=True)
-        barrier()
-        s0.record()
-        for _ in range(20):
-            step(logits, target)
-        s1.record()
-        barrier()
-        sus_ms = max_over_ranks(s0.elapsed_time(s1)) / 20
-        sus_clocks = sus_sampler.stop() if (rank == 0 and not args.no_clocks) else None
-        sustained = {"ms_per_step": sus_ms, "value": rows * world / (sus_ms * 1e-3), "unit": "rows/s", "after_steps_of_load": 160,
-                     "clocks": sus_clocks}
+    # ---- weak scaling beside it (N > 1): every rank holds the whole configuration's row count ----
+    weak = None
+    if world > 1 and not args.quick:
+        del logits, target
+        torch.supa.empty_cache()
+        wx, wt_host = make_inputs(rows_total, seed=100 + rank)
+        wt = wt_host.to(device)
+        for _ in range(3):
+            step(wx, wt)
+        weak_ms, _ = timed(wx, wt, max(3, args.steps // 2))
+        weak = {"ms_per_step": weak_ms, "value": rows_total * world / (weak_ms * 1e-3), "unit": "rows/s", "rows_per_gpu": rows_total,
+                "scaling": "weak"}
+        del wx, wt
+        torch.supa.empty_cache()
+        logits, host_target = make_inputs(rows, seed=rank)
+        target = host_target.to(device)
 
-    # ---- end to end: host buffers -> loss on the host ---------------------------------------------
+    # ---- end to end: host buffers -> loss on the host ----
     e2e = None
     if args.quick:
         args.no_cpu_baseline = True
@@ -380,8 +411,8 @@ def run_ours(args):
             barrier()
             e2e_ms = max_over_ranks(s0.elapsed_time(s1)) / e2e_steps
             wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-            e2e = {"value": rows * world / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "wall_ms_per_step": wall_ms,
-                   "steps": e2e_steps, "h2d_bytes_per_step": (nbytes + rows * 8) * world, "d2h_bytes_per_step": esize * world,
+            e2e = {"value": rows_total / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms, "wall_ms_per_step": wall_ms,
+                   "steps": e2e_steps, "h2d_bytes_per_step": rows_total * classes * esize + rows_total * 8, "d2h_bytes_per_step": esize * world,
                    "api": "tensor.to('supa', non_blocking) from pinned memory; " + ("sharded_cross_entropy" if comm is not None else "F.cross_entropy") + "; backward; loss.item()",
                    "loss": e2e_loss}
             del host_logits
@@ -389,7 +420,7 @@ def run_ours(args):
             e2e = {"value": None, "unit": "rows/s", "skipped": "host memory too small for a pinned copy of the logits"}
     torch.supa.empty_cache()
 
-    # ---- CPU baseline (rank 0, N = 1 only) --------------------------------------------------------
+    # ---- CPU baseline (rank 0, N = 1 only) ----
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle
@@ -400,28 +431,39 @@ def run_ours(args):
         cpu_baseline = {"value": sample_rows / sec, "unit": "rows/s", "cores": used, "kind": "port",
                         "sample": f"PyTorch CPU ATen F.cross_entropy fwd+bwd, best of 2, on {sample_rows} rows x {classes} {dtype_name}"}
 
-    peak, peak_kind = load_peaks()
     alg = algorithmic_bytes(rows, classes, esize)
+    moved = moved_bytes(rows, classes, esize, ignored_local)
     achieved = alg / (kernel_ms * 1e-3) / 1e9
+    achieved_moved = moved / (kernel_ms * 1e-3) / 1e9
+    variant = capi.ce_kernel_variant(capi.torch_dtype_code(dtype), rows, classes)
     extras = None
-    if rank == 0 and world == 1 and args.extras:
-        extras = benchmarks.run_extras(device, peak, quick=args.quick, profile=args.extras == 2)
+    if rank == 0 and world == 1 and args.extras and not args.quick:
+        extras = bench_extras.run_extras(device, peak, profile=args.extras == 2)
+    # my kernels per step: count, fused sweep, loss sum + finish (the two exchanges ride inside the count and the loss kernel),
+    # fill of the root gradient (by autograd), rescale; through NCCL the loss sum and its finish are two launches
+    launches_per_step = 5 if (comm is None or comm.peer_handle) else 6
 
     if rank == 0:
+        traffic_per_row = NCU_TRAFFIC_PER_ROW.get(args.workload)
         line = {
-            "metric": "cross_entropy_fwd_bwd_rows_per_s", "value": rows * world / (ms_per_step * 1e-3), "unit": "rows/s", "n_gpus": world,
+            "metric": "cross_entropy_fwd_bwd_rows_per_s", "value": rows_total / (ms_per_step * 1e-3), "unit": "rows/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
-            "config": {"workload": args.workload, "rows_per_gpu": rows, "classes": classes, "ignore_fraction": ignore_frac,
-                       "label_smoothing": eps, "reduction": "mean", "parallelism": f"rows sharded x{world}",
-                       "api": "F.cross_entropy on the supa device + backward" if world == 1 else "sharded_cross_entropy + backward",
-                       "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs smaller than 2x L2"},
-            "loss": loss_value, "status_word": status_word,
-            "kernel_variant": capi.ce_kernel_variant(capi.torch_dtype_code(dtype), rows, classes),
+            "scaling": "strong", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+            "config": cfg,
+            "notes": {"rows_per_gpu": rows, "timed_after": "warm-up" if args.quick else "warm-up + 160 steps of continuous load (power-capped clocks)",
+                      "api": "F.cross_entropy on the supa device + backward" if world == 1 else "sharded_cross_entropy + backward",
+                      "exchange": None if comm is None else ("peer memory inside the count and loss kernels" if comm.peer_handle else "ncclAllReduce x2"),
+                      "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs smaller than 2x L2"},
+            "loss": loss_value, "status_word": status_word, "kernel_variant": variant,
+            "burst": {"ms_per_step": burst_ms, "value": rows_total / (burst_ms * 1e-3), "unit": "rows/s",
+                      "note": f"{args.steps} steps right after the warm-up, before the power cap lowers the clock"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "frac_of_8TBs_nominal": achieved / 8000.0, "kernel": "ce_resident_kernel",
-                         "kernel_ms": kernel_ms, "algorithmic_bytes": alg, "traffic": TRAFFIC.get((args.workload, rows))},
-            "hbm_gbs_whole_step": alg / (ms_per_step * 1e-3) / 1e9, "sustained": sustained,
+                         "peak_kind": peak_kind, "frac_of_8TBs_nominal": achieved / 8000.0, "kernel": KERNEL_NAMES.get(variant, str(variant)),
+                         "kernel_ms": kernel_ms, "algorithmic_bytes": alg,
+                         "moved_bytes": moved, "achieved_moved": achieved_moved, "frac_moved": achieved_moved / peak,
+                         "moved_note": "bytes the kernel has to move: rows whose target is ignore_index are not read",
+                         "traffic": None if traffic_per_row is None else traffic_per_row * rows},
+            "hbm_gbs_whole_step": alg / (ms_per_step * 1e-3) / 1e9, "weak": weak,
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
@@ -437,21 +479,23 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--rows", type=int, default=0, help="override rows per GPU (small profiling captures)")
+    ap.add_argument("--rows", type=int, default=0, help="override the total row count (small profiling captures)")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--quick", action="store_true", help="profiling mode: no clock warm loop, no e2e, no CPU baseline")
+    ap.add_argument("--quick", action="store_true", help="profiling mode: no load loop, no weak-scaling leg, no e2e, no CPU baseline, no extras")
     ap.add_argument("--force-generic", action="store_true", help="tuning: always use the generic two-sweep kernel")
     ap.add_argument("--no-clocks", action="store_true", help="diagnostic: do not sample clocks during the run")
     ap.add_argument("--tune-variant", type=int, default=-1, help="tuning: force the resident kernel's cluster size (1, 2, 4)")
     ap.add_argument("--tune-keep", type=int, default=-1, help="tuning: 0 recompute bf16 exponentials in the gradient sweep, 1 keep them")
     ap.add_argument("--tune-window", type=int, default=-1, help="tuning: next-row chunks folded during the statistics exchange")
-    ap.add_argument("--extras", type=int, default=0, help="1: also time the elementwise / reduction configurations; 2: same, one launch each (for profilers)")
+    ap.add_argument("--extras", type=int, default=1,
+                    help="1 (default, N = 1): also time the other configurations (elementwise, reductions, log_softmax ...); 0: skip them; "
+                         "2: one launch each (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

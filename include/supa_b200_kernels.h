@@ -57,6 +57,7 @@ typedef enum sb_dtype {
 /* Bits of the device status word. */
 #define SB_STATUS_TARGET_OUT_OF_RANGE 0x1 /* a class index outside [0, classes) and != ignore_index */
 #define SB_STATUS_KERNEL_TIMEOUT 0x2      /* a bounded wait inside a kernel ran out; its results are invalid */
+#define SB_STATUS_GRADIENT_LOST 0x4      /* sb_ce_rescale_grad was asked to undo a factor of zero */
 
 typedef enum sb_reduction { SB_REDUCTION_NONE = 0, SB_REDUCTION_MEAN = 1, SB_REDUCTION_SUM = 2 } sb_reduction;
 
@@ -107,8 +108,17 @@ typedef struct sb_ce_args {
   const float* class_weight; /* [classes] fp32 per-class weights (the `weight` argument of cross_entropy), or NULL.
                                 Row i's loss and gradient are multiplied by class_weight[target_i]; with mean the
                                 denominator acc[1] must then be the sum of those weights (sb_ce_count_weighted).
-                                Only with label_smoothing == 0. */
+                                With label_smoothing > 0 the smoothing term weights every class c of the row by
+                                class_weight[c], as the upstream composite does (CrossEntropyLoss.cpp:50); that
+                                combination runs on the two-sweep kernel. */
+  uint32_t flags;            /* SB_CE_FLAG_* */
 } sb_ce_args;
+
+/* The launch directly before this one on the same stream is sb_ce_count_valid / sb_ce_count_weighted /
+ * sb_ce_count_exchange of the same call (it produces acc[1]).  The sweep may then start its loads while that
+ * kernel still runs (programmatic dependent launch); it waits for acc[1] before the first gradient is formed.
+ * Do not set it when anything else precedes the sweep on the stream. */
+#define SB_CE_FLAG_AFTER_COUNT 0x1u
 
 /* Counts rows with target != ignore_index into acc[1] (as a double) and zeroes acc[0]; flags
  * out-of-range targets in *status.  Replaces the `counts[row]` side buffer of
@@ -137,12 +147,50 @@ SB_API int sb_ce_loss_finish(const double* acc, int32_t reduction, void* out, in
 SB_API int sb_ce_loss_sum_finish(const float* row_loss, int64_t rows, double* acc, int32_t reduction, void* out,
                                  int32_t dtype, sb_stream_t stream);
 
-/* grad[i] *= factor where factor = *scale / *applied_in (device floats; a null applied_in stands for 1, the
- * state right after the fused sweep); *applied_out = *scale.  One launch: the sweep is skipped on the device
- * when the factor is exactly 1, and applied_out must be a different word from applied_in (callers alternate
- * between two).  Used by the autograd node when the upstream gradient of a mean/sum loss is not 1. */
-SB_API int sb_ce_rescale_grad(void* grad, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype,
-                              const float* applied_in, float* applied_out, sb_stream_t stream);
+/* dst[i] = src[i] * factor where factor = *scale / *applied_in (device floats; a null applied_in stands for 1, the
+ * state right after the fused sweep).  dst may be src (in place): the sweep is then skipped on the device when the
+ * factor is exactly 1.  When applied_out is not null, *applied_out = *scale records the factor now folded into an
+ * in-place buffer; it must be a different word from applied_in (callers alternate between two).  A stored factor
+ * of zero cannot be undone: the kernel then sets SB_STATUS_GRADIENT_LOST in *status (may be NULL) and writes NaN,
+ * unless *scale is zero too.  Used by the autograd node when the upstream gradient of a mean/sum loss is not 1. */
+SB_API int sb_ce_rescale_grad(const void* src, void* dst, int32_t dtype, int64_t numel, const void* scale, int32_t scale_dtype,
+                              const float* applied_in, float* applied_out, int32_t* status, sb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The two scalar exchanges of row-sharded cross entropy, done by the bookkeeping kernels themselves.
+ *
+ * Replaces the all-reduce of ProcessGroupBCCL::allreduce (torch_supa/csrc/distributed/ProcessGroupBCCL.cpp:3723-3790)
+ * for the two 8-byte messages of this path: every rank (one process per GPU) owns a small slot array in its device
+ * memory that all other ranks have mapped (CUDA IPC); a kernel publishes its partial with plain stores into every
+ * peer's array, then waits (bounded) for the partials of all ranks in its own array and adds them in rank order,
+ * so that every rank gets the same bits.  No NCCL launch sits between the count, the sweep and the loss.
+ *
+ *   slots[r]  device address, valid on THIS GPU, of rank r's slot array (SB_XCHG_SLOT_BYTES bytes, zeroed once
+ *             before first use); slots[rank] is this GPU's own array.
+ *   seq       number of this exchange on the communicator: 1, 2, 3, ... in the same order on every rank.
+ * A wait that runs out (default 10 s, see sb_set_tuning key 5) sets SB_STATUS_KERNEL_TIMEOUT in *status, and the
+ * kernel finishes with the partials that did arrive; nothing hangs.
+ * ------------------------------------------------------------------------------------------ */
+#define SB_XCHG_MAX_RANKS 8
+#define SB_XCHG_DEPTH 4
+#define SB_XCHG_SLOT_BYTES (SB_XCHG_DEPTH * SB_XCHG_MAX_RANKS * 16)
+typedef struct sb_xchg {
+  void* slots[SB_XCHG_MAX_RANKS];
+  int32_t rank;
+  int32_t nranks;
+  uint64_t seq;
+} sb_xchg;
+
+/* sb_ce_count_valid (class_weight == NULL) or sb_ce_count_weighted in one launch and with no memset, followed, when
+ * x is not NULL, by the exchange: acc[1] = sum over ranks, acc[0] = 0. */
+SB_API int sb_ce_count_exchange(const int64_t* target, const float* class_weight, int64_t rows, int64_t classes,
+                                int64_t ignore_index, double* acc, int32_t* status, const sb_xchg* x, sb_stream_t stream);
+
+/* sb_ce_loss_sum_finish with the exchange of the loss sum between the sum and the division when x is not NULL:
+ * acc[0] = sum over ranks of the local fixed-order sums.  Launched as a programmatic dependent of the kernel
+ * before it (it waits for that kernel's results before it reads anything). */
+SB_API int sb_ce_loss_exchange(const float* row_loss, int64_t rows, double* acc, int32_t reduction, void* out, int32_t dtype,
+                               int32_t* status, const sb_xchg* x, sb_stream_t stream);
 
 /* Cross entropy (mean or sum) for callers that cannot allocate device memory.
  *
@@ -170,7 +218,7 @@ SB_API int sb_ce_loss_static_scratch(const sb_ce_args* args, void* loss_out, sb_
 
 /* Which kernel family sb_ce_forward_backward will use for this shape: 0 = generic two-sweep rows,
  * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
- * of 2/4 CTAs.  For diagnostics and benchmarks. */
+ * of 2/4 CTAs, 8 = rows shorter than 16 KB held in registers.  For diagnostics and benchmarks. */
 SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
 
 /* Tuning hook for benchmarks and profiling (process-wide, not thread-safe against running launches):
@@ -179,7 +227,8 @@ SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
  * key 2 = chunks of the next row the resident kernel folds while a row's statistics are exchanged
  * (-1 automatic, 0..64);
  * key 3 = how the resident kernel forms bf16 gradients: 1 (default) rescales the exponentials kept from the statistics
- * sweep (one ex2 per logit, one more bf16 rounding), 0 recomputes them (two ex2 per logit). */
+ * sweep (one ex2 per logit, one more bf16 rounding), 0 recomputes them (two ex2 per logit);
+ * key 5 = limit, in milliseconds, of the waits of sb_ce_count_exchange / sb_ce_loss_exchange (1..60000, default 10000). */
 SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------
@@ -320,7 +369,13 @@ typedef enum sb_ew_op {
   SB_EW_GE = 35,
   SB_EW_WHERE = 36,             /* in0(condition) ? in1 : in2 */
   SB_EW_MASKED_FILL = 37,       /* in1(mask) ? scalar : in0 */
-  SB_EW_OP_COUNT = 38
+  /* div with a rounding mode (torch_supa/csrc/aten/ops/kernels/elementwise/BinaryDivTruncKernel.cu,
+   * BinaryDivFloorKernel.cu).  Floating types: trunc(a / b), and the floor division of Python (quotient from the
+   * exact remainder, corrected by one where the signs differ).  Integer types: C division, and the same rounded
+   * towards minus infinity; an integer division by zero yields 0 instead of raising as the CPU does. */
+  SB_EW_DIV_TRUNC = 38,
+  SB_EW_DIV_FLOOR = 39,
+  SB_EW_OP_COUNT = 40
 } sb_ew_op;
 
 typedef struct sb_ew_desc {
@@ -353,7 +408,15 @@ SB_API int sb_elementwise_path(const sb_ew_desc* desc);
  * Accumulation is fp32 for fp16/bf16/fp32 inputs, fp64 for fp64, int64 for integers; amax is exact and
  * propagates NaN.
  * ------------------------------------------------------------------------------------------ */
-typedef enum sb_reduce_op { SB_RED_SUM = 0, SB_RED_MEAN = 1, SB_RED_AMAX = 2, SB_RED_AMIN = 3, SB_RED_OP_COUNT = 4 } sb_reduce_op;
+typedef enum sb_reduce_op {
+  SB_RED_SUM = 0,
+  SB_RED_MEAN = 1,
+  SB_RED_AMAX = 2,
+  SB_RED_AMIN = 3,
+  SB_RED_PROD = 4,   /* prod_kernel_cuda of the reference's reduce family (kernels/reduce/ReduceOps) */
+  SB_RED_NANSUM = 5, /* sum with NaN counted as zero */
+  SB_RED_OP_COUNT = 6
+} sb_reduce_op;
 
 typedef struct sb_reduce_desc {
   int32_t op;        /* sb_reduce_op */
@@ -375,6 +438,53 @@ SB_API int sb_reduce(const sb_reduce_desc* desc, sb_stream_t stream);
 /* 0 = inner-contiguous rows, 1 = rows split over several CTAs (two stage), 2 = outer (column) reduce,
  * 3 = generic. */
 SB_API int sb_reduce_path(const sb_reduce_desc* desc);
+
+/* ------------------------------------------------------------------------------------------
+ * Reductions with an index or a second moment, over the middle dimension of a contiguous [outer, L, inner] view.
+ *
+ * sb_arg_reduce: extremum and / or its position along L (argmax, argmin, max.dim, min.dim; the reference routes them
+ * through the same reduce family, kernels/reduce/Reduce.cuh:1040-1333, with the index rules of its CPU golden): of equal
+ * extrema the lowest index wins; a NaN beats every number, for max and for min, and of several NaN the first.
+ * `values` (in `dtype`) and `indices` (int64) have outer * inner elements; either may be NULL.  Bit-exact.
+ *
+ * sb_moments: variance or standard deviation with the given correction (M2 / max(0, L - correction)), and optionally
+ * the mean, in `dtype` (torch_supa/csrc/aten/ops/StdVar.cpp:34-63).  Accumulated in fp64.
+ *
+ * scratch: sb_reduce_ext_scratch_bytes(...) bytes, 8-byte aligned, needed only when few long rows are cut into
+ * segments (the call returns 0 otherwise).
+ * ------------------------------------------------------------------------------------------ */
+SB_API size_t sb_reduce_ext_scratch_bytes(int32_t dtype, int64_t outer, int64_t L, int64_t inner, int32_t moments);
+SB_API int sb_arg_reduce(const void* in, int32_t dtype, int64_t outer, int64_t L, int64_t inner, int32_t is_max, void* values,
+                         int64_t* indices, void* scratch, size_t scratch_bytes, sb_stream_t stream);
+SB_API int sb_moments(const void* in, int32_t dtype, int64_t outer, int64_t L, int64_t inner, double correction, int32_t take_sqrt,
+                      void* out, void* mean_out, void* scratch, size_t scratch_bytes, sb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Cross entropy with class-probability ("soft") targets, forward and backward.
+ *
+ * Replaces cross_entropy_prob_kernel (torch_supa/csrc/aten/ops/kernels/elementwise/CrossEntropyLossKernel.cu:532-576,
+ * selected at :721) and, for the gradient, the composite the reference differentiates through.  With
+ * q_c = target_c (1 - eps) + eps / C and w = class_weight (1 when NULL):
+ *   loss_i  = sum_c w_c q_ic (lse_i - x_ic)
+ *   grad_ic = (softmax_ic * sum_k w_k q_ik - w_c q_ic) * grad_scale * row_grad_out_i
+ * row_loss[i] = loss_i * loss_scale.  `mean` divides by the number of rows, which the caller folds into loss_scale and
+ * grad_scale (no count is needed); sum the row losses with sb_ce_loss_sum_finish(reduction = sum).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct sb_ce_prob_args {
+  const void* logits;        /* [rows, classes] row-major */
+  const void* target;        /* [rows, classes] probabilities, same dtype */
+  int32_t dtype;             /* SB_F32, SB_BF16 or SB_F16 */
+  void* grad_logits;         /* [rows, classes] same dtype, or NULL for forward only; must not alias logits or target */
+  float* row_loss;           /* [rows] */
+  const float* row_grad_out; /* [rows] upstream gradient per row, or NULL for 1 */
+  const float* class_weight; /* [classes] fp32, or NULL */
+  int64_t rows;
+  int64_t classes;
+  float label_smoothing;
+  float grad_scale;
+  float loss_scale;
+} sb_ce_prob_args;
+SB_API int sb_ce_prob_forward_backward(const sb_ce_prob_args* args, sb_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

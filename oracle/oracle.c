@@ -257,6 +257,149 @@ ORACLE_API void oracle_reduce_rows(const float* x, int64_t rows, int64_t len, in
   }
 }
 
+/* Cross entropy with class weights, label smoothing and class-index targets: the arithmetic of the upstream composite the
+ * reference reaches for every weighted call (torch_supa/csrc/aten/ops/CrossEntropyLoss.cpp:23-33,50): the nll part is
+ * weighted by w[t_i], the smoothing part weights every class c by w[c]; mean divides both by sum_i w[t_i].
+ *   loss_i  = (1 - eps) w[t_i] (lse_i - x[i, t_i]) + eps / C * sum_c w[c] (lse_i - x[i, c])
+ *   grad_ic = softmax_ic ((1 - eps) w[t_i] + eps / C * W) - (1 - eps) w[t_i] [c == t_i] - eps / C * w[c],  W = sum_c w[c]
+ * weight == NULL means all ones (then this equals oracle_cross_entropy). */
+ORACLE_API int64_t oracle_cross_entropy_weighted(const float* logits, const int64_t* target, const float* weight, int64_t rows,
+                                                 int64_t classes, int64_t ignore_index, double label_smoothing, int reduction,
+                                                 double grad_out, const double* row_grad_out, double* loss, double* grad) {
+  int64_t bad = 0;
+  double denom = 0.0, total = 0.0, wsum = 0.0;
+  for (int64_t c = 0; c < classes; ++c) wsum += weight ? (double)weight[c] : 1.0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t t = target[i];
+    if (t != ignore_index && t >= 0 && t < classes) denom += weight ? (double)weight[t] : 1.0;
+  }
+  for (int64_t i = 0; i < rows; ++i) {
+    const float* x = logits + i * classes;
+    const int64_t t = target[i];
+    int ignored = (t == ignore_index);
+    if (!ignored && (t < 0 || t >= classes)) {
+      ++bad;
+      ignored = 1;
+    }
+    double li = 0.0;
+    if (!ignored) {
+      const double lse = row_lse(x, classes, NULL);
+      const double wt = weight ? (double)weight[t] : 1.0;
+      double swx = 0.0;
+      for (int64_t c = 0; c < classes; ++c) swx += (weight ? (double)weight[c] : 1.0) * (double)x[c];
+      li = (1.0 - label_smoothing) * wt * (lse - (double)x[t]) + label_smoothing / (double)classes * (wsum * lse - swx);
+      if (grad) {
+        double scale = grad_out;
+        if (reduction == RED_MEAN) scale /= denom;
+        if (reduction == RED_NONE && row_grad_out) scale *= row_grad_out[i];
+        const double pfac = (1.0 - label_smoothing) * wt + label_smoothing / (double)classes * wsum;
+        for (int64_t c = 0; c < classes; ++c) {
+          double g = exp((double)x[c] - lse) * pfac - label_smoothing / (double)classes * (weight ? (double)weight[c] : 1.0);
+          if (c == t) g -= (1.0 - label_smoothing) * wt;
+          grad[i * classes + c] = g * scale;
+        }
+      }
+    } else if (grad) {
+      for (int64_t c = 0; c < classes; ++c) grad[i * classes + c] = 0.0;
+    }
+    if (reduction == RED_NONE) loss[i] = li;
+    else total += li;
+  }
+  if (reduction == RED_MEAN) loss[0] = denom > 0.0 ? total / denom : NAN;
+  else if (reduction == RED_SUM) loss[0] = total;
+  return bad;
+}
+
+/* Cross entropy with class-probability targets (cross_entropy_prob_kernel,
+ * torch_supa/csrc/aten/ops/kernels/elementwise/CrossEntropyLossKernel.cu:545-564, with the smoothing and the weights
+ * of the composite): q_c = t_c (1 - eps) + eps / C,
+ *   loss_i = sum_c w[c] q_ic (lse_i - x[i, c]);  mean divides by the number of rows;
+ *   grad_ic = softmax_ic * sum_k w[k] q_ik - w[c] q_ic. */
+ORACLE_API void oracle_cross_entropy_prob(const float* logits, const float* target, const float* weight, int64_t rows, int64_t classes,
+                                          double label_smoothing, int reduction, double grad_out, const double* row_grad_out,
+                                          double* loss, double* grad) {
+  double total = 0.0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const float* x = logits + i * classes;
+    const float* t = target + i * classes;
+    const double lse = row_lse(x, classes, NULL);
+    double a = 0.0, li = 0.0;
+    for (int64_t c = 0; c < classes; ++c) {
+      const double q = ((double)t[c] * (1.0 - label_smoothing) + label_smoothing / (double)classes) * (weight ? (double)weight[c] : 1.0);
+      a += q;
+      li += q * (lse - (double)x[c]);
+    }
+    if (grad) {
+      double scale = grad_out;
+      if (reduction == RED_MEAN) scale /= (double)rows;
+      if (reduction == RED_NONE && row_grad_out) scale *= row_grad_out[i];
+      for (int64_t c = 0; c < classes; ++c) {
+        const double q = ((double)t[c] * (1.0 - label_smoothing) + label_smoothing / (double)classes) * (weight ? (double)weight[c] : 1.0);
+        grad[i * classes + c] = (exp((double)x[c] - lse) * a - q) * scale;
+      }
+    }
+    if (reduction == RED_NONE) loss[i] = li;
+    else total += li;
+  }
+  if (reduction == RED_MEAN) loss[0] = rows > 0 ? total / (double)rows : NAN;
+  else if (reduction == RED_SUM) loss[0] = total;
+}
+
+/* Extremum and its index along the middle dimension of [outer, len, inner] (the reduce family behind argmax / max.dim,
+ * torch_supa/csrc/aten/ops/kernels/reduce/Reduce.cuh:1040-1333, with the index rules of the CPU golden): the first of
+ * equal extrema; NaN wins over every number, for max and for min, the first NaN if there are several. */
+ORACLE_API void oracle_arg_reduce(const double* x, int64_t outer, int64_t len, int64_t inner, int is_max, double* values,
+                                  int64_t* indices) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const double* p = x + o * len * inner + i;
+      double best = p[0];
+      int64_t at = 0;
+      for (int64_t k = 1; k < len; ++k) {
+        const double v = p[k * inner];
+        if (best != best) break;
+        if (v != v || (is_max ? v > best : v < best)) {
+          best = v;
+          at = k;
+        }
+      }
+      values[o * inner + i] = best;
+      indices[o * inner + i] = at;
+    }
+}
+
+/* Variance / standard deviation with a correction and the mean, along the middle dimension of [outer, len, inner]
+ * (torch_supa/csrc/aten/ops/StdVar.cpp:34-63): two passes in double, M2 / max(0, len - correction). */
+ORACLE_API void oracle_moments(const double* x, int64_t outer, int64_t len, int64_t inner, double correction, int take_sqrt,
+                               double* out, double* mean_out) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const double* p = x + o * len * inner + i;
+      double m = 0.0, m2 = 0.0;
+      for (int64_t k = 0; k < len; ++k) m += p[k * inner];
+      m /= (double)len;
+      for (int64_t k = 0; k < len; ++k) m2 += (p[k * inner] - m) * (p[k * inner] - m);
+      const double denom = (double)len - correction > 0.0 ? (double)len - correction : 0.0;
+      const double v = m2 / denom;
+      out[o * inner + i] = take_sqrt ? sqrt(v) : v;
+      if (mean_out) mean_out[o * inner + i] = m;
+    }
+}
+
+/* div with a rounding mode on integers (BinaryDivTruncKernel.cu, BinaryDivFloorKernel.cu): C division, and the same
+ * rounded towards minus infinity.  The floating forms are cases 38 / 39 of oracle_ew_scalar. */
+ORACLE_API void oracle_div_int(const int64_t* a, const int64_t* b, int64_t n, int floor_mode, int64_t* out) {
+  for (int64_t i = 0; i < n; ++i) {
+    if (b[i] == 0) {
+      out[i] = 0;
+      continue;
+    }
+    int64_t q = a[i] / b[i];
+    if (floor_mode && (a[i] % b[i] != 0) && ((a[i] < 0) != (b[i] < 0))) q -= 1;
+    out[i] = q;
+  }
+}
+
 /* Elementwise functors in double.  Codes follow the kernel library's sb_ew_op numbering.
  * add/mul: UfuncCUDA_add.cu:13-16 (self + alpha * other), BinaryInternal.h:16-29; the activations are
  * the formulas of the ATen kernels the reference links from its native-op library. */
@@ -293,6 +436,22 @@ ORACLE_API double oracle_ew_scalar(int op, double a, double b, double c, double 
       return (1.0 - s) * s * a * c;
     }
     case 17: return -a;
+    /* 38 / 39: rounding modes of div, in the operands' own precision (fp32 here): 3.0f / 0.3f is exactly 10 in fp32 and
+     * just below 10 in double, and the quotient is what gets truncated */
+    case 38: return (double)truncf((float)a / (float)b);
+    case 39: {  /* c10::div_floor_floating */
+      const float fa = (float)a, fb = (float)b;
+      if (fb == 0.f) return (double)(fa / fb);
+      const float mod = fmodf(fa, fb);
+      float div = (fa - mod) / fb;
+      if (mod != 0.f && (fb < 0.f) != (mod < 0.f)) div -= 1.f;
+      if (div != 0.f) {
+        float fl = floorf(div);
+        if (div - fl > 0.5f) fl += 1.f;
+        return (double)fl;
+      }
+      return (double)copysignf(0.f, fa / fb);
+    }
     default: return NAN;
   }
 }

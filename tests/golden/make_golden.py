@@ -177,6 +177,79 @@ def main():
         d[name + "/grad_out"] = go.numpy()
         d[name + "/grad_in"] = gi.numpy()
         d[name + "/dim"] = np.array([dim])
+    # ---- everything below was added after the cases above and is drawn after them, so their values stay as they were ----
+    # cross entropy with class weights and label smoothing together
+    for name, rows, classes, red in (("cew_mean", 7, 40, "mean"), ("cew_sum", 5, 33, "sum"), ("cew_none", 6, 21, "none")):
+        x = (torch.randn(rows, classes, generator=g) * 2).requires_grad_(True)
+        t = torch.randint(0, classes, (rows,), generator=g)
+        t[1] = -100
+        w = torch.rand(classes, generator=g) + 0.25
+        loss = F.cross_entropy(x, t, weight=w, label_smoothing=0.2, reduction=red)
+        go = torch.randn(loss.shape, generator=g) if red == "none" else torch.tensor(1.5)
+        (grad,) = torch.autograd.grad(loss, x, go)
+        for key, val in (("logits", x.detach()), ("target", t), ("weight", w), ("loss", loss.detach()), ("grad_out", go), ("grad", grad)):
+            d[f"{name}/{key}"] = val.numpy()
+    # cross entropy with class-probability targets, with and without weights and smoothing
+    for name, rows, classes, red, use_w, eps in (("cep_mean", 6, 50, "mean", False, 0.0), ("cep_sum_w", 4, 31, "sum", True, 0.0),
+                                                 ("cep_none_eps", 5, 19, "none", False, 0.1), ("cep_mean_w_eps", 7, 64, "mean", True, 0.3)):
+        x = (torch.randn(rows, classes, generator=g) * 2).requires_grad_(True)
+        t = torch.softmax(torch.randn(rows, classes, generator=g), 1)
+        w = torch.rand(classes, generator=g) + 0.25 if use_w else None
+        loss = F.cross_entropy(x, t, weight=w, label_smoothing=eps, reduction=red)
+        go = torch.randn(loss.shape, generator=g) if red == "none" else torch.tensor(0.5)
+        (grad,) = torch.autograd.grad(loss, x, go)
+        for key, val in (("logits", x.detach()), ("target", t), ("loss", loss.detach()), ("grad_out", go), ("grad", grad)):
+            d[f"{name}/{key}"] = val.numpy()
+        if use_w:
+            d[f"{name}/weight"] = w.numpy()
+        d[f"{name}/eps"] = np.array([eps])
+    # extrema with indices: ties resolve to the first index, NaN wins for max and for min
+    a = torch.randint(-3, 4, (5, 9, 4), generator=g).float()
+    a[1, 3, 2] = float("nan")
+    a[1, 6, 2] = float("nan")
+    a[4, 0, 0] = float("nan")
+    d["arg/x"] = a.numpy()
+    for dim in (0, 1, 2):
+        mv, mi = a.max(dim)
+        nv, ni = a.min(dim)
+        d[f"arg/max{dim}_values"], d[f"arg/max{dim}_indices"] = mv.numpy(), mi.numpy()
+        d[f"arg/min{dim}_values"], d[f"arg/min{dim}_indices"] = nv.numpy(), ni.numpy()
+    d["arg/argmax_flat"] = np.array(a[0].argmax().item())
+    d["arg/argmin_flat"] = np.array(a[0].argmin().item())
+    ai = torch.randint(-50, 50, (6, 11), generator=g, dtype=torch.int32)
+    d["arg/i32"] = ai.numpy()
+    d["arg/i32_argmax1"] = ai.argmax(1).numpy()
+    d["arg/i32_min1_values"], d["arg/i32_min1_indices"] = (v.numpy() for v in ai.min(1))
+    # var / std / var_mean
+    v = torch.randn(4, 37, 3, generator=g) * 3 + 5
+    d["mom/x"] = v.numpy()
+    for dim in (0, 1, 2):
+        d[f"mom/var{dim}"] = v.var(dim).numpy()
+        d[f"mom/std{dim}_c0"] = v.std(dim, correction=0).numpy()
+    d["mom/var_all"] = v.var().numpy()
+    d["mom/var_dims02"] = v.var((0, 2)).numpy()
+    d["mom/mean1"] = v.mean(1).numpy()
+    # prod / nansum
+    pr = torch.rand(5, 12, generator=g) + 0.5
+    d["prod/x"] = pr.numpy()
+    d["prod/dim1"] = pr.prod(1).numpy()
+    d["prod/all"] = pr.prod().numpy()
+    ns = torch.randn(4, 9, generator=g)
+    ns[0, 2] = float("nan")
+    ns[3, :] = float("nan")
+    d["nansum/x"] = ns.numpy()
+    d["nansum/dim1"] = ns.nansum(1).numpy()
+    # div with a rounding mode: floats (signs, zeros, exact multiples) and integers
+    da = torch.tensor([7.5, -7.5, 7.5, -7.5, 6.0, -6.0, 0.0, -0.0, 5.0, 1e-3, 3.0, -3.0])
+    db = torch.tensor([2.0, 2.0, -2.0, -2.0, 3.0, 3.0, 4.0, 4.0, 0.0, 7.0, 0.3, 0.3])
+    d["div/a"], d["div/b"] = da.numpy(), db.numpy()
+    d["div/trunc"] = torch.div(da, db, rounding_mode="trunc").numpy()
+    d["div/floor"] = torch.div(da, db, rounding_mode="floor").numpy()
+    ia = torch.randint(-40, 41, (64,), generator=g, dtype=torch.int32)
+    ib = torch.randint(1, 9, (64,), generator=g, dtype=torch.int32) * (torch.randint(0, 2, (64,), generator=g, dtype=torch.int32) * 2 - 1)
+    d["div/ia"], d["div/ib"] = ia.numpy(), ib.numpy()
+    d["div/itrunc"] = torch.div(ia, ib, rounding_mode="trunc").numpy()
+    d["div/ifloor"] = torch.div(ia, ib, rounding_mode="floor").numpy()
     np.savez_compressed(OUT, **d)
     print("wrote", OUT, OUT.stat().st_size, "bytes,", len(d), "arrays")
 

@@ -22,6 +22,11 @@ def main() -> int:
     comm = LossComm.from_env()
     device = torch.device("supa", local)
     failures = []
+    mode = os.environ.get("SUPA_B200_LOSS_EXCHANGE", "peer")
+    if mode == "peer" and comm.peer_handle == 0:
+        failures.append("the peer-memory exchange could not be set up (CUDA IPC mapping of the slot arrays failed)")
+    if mode == "nccl" and comm.peer_handle != 0:
+        failures.append("SUPA_B200_LOSS_EXCHANGE=nccl was ignored")
     for dtype, rows_per_rank, classes, eps, reduction in ((torch.float32, 37, 1000, 0.0, "mean"), (torch.float32, 64, 32000, 0.1, "mean"),
                                                           (torch.bfloat16, 16, 128256, 0.1, "mean"), (torch.float32, 19, 777, 0.0, "sum")):
         g = torch.Generator().manual_seed(1234)
@@ -50,6 +55,25 @@ def main() -> int:
         tol = (2e-2 if dtype == torch.bfloat16 else 1e-5) * float(gr.abs().max()) + 1e-9
         if err > tol:
             failures.append(f"grad {dtype} {reduction}: max err {err} > {tol}")
+    # several steps back to back without a host synchronisation: the slot rows of the exchange are reused every other step
+    g = torch.Generator().manual_seed(99)
+    rows_per_rank, classes = 64, 4096
+    logits = torch.randn(rows_per_rank * world, classes, generator=g) * 2
+    target = torch.randint(0, classes, (rows_per_rank * world,), generator=g)
+    lo, hi = rank * rows_per_rank, (rank + 1) * rows_per_rank
+    x = logits[lo:hi].to(device).requires_grad_(True)
+    t = target[lo:hi].to(device)
+    losses = []
+    for step in range(12):
+        x.grad = None
+        loss = sharded_cross_entropy(x * (1.0 + 0.125 * step), t, comm)
+        loss.backward()
+        losses.append(loss)
+    for step, loss in enumerate(losses):
+        want = float(F.cross_entropy(logits.double() * (1.0 + 0.125 * step), target))
+        if abs(float(loss.cpu()) - want) > 1e-5 * abs(want):
+            failures.append(f"step {step}: loss {float(loss.cpu())} vs {want}")
+    torch.supa.synchronize()
     # every rank reports; the job fails if any rank saw a mismatch
     flag = torch.tensor([len(failures)], dtype=torch.int64)
     dist.all_reduce(flag)

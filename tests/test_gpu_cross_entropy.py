@@ -166,14 +166,31 @@ def test_rescale_grad(cuda_device):
     for s in (1.0, 0.25, 0.25, 2.0):
         scale = torch.tensor(s, device=cuda_device)
         nxt = 0 if slot is None else 1 - slot
-        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, None if slot is None else applied[slot:slot + 1],
+        capi.ce_rescale_grad(grad, grad, capi.F32, grad.numel(), scale, capi.F32, None if slot is None else applied[slot:slot + 1],
                              applied[nxt:nxt + 1])
         slot = nxt
         torch.cuda.synchronize()
         assert_close(grad.cpu().numpy(), (ref * s).cpu().numpy(), 2e-7, 0, f"scale {s}")
         assert applied[slot].item() == s
     with pytest.raises(capi.KernelError):
-        capi.ce_rescale_grad(grad, capi.F32, grad.numel(), scale, capi.F32, applied[0:1], applied[0:1])
+        capi.ce_rescale_grad(grad, grad, capi.F32, grad.numel(), scale, capi.F32, applied[0:1], applied[0:1])
+    # out of place: the source and the recorded factor stay as they are, a factor of exactly 1 still copies
+    out = torch.zeros_like(grad)
+    before = grad.clone()
+    for s in (2.0, 6.0):
+        capi.ce_rescale_grad(grad, out, capi.F32, grad.numel(), torch.tensor(s, device=cuda_device), capi.F32, applied[slot:slot + 1], None)
+        torch.cuda.synchronize()
+        assert torch.equal(grad, before) and applied[slot].item() == 2.0
+        assert_close(out.cpu().numpy(), (ref * s).cpu().numpy(), 2e-7, 0, f"out of place {s}")
+    # a recorded factor of zero cannot be undone: NaN and a status bit, unless the new factor is zero too
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    zero = torch.zeros(1, device=cuda_device)
+    capi.ce_rescale_grad(grad, out, capi.F32, grad.numel(), zero, capi.F32, zero, None, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and torch.count_nonzero(out).item() == 0
+    capi.ce_rescale_grad(grad, out, capi.F32, grad.numel(), torch.ones(1, device=cuda_device), capi.F32, zero, None, status)
+    torch.cuda.synchronize()
+    assert status.item() == capi.STATUS_GRADIENT_LOST and torch.isnan(out).all()
 
 
 def test_linearity_property_full_vocab(cuda_device):
@@ -204,8 +221,17 @@ def test_linearity_property_full_vocab(cuda_device):
     (150, 100004, torch.float32, 4),    # 400016 B: odd unit count over four CTAs
     (148, 150000, torch.float32, 4),    # 600000 B: 4-CTA cluster
     (75, 300008, torch.float16, 4),
-    (30, 128256, torch.bfloat16, 0),    # too few rows for clusters: generic kernel
-    (64, 32002, torch.float32, 0),      # row pitch not a multiple of 16 bytes: generic kernel
+    (30, 128256, torch.bfloat16, 2),    # fewer rows than clusters: some SMs idle, still one read and one write
+    (64, 32002, torch.float32, 1),      # row pitch not a multiple of 16 bytes: edge units handled apart
+    (64, 50257, torch.bfloat16, 1),     # real vocabularies whose rows start at every 2-byte phase of a 16-byte unit
+    (64, 32001, torch.float32, 1),
+    (64, 151643, torch.bfloat16, 2),
+    (37, 300007, torch.float16, 4),
+    (150, 50257, torch.float32, 2),     # 201028 B: ragged rows over a 2-CTA cluster
+    (4096, 2048, torch.float32, 8),     # short rows: held in registers
+    (1000, 4093, torch.bfloat16, 8),    # short ragged rows, one 128-thread group each
+    (3000, 100, torch.float32, 8),      # one warp per row
+    (777, 1023, torch.float16, 8),
 ])
 def test_resident_variants(cuda_device, rows, classes, dtype, variant):
     """The shared-memory-resident kernels (single CTA and 2/4-CTA clusters) against the oracle."""
@@ -227,14 +253,161 @@ def test_resident_variants(cuda_device, rows, classes, dtype, variant):
             assert_close(grad * scale, egrad * scale, 1e-5, 3e-7, f"grad {red}")
         else:
             assert rel_err(loss, eloss[0]) <= 1e-2
+            # fp16 stores p / |V|: one subnormal step (2^-24) of the stored value is the floor of what can be resolved
             assert_close(grad * scale, egrad * scale, 1.6e-2 if dtype == torch.bfloat16 else 2e-3,
-                         1e-4 if dtype == torch.bfloat16 else 2e-5, f"grad {red}")
+                         1e-4 if dtype == torch.bfloat16 else max(2e-5, 2.0 ** -24 * scale), f"grad {red}")
         assert np.all(grad[(target == -100).numpy()] == 0)
     # forward only and per-row losses
     loss_n, none = _run(cuda_device, logits, target, reduction="none", want_grad=False)
     eloss_n, _, _ = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, 0.0, "none", want_grad=False)
     assert none is None
     assert_close(loss_n, eloss_n, 2e-6, 2e-6, "row losses")
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(40, 50257, torch.bfloat16), (40, 32001, torch.float32), (300, 1001, torch.bfloat16),
+                                                (33, 151643, torch.bfloat16)])
+def test_unaligned_base_and_in_place(cuda_device, rows, classes, dtype):
+    """Logits that start in the middle of a 16-byte unit (a view one element into a larger buffer), overwritten in place
+    by their gradient: neither the element before the first row nor the one after the last row may change."""
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(classes + rows)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::9] = -100
+    buf = torch.full((rows * classes + 16,), 7.0, dtype=dtype, device=cuda_device)
+    view = buf[1:1 + rows * classes].view(rows, classes)
+    view.copy_(logits)
+    row_loss = torch.empty(rows, dtype=torch.float32, device=cuda_device)
+    acc = torch.zeros(2, dtype=torch.float64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    td = target.to(cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    capi.ce_count_valid(td, rows, classes, -100, acc, status, stream)
+    a = capi.CEArgs()
+    a.logits = a.grad_logits = view.data_ptr()
+    a.dtype, a.reduction, a.target = capi.torch_dtype_code(dtype), capi.REDUCTION_MEAN, td.data_ptr()
+    a.row_loss, a.acc, a.rows, a.classes, a.ignore_index = row_loss.data_ptr(), acc.data_ptr(), rows, classes, -100
+    a.label_smoothing, a.grad_scale, a.status, a.flags = 0.1, 1.0, status.data_ptr(), capi.CE_FLAG_AFTER_COUNT
+    capi.ce_forward_backward(a, stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert float(buf[0]) == 7.0 and bool((buf[1 + rows * classes:] == 7.0).all()), "bytes outside the rows were written"
+    eloss, egrad, bad = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, 0.1, "mean")
+    scale = float((target != -100).sum())
+    grad = view.float().cpu().numpy()
+    tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
+    assert_close(grad * scale, egrad * scale, tol[0], tol[1], "in-place gradient")
+    assert np.all(grad[(target == -100).numpy()] == 0)
+    want = float(row_loss.double().sum()) / scale
+    assert rel_err(want, eloss[0]) <= (2e-6 if dtype == torch.float32 else 1e-3)
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(64, 32000, torch.float32), (48, 50257, torch.bfloat16), (300, 1000, torch.float32),
+                                                (16, 10, torch.float32), (40, 5003, torch.float16)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_class_weights_with_label_smoothing(cuda_device, rows, classes, dtype, reduction):
+    """Class weights together with label smoothing: the smoothing term weights every class by its own weight; against
+    PyTorch CPU in float64."""
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(3 * rows + classes)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::5] = -100
+    w = torch.rand(classes, generator=g) + 0.25
+    xr = logits.double().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xr, target, weight=w.double(), reduction=reduction, label_smoothing=0.2)
+    go = torch.ones(rows) if reduction == "none" else None
+    ref.backward(go.double() if go is not None else None)
+    loss, grad = F2.cross_entropy_forward_backward(logits.to(cuda_device), target.to(cuda_device), reduction=reduction,
+                                                   class_weight=w.to(cuda_device), label_smoothing=0.2)
+    torch.cuda.synchronize()
+    tol = {torch.float32: (1e-5, 3e-7), torch.bfloat16: (1.6e-2, 1e-4), torch.float16: (2e-3, 2e-5)}[dtype]
+    ltol = 4e-6 if (dtype == torch.float32 or reduction == "none") else tol[0]
+    assert_close(np.atleast_1d(loss.double().cpu().numpy()), np.atleast_1d(ref.detach().numpy()), ltol, 4e-6, "loss")
+    scale = float(w[target[target >= 0]].sum()) if reduction == "mean" else 1.0
+    assert_close(grad.double().cpu().numpy() * scale, xr.grad.numpy() * scale, tol[0], tol[1], "grad")
+    assert float(grad[0].abs().max()) == 0.0, "ignored rows get a zero gradient"
+
+
+def _xchg(cuda_device, nranks, rank, seq, slot_arrays):
+    from torch_supa_b200 import capi
+
+    x = capi.Xchg()
+    for r in range(nranks):
+        x.slots[r] = slot_arrays[r].data_ptr()
+    x.rank, x.nranks, x.seq = rank, nranks, seq
+    return x
+
+
+def test_scalar_exchange_kernels_on_one_gpu(cuda_device):
+    """The exchange inside the count and loss kernels, on one GPU: a job of one rank (its own partial travels through its
+    slot array), and rank 0 of a job of two whose peer's partials are already in place when the kernels start (put
+    there by the host: no kernel here waits for another launch).  The sum runs in rank order."""
+    import struct
+
+    from torch_supa_b200 import capi
+
+    rows, classes = 5000, 300
+    g = torch.Generator().manual_seed(9)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::4] = -100
+    valid = int((target != -100).sum())
+    td = target.to(cuda_device)
+    row_loss = torch.rand(rows, generator=g).to(cuda_device)
+    local_sum = float(row_loss.double().sum())
+    acc = torch.zeros(2, dtype=torch.float64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    loss = torch.empty((), device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    mine = torch.zeros(capi.XCHG_SLOT_BYTES, dtype=torch.uint8, device=cuda_device)
+    # one rank
+    capi.ce_count_exchange(td, None, rows, classes, -100, acc, status, _xchg(cuda_device, 1, 0, 1, [mine]), stream)
+    capi.ce_loss_exchange(row_loss, rows, acc, capi.REDUCTION_MEAN, loss, capi.F32, status, _xchg(cuda_device, 1, 0, 2, [mine]), stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and acc[1].item() == valid
+    assert abs(acc[0].item() - local_sum) <= 1e-9 * local_sum and abs(loss.item() - local_sum / valid) <= 2e-7 * local_sum / valid
+    # rank 0 of two: the peer's slots (source rank 1) of exchanges 3 and 4 are filled before the launches
+    other = torch.zeros(capi.XCHG_SLOT_BYTES, dtype=torch.uint8, device=cuda_device)  # stands for the peer's array: only written to
+    host = bytearray(capi.XCHG_SLOT_BYTES)
+    for seq, value in ((3, 1234.0), (4, 0.5)):
+        off = ((seq % capi.XCHG_DEPTH) * capi.XCHG_MAX_RANKS + 1) * 16
+        host[off:off + 16] = struct.pack("<dQ", value, seq)
+    mine.copy_(torch.frombuffer(host, dtype=torch.uint8))
+    capi.ce_count_exchange(td, None, rows, classes, -100, acc, status, _xchg(cuda_device, 2, 0, 3, [mine, other]), stream)
+    capi.ce_loss_exchange(row_loss, rows, acc, capi.REDUCTION_SUM, loss, capi.F32, status, _xchg(cuda_device, 2, 0, 4, [mine, other]), stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and acc[1].item() == valid + 1234.0
+    assert abs(acc[0].item() - (local_sum + 0.5)) <= 1e-9 * local_sum
+    # what this rank published for its peer: its partials under the right sequence numbers, at source-rank slot 0
+    pub = bytes(other.cpu().numpy())
+    v3, s3 = struct.unpack_from("<dQ", pub, ((3 % capi.XCHG_DEPTH) * capi.XCHG_MAX_RANKS + 0) * 16)
+    v4, s4 = struct.unpack_from("<dQ", pub, ((4 % capi.XCHG_DEPTH) * capi.XCHG_MAX_RANKS + 0) * 16)
+    assert (s3, s4) == (3, 4) and v3 == valid and abs(v4 - local_sum) <= 1e-9 * local_sum
+
+
+def test_scalar_exchange_wait_runs_out(cuda_device):
+    """A peer that never publishes: the bounded wait gives up after its limit, the kernel finishes with the local partial
+    and sets SB_STATUS_KERNEL_TIMEOUT; the context stays usable."""
+    from torch_supa_b200 import capi
+
+    rows, classes = 100, 10
+    td = torch.zeros(rows, dtype=torch.int64, device=cuda_device)
+    acc = torch.zeros(2, dtype=torch.float64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    mine = torch.zeros(capi.XCHG_SLOT_BYTES, dtype=torch.uint8, device=cuda_device)
+    other = torch.zeros(capi.XCHG_SLOT_BYTES, dtype=torch.uint8, device=cuda_device)
+    capi.check("sb_set_tuning", capi.lib().sb_set_tuning(5, 50))  # 50 ms
+    try:
+        capi.ce_count_exchange(td, None, rows, classes, -100, acc, status, _xchg(cuda_device, 2, 0, 1, [mine, other]),
+                               torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+    finally:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(5, 10000))
+    assert status.item() == capi.STATUS_KERNEL_TIMEOUT
+    assert acc[1].item() == rows
+    assert float((torch.ones(4, device=cuda_device) * 2).sum()) == 8.0
 
 
 def test_resident_matches_generic_bitwise_loss_order(cuda_device):

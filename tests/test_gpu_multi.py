@@ -1,4 +1,5 @@
-"""Row-sharded cross entropy on two GPUs of one node (needs at least two GPUs; skipped otherwise)."""
+"""Row-sharded cross entropy on two GPUs of one node (needs at least two GPUs; skipped otherwise), once with the two
+scalars exchanged by the loss kernels through peer memory and once through NCCL all-reduces."""
 import os
 import subprocess
 import sys
@@ -10,9 +11,11 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_cross_entropy_two_gpus():
+@pytest.mark.parametrize("mode,port", [("peer", 29533), ("nccl", 29543)])
+def test_sharded_cross_entropy_two_gpus(mode, port):
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "multi_gpu_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", worker]
-    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+           "--master-port", str(port), worker]
+    env = dict(os.environ, SUPA_B200_LOSS_EXCHANGE=mode)
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]

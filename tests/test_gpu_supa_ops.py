@@ -24,13 +24,13 @@ def supa():
 
 
 def _pair(shape, dtype, seed=0, requires_grad=False, **kw):
-    from torch_supa_b200.testing import create_random_tensor
+    from tests.supa_testing import create_random_tensor
 
     return create_random_tensor(shape, dtype, seed=seed, requires_grad=requires_grad, **kw)
 
 
 def _close(golden, out, dtype=None, loosen=1.0):
-    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+    from tests.supa_testing import ATOL, RTOL, assert_allclose
 
     dtype = dtype or golden.dtype
     assert out.device.type == "supa" and out.dtype == golden.dtype and out.shape == golden.shape
@@ -221,7 +221,7 @@ def test_glu_forward_backward(supa, shape, dim, dtype):
     xr = x_cpu.detach().float().requires_grad_(True)
     yr = F.glu(xr, dim)
     g_cpu, g = _pair(tuple(yr.shape), dtype, seed=1)
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     assert_allclose(yr.detach().to(dtype), y.detach(), 1.6e-2 if dtype == torch.bfloat16 else 2e-3 if dtype == torch.float16 else 3e-6,
                     1e-2 if dtype == torch.bfloat16 else 1e-4 if dtype == torch.float16 else 1e-5)
@@ -241,7 +241,7 @@ def test_swiglu_chain_on_views(supa):
     ref = (F.silu(xr[:, :11008]).bfloat16().float() * xr[:, 11008:])
     ref.backward(g_cpu.float())
     _close(ref.detach().bfloat16(), out.detach(), loosen=1)
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     assert_allclose(xr.grad.bfloat16(), x.grad, 2.4e-2, 2e-2)
 
@@ -251,7 +251,7 @@ def test_swiglu_chain_on_views(supa):
 @pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), 0), ((64, 65536), -1), ((7, 9, 11), (0, 2)),
                                        ((5, 6, 7, 8), None), ((1,), 0), ((3, 1, 5), 1)])
 def test_sum_mean_amax(supa, shape, dim, dtype):
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     x_cpu, x = _pair(shape, dtype)
     n = x_cpu.numel() if dim is None else int(np.prod([shape[d] for d in (dim if isinstance(dim, tuple) else (dim,))]))
@@ -297,7 +297,7 @@ def test_reduction_dtype_rules(supa):
 @pytest.mark.parametrize("shape", [(16,), (1024, 512), (1023, 511), (3, 5, 7)])
 def test_neighbouring_unary_ops_forward_backward(supa, shape, dtype):
     """sigmoid / tanh / exp / log and their autograd formulas (sigmoid_backward, tanh_backward, mul, div) on the device."""
-    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+    from tests.supa_testing import ATOL, RTOL, assert_allclose
 
     for name, fn, positive in (("sigmoid", torch.sigmoid, False), ("tanh", torch.tanh, False), ("exp", torch.exp, False),
                                ("log", torch.log, True)):
@@ -352,15 +352,27 @@ def test_comparisons_extrema_where_masked_fill(supa, dtype):
         assert not bool((n == n).cpu()[1, 2]) and bool((n != n).cpu()[1, 2])
 
 
-def test_cross_entropy_weights_with_label_smoothing_is_refused_loudly(supa):
-    """Class weights together with label smoothing are not fused, and libtorch's composite for them needs operators
-    outside this path (bitwise_not, ...): the call raises and names the missing operator; nothing falls back to the CPU."""
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cross_entropy_weights_with_label_smoothing(supa, reduction, dtype):
+    """Class weights together with label smoothing (the reference reaches the upstream composite for them,
+    CrossEntropyLoss.cpp:23-33,50): same loss and gradient as the CPU."""
+    from tests.supa_testing import assert_allclose
+
     g = torch.Generator().manual_seed(8)
-    x = torch.randn(24, 50, generator=g).to(supa)
-    t = torch.randint(0, 50, (24,), generator=g).to(supa)
-    w = (torch.rand(50, generator=g) + 0.5).to(supa)
-    with pytest.raises(NotImplementedError, match="supa"):
-        F.cross_entropy(x, t, weight=w, label_smoothing=0.1)
+    x_cpu = (torch.randn(24, 500, generator=g) * 2).to(dtype).requires_grad_(True)
+    x = x_cpu.detach().to(supa).requires_grad_(True)
+    t = torch.randint(0, 500, (24,), generator=g)
+    t[::5] = -100
+    w = torch.rand(500, generator=g) + 0.5
+    ref = F.cross_entropy(x_cpu.float(), t, weight=w, label_smoothing=0.1, reduction=reduction)
+    out = F.cross_entropy(x, t.to(supa), weight=w.to(supa), label_smoothing=0.1, reduction=reduction)
+    go = torch.rand(ref.shape, generator=g) + 0.5
+    ref.backward(go)
+    out.backward(go.to(supa).to(out.dtype))
+    rt, at = (2e-5, 1e-6) if dtype == torch.float32 else (1.6e-2, 1e-3)
+    assert_allclose(ref.detach().to(dtype), out.detach(), rt, at)
+    assert_allclose(x_cpu.grad.float(), x.grad.float(), rt, at * 1e-1)
 
 
 # ---- softmax / nll -------------------------------------------------------------------------------------------------
@@ -368,7 +380,7 @@ def test_cross_entropy_weights_with_label_smoothing_is_refused_loudly(supa):
 @pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), -1), ((1025, 513), 0), ((64, 32000), -1),
                                        ((4, 5, 6, 7), 2)])
 def test_log_softmax_forward_backward(supa, shape, dim, dtype):
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     x_cpu, x = _pair(shape, dtype, requires_grad=True)
     g_cpu, g = _pair(shape, dtype, seed=1)
@@ -389,7 +401,7 @@ def test_log_softmax_forward_backward(supa, shape, dim, dtype):
 @pytest.mark.parametrize("shape,dim", [((16,), 0), ((1024, 512), -1), ((1023, 511), 0), ((64, 32000), -1), ((4, 5, 6, 7), 2)])
 def test_softmax_forward_backward(supa, shape, dim, dtype):
     """F.softmax dispatches to _softmax / _softmax_backward_data on the device (autograd wiring from libtorch)."""
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     x_cpu, x = _pair(shape, dtype, requires_grad=True)
     g_cpu, g = _pair(shape, dtype, seed=1)
@@ -409,7 +421,7 @@ def test_softmax_forward_backward(supa, shape, dim, dtype):
 @pytest.mark.parametrize("shape", [(16, 10), (1024, 512), (2000, 1000), (100, 20000)])
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
 def test_nll_loss_forward_backward_weight(supa, shape, reduction, dtype):
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     g = torch.Generator().manual_seed(shape[0])
     logp_cpu = F.log_softmax(torch.randn(*shape, generator=g), 1).to(dtype).requires_grad_(True)
@@ -438,7 +450,7 @@ def test_nll_loss_forward_backward_weight(supa, shape, reduction, dtype):
 def test_nll_loss2d_and_spatial_cross_entropy(supa, shape, reduction, dtype):
     """(N, C, H, W) inputs: F.nll_loss dispatches to nll_loss2d_forward / backward, F.cross_entropy to log_softmax over
     dim 1 followed by them (the 4-D shape (2, 19, 512, 1024) is the reference's segmentation case)."""
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     if shape[2] >= 512 and (dtype != torch.float32 or reduction == "sum"):
         pytest.skip("the large shape runs once per reduction family")
@@ -485,7 +497,7 @@ def test_nll_loss2d_and_spatial_cross_entropy(supa, shape, reduction, dtype):
 def test_binary_cross_entropy_with_logits_forward_backward(supa, shape, dtype, reduction, with_weight, with_pos_weight, pos_weight_shape):
     """The parameter list of the reference's test (test/test_binary_misc_ops_kernels.py:176-245) plus the backward
     pass, which runs our own autograd node (one fused kernel) instead of libtorch's operator chain."""
-    from torch_supa_b200.testing import ATOL, RTOL, assert_allclose
+    from tests.supa_testing import ATOL, RTOL, assert_allclose
 
     g = torch.Generator().manual_seed(shape[0])
     x_cpu = (torch.rand(*shape, generator=g) * 10 - 5).to(dtype)
@@ -521,7 +533,7 @@ def test_binary_cross_entropy_with_logits_forward_backward(supa, shape, dtype, r
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_cross_entropy_forward_backward(supa, shape, reduction, dtype):
     """F.cross_entropy through the dispatcher (test/test_loss.py:235-276), with ignore_index and label smoothing."""
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     g = torch.Generator().manual_seed(shape[1])
     x_cpu = (torch.randn(*shape, generator=g) * 2).to(dtype)
@@ -554,7 +566,7 @@ def test_cross_entropy_forward_backward(supa, shape, reduction, dtype):
 def test_cross_entropy_class_weights_forward_backward(supa, shape, reduction, dtype):
     """F.cross_entropy(..., weight=w) stays on the fused kernel when there is no label smoothing (weights together with
     smoothing go to libtorch's composite, whose mask operators are outside this path)."""
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     g = torch.Generator().manual_seed(shape[0])
     x_cpu = (torch.randn(*shape, generator=g) * 2).to(dtype)
@@ -608,10 +620,67 @@ def test_cross_entropy_backward_twice_and_scaled(supa):
     g2 = x.grad.clone()
     ref = F.cross_entropy(x_cpu, t)
     ref.backward()
-    from torch_supa_b200.testing import assert_allclose
+    from tests.supa_testing import assert_allclose
 
     assert_allclose(x_cpu.grad * 32, g2 * 32, 1e-5, 3e-7)
     assert_allclose(x_cpu.grad * 8, g1 * 32, 1e-5, 3e-7)
+
+
+def test_cross_entropy_retained_graph_hands_out_independent_gradients(supa):
+    """torch.autograd.grad twice on a retained graph, no clone in between: the tensor returned first must not change
+    when the second call runs with another upstream gradient, and both must match the CPU."""
+    from tests.supa_testing import assert_allclose
+
+    x_cpu, x = _pair((48, 3000), torch.float32, requires_grad=True)
+    t = torch.randint(0, 3000, (48,), generator=torch.Generator().manual_seed(2))
+    loss = F.cross_entropy(x, t.to(supa), label_smoothing=0.1)
+    ref = F.cross_entropy(x_cpu, t, label_smoothing=0.1)
+    (g1,) = torch.autograd.grad(loss, x, torch.tensor(0.5).to(supa), retain_graph=True)
+    g1_copy = g1.cpu().clone()
+    (g2,) = torch.autograd.grad(loss, x, torch.tensor(3.0).to(supa), retain_graph=True)
+    (g3,) = torch.autograd.grad(loss, x, torch.tensor(1.0).to(supa))
+    (r,) = torch.autograd.grad(ref, x_cpu)
+    assert torch.equal(g1.cpu(), g1_copy), "the first result changed under its holder"
+    assert g1.data_ptr() != g2.data_ptr() and g2.data_ptr() != g3.data_ptr()
+    for got, f in ((g1, 0.5), (g2, 3.0), (g3, 1.0)):
+        assert_allclose(r * 48 * f, got * 48, 1e-5, 3e-7)
+
+
+def test_cross_entropy_zero_upstream_then_one_raises_instead_of_dividing(supa):
+    """An upstream gradient of zero wipes the stored gradient; a later backward on the retained graph cannot undo that
+    and says so at the next synchronisation instead of returning NaN silently."""
+    _, x = _pair((16, 300), torch.float32, requires_grad=True)
+    t = torch.randint(0, 300, (16,), generator=torch.Generator().manual_seed(3)).to(supa)
+    loss = F.cross_entropy(x, t)
+    (g0,) = torch.autograd.grad(loss, x, torch.tensor(0.0).to(supa), retain_graph=True)
+    assert float(g0.cpu().abs().max()) == 0.0
+    (g1,) = torch.autograd.grad(loss, x, torch.tensor(1.0).to(supa), retain_graph=True)
+    with pytest.raises(RuntimeError, match="zero upstream"):
+        g1.cpu()
+    torch.supa.synchronize()  # the device and the status word are usable again
+    assert float(F.cross_entropy(x.detach(), t).cpu()) > 0
+
+
+def test_cross_entropy_fp16_survives_loss_scaling(supa):
+    """fp16 logits with a loss-scaling upstream gradient: most probabilities over the row count are below fp16's
+    smallest subnormal, so the gradient must be formed with the upstream factor folded in before it is rounded."""
+    from tests.supa_testing import assert_allclose
+
+    rows, classes, scale = 32768, 64, 1024.0  # a power of two that an fp16 loss can be multiplied by without overflowing
+    g = torch.Generator().manual_seed(4)
+    x_cpu = torch.randn(rows, classes, generator=g).half()
+    t = torch.randint(0, classes, (rows,), generator=g)
+    x = x_cpu.to(supa).requires_grad_(True)
+    loss = F.cross_entropy(x, t.to(supa))
+    (loss * scale).backward()
+    xr = x_cpu.double().requires_grad_(True)
+    (F.cross_entropy(xr, t) * scale).backward()
+    got, want = x.grad.cpu().double(), xr.grad
+    assert float(got.abs().max()) > 0
+    small = want.abs() < 0.5  # everything but the class of the target
+    rel = ((got - want).abs() / want.abs().clamp_min(1e-30))[small & (want.abs() > 1e-3)]
+    assert float(rel.max()) <= 1e-2, f"relative error {float(rel.max())}"
+    assert_allclose(want.float(), got.float(), 2e-3, 1e-5)
 
 
 def test_out_of_range_target_raises_at_the_next_sync_and_device_survives(supa):

@@ -139,3 +139,86 @@ def test_two_process_gloo_sharded_loss(tmp_path):
     out = tmp_path / "ok.txt"
     mp.spawn(_sharded_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     assert float(out.read_text()) == 2.0
+
+
+# ---- the exchange protocol of the loss kernels, restated on the host -------------------------------------------------
+# The kernels publish a partial as (value, sequence number) into slot (seq % DEPTH, source rank) of every rank's array and
+# add what arrives in their own array in rank order.  The same steps on shared host memory, two processes, many
+# exchanges back to back: slot rows are reused every DEPTH exchanges and no rank may read a stale or a future value.
+def _slot_index(seq, src_rank, depth, max_ranks):
+    return (seq % depth) * max_ranks + src_rank
+
+
+def _host_exchange(arrays, rank, world, seq, local, depth, max_ranks, deadline_s=20.0):
+    import time
+
+    for peer in range(world):
+        slot = arrays[peer][_slot_index(seq, rank, depth, max_ranks)]
+        slot[0] = local          # value first ...
+        slot[1] = float(seq)     # ... then the number a reader waits for
+    mine = arrays[rank]
+    total = 0.0
+    t0 = time.time()
+    for src in range(world):
+        slot = mine[_slot_index(seq, src, depth, max_ranks)]
+        while slot[1] != float(seq):
+            if time.time() - t0 > deadline_s:
+                raise TimeoutError(f"rank {rank}: partial of rank {src} for exchange {seq} never arrived")
+        total += float(slot[0])
+    return total
+
+
+def _exchange_worker(rank, world, port, arrays, out_path):
+    sys.path.insert(0, str(ROOT))
+    import torch.distributed as dist
+
+    from torch_supa_b200 import capi
+    from torch_supa_b200.distributed import PEER_HANDLE_BYTES, gather_peer_handles
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    # the handle hand-over the GPU path uses, with stand-in bytes
+    mine = bytes([rank + 1]) * PEER_HANDLE_BYTES
+    handles = gather_peer_handles(store, "test/peer", rank, world, mine)
+    ok = handles == b"".join(bytes([r + 1]) * PEER_HANDLE_BYTES for r in range(world))
+    seq = 0
+    for step in range(50):
+        # count exchange, then loss exchange, as fused_forward issues them; rank 1 lags now and then
+        if rank == 1 and step % 7 == 3:
+            import time
+
+            time.sleep(0.01)
+        seq += 1
+        count = _host_exchange(arrays, rank, world, seq, float(10 * step + rank), capi.XCHG_DEPTH, capi.XCHG_MAX_RANKS)
+        seq += 1
+        loss = _host_exchange(arrays, rank, world, seq, 0.5 * step + 0.25 * rank, capi.XCHG_DEPTH, capi.XCHG_MAX_RANKS)
+        ok = ok and count == sum(10 * step + r for r in range(world)) and loss == sum(0.5 * step + 0.25 * r for r in range(world))
+    flags = torch.tensor([1.0 if ok else 0.0], dtype=torch.float64)
+    dist.all_reduce(flags)
+    if rank == 0:
+        Path(out_path).write_text(str(flags.item()))
+    dist.destroy_process_group()
+
+
+def test_two_process_slot_exchange_protocol(tmp_path):
+    from torch_supa_b200 import capi
+
+    world = 2
+    arrays = [torch.zeros(capi.XCHG_DEPTH * capi.XCHG_MAX_RANKS, 2, dtype=torch.float64).share_memory_() for _ in range(world)]
+    out = tmp_path / "ok.txt"
+    mp.spawn(_exchange_worker, args=(world, _free_port(), arrays, str(out)), nprocs=world, join=True)
+    assert float(out.read_text()) == 2.0
+
+
+def test_exchange_mode_from_environment(monkeypatch):
+    from torch_supa_b200.distributed import exchange_mode
+
+    monkeypatch.delenv("SUPA_B200_LOSS_EXCHANGE", raising=False)
+    assert exchange_mode() == "peer"
+    monkeypatch.setenv("SUPA_B200_LOSS_EXCHANGE", "NCCL")
+    assert exchange_mode() == "nccl"
+    monkeypatch.setenv("SUPA_B200_LOSS_EXCHANGE", "gloo")
+    with pytest.raises(ValueError):
+        exchange_mode()

@@ -124,3 +124,74 @@ def test_binary(golden):
     f = golden["bin/f32"].astype(np.float64)
     assert_close(oracle.c_elementwise(2, f, f.T.copy(), alpha=2.5), golden["bin/add_alpha"], 2e-6, 2e-6, "add alpha")
     assert_close(oracle.c_elementwise(3, f.T.copy(), f), golden["bin/mul_t"], 2e-6, 2e-6, "mul")
+
+
+# ---- rows added later: weights with smoothing, probability targets, indexed extrema, moments, prod / nansum, div modes ----
+@pytest.mark.parametrize("name", ["cew_mean", "cew_sum", "cew_none"])
+def test_cross_entropy_weights_and_smoothing(golden, name):
+    red = name.split("_")[1]
+    go = golden[name + "/grad_out"]
+    loss, grad, bad = oracle.c_cross_entropy_weighted(
+        golden[name + "/logits"], golden[name + "/target"], golden[name + "/weight"], -100, 0.2, red,
+        grad_out=1.0 if red == "none" else float(go), row_grad_out=go if red == "none" else None)
+    assert bad == 0
+    assert_close(loss, np.atleast_1d(golden[name + "/loss"]), 2e-6, 2e-6, name + " loss")
+    assert_close(grad, golden[name + "/grad"], 1e-5, 2e-7, name + " grad")
+
+
+def test_weighted_oracle_without_weights_is_the_plain_one(golden):
+    name = "ce_6x130_mean_ign2_eps1"
+    a = oracle.c_cross_entropy(golden[name + "/logits"], golden[name + "/target"], -100, 0.1, "mean")
+    b = oracle.c_cross_entropy_weighted(golden[name + "/logits"], golden[name + "/target"], None, -100, 0.1, "mean")
+    assert_close(b[0], a[0], 1e-14, 0, "loss")
+    assert_close(b[1], a[1], 1e-12, 1e-18, "grad")
+
+
+@pytest.mark.parametrize("name", ["cep_mean", "cep_sum_w", "cep_none_eps", "cep_mean_w_eps"])
+def test_cross_entropy_probability_targets(golden, name):
+    red = name.split("_")[1]
+    go = golden[name + "/grad_out"]
+    w = golden[name + "/weight"] if name + "/weight" in golden.files else None
+    loss, grad = oracle.c_cross_entropy_prob(golden[name + "/logits"], golden[name + "/target"], w, float(golden[name + "/eps"][0]), red,
+                                             grad_out=1.0 if red == "none" else float(go), row_grad_out=go if red == "none" else None)
+    assert_close(loss, np.atleast_1d(golden[name + "/loss"]), 2e-6, 2e-6, name + " loss")
+    assert_close(grad, golden[name + "/grad"], 1e-5, 2e-7, name + " grad")
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2])
+@pytest.mark.parametrize("is_max", [True, False])
+def test_indexed_extrema(golden, dim, is_max):
+    values, indices = oracle.c_arg_reduce(golden["arg/x"], dim, is_max)
+    key = f"arg/{'max' if is_max else 'min'}{dim}"
+    assert np.array_equal(indices, golden[key + "_indices"])
+    assert np.array_equal(values, golden[key + "_values"].astype(np.float64), equal_nan=True)
+
+
+def test_indexed_extrema_flat_and_int(golden):
+    x = golden["arg/x"][0]
+    assert oracle.c_arg_reduce(x.reshape(-1), 0, True)[1] == golden["arg/argmax_flat"]
+    assert oracle.c_arg_reduce(x.reshape(-1), 0, False)[1] == golden["arg/argmin_flat"]
+    assert np.array_equal(oracle.c_arg_reduce(golden["arg/i32"], 1, True)[1], golden["arg/i32_argmax1"])
+    v, i = oracle.c_arg_reduce(golden["arg/i32"], 1, False)
+    assert np.array_equal(i, golden["arg/i32_min1_indices"]) and np.array_equal(v, golden["arg/i32_min1_values"])
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_moments(golden, dim):
+    x = golden["mom/x"]
+    assert_close(oracle.c_moments(x, dim, 1.0, False)[0], golden[f"mom/var{dim}"], 2e-6, 1e-6, "var")
+    assert_close(oracle.c_moments(x, dim, 0.0, True)[0], golden[f"mom/std{dim}_c0"], 2e-6, 1e-6, "std")
+    if dim == 1:
+        assert_close(oracle.c_moments(x, 1)[1], golden["mom/mean1"], 2e-6, 1e-6, "mean")
+    assert_close(oracle.c_moments(x.reshape(-1), 0)[0], golden["mom/var_all"], 2e-6, 1e-6, "var of all")
+
+
+def test_div_rounding_modes(golden):
+    a, b = golden["div/a"], golden["div/b"]
+    for code, key in ((38, "trunc"), (39, "floor")):
+        got = oracle.c_elementwise(code, a, b)
+        want = golden["div/" + key].astype(np.float64)
+        assert np.array_equal(got, want, equal_nan=True), key
+        assert np.array_equal(np.signbit(got), np.signbit(want)), key + ": sign of zero"
+    assert np.array_equal(oracle.c_div_int(golden["div/ia"], golden["div/ib"], False), golden["div/itrunc"])
+    assert np.array_equal(oracle.c_div_int(golden["div/ia"], golden["div/ib"], True), golden["div/ifloor"])

@@ -41,6 +41,20 @@ def test_static_scratch_matches_caller_scratch_twice(cuda_device, dtype):
         assert status.item() == 0
         assert loss.item() == ref_loss.item(), "same kernels, same order: the loss is bit-identical"
         assert torch.equal(grad, ref_grad)
+        # the reason this entry point exists: a repeated call (the first one per device resolves the array's address) takes no
+        # memory from the device, neither through the caching allocator of the process nor behind its back
+        grad.zero_()
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        stats_before = torch.cuda.memory_stats()
+        _static_call(logits, target, grad, loss, status, red, eps)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        stats_after = torch.cuda.memory_stats()
+        assert free_after == free_before, "device memory was allocated during the call"
+        for key in ("allocation.all.allocated", "segment.all.allocated", "reserved_bytes.all.current"):
+            assert stats_after[key] == stats_before[key], key
+        assert loss.item() == ref_loss.item() and torch.equal(grad, ref_grad)
 
 
 def test_static_scratch_rejects_what_it_cannot_hold(cuda_device):

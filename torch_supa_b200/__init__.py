@@ -50,4 +50,4 @@ torch.utils.rename_privateuse1_backend("supa")
 torch._register_device_module("supa", supa)
 torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module=True, for_storage=True)
 
-from . import distributed, testing  # noqa: E402,F401
+from . import distributed  # noqa: E402,F401

@@ -20,14 +20,16 @@ BOOL, U8, I8, I16, I32, I64, F16, BF16, F32, F64 = range(10)
 # sb_reduction
 REDUCTION_NONE, REDUCTION_MEAN, REDUCTION_SUM = 0, 1, 2
 STATUS_TARGET_OUT_OF_RANGE = 0x1
+STATUS_KERNEL_TIMEOUT = 0x2
+STATUS_GRADIENT_LOST = 0x4
 
 # sb_ew_op
 (EW_COPY, EW_FILL, EW_ADD, EW_MUL, EW_SUB, EW_DIV, EW_GELU_ERF, EW_GELU_TANH, EW_SILU, EW_GLU, EW_GELU_ERF_BWD,
  EW_GELU_TANH_BWD, EW_SILU_BWD, EW_GLU_BWD_A, EW_GLU_BWD_B, EW_ADD_SCALAR, EW_MUL_SCALAR, EW_NEG, EW_BCE_LOGITS,
  EW_BCE_LOGITS_PW, EW_BCE_LOGITS_BWD, EW_BCE_LOGITS_PW_BWD, EW_SIGMOID, EW_TANH, EW_EXP, EW_LOG, EW_SIGMOID_BWD, EW_TANH_BWD,
- EW_MAXIMUM, EW_MINIMUM, EW_EQ, EW_NE, EW_LT, EW_LE, EW_GT, EW_GE, EW_WHERE, EW_MASKED_FILL) = range(38)
+ EW_MAXIMUM, EW_MINIMUM, EW_EQ, EW_NE, EW_LT, EW_LE, EW_GT, EW_GE, EW_WHERE, EW_MASKED_FILL, EW_DIV_TRUNC, EW_DIV_FLOOR) = range(40)
 # sb_reduce_op
-RED_SUM, RED_MEAN, RED_AMAX, RED_AMIN = range(4)
+RED_SUM, RED_MEAN, RED_AMAX, RED_AMIN, RED_PROD, RED_NANSUM = range(6)
 
 
 class CEArgs(C.Structure):
@@ -36,7 +38,26 @@ class CEArgs(C.Structure):
         ("grad_logits", C.c_void_p), ("row_loss", C.c_void_p), ("row_lse", C.c_void_p),
         ("row_grad_out", C.c_void_p), ("acc", C.c_void_p), ("rows", C.c_int64), ("classes", C.c_int64),
         ("ignore_index", C.c_int64), ("label_smoothing", C.c_float), ("grad_scale", C.c_float),
-        ("status", C.c_void_p), ("class_weight", C.c_void_p),
+        ("status", C.c_void_p), ("class_weight", C.c_void_p), ("flags", C.c_uint32),
+    ]
+
+
+CE_FLAG_AFTER_COUNT = 0x1
+XCHG_MAX_RANKS, XCHG_DEPTH = 8, 4
+XCHG_SLOT_BYTES = XCHG_DEPTH * XCHG_MAX_RANKS * 16
+
+
+class Xchg(C.Structure):
+    """sb_xchg: where the ranks of a row-sharded job publish their partial sums."""
+    _fields_ = [("slots", C.c_void_p * XCHG_MAX_RANKS), ("rank", C.c_int32), ("nranks", C.c_int32), ("seq", C.c_uint64)]
+
+
+class CEProbArgs(C.Structure):
+    """sb_ce_prob_args: cross entropy with class-probability targets."""
+    _fields_ = [
+        ("logits", C.c_void_p), ("target", C.c_void_p), ("dtype", C.c_int32), ("grad_logits", C.c_void_p), ("row_loss", C.c_void_p),
+        ("row_grad_out", C.c_void_p), ("class_weight", C.c_void_p), ("rows", C.c_int64), ("classes", C.c_int64),
+        ("label_smoothing", C.c_float), ("grad_scale", C.c_float), ("loss_scale", C.c_float),
     ]
 
 
@@ -100,6 +121,7 @@ def lib() -> C.CDLL:
         _lib.sb_reduce_scratch_bytes.restype = C.c_size_t
         _lib.sb_nll_loss_nd_scratch_bytes.restype = C.c_size_t
         _lib.sb_bce_logits_scratch_bytes.restype = C.c_size_t
+        _lib.sb_reduce_ext_scratch_bytes.restype = C.c_size_t
     return _lib
 
 
@@ -156,10 +178,22 @@ def ce_loss_sum_finish(row_loss, rows, acc, reduction, out, dtype, stream=0):
                                                                C.c_void_p(stream)))
 
 
-def ce_rescale_grad(grad, dtype, numel, scale, scale_dtype, applied_in, applied_out, stream=0):
-    check("sb_ce_rescale_grad", lib().sb_ce_rescale_grad(_p(grad), C.c_int32(dtype), C.c_int64(numel), _p(scale),
-                                                         C.c_int32(scale_dtype), _p(applied_in), _p(applied_out),
+def ce_rescale_grad(src, dst, dtype, numel, scale, scale_dtype, applied_in, applied_out, status=None, stream=0):
+    check("sb_ce_rescale_grad", lib().sb_ce_rescale_grad(_p(src), _p(dst), C.c_int32(dtype), C.c_int64(numel), _p(scale),
+                                                         C.c_int32(scale_dtype), _p(applied_in), _p(applied_out), _p(status),
                                                          C.c_void_p(stream)))
+
+
+def ce_count_exchange(target, class_weight, rows, classes, ignore_index, acc, status=None, xchg: "Xchg | None" = None, stream=0):
+    check("sb_ce_count_exchange", lib().sb_ce_count_exchange(_p(target), _p(class_weight), C.c_int64(rows), C.c_int64(classes),
+                                                             C.c_int64(ignore_index), _p(acc), _p(status),
+                                                             C.byref(xchg) if xchg is not None else None, C.c_void_p(stream)))
+
+
+def ce_loss_exchange(row_loss, rows, acc, reduction, out, dtype, status=None, xchg: "Xchg | None" = None, stream=0):
+    check("sb_ce_loss_exchange", lib().sb_ce_loss_exchange(_p(row_loss), C.c_int64(rows), _p(acc), C.c_int32(reduction), _p(out),
+                                                           C.c_int32(dtype), _p(status),
+                                                           C.byref(xchg) if xchg is not None else None, C.c_void_p(stream)))
 
 
 CE_STATIC_MAX_ROWS = 65536
@@ -168,6 +202,27 @@ CE_STATIC_MAX_ROWS = 65536
 def ce_loss_static_scratch(args: CEArgs, loss_out, stream=0):
     """Whole mean/sum cross entropy with the scratch buffers inside the library (no device allocation)."""
     check("sb_ce_loss_static_scratch", lib().sb_ce_loss_static_scratch(C.byref(args), _p(loss_out), C.c_void_p(stream)))
+
+
+def ce_prob_forward_backward(args: CEProbArgs, stream=0):
+    check("sb_ce_prob_forward_backward", lib().sb_ce_prob_forward_backward(C.byref(args), C.c_void_p(stream)))
+
+
+def reduce_ext_scratch_bytes(dtype, outer, length, inner, moments) -> int:
+    return int(lib().sb_reduce_ext_scratch_bytes(C.c_int32(dtype), C.c_int64(outer), C.c_int64(length), C.c_int64(inner),
+                                                 C.c_int32(1 if moments else 0)))
+
+
+def arg_reduce(inp, dtype, outer, length, inner, is_max, values, indices, scratch=None, scratch_bytes=0, stream=0):
+    check("sb_arg_reduce", lib().sb_arg_reduce(_p(inp), C.c_int32(dtype), C.c_int64(outer), C.c_int64(length), C.c_int64(inner),
+                                               C.c_int32(1 if is_max else 0), _p(values), _p(indices), _p(scratch),
+                                               C.c_size_t(scratch_bytes), C.c_void_p(stream)))
+
+
+def moments(inp, dtype, outer, length, inner, correction, take_sqrt, out, mean_out=None, scratch=None, scratch_bytes=0, stream=0):
+    check("sb_moments", lib().sb_moments(_p(inp), C.c_int32(dtype), C.c_int64(outer), C.c_int64(length), C.c_int64(inner),
+                                         C.c_double(correction), C.c_int32(1 if take_sqrt else 0), _p(out), _p(mean_out), _p(scratch),
+                                         C.c_size_t(scratch_bytes), C.c_void_p(stream)))
 
 
 def ce_kernel_variant(dtype, rows, classes) -> int:

@@ -162,6 +162,9 @@ void add_kernel(at::TensorIteratorBase& iter, const at::Scalar& alpha) {
 void mul_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_MUL, SB_EW_MUL_SCALAR, /*scalar_first_ok=*/true, 1.0, 1); }
 
 void div_true_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_DIV, -1, false, 1.0, 1); }
+// div with rounding_mode = "trunc" / "floor" (torch_supa/csrc/aten/ops/kernels/elementwise/BinaryDivTruncKernel.cu, BinaryDivFloorKernel.cu)
+void div_trunc_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_DIV_TRUNC, -1, false, 1.0, 1); }
+void div_floor_kernel(at::TensorIteratorBase& iter) { launch_binary(iter, SB_EW_DIV_FLOOR, -1, false, 1.0, 1); }
 
 void neg_kernel(at::TensorIteratorBase& iter) { launch_elementwise(iter, SB_EW_NEG, iter.common_dtype()); }
 
@@ -244,6 +247,8 @@ namespace at::native {
 REGISTER_PRIVATEUSE1_DISPATCH(add_stub, &supa::add_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(mul_stub, &supa::mul_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(div_true_stub, &supa::div_true_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(div_trunc_stub, &supa::div_trunc_kernel)
+REGISTER_PRIVATEUSE1_DISPATCH(div_floor_stub, &supa::div_floor_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(neg_stub, &supa::neg_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(GeluKernel, &supa::gelu_kernel)
 REGISTER_PRIVATEUSE1_DISPATCH(GeluBackwardKernel, &supa::gelu_backward_kernel)

@@ -19,6 +19,7 @@
 
 #include "Common.h"
 #include "dist/NcclComm.h"
+#include "dist/PeerExchange.h"
 
 namespace supa {
 
@@ -384,14 +385,12 @@ at::Tensor nll_loss2d_backward(const at::Tensor& grad_output, const at::Tensor& 
 
 // ---- cross entropy ---------------------------------------------------------------------------------------------
 // Which calls take the fused kernel.  Wider than the reference's predicate (CrossEntropyLoss.cpp:23-33: 2-D
-// fp32, no smoothing): 16-bit logits, label smoothing, 1-D logits and class weights (without smoothing) are fused
-// too; weights together with smoothing, probability targets, fp64 and K-dimensional inputs go to libtorch's composite (log_softmax + nll_loss ...),
+// fp32, no smoothing): 16-bit logits, label smoothing, 1-D logits and class weights (with or without smoothing) are
+// fused too; probability targets, fp64 and K-dimensional inputs go to libtorch's composite (log_softmax + nll_loss ...),
 // whose pieces are registered above.
 bool fused_path(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, double label_smoothing) {
-  // class weights are fused when there is no label smoothing (the smoothing term would weight every class of a row)
   bool has_weight = weight.has_value() && weight->defined();
-  if (has_weight && label_smoothing == 0.0 && is_supa(*weight) && weight->dim() == 1 && weight->numel() == self.size(-1) &&
-      c10::isFloatingType(weight->scalar_type()))
+  if (has_weight && is_supa(*weight) && weight->dim() == 1 && weight->numel() == self.size(-1) && c10::isFloatingType(weight->scalar_type()))
     has_weight = false;  // this one the kernel takes
   const at::ScalarType dt = self.scalar_type();
   const bool dtype_ok = dt == at::kFloat || dt == at::kBFloat16 || dt == at::kHalf;
@@ -406,46 +405,57 @@ at::Tensor fused_weight(const c10::optional<at::Tensor>& weight) {
   return weight->to(at::kFloat).contiguous();
 }
 
+// How the ranks of a row-sharded job exchange the two scalars: through peer memory inside the bookkeeping kernels
+// (preferred), else through two NCCL all-reduces; neither on a single GPU.
+struct Exchange {
+  NcclComm* nccl = nullptr;
+  PeerExchange* peer = nullptr;
+  bool any() const { return nccl || peer; }
+};
+
 struct FusedResult {
   at::Tensor loss;      // 0-d in the logits' dtype (mean, sum) or [N] (none)
   at::Tensor grad;      // [N, C] logit gradient for an upstream gradient of 1 (mean, sum with want_grad)
   at::Tensor row_lse;   // [N] fp32 (none with want_grad)
   at::Tensor applied;   // two device floats used alternately: the upstream factor currently folded into `grad`
+  at::Tensor acc;       // {loss sum, denominator} as two doubles (kept for a backward that runs the sweep again)
 };
 
-// The launch sequence of include/supa_b200_kernels.h: count -> [all-reduce] -> fused sweep -> loss sum ->
-// [all-reduce] -> finish.  `comm` is null on a single GPU.
-FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, const at::Tensor& class_weight, int64_t reduction,
-                          int64_t ignore_index, double label_smoothing, bool want_grad, NcclComm* comm) {
-  const c10::DeviceGuard guard(self.device());
-  const at::Tensor logits = self.contiguous();
-  const at::Tensor tgt = target.contiguous();
-  const int64_t rows = logits.dim() == 1 ? 1 : logits.size(0);
-  const int64_t classes = logits.size(-1);
-  const int red = reduction_code(reduction);
-  sb_stream_t stream = stream_of(logits);
-  FusedResult r;
-  const auto f32 = logits.options().dtype(at::kFloat);
-  at::Tensor row_loss = at::empty({std::max<int64_t>(rows, 1)}, f32);
-  at::Tensor acc = at::empty({2}, logits.options().dtype(at::kDouble));
-
+sb_ce_args ce_args(const at::Tensor& logits, const at::Tensor& tgt, const at::Tensor& class_weight, int red, int64_t ignore_index,
+                   double label_smoothing) {
   sb_ce_args a{};
   a.logits = logits.const_data_ptr();
   a.dtype = dtype_code(logits.scalar_type());
   a.reduction = red;
   a.target = tgt.const_data_ptr<int64_t>();
-  a.row_loss = row_loss.data_ptr<float>();
-  a.acc = acc.data_ptr<double>();
-  a.rows = rows;
-  a.classes = classes;
+  a.rows = logits.dim() == 1 ? 1 : logits.size(0);
+  a.classes = logits.size(-1);
   a.ignore_index = ignore_index;
   a.label_smoothing = static_cast<float>(label_smoothing);
   a.grad_scale = 1.f;
   a.status = status_word(logits.device().index());
   a.class_weight = class_weight.defined() ? class_weight.const_data_ptr<float>() : nullptr;  // fp32, contiguous (see fused_weight)
+  return a;
+}
+
+// The launch sequence of include/supa_b200_kernels.h: count [+ exchange] -> fused sweep -> loss sum [+ exchange] + finish.
+// want_grad: the sweep also writes the logit gradient, scaled for an upstream gradient of 1.
+FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, const at::Tensor& class_weight, int64_t reduction,
+                          int64_t ignore_index, double label_smoothing, bool want_grad, bool want_lse, Exchange ex) {
+  const c10::DeviceGuard guard(self.device());
+  const at::Tensor logits = self.contiguous();
+  const at::Tensor tgt = target.contiguous();
+  const int red = reduction_code(reduction);
+  sb_stream_t stream = stream_of(logits);
+  FusedResult r;
+  const auto f32 = logits.options().dtype(at::kFloat);
+  sb_ce_args a = ce_args(logits, tgt, class_weight, red, ignore_index, label_smoothing);
+  const int64_t rows = a.rows;
+  at::Tensor row_loss = at::empty({std::max<int64_t>(rows, 1)}, f32);
+  a.row_loss = row_loss.data_ptr<float>();
 
   if (red == SB_REDUCTION_NONE) {
-    if (want_grad) {
+    if (want_lse) {
       r.row_lse = at::empty({std::max<int64_t>(rows, 1)}, f32);
       a.row_lse = r.row_lse.data_ptr<float>();
     }
@@ -455,48 +465,98 @@ FusedResult fused_forward(const at::Tensor& self, const at::Tensor& target, cons
     return r;
   }
 
-  if (a.class_weight)
-    check_kernel(sb_ce_count_weighted(tgt.const_data_ptr<int64_t>(), a.class_weight, rows, classes, ignore_index, acc.data_ptr<double>(),
-                                      a.status, stream),
-                 "supa cross_entropy weight sum");
-  else
-    check_kernel(sb_ce_count_valid(tgt.const_data_ptr<int64_t>(), rows, classes, ignore_index, acc.data_ptr<double>(), a.status, stream),
-                 "supa cross_entropy count");
-  if (comm) comm->all_reduce_sum_f64(acc.data_ptr<double>() + 1, 1, stream);
-  if (want_grad) {
+  r.acc = at::empty({2}, logits.options().dtype(at::kDouble));
+  a.acc = r.acc.data_ptr<double>();
+  if (want_grad) {  // allocated before the count so that nothing sits between the count and the sweep on the stream
     r.grad = at::empty_like(logits);
     a.grad_logits = r.grad.data_ptr();
   }
-  check_kernel(sb_ce_forward_backward(&a, stream), "supa cross_entropy");
   r.loss = at::empty({}, logits.options());
-  if (!comm) {
-    check_kernel(sb_ce_loss_sum_finish(row_loss.const_data_ptr<float>(), rows, acc.data_ptr<double>(), red, r.loss.data_ptr(),
-                                       dtype_code(logits.scalar_type()), stream),
-                 "supa cross_entropy loss sum");
+  if (ex.peer) {
+    const sb_xchg x = ex.peer->next();
+    check_kernel(sb_ce_count_exchange(a.target, a.class_weight, rows, a.classes, ignore_index, r.acc.data_ptr<double>(), a.status, &x, stream),
+                 "supa cross_entropy count");
+    a.flags = SB_CE_FLAG_AFTER_COUNT;
   } else {
-    check_kernel(sb_ce_loss_sum(row_loss.const_data_ptr<float>(), rows, acc.data_ptr<double>(), stream), "supa cross_entropy loss sum");
-    comm->all_reduce_sum_f64(acc.data_ptr<double>(), 1, stream);
-    check_kernel(sb_ce_loss_finish(acc.const_data_ptr<double>(), red, r.loss.data_ptr(), dtype_code(logits.scalar_type()), stream),
-                 "supa cross_entropy loss finish");
+    check_kernel(sb_ce_count_exchange(a.target, a.class_weight, rows, a.classes, ignore_index, r.acc.data_ptr<double>(), a.status, nullptr, stream),
+                 "supa cross_entropy count");
+    if (ex.nccl) ex.nccl->all_reduce_sum_f64(r.acc.data_ptr<double>() + 1, 1, stream);
+    else a.flags = SB_CE_FLAG_AFTER_COUNT;
   }
-  if (want_grad) {
-    r.applied = at::empty({2}, f32);  // written by the first rescale; until then the factor is 1 by construction
+  check_kernel(sb_ce_forward_backward(&a, stream), "supa cross_entropy");
+  const int out_dtype = dtype_code(logits.scalar_type());
+  if (ex.peer) {
+    const sb_xchg x = ex.peer->next();
+    check_kernel(sb_ce_loss_exchange(row_loss.const_data_ptr<float>(), rows, r.acc.data_ptr<double>(), red, r.loss.data_ptr(), out_dtype, a.status,
+                                     &x, stream),
+                 "supa cross_entropy loss sum");
+  } else if (ex.nccl) {
+    check_kernel(sb_ce_loss_sum(row_loss.const_data_ptr<float>(), rows, r.acc.data_ptr<double>(), stream), "supa cross_entropy loss sum");
+    ex.nccl->all_reduce_sum_f64(r.acc.data_ptr<double>(), 1, stream);
+    check_kernel(sb_ce_loss_finish(r.acc.const_data_ptr<double>(), red, r.loss.data_ptr(), out_dtype, stream), "supa cross_entropy loss finish");
+  } else {
+    check_kernel(sb_ce_loss_exchange(row_loss.const_data_ptr<float>(), rows, r.acc.data_ptr<double>(), red, r.loss.data_ptr(), out_dtype, a.status,
+                                     nullptr, stream),
+                 "supa cross_entropy loss sum");
   }
+  if (want_grad) r.applied = at::empty({2}, f32);  // written by the first rescale; until then the factor is 1 by construction
   return r;
 }
 
+// The gradient a mean / sum forward stored carries the factor `applied` (1 after forward).  The first backward folds the
+// upstream value in on the device, in place (the sweep is skipped there when it is 1), and hands the buffer out; later
+// backward calls on a retained graph write into a fresh tensor, so no tensor handed out earlier changes under its holder.
+at::Tensor apply_upstream(torch::autograd::AutogradContext* ctx, const at::Tensor& stored, const at::Tensor& applied, const at::Tensor& go) {
+  const c10::DeviceGuard guard(stored.device());
+  at::Tensor scale = go.reshape({1});
+  if (!is_supa(scale)) scale = scale.to(stored.device());
+  const at::ScalarType st = scale.scalar_type();
+  if (st != at::kFloat && st != at::kBFloat16 && st != at::kHalf && st != at::kDouble) scale = scale.to(at::kFloat);
+  scale = scale.contiguous();
+  const int64_t slot = ctx->saved_data["applied_slot"].toInt();
+  int32_t* status = status_word(stored.device().index());
+  if (slot < 0) {
+    check_kernel(sb_ce_rescale_grad(stored.const_data_ptr(), stored.data_ptr(), dtype_code(stored.scalar_type()), stored.numel(),
+                                    scale.const_data_ptr(), dtype_code(scale.scalar_type()), nullptr, applied.data_ptr<float>(), status,
+                                    stream_of(stored)),
+                 "supa cross_entropy rescale");
+    ctx->saved_data["applied_slot"] = static_cast<int64_t>(0);
+    return stored;
+  }
+  at::Tensor fresh = at::empty_like(stored);
+  check_kernel(sb_ce_rescale_grad(stored.const_data_ptr(), fresh.data_ptr(), dtype_code(stored.scalar_type()), stored.numel(),
+                                  scale.const_data_ptr(), dtype_code(scale.scalar_type()), applied.const_data_ptr<float>() + slot, nullptr,
+                                  status, stream_of(stored)),
+               "supa cross_entropy rescale");
+  return fresh;
+}
+
+// Autograd node.  Three ways to the logit gradient:
+//  * mean / sum on fp32 and bf16 logits: the forward sweep already wrote it, scaled for an upstream gradient of 1;
+//    the first backward folds the real upstream value into that buffer in place (skipped on the device when it is 1)
+//    and hands the buffer out; later backward calls on a retained graph write into a fresh tensor, so no tensor handed
+//    out earlier changes under its holder;
+//  * fp16 logits: a gradient stored before the upstream factor is known would flush to zero (p / |V| < 6e-8 for most
+//    classes) and a loss scale applied afterwards could not bring it back, so forward keeps the logits and backward
+//    runs the sweep with the upstream value folded in before anything is rounded to fp16;
+//  * reduction none: per-row upstream values, same second sweep.
 class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFunction> {
  public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& self, const at::Tensor& target,
                             const c10::optional<at::Tensor>& weight, int64_t reduction, int64_t ignore_index, double label_smoothing,
-                            int64_t comm_handle) {
-    NcclComm* comm = comm_handle ? NcclComm::from_handle(comm_handle) : nullptr;
+                            int64_t comm_handle, int64_t peer_handle) {
+    Exchange ex;
+    if (comm_handle) ex.nccl = NcclComm::from_handle(comm_handle);
+    if (peer_handle) ex.peer = PeerExchange::from_handle(peer_handle);
     const at::Tensor class_weight = fused_weight(weight);
-    FusedResult r = fused_forward(self, target, class_weight, reduction, ignore_index, label_smoothing, /*want_grad=*/true, comm);
+    const bool recompute = reduction == at::Reduction::None || self.scalar_type() == at::kHalf;
+    FusedResult r = fused_forward(self, target, class_weight, reduction, ignore_index, label_smoothing, /*want_grad=*/!recompute,
+                                  /*want_lse=*/false, ex);
     ctx->saved_data["reduction"] = reduction;
     ctx->saved_data["ignore_index"] = ignore_index;
     ctx->saved_data["label_smoothing"] = label_smoothing;
-    if (reduction == at::Reduction::None) ctx->save_for_backward({self, target, r.row_lse, class_weight});
+    ctx->saved_data["recompute"] = recompute;
+    if (recompute) ctx->save_for_backward({self, target, class_weight, r.acc});
     else ctx->save_for_backward({r.grad, r.applied});
     ctx->saved_data["applied_slot"] = static_cast<int64_t>(-1);  // which word of `applied` is valid; -1 = none (factor 1)
     ctx->saved_data["shape_1d"] = self.dim() == 1;
@@ -508,82 +568,178 @@ class CrossEntropyFunction : public torch::autograd::Function<CrossEntropyFuncti
     const int64_t reduction = ctx->saved_data["reduction"].toInt();
     const at::Tensor& go = grad_outputs[0];
     at::Tensor grad_self;
-    if (!go.defined()) return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
-    if (reduction == at::Reduction::None) {
-      // per-row upstream gradients: one more fused sweep with the saved logits (1 read + 1 write)
+    const auto result = [&] { return std::vector<at::Tensor>{grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()}; };
+    if (!go.defined()) return result();
+    if (ctx->saved_data["recompute"].toBool()) {
+      // one more fused sweep with the saved logits (1 read + 1 write), the upstream values folded in per row
       const at::Tensor logits = saved[0].contiguous();
       const at::Tensor tgt = saved[1].contiguous();
       const c10::DeviceGuard guard(logits.device());
-      const int64_t rows = logits.dim() == 1 ? 1 : logits.size(0);
-      at::Tensor row_go = go.reshape({rows}).to(at::kFloat).contiguous();
-      at::Tensor row_loss = at::empty({std::max<int64_t>(rows, 1)}, row_go.options());
+      const int red = reduction_code(reduction);
+      sb_ce_args a = ce_args(logits, tgt, saved[2], red, ctx->saved_data["ignore_index"].toInt(), ctx->saved_data["label_smoothing"].toDouble());
+      at::Tensor upstream = go;
+      if (!is_supa(upstream)) upstream = upstream.to(logits.device());
+      at::Tensor row_go = upstream.to(at::kFloat).reshape({-1}).expand({a.rows}).contiguous();
+      at::Tensor row_loss = at::empty({std::max<int64_t>(a.rows, 1)}, row_go.options());
       grad_self = at::empty_like(logits);
-      sb_ce_args a{};
-      a.logits = logits.const_data_ptr();
-      a.dtype = dtype_code(logits.scalar_type());
-      a.reduction = SB_REDUCTION_NONE;
-      a.target = tgt.const_data_ptr<int64_t>();
       a.grad_logits = grad_self.data_ptr();
       a.row_loss = row_loss.data_ptr<float>();
       a.row_grad_out = row_go.const_data_ptr<float>();
-      a.rows = rows;
-      a.classes = logits.size(-1);
-      a.ignore_index = ctx->saved_data["ignore_index"].toInt();
-      a.label_smoothing = static_cast<float>(ctx->saved_data["label_smoothing"].toDouble());
-      a.grad_scale = 1.f;
-      a.status = status_word(logits.device().index());
-      a.class_weight = saved[3].defined() ? saved[3].const_data_ptr<float>() : nullptr;
+      if (red != SB_REDUCTION_NONE) a.acc = saved[3].const_data_ptr<double>();  // the (global) denominator of `mean`
       check_kernel(sb_ce_forward_backward(&a, stream_of(logits)), "supa cross_entropy backward");
       grad_self = grad_self.view(saved[0].sizes());
-    } else {
-      // The stored gradient carries the factor `applied` (1 after forward).  Fold in the new upstream value
-      // on the device; the sweep is skipped there when nothing changes.
-      grad_self = saved[0];
-      const at::Tensor applied = saved[1];
-      const c10::DeviceGuard guard(grad_self.device());
-      at::Tensor scale = go.reshape({1});
-      if (!is_supa(scale)) scale = scale.to(grad_self.device());
-      const at::ScalarType st = scale.scalar_type();
-      if (st != at::kFloat && st != at::kBFloat16 && st != at::kHalf && st != at::kDouble) scale = scale.to(at::kFloat);
-      scale = scale.contiguous();
-      const int64_t slot = ctx->saved_data["applied_slot"].toInt();
-      const int64_t next = slot < 0 ? 0 : 1 - slot;
-      check_kernel(sb_ce_rescale_grad(grad_self.data_ptr(), dtype_code(grad_self.scalar_type()), grad_self.numel(),
-                                      scale.const_data_ptr(), dtype_code(scale.scalar_type()),
-                                      slot < 0 ? nullptr : applied.const_data_ptr<float>() + slot, applied.data_ptr<float>() + next,
-                                      stream_of(grad_self)),
-                   "supa cross_entropy rescale");
-      ctx->saved_data["applied_slot"] = next;
-      if (ctx->saved_data["shape_1d"].toBool()) grad_self = grad_self.reshape({grad_self.size(-1)});
+      return result();
     }
-    return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+    grad_self = apply_upstream(ctx, saved[0], saved[1], go);
+    if (ctx->saved_data["shape_1d"].toBool()) grad_self = grad_self.reshape({grad_self.size(-1)});
+    return result();
   }
 };
 
 at::Tensor cross_entropy_fused(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight,
-                               int64_t reduction, int64_t ignore_index, double label_smoothing, int64_t comm_handle) {
+                               int64_t reduction, int64_t ignore_index, double label_smoothing, int64_t comm_handle, int64_t peer_handle) {
   const bool has_weight = weight.has_value() && weight->defined();
   if (at::GradMode::is_enabled() && self.requires_grad())
     return CrossEntropyFunction::apply(self, target, has_weight ? weight : c10::nullopt, reduction, ignore_index, label_smoothing,
-                                       comm_handle);
-  NcclComm* comm = comm_handle ? NcclComm::from_handle(comm_handle) : nullptr;
-  return fused_forward(self, target, fused_weight(weight), reduction, ignore_index, label_smoothing, /*want_grad=*/false, comm).loss;
+                                       comm_handle, peer_handle);
+  Exchange ex;
+  if (comm_handle) ex.nccl = NcclComm::from_handle(comm_handle);
+  if (peer_handle) ex.peer = PeerExchange::from_handle(peer_handle);
+  return fused_forward(self, target, fused_weight(weight), reduction, ignore_index, label_smoothing, /*want_grad=*/false, /*want_lse=*/false, ex)
+      .loss;
+}
+
+// ---- class-probability targets ---------------------------------------------------------------------------------------
+// Float targets of the logits' shape (CrossEntropyLoss.cpp:43-45 and cross_entropy_prob_kernel of the reference).
+bool prob_path(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, double label_smoothing) {
+  const at::ScalarType dt = self.scalar_type();
+  if (!(dt == at::kFloat || dt == at::kBFloat16 || dt == at::kHalf)) return false;
+  if (!c10::isFloatingType(target.scalar_type()) || !is_supa(target) || target.sizes() != self.sizes()) return false;
+  if (!(self.dim() == 2 || self.dim() == 1) || self.size(-1) == 0) return false;
+  if (weight.has_value() && weight->defined() &&
+      !(is_supa(*weight) && weight->dim() == 1 && weight->numel() == self.size(-1) && c10::isFloatingType(weight->scalar_type())))
+    return false;
+  if (at::GradMode::is_enabled() && target.requires_grad()) return false;  // a gradient for the targets: the composite has it
+  return label_smoothing >= 0.0 && label_smoothing <= 1.0;
+}
+
+struct ProbResult {
+  at::Tensor loss, grad;
+};
+
+// One launch of the fused kernel (+ the fixed-order sum for mean / sum).  row_go: per-row upstream values (reduction none
+// in backward), undefined for 1.
+ProbResult prob_forward(const at::Tensor& self, const at::Tensor& target, const at::Tensor& class_weight, int64_t reduction,
+                        double label_smoothing, bool want_grad, const at::Tensor& row_go, bool want_loss) {
+  const c10::DeviceGuard guard(self.device());
+  const at::Tensor logits = self.contiguous();
+  at::Tensor tgt = target.contiguous();
+  if (tgt.scalar_type() != logits.scalar_type()) tgt = tgt.to(logits.scalar_type());
+  const int red = reduction_code(reduction);
+  const int64_t rows = logits.dim() == 1 ? 1 : logits.size(0);
+  const auto f32 = logits.options().dtype(at::kFloat);
+  at::Tensor row_loss = at::empty({std::max<int64_t>(rows, 1)}, f32);
+  ProbResult r;
+  sb_ce_prob_args a{};
+  a.logits = logits.const_data_ptr();
+  a.target = tgt.const_data_ptr();
+  a.dtype = dtype_code(logits.scalar_type());
+  a.row_loss = row_loss.data_ptr<float>();
+  a.class_weight = class_weight.defined() ? class_weight.const_data_ptr<float>() : nullptr;
+  a.rows = rows;
+  a.classes = logits.size(-1);
+  a.label_smoothing = static_cast<float>(label_smoothing);
+  const float inv = (red == SB_REDUCTION_MEAN && rows > 0) ? static_cast<float>(1.0 / static_cast<double>(rows)) : 1.f;
+  a.grad_scale = inv;
+  a.loss_scale = inv;
+  if (row_go.defined()) a.row_grad_out = row_go.const_data_ptr<float>();
+  if (want_grad) {
+    r.grad = at::empty_like(logits);
+    a.grad_logits = r.grad.data_ptr();
+  }
+  sb_stream_t stream = stream_of(logits);
+  check_kernel(sb_ce_prob_forward_backward(&a, stream), "supa cross_entropy (probability targets)");
+  if (!want_loss) return r;
+  if (red == SB_REDUCTION_NONE) {
+    at::Tensor out = logits.dim() == 1 ? row_loss.reshape({}) : row_loss.narrow(0, 0, rows);
+    r.loss = out.scalar_type() == logits.scalar_type() ? out : out.to(logits.scalar_type());
+    return r;
+  }
+  r.loss = at::empty({}, logits.options());
+  if (rows == 0) {  // mean of nothing: NaN, sum: 0 (the CPU's results)
+    r.loss.fill_(red == SB_REDUCTION_MEAN ? std::numeric_limits<double>::quiet_NaN() : 0.0);
+    return r;
+  }
+  at::Tensor acc = at::empty({2}, logits.options().dtype(at::kDouble));
+  check_kernel(sb_ce_loss_sum_finish(row_loss.const_data_ptr<float>(), rows, acc.data_ptr<double>(), SB_REDUCTION_SUM, r.loss.data_ptr(),
+                                     dtype_code(logits.scalar_type()), stream),
+               "supa cross_entropy loss sum");
+  return r;
+}
+
+class CrossEntropyProbFunction : public torch::autograd::Function<CrossEntropyProbFunction> {
+ public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& self, const at::Tensor& target,
+                            const c10::optional<at::Tensor>& weight, int64_t reduction, double label_smoothing) {
+    const at::Tensor class_weight = fused_weight(weight);
+    // fp16 and reduction none form the gradient in backward, with the upstream values folded in before rounding
+    const bool recompute = reduction == at::Reduction::None || self.scalar_type() == at::kHalf;
+    ProbResult r = prob_forward(self, target, class_weight, reduction, label_smoothing, !recompute, at::Tensor(), true);
+    ctx->saved_data["reduction"] = reduction;
+    ctx->saved_data["label_smoothing"] = label_smoothing;
+    ctx->saved_data["recompute"] = recompute;
+    ctx->saved_data["applied_slot"] = static_cast<int64_t>(-1);
+    if (recompute) ctx->save_for_backward({self, target, class_weight});
+    else ctx->save_for_backward({r.grad, at::empty({2}, self.options().dtype(at::kFloat))});
+    return r.loss;
+  }
+  static std::vector<at::Tensor> backward(torch::autograd::AutogradContext* ctx, std::vector<at::Tensor> grad_outputs) {
+    const auto saved = ctx->get_saved_variables();
+    const at::Tensor& go = grad_outputs[0];
+    at::Tensor grad_self;
+    if (go.defined()) {
+      if (ctx->saved_data["recompute"].toBool()) {
+        const at::Tensor& self = saved[0];
+        const int64_t rows = self.dim() == 1 ? 1 : self.size(0);
+        at::Tensor upstream = is_supa(go) ? go : go.to(self.device());
+        at::Tensor row_go = upstream.to(at::kFloat).reshape({-1}).expand({rows}).contiguous();
+        grad_self = prob_forward(self, saved[1], saved[2], ctx->saved_data["reduction"].toInt(), ctx->saved_data["label_smoothing"].toDouble(),
+                                 true, row_go, false)
+                        .grad.view(self.sizes());
+      } else {
+        grad_self = apply_upstream(ctx, saved[0], saved[1], go).view(saved[0].sizes());
+      }
+    }
+    return {grad_self, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+at::Tensor cross_entropy_prob(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, int64_t reduction,
+                              int64_t ignore_index, double label_smoothing) {
+  TORCH_CHECK(ignore_index < 0, "ignore_index is not supported for floating point target");
+  const bool has_weight = weight.has_value() && weight->defined();
+  if (at::GradMode::is_enabled() && self.requires_grad())
+    return CrossEntropyProbFunction::apply(self, target, has_weight ? weight : c10::nullopt, reduction, label_smoothing);
+  return prob_forward(self, target, fused_weight(weight), reduction, label_smoothing, false, at::Tensor(), true).loss;
 }
 
 at::Tensor cross_entropy_loss(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight,
                               int64_t reduction, int64_t ignore_index, double label_smoothing) {
+  if (prob_path(self, target, weight, label_smoothing)) return cross_entropy_prob(self, target, weight, reduction, ignore_index, label_smoothing);
   if (!fused_path(self, target, weight, label_smoothing))
     return at::native::cross_entropy_loss_symint(self, target, weight, reduction, c10::SymInt(ignore_index), label_smoothing);
-  return cross_entropy_fused(self, target, weight, reduction, ignore_index, label_smoothing, 0);
+  return cross_entropy_fused(self, target, weight, reduction, ignore_index, label_smoothing, 0, 0);
 }
 
-// supa_b200::sharded_cross_entropy: the same fused path with the two scalar all-reduces of the row-sharded
-// multi-GPU protocol (valid-row count before the sweep, loss sum after it) on the communicator `comm`.
+// supa_b200::sharded_cross_entropy: the same fused path with the two scalar exchanges of the row-sharded
+// multi-GPU protocol (valid-row count before the sweep, loss sum after it): through the peer-memory exchange `peer`
+// when given, else through the NCCL communicator `comm`.
 at::Tensor sharded_cross_entropy(const at::Tensor& self, const at::Tensor& target, int64_t reduction, int64_t ignore_index,
-                                 double label_smoothing, int64_t comm) {
+                                 double label_smoothing, int64_t comm, int64_t peer) {
   TORCH_CHECK(fused_path(self, target, c10::nullopt, label_smoothing),
               "sharded_cross_entropy: expected [rows, classes] fp32/bf16/fp16 logits and int64 class targets on a supa device");
-  return cross_entropy_fused(self, target, c10::nullopt, reduction, ignore_index, label_smoothing, reduction == at::Reduction::None ? 0 : comm);
+  const bool none = reduction == at::Reduction::None;
+  return cross_entropy_fused(self, target, c10::nullopt, reduction, ignore_index, label_smoothing, (none || peer) ? 0 : comm, none ? 0 : peer);
 }
 
 }  // namespace
@@ -614,6 +770,6 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
 TORCH_LIBRARY_IMPL(_, AutogradPrivateUse1, m) { m.fallback(torch::CppFunction::makeFallthrough()); }
 
 TORCH_LIBRARY(supa_b200, m) {
-  m.def("sharded_cross_entropy(Tensor self, Tensor target, int reduction, int ignore_index, float label_smoothing, int comm) -> Tensor");
+  m.def("sharded_cross_entropy(Tensor self, Tensor target, int reduction, int ignore_index, float label_smoothing, int comm, int peer=0) -> Tensor");
 }
 TORCH_LIBRARY_IMPL(supa_b200, PrivateUse1, m) { m.impl("sharded_cross_entropy", TORCH_FN(supa::sharded_cross_entropy)); }

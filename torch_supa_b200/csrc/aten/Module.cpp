@@ -8,6 +8,7 @@
 
 #include "Common.h"
 #include "dist/NcclComm.h"
+#include "dist/PeerExchange.h"
 
 namespace {
 
@@ -100,6 +101,21 @@ SUPA_EXPORT int supa_nccl_abort(int64_t handle) {
 }
 SUPA_EXPORT int supa_nccl_all_reduce(int64_t handle, void* data, int64_t count, int dtype, int op, void* stream) {
   return guarded([&] { supa::NcclComm::from_handle(handle)->all_reduce(data, count, dtype, op, stream); });
+}
+
+
+// ---- peer-memory exchange of the loss scalars (see dist/PeerExchange.h) -----------------------------------------
+SUPA_EXPORT int supa_peer_create(int nranks, int rank, int device, int64_t* handle) {
+  return guarded([&] { *handle = (new supa::PeerExchange(nranks, rank, device))->handle(); });
+}
+SUPA_EXPORT int supa_peer_export(int64_t handle, char* out64) {
+  return guarded([&] { supa::PeerExchange::from_handle(handle)->export_handle(out64); });
+}
+SUPA_EXPORT int supa_peer_open(int64_t handle, const char* handles) {
+  return guarded([&] { supa::PeerExchange::from_handle(handle)->open_peers(handles); });
+}
+SUPA_EXPORT int supa_peer_destroy(int64_t handle) {
+  return guarded([&] { delete supa::PeerExchange::from_handle(handle); });
 }
 
 }  // extern "C"

@@ -238,6 +238,22 @@ SUPA_BINARY_ALPHA(add, at::native::structured_ufunc_add_CPU)  // impl: add_stub(
 SUPA_BINARY_ALPHA(sub, at::native::structured_sub_out)        // impl: add_stub(device_type(), *this, -alpha)
 SUPA_BINARY(mul, at::native::structured_mul_out)              // impl: mul_stub(device_type(), *this)
 SUPA_BINARY(div, at::native::structured_div_out)              // impl: div_true_stub(device_type(), *this)
+// div(self, other, rounding_mode): impl picks div_true_stub / div_trunc_stub / div_floor_stub by the mode
+at::Tensor div_mode(const at::Tensor& self, const at::Tensor& other, c10::optional<c10::string_view> mode) {
+  return run_functional<at::native::structured_div_out_mode>(
+      device_of_args({self, other}), [&](auto& op) { op.meta(self, other, mode); },
+      [&](auto& op, const at::Tensor& out) { op.impl(self, other, mode, out); });
+}
+at::Tensor& div_mode_(at::Tensor& self, const at::Tensor& other, c10::optional<c10::string_view> mode) {
+  return run_inplace<at::native::structured_div_out_mode>(
+      device_of_args({self, other}), self, [&](auto& op) { op.meta(self, other, mode); },
+      [&](auto& op, const at::Tensor& out) { op.impl(self, other, mode, out); });
+}
+at::Tensor& div_mode_out(const at::Tensor& self, const at::Tensor& other, c10::optional<c10::string_view> mode, at::Tensor& out) {
+  return run_out<at::native::structured_div_out_mode>(
+      device_of_args({self, other, out}), out, [&](auto& op) { op.meta(self, other, mode); },
+      [&](auto& op, const at::Tensor& o) { op.impl(self, other, mode, o); });
+}
 SUPA_UNARY(neg, at::native::structured_neg_out)
 SUPA_UNARY(silu, at::native::structured_silu_out)
 
@@ -482,6 +498,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("div.Tensor", TORCH_FN(supa::div_tensor));
   m.impl("div_.Tensor", TORCH_FN(supa::div_tensor_));
   m.impl("div.out", TORCH_FN(supa::div_out));
+  m.impl("div.Tensor_mode", TORCH_FN(supa::div_mode));
+  m.impl("div_.Tensor_mode", TORCH_FN(supa::div_mode_));
+  m.impl("div.out_mode", TORCH_FN(supa::div_mode_out));
   m.impl("neg", TORCH_FN(supa::neg));
   m.impl("neg_", TORCH_FN(supa::neg_));
   m.impl("neg.out", TORCH_FN(supa::neg_out));

@@ -22,6 +22,7 @@ struct CEParams {
   int dtype;
   int32_t* status;           // nullable
   const float* class_weight; // nullable: fp32 [classes]; multiplies the loss and the gradient of a row by w[target]
+  uint32_t flags;            // SB_CE_FLAG_* of sb_ce_args
 };
 
 // loss of one non-ignored row; sum_x is the plain sum of the row's logits.
@@ -51,12 +52,19 @@ __device__ __forceinline__ void ce_store_loss(double loss_sum, double count, int
   }
 }
 
-// Kernel families (defined in cross_entropy.cu and cross_entropy_tma.cu).
+// Kernel families (defined in cross_entropy.cu, cross_entropy_rows.cu and cross_entropy_tma.cu).
 int ce_launch_generic(const CEParams& p, cudaStream_t st);
-int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant);
-// Chooses the family for a shape: 0 generic, 1/2/4 = resident in shared memory of a 1/2/4-CTA cluster.
+int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant, bool pdl);
+// Rows of less than 16 KB held in registers (one warp or one 128-thread group per row): one read and one write
+// per logit.  rows_reg_applies says whether the shape and the pointers qualify.
+bool rows_reg_applies(int dtype, int64_t classes, const void* logits, const void* grad);
+int ce_launch_rows_reg(const CEParams& p, cudaStream_t st);
+// Chooses the resident family for a shape: 0 none, 1/2/4 = resident in shared memory of a 1/2/4-CTA cluster.
 int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logits, const void* grad);
+// What ce_dispatch will run: 0 generic two-sweep rows, 1/2/4 resident, 8 rows in registers.
+int ce_choose_family(const CEParams& p);
 int ce_dispatch(const CEParams& p, cudaStream_t st);
+int xchg_set_timeout_ms(int ms);  // limit of the waits of the exchange kernels
 // log_softmax (mode 1) or softmax (mode 2) over rows of `dim` elements through the resident pipeline; SB_ERR_UNSUPPORTED
 // if the shape does not qualify.
 int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int64_t dim, int mode, cudaStream_t st);

@@ -83,6 +83,14 @@ __device__ __forceinline__ void st_stream_u4(void* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// launch_dependents lets the next kernel of the stream start while this one still runs, provided that kernel
+// was launched with the programmatic-stream-serialization attribute; grid_dep_wait, executed in such a kernel,
+// returns once every kernel before it in the stream has completed and its writes are visible.  Both are no-ops
+// in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- reductions --------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -21,8 +21,16 @@
 // Arithmetic uses the packed fp32 pair instructions of sm_100 (fma/add .f32x2), packed bf16 maxima and
 // ex2.approx; the row statistics are in base 2 (max2 = max * log2 e).
 //
+// Rows whose pitch is not a multiple of 16 bytes (vocabularies such as 50257 or 151643) run the same pipeline
+// (kRagged): the loader fetches the 16-byte aligned superset of the row, so the row begins `head` elements into
+// its first unit and may end inside its last one; those two edge units are left out of the vector sweeps and of
+// the bulk stores, and one thread handles their few elements with scalar arithmetic and ordinary stores, so a
+// neighbouring row's bytes are never written.
+//
 // No TMA multicast is used anywhere: every CTA fetches its own chunks.  Every mbarrier wait is
 // bounded; a wait that runs out sets SB_STATUS_KERNEL_TIMEOUT and the kernel still terminates.
+#include <type_traits>
+
 #include "ce_common.cuh"
 
 namespace sb {
@@ -45,6 +53,7 @@ struct ResidentParams {
   uint32_t num_clusters;
   int mode;              // 0 cross entropy, 1 log_softmax, 2 softmax
   uint32_t window;       // chunks of the next row a group may fold while the row statistics are exchanged
+  uint64_t row_bytes;    // exact bytes of one row (classes * sizeof(T)); row_units covers the widest aligned superset
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -366,6 +375,18 @@ __device__ __forceinline__ uint4 grad_from_kept(const uint4& r, float2 factor2, 
   return U::pack(f);
 }
 
+// The same on bf16 pairs directly: one packed FMA per pair instead of unpack + fp32 FMA + pack.  The factor and the
+// smoothing share are rounded to bf16 first (2^-9 relative each, on top of the 2^-9 of the kept value and of the
+// result); the class of the target is patched separately from fp32 arithmetic.
+__device__ __forceinline__ uint4 grad_from_kept_bf16(const uint4& r, __nv_bfloat162 factor, __nv_bfloat162 nsub) {
+  uint4 o;
+  const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&r);
+  __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = __hfma2(in[i], factor, nsub);
+  return o;
+}
+
 // Gradient of one vector: (2^(x log2e - lse2)) * scale - sub.
 template <typename T>
 __device__ __forceinline__ uint4 grad_vector(const uint4& r, float2 neg_lse2, float2 scale2, float2 nsub2) {
@@ -397,6 +418,59 @@ __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
   return U::pack(f);
 }
 
+// Where a row lies in 16-byte units.  With an aligned pitch this is the same for every row; with kRagged the row
+// starts head_e elements into its first unit and owns only tail_e elements of its last one.
+struct RowGeom {
+  uint32_t head_e;   // elements of the first unit that belong to the previous row
+  uint32_t tail_e;   // elements of the last unit that belong to this row; 0 = all of them
+  uint32_t span;     // units the row touches
+  int64_t byte_off;  // byte offset of the first unit from the tensor's base pointer
+};
+
+// Statistics of the elements [e0, e1) of one edge unit (the others belong to a neighbouring row).
+template <typename T, bool kSumX>
+__device__ __forceinline__ void edge_stats(RowStats& st, const void* unit, uint32_t e0, uint32_t e1) {
+  constexpr int E = 16 / sizeof(T);
+  const T* x = static_cast<const T*>(unit);
+  uint4 r[1];
+  T* re = reinterpret_cast<T*>(&r[0]);
+  float sx = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const bool mine = static_cast<uint32_t>(e) >= e0 && static_cast<uint32_t>(e) < e1;
+    const T v = x[e];
+    re[e] = mine ? v : from_float<T>(-CUDART_INF_F);
+    if (mine) sx += to_float(v);
+  }
+  stats_update<T, 1, false>(st, r);
+  if (kSumX) st.sx[0].x += sx;
+}
+
+// Output of the elements [e0, e1) of one edge unit, written to global memory one element at a time.  `out` points at
+// the class of element e0.
+template <typename T, int MODE>
+__device__ __forceinline__ void edge_output(const void* unit, T* out, uint32_t e0, uint32_t e1, int64_t class0, int64_t target,
+                                            bool ignored, float neg_lse2, float lse, float scale, float sub_all, float sub_t) {
+  constexpr int E = 16 / sizeof(T);
+  const T* x = static_cast<const T*>(unit);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    if (static_cast<uint32_t>(e) >= e0 && static_cast<uint32_t>(e) < e1) {
+      float g = 0.f;
+      if (!ignored) {
+        const float xv = to_float(x[e]);
+        if (MODE == 1) {
+          g = xv - lse;
+        } else {
+          g = fmaf(ex2(fmaf(xv, kLog2e, neg_lse2)), scale, -sub_all);
+          if (MODE == 0 && class0 + (e - static_cast<int>(e0)) == target) g -= sub_t;
+        }
+      }
+      out[e - static_cast<int>(e0)] = from_float<T>(g);
+    }
+  }
+}
+
 // kKeep (cross entropy on 16-bit logits, at most kKeepChunks chunks per group and row): the statistics sweep overwrites
 // each chunk with its exponentials 2^(x log2e - m), m being the thread's running maximum at that chunk, and the gradient
 // sweep only rescales them: one ex2 per logit instead of two and a third fewer instructions, which is what limits this
@@ -404,7 +478,7 @@ __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
 // rounded to bf16 once more than in the two-ex2 form (relative error 2^-8 instead of 2^-9 on the gradient, still far
 // inside the 1e-2 the reference allows for bf16, whose own backward starts from bf16 log-probabilities).
 constexpr int kKeepChunks = 4;
-template <typename T, int CLUSTER, bool kSumX, int MODE, bool kKeep = false>
+template <typename T, int CLUSTER, bool kSumX, int MODE, bool kKeep = false, bool kRagged = false>
 __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(ResidentParams rp) {
   extern __shared__ __align__(128) unsigned char smem[];
   using U = Unit<T>;
@@ -412,6 +486,10 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
   constexpr int G = kGroups, TG = kGroupThreads, NV = kVecPerThread;
   constexpr uint32_t kChunkBytes = kChunkUnits * 16;
   const CEParams& p = rp.p;
+
+  // The next kernel of the stream may be scheduled as soon as this one's CTAs are resident (it waits for this
+  // kernel's results itself if it was launched as a programmatic dependent; otherwise this changes nothing).
+  grid_dep_launch();
 
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t cpg = rp.nch / G;   // chunks per group and row
@@ -424,9 +502,53 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
 
   // this CTA's slice of a row, in 16-byte units
   const uint32_t slice_begin = cta_rank * rp.slice_units;
-  const uint32_t slice_end = min(slice_begin + rp.slice_units, rp.row_units);
-  const uint32_t slice_len = slice_end > slice_begin ? slice_end - slice_begin : 0;
-  const size_t row_bytes = static_cast<size_t>(rp.row_units) * 16;
+  const uint32_t base_mis = kRagged ? static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.logits) & 15) : 0;
+  auto row_geom = [&](int64_t row) -> RowGeom {
+    RowGeom g;
+    if constexpr (!kRagged) {
+      g.head_e = 0;
+      g.tail_e = 0;
+      g.span = rp.row_units;
+      g.byte_off = row * static_cast<int64_t>(rp.row_bytes);
+    } else {
+      const uint64_t a0 = base_mis + static_cast<uint64_t>(row) * rp.row_bytes;  // the row's address modulo 16 is a0 modulo 16
+      const uint32_t head_b = static_cast<uint32_t>(a0 & 15);
+      const uint64_t total = head_b + rp.row_bytes;
+      g.head_e = head_b / sizeof(T);
+      g.tail_e = static_cast<uint32_t>(total & 15) / sizeof(T);
+      g.span = static_cast<uint32_t>((total + 15) >> 4);
+      g.byte_off = row * static_cast<int64_t>(rp.row_bytes) - head_b;
+    }
+    return g;
+  };
+  auto slice_len_of = [&](const RowGeom& g) -> uint32_t {
+    return g.span > slice_begin ? min(rp.slice_units, g.span - slice_begin) : 0;
+  };
+  // Units of chunk `cl` of group `g` that lie in the slice, and which of them [v_lo, v_hi) are whole (not edge units).
+  auto chunk_range = [&](const RowGeom& rg, uint32_t slice_len, uint32_t g, uint32_t cl, uint32_t& u0, uint32_t& len, uint32_t& v_lo,
+                         uint32_t& v_hi) {
+    u0 = (cl * G + g) * kChunkUnits;
+    len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+    v_lo = 0;
+    v_hi = len;
+    if constexpr (kRagged) {
+      if (len) {
+        if (rg.head_e && slice_begin + u0 == 0) v_lo = 1;
+        if (rg.tail_e && slice_begin + u0 + len == rg.span && v_hi > v_lo) v_hi = len - 1;
+      }
+    }
+  };
+
+  // In a full chunk that holds an edge unit, which of the calling thread's NV vectors that unit is (-1: none).  The first
+  // unit of a chunk is vector 0 of thread 0, the last one vector NV - 1 of the last thread.
+  auto edge_vector = [&](uint32_t len, uint32_t v_lo, uint32_t v_hi) -> int {
+    if constexpr (kRagged) {
+      const uint32_t t_in_group = (threadIdx.x % TG);
+      if (v_lo && t_in_group == 0) return 0;
+      if (v_hi < len && t_in_group == TG - 1) return NV - 1;
+    }
+    return -1;
+  };
 
   if (tid == 0) {
     for (uint32_t b = 0; b < rp.nbuf; ++b) {
@@ -460,6 +582,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     int64_t next_load = 0, ld_k = 0;
     uint32_t ld_j = 0, ld_cl = 0;
     bool ld_skip = false;  // the row being loaded is ignored: its logits are never read
+    RowGeom ld_geom = row_geom(cluster_id);
+    uint32_t ld_slice = slice_len_of(ld_geom);
     int64_t ld_target = (MODE == 0 && lane == 0 && nrows_local > 0) ? p.target[cluster_id] : 0;
     auto load_next = [&]() {  // loads the group's next chunk into the buffer its ring position names
       if (next_load >= per_group) return;
@@ -470,13 +594,15 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
           ld_skip = tr == p.ignore_index || tr < 0 || tr >= p.classes;  // the consumers' notion of "ignored"
           if (ld_k + 1 < nrows_local) ld_target = p.target[row + rp.num_clusters];
         }
+        ld_geom = row_geom(row);
+        ld_slice = slice_len_of(ld_geom);
       }
       const uint32_t u0 = (ld_cl * G + g) * kChunkUnits;
-      const uint32_t len = (!ld_skip && u0 < slice_len) ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+      const uint32_t len = (!ld_skip && u0 < ld_slice) ? min(static_cast<uint32_t>(kChunkUnits), ld_slice - u0) : 0;
       const uint32_t bar = full_base + 8 * ld_j;
       if (len) {
         const unsigned char* src =
-            static_cast<const unsigned char*>(p.logits) + row * row_bytes + static_cast<size_t>(slice_begin + u0) * 16;
+            static_cast<const unsigned char*>(p.logits) + ld_geom.byte_off + static_cast<int64_t>(slice_begin + u0) * 16;
         mbar_expect_tx(bar, len * 16);
         bulk_g2s(ring_base + ld_j * kChunkBytes, src, len * 16, bar);
       } else {
@@ -500,15 +626,17 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       }
       if (lane == 0) {
         const int64_t row = cluster_id + k * static_cast<int64_t>(rp.num_clusters);
+        const RowGeom rg = row_geom(row);
+        const uint32_t slice_len = slice_len_of(rg);
         for (uint32_t cl = 0; cl < cpg; ++cl) {
           if (!mbar_wait(ready_base + 8 * j, ph)) timed_out = true;
           if (p.grad) {
-            const uint32_t u0 = (cl * G + g) * kChunkUnits;
-            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
-            if (len) {
+            uint32_t u0, len, v_lo, v_hi;
+            chunk_range(rg, slice_len, g, cl, u0, len, v_lo, v_hi);
+            if (v_hi > v_lo) {  // whole units only: the edge units of a ragged row are written by a consumer thread
               unsigned char* dst =
-                  static_cast<unsigned char*>(p.grad) + row * row_bytes + static_cast<size_t>(slice_begin + u0) * 16;
-              bulk_s2g(dst, ring_base + j * kChunkBytes, len * 16);
+                  static_cast<unsigned char*>(p.grad) + rg.byte_off + static_cast<int64_t>(slice_begin + u0 + v_lo) * 16;
+              bulk_s2g(dst, ring_base + j * kChunkBytes + v_lo * 16, (v_hi - v_lo) * 16);
             }
             bulk_commit();
             bulk_wait_read<1>();  // every store of this thread but the newest has finished reading shared memory
@@ -547,18 +675,38 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
   const int64_t elems_per_chunk = static_cast<int64_t>(kChunkUnits) * E;
   const int64_t slice_elem0 = static_cast<int64_t>(slice_begin) * E;
   float base_scale = p.grad_scale;  // gradient scale that does not depend on the row
-  if (p.grad && p.reduction == SB_REDUCTION_MEAN) base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
+  // `mean` divides by the valid-row count, which the kernel before this one in the stream produces.  When the launch
+  // allows this kernel to start under that one, the copy-engine warps fill the ring in the meantime and the consumers wait
+  // here.  (Waiting later, right before the first gradient sweep, put the wait inside the row loop and cost the 16-bit
+  // sweeps 4 % on B200.)
+  if (p.grad && p.reduction == SB_REDUCTION_MEAN) {
+    grid_dep_wait();
+    base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
+  }
+
+  // Edge units of a ragged row inside chunk (u0, len, v_lo, v_hi): the thread that owns the unit's vector in the sweeps
+  // (thread 0 for the first unit of a chunk, thread (len - 1) % TG for the last) folds its elements.
+  auto edge_fold = [&](RowStats& st, const RowGeom& rg, const unsigned char* chunk, uint32_t len, uint32_t v_lo, uint32_t v_hi) {
+    if constexpr (kRagged) {
+      if (len) {
+        if (v_lo && gt == 0) edge_stats<T, kSumX>(st, chunk, rg.head_e, (rg.span == 1 && rg.tail_e) ? rg.tail_e : static_cast<uint32_t>(E));
+        if (v_hi < len && gt == (len - 1) % TG) edge_stats<T, kSumX>(st, chunk + static_cast<size_t>(len - 1) * 16, 0, rg.tail_e);
+      }
+    }
+  };
 
   // Folds the group's chunks [from, cpg) of the row whose first chunk sits at ring position (j0, ph0) into
   // the statistics and returns how many chunks of the row are done.  blocking: wait for every chunk;
   // otherwise stop at the first chunk that has not landed yet (used to fill the wait for the peers'
   // statistics with the next row's work).
-  auto fold_chunks = [&](RowStats& st, uint32_t j0, uint32_t ph0, uint32_t from, uint32_t to, bool skip, bool blocking) -> uint32_t {
+  auto fold_chunks = [&](RowStats& st, const RowGeom& rg, uint32_t j0, uint32_t ph0, uint32_t from, uint32_t to, bool skip,
+                         bool blocking) -> uint32_t {
     uint32_t j = j0 + from, ph = ph0;
     if (j >= nbg) {  // from < cpg < nbg: one wrap at most
       j -= nbg;
       ph ^= 1;
     }
+    const uint32_t slice_len = slice_len_of(rg);
     uint32_t cl = from;
     for (; cl < to; ++cl) {
       const uint32_t bar = full0 + 8 * j;
@@ -568,20 +716,31 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         break;
       }
       if (!skip) {
-        const uint32_t u0 = (cl * G + grp) * kChunkUnits;
-        const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
-        const uint4* buf = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
+        uint32_t u0, len, v_lo, v_hi;
+        chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
+        const unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
+        const uint4* buf = reinterpret_cast<const uint4*>(chunk) + gt;
         if (len == kChunkUnits) {
           uint4 r[NV];
 #pragma unroll
           for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
-          stats_update<T, NV, kSumX>(st, r);
+          const int skip = edge_vector(len, v_lo, v_hi);  // -1 except for the one thread that holds an edge unit of a ragged row
+          if (skip < 0) {
+            stats_update<T, NV, kSumX>(st, r);
+          } else {
+            uint4 rest[NV - 1];
+#pragma unroll
+            for (int q = 0; q < NV - 1; ++q) rest[q] = skip == 0 ? r[q + 1] : r[q];  // skip is 0 or NV - 1
+            stats_update<T, NV - 1, kSumX>(st, rest);
+          }
         } else {
-          for (uint32_t v = gt; v < len; v += TG) {  // ragged last chunk of the slice
+          for (uint32_t v = gt; v < v_hi; v += TG) {  // short last chunk of the slice
+            if (v < v_lo) continue;
             uint4 r[1] = {buf[v - gt]};
             stats_update<T, 1, kSumX>(st, r);
           }
         }
+        edge_fold(st, rg, chunk, len, v_lo, v_hi);
       }
       if (++j == nbg) {
         j = 0;
@@ -606,19 +765,21 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     const bool ignored = is_ignored(t);
     if (MODE == 0 && ignored && t != p.ignore_index && tid == 0 && cta_rank == 0 && p.status)
       atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+    const RowGeom rg = row_geom(row);
+    const uint32_t slice_len = slice_len_of(rg);
+    const int64_t t_slice = t + rg.head_e - slice_elem0;  // element position of the target in this CTA's slice
 
     // ---- sweep A: statistics as the group's chunks land (the first a_done chunks are folded already) ----
     float mref[kKeepChunks];          // kept mode: the maximum each of the group's chunks was scaled by (per thread)
     uint32_t t_cl = 0xffffffffu, t_off = 0;  // kept mode: chunk of this group and element offset of the target, if this thread owns it
     if constexpr (kKeep) {
       if (!ignored) {
-        const int64_t tl = t - slice_elem0;
-        if (tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
-          const uint32_t tu = static_cast<uint32_t>(tl) / E;
+        if (t_slice >= 0 && t_slice < static_cast<int64_t>(slice_len) * E) {
+          const uint32_t tu = static_cast<uint32_t>(t_slice) / E;
           const uint32_t c = tu / kChunkUnits, v = tu % kChunkUnits;
           if (c % G == grp && v % TG == gt) {
             t_cl = c / G;
-            t_off = static_cast<uint32_t>(tl) - c * (kChunkUnits * E);
+            t_off = static_cast<uint32_t>(t_slice) - c * (kChunkUnits * E);
           }
         }
       }
@@ -629,8 +790,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         if (static_cast<uint32_t>(cl) < cpg) {
           if (!mbar_wait(full0 + 8 * j, ph)) timed_out = true;
           if (!ignored) {
-            const uint32_t u0 = (cl * G + grp) * kChunkUnits;
-            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+            uint32_t u0, len, v_lo, v_hi;
+            chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
             unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
             uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
             // the logit of the target is needed for the loss: its owner saves it before the chunk is overwritten
@@ -639,25 +800,39 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
               uint4 r[NV], e[NV];
 #pragma unroll
               for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
-              stats_update<T, NV, kSumX, true>(st, r, e);
+              const int skip = edge_vector(len, v_lo, v_hi);  // -1 except for the one thread that holds an edge unit of a ragged row
+              if (skip < 0) {
+                stats_update<T, NV, kSumX, true>(st, r, e);
 #pragma unroll
-              for (int q = 0; q < NV; ++q) buf[q * TG] = e[q];
+                for (int q = 0; q < NV; ++q) buf[q * TG] = e[q];
+              } else {  // the edge unit keeps its logits (its few elements are handled in scalar form)
+                uint4 rest[NV - 1], erest[NV - 1];
+#pragma unroll
+                for (int q = 0; q < NV - 1; ++q) rest[q] = skip == 0 ? r[q + 1] : r[q];  // skip is 0 or NV - 1
+                stats_update<T, NV - 1, kSumX, true>(st, rest, erest);
+#pragma unroll
+                for (int q = 0; q < NV - 1; ++q) buf[(skip == 0 ? q + 1 : q) * TG] = erest[q];
+              }
             } else {
-              // ragged last chunk of the slice: one maximum for all of this thread's vectors, then the exponentials
+              // short last chunk of the slice: one maximum for all of this thread's vectors, then the exponentials; an edge
+              // unit keeps its logits
               float vm = -CUDART_INF_F;
-              for (uint32_t v = gt; v < len; v += TG) vm = max_nan(vm, U::vmax(buf[v - gt]));
+              for (uint32_t v = gt; v < v_hi; v += TG)
+                if (v >= v_lo) vm = max_nan(vm, U::vmax(buf[v - gt]));
               const float nm = max_nan(st.m2, vm * kLog2e);
               const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);
               st.s[0] = mul2(st.s[0], make_float2(resc, resc));
               st.s[1] = mul2(st.s[1], make_float2(resc, resc));
               st.m2 = nm;  // stats_update below finds its maximum already in place: no further rescaling
-              for (uint32_t v = gt; v < len; v += TG) {
+              for (uint32_t v = gt; v < v_hi; v += TG) {
+                if (v < v_lo) continue;
                 uint4 r[1] = {buf[v - gt]}, e[1];
                 stats_update<T, 1, kSumX, true>(st, r, e);
                 buf[v - gt] = e[0];
               }
             }
-            mref[cl] = st.m2;
+            mref[cl] = st.m2;  // what the kept values of this chunk are relative to (the edge fold below may raise st.m2 further)
+            edge_fold(st, rg, chunk, len, v_lo, v_hi);
           }
           if (++j == nbg) {
             j = 0;
@@ -666,7 +841,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         }
       }
     } else {
-      fold_chunks(st, cj, cphase, a_done, cpg, ignored, true);
+      fold_chunks(st, rg, cj, cphase, a_done, cpg, ignored, true);
     }
 
     // ---- CTA reduce; the other warps go on to the next row's chunks while warp 0 combines ----
@@ -700,13 +875,12 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         if (lane == 0) {
           // x[target] if it lies in this CTA's slice: chunk c of the row belongs to group c % G
           float xt = 0.f;
-          const int64_t tl = t - slice_elem0;
           if (kKeep) {  // saved by its owner during the sweep (ordered by the barrier above); 0 when another CTA holds the target
             xt = tail->xt_kept;
             tail->xt_kept = 0.f;
-          } else if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(slice_len) * E) {
-            const uint32_t c = static_cast<uint32_t>(tl / elems_per_chunk);
-            const uint32_t off = static_cast<uint32_t>(tl - c * elems_per_chunk);
+          } else if (MODE == 0 && t_slice >= 0 && t_slice < static_cast<int64_t>(slice_len) * E) {
+            const uint32_t c = static_cast<uint32_t>(t_slice / elems_per_chunk);
+            const uint32_t off = static_cast<uint32_t>(t_slice - c * elems_per_chunk);
             const uint32_t og = c % G, ocl = c / G;
             uint32_t oj = cj + ocl, oph = cphase;  // every group is at the same ring position
             if (oj >= nbg) {
@@ -741,7 +915,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         nj -= nbg;
         nph ^= 1;
       }
-      a_done = fold_chunks(st, nj, nph, 0, min(cpg, rp.window), is_ignored(t_next), false);
+      a_done = fold_chunks(st, row_geom(row + rp.num_clusters), nj, nph, 0, min(cpg, rp.window), is_ignored(t_next), false);
     }
     if (CLUSTER > 1) {
       cluster_wait();
@@ -794,28 +968,63 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
       // x[target] with the same arithmetic and a single rounding.
       const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
+      // Edge units of a ragged row: the thread that owns the unit's vector computes its few elements from the logits
+      // still in shared memory, before its own sweep below overwrites them, and writes them to global memory itself (the
+      // bulk store covers whole units only).
+      auto edge_store = [&](const unsigned char* chunk, uint32_t u0, uint32_t len, uint32_t v_lo, uint32_t v_hi) {
+        if constexpr (kRagged) {
+          if (len) {
+            T* grow = reinterpret_cast<T*>(static_cast<unsigned char*>(p.grad) + row * static_cast<int64_t>(rp.row_bytes));
+            if (v_lo && gt == 0) {
+              const uint32_t e1 = (rg.span == 1 && rg.tail_e) ? rg.tail_e : static_cast<uint32_t>(E);
+              edge_output<T, MODE>(chunk, grow, rg.head_e, e1, 0, t, ignored, neg_lse2.x, lse, scale, sub_all, sub_t);
+            }
+            if (v_hi < len && gt == (len - 1) % TG) {
+              const int64_t class0 = static_cast<int64_t>(rg.span - 1) * E - rg.head_e;
+              edge_output<T, MODE>(chunk + static_cast<size_t>(len - 1) * 16, grow + class0, 0, rg.tail_e, class0, t, ignored, neg_lse2.x,
+                                   lse, scale, sub_all, sub_t);
+            }
+          }
+        }
+      };
       if constexpr (kKeep) {
         // the chunks hold 2^(x log2e - mref): the gradient is that times 2^(mref - lse2) * scale, minus the smoothing share
         uint32_t j = cj;
 #pragma unroll
         for (int cl = 0; cl < kKeepChunks; ++cl) {
           if (static_cast<uint32_t>(cl) < cpg) {
-            const uint32_t u0 = (cl * G + grp) * kChunkUnits;
-            const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
+            uint32_t u0, len, v_lo, v_hi;
+            chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
             unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
             uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
+            edge_store(chunk, u0, len, v_lo, v_hi);
             if (!ignored) {
               const float mr = mref[cl] == -CUDART_INF_F ? 0.f : mref[cl];  // the sweep scaled an all -inf chunk by 2^0
               const float factor = ex2(mr + neg_lse2.x) * scale;
-              const float2 factor2 = make_float2(factor, factor);
-              if (len == kChunkUnits) {
-                uint4 r[NV];
+              if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                // bf16: one packed FMA per pair (fp16 stays on fp32 pairs: its factor, about 1 / rows, would be subnormal)
+                const __nv_bfloat162 fb = __float2bfloat162_rn(factor);
+                const __nv_bfloat162 nb = __float2bfloat162_rn(-sub_all);
+                if (len == kChunkUnits) {
+                  uint4 r[NV];
 #pragma unroll
-                for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+                  for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
 #pragma unroll
-                for (int q = 0; q < NV; ++q) buf[q * TG] = grad_from_kept<T>(r[q], factor2, nsub2);
+                  for (int q = 0; q < NV; ++q) buf[q * TG] = grad_from_kept_bf16(r[q], fb, nb);
+                } else {
+                  for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_from_kept_bf16(buf[v - gt], fb, nb);
+                }
               } else {
-                for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_from_kept<T>(buf[v - gt], factor2, nsub2);
+                const float2 factor2 = make_float2(factor, factor);
+                if (len == kChunkUnits) {
+                  uint4 r[NV];
+#pragma unroll
+                  for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
+#pragma unroll
+                  for (int q = 0; q < NV; ++q) buf[q * TG] = grad_from_kept<T>(r[q], factor2, nsub2);
+                } else {
+                  for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = grad_from_kept<T>(buf[v - gt], factor2, nsub2);
+                }
               }
               if (static_cast<uint32_t>(cl) == t_cl) reinterpret_cast<T*>(chunk)[t_off] = from_float<T>(g_target);
             } else {
@@ -830,10 +1039,13 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       } else {
       uint32_t j = cj;
       for (uint32_t cl = 0; cl < cpg; ++cl) {
-        const uint32_t u0 = (cl * G + grp) * kChunkUnits;
-        const uint32_t len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
-        uint4* buf = reinterpret_cast<uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
+        uint32_t u0, len, v_lo, v_hi;
+        chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
+        unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
+        uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
+        edge_store(chunk, u0, len, v_lo, v_hi);  // reads the edge units' logits: before the sweep below may touch them
         if (!ignored) {
+          // edge units are swept with the rest: what comes out of them is never stored
           if (len == kChunkUnits) {
             uint4 r[NV];
 #pragma unroll
@@ -846,9 +1058,9 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
               buf[v - gt] = MODE != 1 ? grad_vector<T>(buf[v - gt], neg_lse2, scale2, nsub2) : shift_vector<T>(buf[v - gt], neg_lse_nat2);
           }
           // position of the target inside this chunk, in elements
-          const int64_t tl = t - (slice_elem0 + static_cast<int64_t>(u0) * E);
+          const int64_t tl = t_slice - static_cast<int64_t>(u0) * E;
           if (MODE == 0 && tl >= 0 && tl < static_cast<int64_t>(len) * E && (static_cast<uint32_t>(tl) / E) % TG == gt)
-            reinterpret_cast<T*>(ring + static_cast<size_t>(j) * kChunkBytes)[tl] = from_float<T>(g_target);
+            reinterpret_cast<T*>(chunk)[tl] = from_float<T>(g_target);
         } else {
           for (uint32_t v = gt; v < len; v += TG) buf[v - gt] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -880,9 +1092,32 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
 
 size_t resident_smem_bytes(uint32_t nbuf) { return static_cast<size_t>(nbuf) * kChunkUnits * 16 + sizeof(Tail); }
 
+// Rows in 16-byte units.  A row whose pitch or base address is not a multiple of 16 bytes is fetched as its aligned
+// superset, which is widest when the row starts in the last element slot of a unit.
+struct RowLayout {
+  uint64_t row_bytes;
+  uint32_t row_units;  // units of the widest superset
+  bool ragged;
+  bool ok;
+};
+RowLayout row_layout(int dtype, int64_t classes, const void* logits, const void* out) {
+  RowLayout l{};
+  const uint64_t es = static_cast<uint64_t>(dtype_size(dtype));
+  l.row_bytes = static_cast<uint64_t>(classes) * es;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(logits), b = reinterpret_cast<uintptr_t>(out);
+  l.ragged = (l.row_bytes % 16) != 0 || (a % 16) != 0;
+  // the output is written from the same shared-memory image: it needs the input's position within a unit
+  l.ok = es != 0 && a % es == 0 && (out == nullptr || (b % 16) == (a % 16));
+  const uint64_t units = l.ragged ? (l.row_bytes + (16 - es) + 15) / 16 : l.row_bytes / 16;
+  if (units > 0x7fffffffULL) l.ok = false;
+  l.row_units = static_cast<uint32_t>(units);
+  return l;
+}
+
 // Geometry for a row of `row_units` 16-byte units split over `cluster` CTAs.  Returns false when the
 // slice does not fit next to at least one spare buffer per group.
-bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, ResidentParams* rp) {
+bool resident_geometry(const RowLayout& l, int cluster, size_t smem_limit, ResidentParams* rp) {
+  const uint32_t row_units = l.row_units;
   const uint32_t slice_units = (row_units + cluster - 1) / cluster;
   uint32_t cpg = (slice_units + kGroups * kChunkUnits - 1) / (kGroups * kChunkUnits);
   if (cpg == 0) cpg = 1;
@@ -895,13 +1130,16 @@ bool resident_geometry(uint32_t row_units, int cluster, size_t smem_limit, Resid
   rp->chunk_units = kChunkUnits;
   rp->slice_units = slice_units;
   rp->row_units = row_units;
+  rp->row_bytes = l.row_bytes;
   rp->window = 0;  // set by the launcher, which knows the element type
   return true;
 }
 
-template <typename T, int CLUSTER, bool SUMX, int MODE, bool KEEP = false>
-int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
-  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX, MODE, KEEP>;
+// pdl: launch as a programmatic dependent of the kernel before it in the stream (the caller vouches that this kernel is
+// the library's own valid-row count, whose only product, acc[1], the kernel reads behind grid_dep_wait).
+template <typename T, int CLUSTER, bool SUMX, int MODE, bool KEEP = false, bool RAGGED = false>
+int launch_resident_cfg(ResidentParams rp, cudaStream_t st, bool pdl) {
+  auto kernel = ce_resident_kernel<T, CLUSTER, SUMX, MODE, KEEP, RAGGED>;
   const size_t smem = resident_smem_bytes(rp.nbuf);
   static thread_local int configured_device = -1;  // per (instantiation, thread): attribute set for this device
   int dev = 0;
@@ -911,18 +1149,20 @@ int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
       return SB_ERR_CUDA;
     configured_device = dev;
   }
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = CLUSTER;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   int clusters = sm_count() / CLUSTER;
   if (CLUSTER > 1) {
     cudaLaunchConfig_t probe = {};
     probe.gridDim = dim3(sm_count() / CLUSTER * CLUSTER);
     probe.blockDim = dim3(kResidentThreads);
     probe.dynamicSmemBytes = smem;
-    probe.attrs = &attr;
+    probe.attrs = attr;
     probe.numAttrs = 1;
     int max_clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &probe) == cudaSuccess && max_clusters > 0 &&
@@ -938,8 +1178,8 @@ int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
   cfg.blockDim = dim3(kResidentThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kernel, rp) != cudaSuccess) {
     cudaGetLastError();
     return SB_ERR_CUDA;
@@ -947,70 +1187,81 @@ int launch_resident_cfg(ResidentParams rp, cudaStream_t st) {
   return SB_OK;
 }
 
-template <typename T, int CLUSTER>
-int launch_resident(ResidentParams rp, cudaStream_t st) {
+template <typename T, int CLUSTER, bool RAGGED>
+int launch_resident(ResidentParams rp, cudaStream_t st, bool pdl) {
   // Chunks of the next row a group folds while a row's statistics are exchanged.  Measured on B200: with
   // 4-byte elements the sweeps are short next to the memory time and filling the exchange with the next
   // row's statistics gains 8 %; with 2-byte elements the sweeps set the pace and the same reordering only
   // delays the gradient sweep that frees the buffers the next loads need (-5 % per chunk), so it stays off.
   const uint32_t spare = (rp.nbuf - rp.nch) / kGroups;
   rp.window = g_ce_window_chunks >= 0 ? static_cast<uint32_t>(g_ce_window_chunks) : (sizeof(T) == 4 && spare > 1 ? spare - 1 : 0);
-  if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1>(rp, st);
-  if (rp.mode == 2) return launch_resident_cfg<T, CLUSTER, false, 2>(rp, st);
+  if (rp.mode == 1) return launch_resident_cfg<T, CLUSTER, false, 1, false, RAGGED>(rp, st, false);
+  if (rp.mode == 2) return launch_resident_cfg<T, CLUSTER, false, 2, false, RAGGED>(rp, st, false);
   const bool sumx = rp.p.label_smoothing != 0.f;
   if constexpr (sizeof(T) == 2) {
     // 16-bit logits with a gradient: keep the exponentials of the statistics sweep (see ce_resident_kernel); in fp16 a kept
     // value below 2^-14 is subnormal, an absolute error of at most 2^-25 on a probability
     if (g_ce_keep != 0 && rp.p.grad && rp.nch / kGroups <= static_cast<uint32_t>(kKeepChunks)) {
       rp.window = 0;
-      return sumx ? launch_resident_cfg<T, CLUSTER, true, 0, true>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0, true>(rp, st);
+      return sumx ? launch_resident_cfg<T, CLUSTER, true, 0, true, RAGGED>(rp, st, pdl)
+                  : launch_resident_cfg<T, CLUSTER, false, 0, true, RAGGED>(rp, st, pdl);
     }
   }
-  return sumx ? launch_resident_cfg<T, CLUSTER, true, 0>(rp, st) : launch_resident_cfg<T, CLUSTER, false, 0>(rp, st);
+  return sumx ? launch_resident_cfg<T, CLUSTER, true, 0, false, RAGGED>(rp, st, pdl)
+              : launch_resident_cfg<T, CLUSTER, false, 0, false, RAGGED>(rp, st, pdl);
 }
 
 template <typename T>
-int launch_resident_t(const ResidentParams& rp, cudaStream_t st, int variant) {
+int launch_resident_t(const ResidentParams& rp, cudaStream_t st, int variant, bool ragged, bool pdl) {
+  if (ragged) {
+    switch (variant) {
+      case 1: return launch_resident<T, 1, true>(rp, st, pdl);
+      case 2: return launch_resident<T, 2, true>(rp, st, pdl);
+      case 4: return launch_resident<T, 4, true>(rp, st, pdl);
+      default: return SB_ERR_INVALID_ARGUMENT;
+    }
+  }
   switch (variant) {
-    case 1: return launch_resident<T, 1>(rp, st);
-    case 2: return launch_resident<T, 2>(rp, st);
-    case 4: return launch_resident<T, 4>(rp, st);
+    case 1: return launch_resident<T, 1, false>(rp, st, pdl);
+    case 2: return launch_resident<T, 2, false>(rp, st, pdl);
+    case 4: return launch_resident<T, 4, false>(rp, st, pdl);
     default: return SB_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int launch_resident_any(const ResidentParams& rp, int dtype, cudaStream_t st, int variant, bool ragged, bool pdl) {
+  switch (dtype) {
+    case SB_F32: return launch_resident_t<float>(rp, st, variant, ragged, pdl);
+    case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant, ragged, pdl);
+    case SB_F16: return launch_resident_t<__half>(rp, st, variant, ragged, pdl);
+    default: return SB_ERR_UNSUPPORTED;
   }
 }
 
 }  // namespace
 
+// 0: no resident kernel for this shape; 1 / 2 / 4: cluster size.  Rows shorter than 16 KB are left to the kernels that
+// hold a row in registers (the per-row barriers of this pipeline would dominate them).
 int ce_choose_variant(int dtype, int64_t rows, int64_t classes, const void* logits, const void* grad) {
-  const int64_t row_bytes = classes * dtype_size(dtype);
   if (rows <= 0 || classes <= 0) return 0;
-  if (row_bytes % 16) return 0;  // bulk copies need 16-byte aligned row starts
-  if (reinterpret_cast<uintptr_t>(logits) % 16 || reinterpret_cast<uintptr_t>(grad) % 16) return 0;
-  if (row_bytes < 16 * 1024) return 0;  // short rows: the per-row barriers would dominate
-  if (row_bytes / 16 > 0x7fffffffLL) return 0;
+  const RowLayout l = row_layout(dtype, classes, logits, grad);
+  if (!l.ok) return 0;
+  if (l.row_bytes < 16 * 1024) return 0;
   const size_t limit = static_cast<size_t>(max_smem_optin());
   ResidentParams rp;
   const int candidates[3] = {1, 2, 4};
-  for (int c : candidates) {
-    if (c > 1 && rows < sm_count() / c) continue;  // too few rows to keep every SM busy with clusters
-    if (resident_geometry(static_cast<uint32_t>(row_bytes / 16), c, limit, &rp)) return c;
-  }
+  for (int c : candidates)
+    if (resident_geometry(l, c, limit, &rp)) return c;
   return 0;
 }
 
-int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant) {
+int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant, bool pdl) {
   ResidentParams rp;
   rp.p = p;
   rp.mode = 0;
-  const int64_t row_bytes = p.classes * dtype_size(p.dtype);
-  if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
-    return SB_ERR_INVALID_ARGUMENT;
-  switch (p.dtype) {
-    case SB_F32: return launch_resident_t<float>(rp, st, variant);
-    case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant);
-    case SB_F16: return launch_resident_t<__half>(rp, st, variant);
-    default: return SB_ERR_UNSUPPORTED;
-  }
+  const RowLayout l = row_layout(p.dtype, p.classes, p.logits, p.grad);
+  if (!l.ok || !resident_geometry(l, variant, static_cast<size_t>(max_smem_optin()), &rp)) return SB_ERR_INVALID_ARGUMENT;
+  return launch_resident_any(rp, p.dtype, st, variant, l.ragged, pdl);
 }
 
 // log_softmax over the last dimension with the row resident in shared memory (same pipeline as the cross
@@ -1029,23 +1280,26 @@ int lsm_launch_resident(const void* in, void* out, int dtype, int64_t rows, int6
   rp.p.dtype = dtype;
   rp.p.grad_scale = 1.f;
   rp.mode = mode;
-  const int64_t row_bytes = dim * dtype_size(dtype);
-  if (!resident_geometry(static_cast<uint32_t>(row_bytes / 16), variant, static_cast<size_t>(max_smem_optin()), &rp))
-    return SB_ERR_UNSUPPORTED;
-  switch (dtype) {
-    case SB_F32: return launch_resident_t<float>(rp, st, variant);
-    case SB_BF16: return launch_resident_t<__nv_bfloat16>(rp, st, variant);
-    case SB_F16: return launch_resident_t<__half>(rp, st, variant);
-    default: return SB_ERR_UNSUPPORTED;
-  }
+  const RowLayout l = row_layout(dtype, dim, in, out);
+  if (!l.ok || !resident_geometry(l, variant, static_cast<size_t>(max_smem_optin()), &rp)) return SB_ERR_UNSUPPORTED;
+  return launch_resident_any(rp, dtype, st, variant, l.ragged, false);
+}
+
+int ce_choose_family(const CEParams& p) {
+  // class weights together with label smoothing weight every class of the row: only the two-sweep kernel reads them
+  if (p.class_weight && p.label_smoothing != 0.f) return 0;
+  if (g_ce_force_variant == 0) return 0;
+  int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
+  if (g_ce_force_variant > 0 && variant != 0) variant = g_ce_force_variant;  // falls back if it does not fit
+  if (variant != 0) return variant;
+  return rows_reg_applies(p.dtype, p.classes, p.logits, p.grad) ? 8 : 0;
 }
 
 int ce_dispatch(const CEParams& p, cudaStream_t st) {
-  int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
-  if (g_ce_force_variant == 0) variant = 0;
-  if (g_ce_force_variant > 0 && variant != 0) variant = g_ce_force_variant;  // falls back to generic if it does not fit
-  if (variant != 0) {
-    const int rc = ce_launch_resident(p, st, variant);
+  const int family = ce_choose_family(p);
+  if (family == 8) return ce_launch_rows_reg(p, st);
+  if (family != 0) {
+    const int rc = ce_launch_resident(p, st, family, (p.flags & SB_CE_FLAG_AFTER_COUNT) != 0);
     if (rc == SB_OK) return rc;
   }
   return ce_launch_generic(p, st);
@@ -1069,9 +1323,14 @@ extern "C" int sb_set_tuning(int32_t key, int32_t value) {
     sb::g_ce_window_chunks = value;
     return SB_OK;
   }
+  if (key == 5 && value >= 1 && value <= 60000) return sb::xchg_set_timeout_ms(value);
   return SB_ERR_INVALID_ARGUMENT;
 }
 
 extern "C" int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes) {
-  return sb::ce_choose_variant(dtype, rows, classes, nullptr, nullptr);
+  sb::CEParams p{};
+  p.dtype = dtype;
+  p.rows = rows;
+  p.classes = classes;
+  return sb::ce_choose_family(p);
 }

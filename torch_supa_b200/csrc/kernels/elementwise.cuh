@@ -153,6 +153,38 @@ SB_DEFINE_OP(SB_EW_DIV, 2, {
   if constexpr (std::is_floating_point<CT>::value) return a / b;
   else return a;
 })
+// trunc(a / b); integers: C division (0 for a zero divisor: nothing traps on the device).
+SB_DEFINE_OP(SB_EW_DIV_TRUNC, 2, {
+  if constexpr (std::is_same<CT, bool>::value) return a && b;
+  else if constexpr (std::is_floating_point<CT>::value) return trunc(a / b);
+  else return b == 0 ? CT(0) : (b == CT(-1) ? CT(0) - a : a / b);
+})
+// Python's floor division.  Floating types: the quotient of (a - fmod(a, b)) by b, one less when the remainder and the
+// divisor differ in sign, then floored with the half-way guard of c10::div_floor_floating; a zero divisor gives a / b.
+SB_DEFINE_OP(SB_EW_DIV_FLOOR, 2, {
+  if constexpr (std::is_same<CT, bool>::value) {
+    return a && b;
+  } else if constexpr (std::is_floating_point<CT>::value) {
+    if (b == CT(0)) return a / b;
+    const CT mod = fmod(a, b);
+    CT div = (a - mod) / b;
+    if (mod != CT(0) && (b < CT(0)) != (mod < CT(0))) div -= CT(1);
+    CT floordiv;
+    if (div != CT(0)) {
+      floordiv = floor(div);
+      if (div - floordiv > CT(0.5)) floordiv += CT(1);
+    } else {
+      floordiv = copysign(CT(0), a / b);
+    }
+    return floordiv;
+  } else {
+    if (b == 0) return CT(0);
+    if (b == CT(-1)) return CT(0) - a;
+    CT q = a / b;
+    if ((a % b != 0) && ((a < 0) != (b < 0))) q -= 1;
+    return q;
+  }
+})
 SB_DEFINE_OP(SB_EW_ADD_SCALAR, 1, {
   if constexpr (std::is_same<CT, bool>::value) return a || (s.alpha && s.scalar);
   else return a + s.alpha * s.scalar;
@@ -343,7 +375,7 @@ __device__ __forceinline__ CT ew_apply_runtime(int op, CT a, CT b, CT c, const O
     SB_CASE(SB_EW_COPY) SB_CASE(SB_EW_FILL) SB_CASE(SB_EW_ADD) SB_CASE(SB_EW_MUL) SB_CASE(SB_EW_SUB)
     SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG) SB_CASE(SB_EW_MAXIMUM) SB_CASE(SB_EW_MINIMUM)
     SB_CASE(SB_EW_EQ) SB_CASE(SB_EW_NE) SB_CASE(SB_EW_LT) SB_CASE(SB_EW_LE) SB_CASE(SB_EW_GT) SB_CASE(SB_EW_GE)
-    SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL)
+    SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL) SB_CASE(SB_EW_DIV_TRUNC) SB_CASE(SB_EW_DIV_FLOOR)
 #undef SB_CASE
     default: break;
   }

@@ -26,7 +26,7 @@ int ew_launch_f32(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
     SB_CASE(SB_EW_BCE_LOGITS) SB_CASE(SB_EW_BCE_LOGITS_PW) SB_CASE(SB_EW_BCE_LOGITS_BWD) SB_CASE(SB_EW_BCE_LOGITS_PW_BWD)
     SB_CASE(SB_EW_SIGMOID) SB_CASE(SB_EW_TANH) SB_CASE(SB_EW_EXP) SB_CASE(SB_EW_LOG) SB_CASE(SB_EW_SIGMOID_BWD) SB_CASE(SB_EW_TANH_BWD)
     SB_CASE(SB_EW_MAXIMUM) SB_CASE(SB_EW_MINIMUM) SB_CASE(SB_EW_EQ) SB_CASE(SB_EW_NE) SB_CASE(SB_EW_LT) SB_CASE(SB_EW_LE) SB_CASE(SB_EW_GT)
-    SB_CASE(SB_EW_GE) SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL)
+    SB_CASE(SB_EW_GE) SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL) SB_CASE(SB_EW_DIV_TRUNC) SB_CASE(SB_EW_DIV_FLOOR)
 #undef SB_CASE
     default: return SB_ERR_UNSUPPORTED;
   }

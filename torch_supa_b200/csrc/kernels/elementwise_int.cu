@@ -13,7 +13,7 @@ int launch_ct(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
     SB_CASE(SB_EW_COPY) SB_CASE(SB_EW_FILL) SB_CASE(SB_EW_ADD) SB_CASE(SB_EW_MUL) SB_CASE(SB_EW_SUB)
     SB_CASE(SB_EW_ADD_SCALAR) SB_CASE(SB_EW_MUL_SCALAR) SB_CASE(SB_EW_NEG)
     SB_CASE(SB_EW_MAXIMUM) SB_CASE(SB_EW_MINIMUM) SB_CASE(SB_EW_EQ) SB_CASE(SB_EW_NE) SB_CASE(SB_EW_LT) SB_CASE(SB_EW_LE) SB_CASE(SB_EW_GT)
-    SB_CASE(SB_EW_GE) SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL)
+    SB_CASE(SB_EW_GE) SB_CASE(SB_EW_WHERE) SB_CASE(SB_EW_MASKED_FILL) SB_CASE(SB_EW_DIV_TRUNC) SB_CASE(SB_EW_DIV_FLOOR)
 #undef SB_CASE
     default: return SB_ERR_UNSUPPORTED;
   }

@@ -1,4 +1,4 @@
-// Reductions sum / mean / amax / amin over any set of dimensions.
+// Reductions sum / mean / amax / amin / prod / nansum over any set of dimensions.
 //
 // Path 0  rows       the reduced run is contiguous (unit input stride on dimension 0) and every other
 //                    dimension is kept: one CTA (long rows) or one warp (short rows) per output,
@@ -52,11 +52,30 @@ struct RedGenericParams {
 };
 
 // ---- functors -----------------------------------------------------------------------------------------------
+// `pre` is applied to every element as it is loaded (not to partial results).
 template <typename A> struct SumOp {
   static constexpr bool kMinMax = false;
   static constexpr bool kIsMax = false;
   __device__ static __forceinline__ A identity() { return A(0); }
+  __device__ static __forceinline__ A pre(A x) { return x; }
   __device__ static __forceinline__ A combine(A a, A b) { return a + b; }
+};
+template <typename A> struct NanSumOp {  // NaN elements count as zero
+  static constexpr bool kMinMax = false;
+  static constexpr bool kIsMax = false;
+  __device__ static __forceinline__ A identity() { return A(0); }
+  __device__ static __forceinline__ A pre(A x) {
+    if constexpr (std::is_floating_point<A>::value) return x != x ? A(0) : x;
+    else return x;
+  }
+  __device__ static __forceinline__ A combine(A a, A b) { return a + b; }
+};
+template <typename A> struct ProdOp {
+  static constexpr bool kMinMax = false;
+  static constexpr bool kIsMax = false;
+  __device__ static __forceinline__ A identity() { return A(1); }
+  __device__ static __forceinline__ A pre(A x) { return x; }
+  __device__ static __forceinline__ A combine(A a, A b) { return a * b; }
 };
 // max / min propagate NaN (amax semantics).  fp32 uses the single-instruction max.NaN / min.NaN forms.
 template <typename A> struct MaxOp {
@@ -67,6 +86,7 @@ template <typename A> struct MaxOp {
     else if constexpr (std::is_same<A, double>::value) return -CUDART_INF;
     else return INT64_MIN;
   }
+  __device__ static __forceinline__ A pre(A x) { return x; }
   __device__ static __forceinline__ A combine(A a, A b) {
     if constexpr (std::is_same<A, float>::value) {
       float r;
@@ -87,6 +107,7 @@ template <typename A> struct MinOp {
     else if constexpr (std::is_same<A, double>::value) return CUDART_INF;
     else return INT64_MAX;
   }
+  __device__ static __forceinline__ A pre(A x) { return x; }
   __device__ static __forceinline__ A combine(A a, A b) {
     if constexpr (std::is_same<A, float>::value) {
       float r;
@@ -209,14 +230,14 @@ __device__ __forceinline__ A thread_reduce_run(const void* in, int dtype, int64_
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], f[u][k]);
+        for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], F::pre(f[u][k]));
       }
     }
     for (; i < nvec; i += THREADS) {  // remainder, one vector at a time
       A f[VEC];
       IO::template load<A, VEC>(in, base + i * VEC, dtype, f);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], f[k]);
+      for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], F::pre(f[k]));
     }
     r = acc[0];
 #pragma unroll
@@ -225,7 +246,7 @@ __device__ __forceinline__ A thread_reduce_run(const void* in, int dtype, int64_
   for (int64_t e = nvec * VEC + threadIdx.x; e < n; e += THREADS) {
     A one[1];
     IO::template load<A, 1>(in, base + e, dtype, one);
-    r = F::combine(r, one[0]);
+    r = F::combine(r, F::pre(one[0]));
   }
   return r;
 }
@@ -259,7 +280,7 @@ __global__ void __launch_bounds__(THREADS) red_rows_warp_kernel(RedParams p) {
     for (int64_t e = lane; e < p.L; e += 32) {
       A one[1];
       IO::template load<A, 1>(p.in, in_off + e, p.in_dtype, one);
-      v = F::combine(v, one[0]);
+      v = F::combine(v, F::pre(one[0]));
     }
     v = warp_reduce<F, A>(v);
     if (lane == 0) {
@@ -322,7 +343,7 @@ __global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
     for (int64_t j = ty; j < p.L; j += 8) {
       A one[1];
       IO::template load<A, 1>(p.in, in_base + col * p.keep_in_strides[0] + j * p.red_stride, p.in_dtype, one);
-      v = F::combine(v, one[0]);
+      v = F::combine(v, F::pre(one[0]));
     }
   }
   sm[ty][tx] = v;
@@ -360,7 +381,7 @@ __global__ void __launch_bounds__(256) red_generic_kernel(RedGenericParams p) {
       }
       A one[1];
       DynamicIO::load<A, 1>(p.in, off, p.in_dtype, one);
-      v = F::combine(v, one[0]);
+      v = F::combine(v, F::pre(one[0]));
     }
     A res[1] = {apply_scale<A>(v, p.scale)};
     DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, res);
@@ -577,6 +598,8 @@ int launch_op(int op, const Plan& plan, cudaStream_t st) {
     case SB_RED_SUM: case SB_RED_MEAN: return launch_paths<IO, SumOp<A>, A>(plan, st);
     case SB_RED_AMAX: return launch_paths<IO, MaxOp<A>, A>(plan, st);
     case SB_RED_AMIN: return launch_paths<IO, MinOp<A>, A>(plan, st);
+    case SB_RED_PROD: return launch_paths<IO, ProdOp<A>, A>(plan, st);
+    case SB_RED_NANSUM: return launch_paths<IO, NanSumOp<A>, A>(plan, st);
     default: return SB_ERR_INVALID_ARGUMENT;
   }
 }

@@ -195,6 +195,9 @@ void check_status_word(c10::DeviceIndex device, cudaStream_t stream) {
   SUPA_CUDA_CHECK(err);
   if (word & SB_STATUS_KERNEL_TIMEOUT)
     TORCH_CHECK(false, "a supa kernel gave up on a bounded wait; its results are invalid");
+  if (word & SB_STATUS_GRADIENT_LOST)
+    TORCH_CHECK(false, "cross_entropy: backward through a retained graph after a backward with a zero upstream gradient, which wiped "
+                       "the stored gradient; run the forward again");
   if (word & SB_STATUS_TARGET_OUT_OF_RANGE) TORCH_CHECK_INDEX(false, "Target is out of bounds.");
 }
 

@@ -2,10 +2,14 @@
 
 Every operator on the path is independent per row, so N GPUs each hold a contiguous block of rows and
 need no communication, with one exception: ``cross_entropy`` with ``mean`` / ``sum`` reduction, which
-all-reduces two scalars, the valid-row count (before the fused sweep, so that gradients are written
+sums two scalars over the ranks, the valid-row count (before the fused sweep, so that gradients are written
 already scaled by 1/|V|) and the loss sum (after it).  The reference would reach BCCL through
-``torch.distributed.all_reduce`` (``torch_supa/csrc/distributed/ProcessGroupBCCL.cpp:3740-3790``); here a
-small NCCL communicator on raw pointers does it, because ProcessGroupNCCL only accepts CUDA tensors.
+``torch.distributed.all_reduce`` (``torch_supa/csrc/distributed/ProcessGroupBCCL.cpp:3740-3790``).  Here the
+bookkeeping kernels of the loss exchange the two values themselves through peer device memory (NVLink stores
+into slot arrays mapped with CUDA IPC; ``csrc/dist/PeerExchange.h``), so no collective launch sits between the
+count, the sweep and the loss; a small NCCL communicator on raw pointers is the route when the arrays cannot
+be mapped (and serves ``all_reduce_`` on supa tensors in general, because ProcessGroupNCCL only accepts CUDA
+tensors).  ``SUPA_B200_LOSS_EXCHANGE=nccl`` forces the NCCL route.
 """
 from __future__ import annotations
 
@@ -38,8 +42,28 @@ def combine_loss(local_loss_sum: float, local_valid_rows: float, reduction: str,
     raise ValueError("combine_loss handles the mean and sum reductions")
 
 
+PEER_MAX_RANKS = 8      # SB_XCHG_MAX_RANKS
+PEER_HANDLE_BYTES = 64  # sizeof(cudaIpcMemHandle_t)
+
+
+def exchange_mode() -> str:
+    """``peer`` (default) or ``nccl``, from SUPA_B200_LOSS_EXCHANGE."""
+    mode = os.environ.get("SUPA_B200_LOSS_EXCHANGE", "peer").strip().lower()
+    if mode not in ("peer", "nccl"):
+        raise ValueError(f"SUPA_B200_LOSS_EXCHANGE must be 'peer' or 'nccl', got {mode!r}")
+    return mode
+
+
+def gather_peer_handles(store, key: str, rank: int, world_size: int, mine: bytes) -> bytes:
+    """Publishes this rank's handle under ``key/rank`` and returns all handles in rank order.  ``store`` is any
+    object with the ``set`` / ``get`` of a torch.distributed store (``get`` blocks until the key exists)."""
+    store.set(f"{key}/{rank}", mine)
+    return b"".join(bytes(store.get(f"{key}/{r}")) for r in range(world_size))
+
+
 class LossComm:
-    """NCCL communicator for supa tensors (one process per GPU)."""
+    """The exchange of a row-sharded loss between supa devices (one process per GPU): an NCCL communicator
+    plus, when the ranks can map each other's memory, the peer-memory slot arrays the loss kernels use."""
 
     def __init__(self, rank: int, world_size: int, device_index: int, unique_id: bytes):
         from . import _check, _load
@@ -49,6 +73,29 @@ class LossComm:
         handle = ctypes.c_int64(0)
         _check(self._host.supa_nccl_init(world_size, unique_id, rank, device_index, ctypes.byref(handle)))
         self.handle = handle.value
+        self.peer_handle = 0
+
+    def enable_peer_exchange(self, store, key: str = "supa_b200/peer") -> bool:
+        """Maps the slot arrays of all ranks (collective: every rank calls it).  Returns False, on every rank,
+        and leaves the NCCL route in place when any rank could not map a peer."""
+        from . import _check
+
+        if self.world_size > PEER_MAX_RANKS:
+            return False
+        handle = ctypes.c_int64(0)
+        _check(self._host.supa_peer_create(self.world_size, self.rank, self.device_index, ctypes.byref(handle)))
+        buf = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+        _check(self._host.supa_peer_export(handle, buf))
+        handles = gather_peer_handles(store, key, self.rank, self.world_size, buf.raw)
+        ok = self._host.supa_peer_open(handle, handles) == 0
+        # agree on the outcome: one rank on the NCCL route and another waiting in a kernel would not meet
+        store.set(f"{key}/ok/{self.rank}", b"1" if ok else b"0")
+        all_ok = all(bytes(store.get(f"{key}/ok/{r}")) == b"1" for r in range(self.world_size))
+        if all_ok:
+            self.peer_handle = handle.value
+        else:
+            self._host.supa_peer_destroy(handle)
+        return all_ok
 
     @staticmethod
     def new_unique_id() -> bytes:
@@ -77,7 +124,10 @@ class LossComm:
         if rank == 0:
             store.set(key, cls.new_unique_id())
         uid = bytes(store.get(key))
-        return cls(rank, world, local, uid)
+        comm = cls(rank, world, local, uid)
+        if world > 1 and exchange_mode() == "peer":
+            comm.enable_peer_exchange(store, key + "/peer")
+        return comm
 
     def all_reduce_(self, tensor: torch.Tensor, op: str = "sum") -> torch.Tensor:
         return torch.ops.supa_b200.all_reduce_(tensor, self.handle, {"sum": 0, "max": 1, "min": 2}[op])
@@ -94,6 +144,9 @@ class LossComm:
         _check(self._host.supa_nccl_abort(ctypes.c_int64(self.handle)))
 
     def close(self) -> None:
+        if self.peer_handle:
+            self._host.supa_peer_destroy(ctypes.c_int64(self.peer_handle))
+            self.peer_handle = 0
         if self.handle:
             self._host.supa_nccl_destroy(ctypes.c_int64(self.handle))
             self.handle = 0
@@ -104,5 +157,7 @@ def sharded_cross_entropy(logits: torch.Tensor, target: torch.Tensor, comm: Loss
     """``F.cross_entropy`` over rows that are sharded across the ranks of ``comm``: every rank passes its own
     row block and receives the global loss; ``loss.backward()`` leaves the local block of the gradient,
     scaled by the global 1/|V| for ``mean``."""
-    handle = comm.handle if (comm is not None and comm.world_size > 1) else 0
-    return torch.ops.supa_b200.sharded_cross_entropy(logits, target, _REDUCTIONS[reduction], ignore_index, label_smoothing, handle)
+    sharded = comm is not None and comm.world_size > 1
+    handle = comm.handle if sharded else 0
+    peer = comm.peer_handle if sharded else 0
+    return torch.ops.supa_b200.sharded_cross_entropy(logits, target, _REDUCTIONS[reduction], ignore_index, label_smoothing, handle, peer)

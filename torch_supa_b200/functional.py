@@ -40,9 +40,9 @@ def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_s
     ``loss`` is a 0-d tensor in the logits' dtype for mean/sum and an fp32 ``[rows]`` tensor for none.
     ``all_reduce``, when given, is called as ``all_reduce(acc_view)`` on a one-element float64 view of the
     device accumulator, first for the valid-row count and then for the loss sum: this is the hook the
-    row-sharded multi-GPU path uses.  ``class_weight`` (fp32 ``[classes]``, only without label smoothing)
-    multiplies each row's loss and gradient by the weight of its target; ``mean`` then divides by the sum of
-    those weights.
+    row-sharded multi-GPU path uses.  ``class_weight`` (fp32 ``[classes]``) multiplies each row's loss and
+    gradient by the weight of its target; ``mean`` then divides by the sum of those weights; with label
+    smoothing the smoothing term weights every class by its own weight, as ``F.cross_entropy`` does.
     """
     assert logits.dim() == 2 and target.dim() == 1 and logits.is_contiguous() and target.is_contiguous()
     rows, classes = logits.shape
@@ -75,6 +75,8 @@ def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_s
     args.grad_scale = grad_scale
     args.status = ws.status.data_ptr()
     args.class_weight = class_weight.data_ptr() if class_weight is not None else None
+    # the count is the launch directly before the sweep: the sweep may start under it
+    args.flags = capi.CE_FLAG_AFTER_COUNT if (red != capi.REDUCTION_NONE and all_reduce is None) else 0
     capi.ce_forward_backward(args, st)
     if red == capi.REDUCTION_NONE:
         return ws.row_loss[:rows], (grad if want_grad else None)
@@ -87,6 +89,76 @@ def cross_entropy_forward_backward(logits, target, *, ignore_index=-100, label_s
         all_reduce(ws.acc[0:1])
         capi.ce_loss_finish(ws.acc, red, loss, code, st)
     return loss, (grad if want_grad else None)
+
+
+def cross_entropy_prob_forward_backward(logits, target, *, label_smoothing=0.0, reduction="mean", want_grad=True, grad_scale=1.0,
+                                        row_grad_out=None, class_weight=None):
+    """Cross entropy with class-probability targets of the logits' shape and dtype: returns ``(loss, grad_logits)``; ``mean``
+    divides by the number of rows."""
+    assert logits.dim() == 2 and target.shape == logits.shape and target.dtype == logits.dtype
+    assert logits.is_contiguous() and target.is_contiguous()
+    rows, classes = logits.shape
+    st = _stream(logits)
+    row_loss = torch.empty(max(rows, 1), dtype=torch.float32, device=logits.device)
+    grad = torch.empty_like(logits) if want_grad else None
+    inv = 1.0 / rows if (reduction == "mean" and rows) else 1.0
+    a = capi.CEProbArgs()
+    a.logits, a.target, a.dtype = logits.data_ptr(), target.data_ptr(), capi.torch_dtype_code(logits.dtype)
+    a.grad_logits = grad.data_ptr() if want_grad else None
+    a.row_loss = row_loss.data_ptr()
+    a.row_grad_out = row_grad_out.data_ptr() if row_grad_out is not None else None
+    a.class_weight = class_weight.data_ptr() if class_weight is not None else None
+    a.rows, a.classes, a.label_smoothing = rows, classes, label_smoothing
+    a.grad_scale, a.loss_scale = grad_scale * inv, inv
+    capi.ce_prob_forward_backward(a, st)
+    if reduction == "none":
+        return row_loss[:rows], grad
+    acc = torch.zeros(2, dtype=torch.float64, device=logits.device)
+    loss = torch.empty((), dtype=logits.dtype, device=logits.device)
+    capi.ce_loss_sum_finish(row_loss, rows, acc, capi.REDUCTION_SUM, loss, capi.torch_dtype_code(logits.dtype), st)
+    return loss, grad
+
+
+def arg_reduce(x, dim, is_max=True, want_values=True):
+    """(values, indices) of the extremum along ``dim`` of a contiguous tensor."""
+    x = x.contiguous()
+    dim %= max(x.dim(), 1)
+    shape = list(x.shape) or [1]
+    outer = 1
+    for s_ in shape[:dim]:
+        outer *= s_
+    inner = 1
+    for s_ in shape[dim + 1:]:
+        inner *= s_
+    out_shape = shape[:dim] + shape[dim + 1:]
+    values = torch.empty(out_shape, dtype=x.dtype, device=x.device) if want_values else None
+    indices = torch.empty(out_shape, dtype=torch.int64, device=x.device)
+    code = capi.torch_dtype_code(x.dtype)
+    need = capi.reduce_ext_scratch_bytes(code, outer, shape[dim], inner, False)
+    scratch = torch.empty(max(need, 1), dtype=torch.uint8, device=x.device)
+    capi.arg_reduce(x, code, outer, shape[dim], inner, is_max, values, indices, scratch if need else None, need, _stream(x))
+    return values, indices
+
+
+def moments(x, dim, correction=1.0, take_sqrt=False):
+    """(variance or standard deviation, mean) along ``dim`` of a contiguous floating tensor."""
+    x = x.contiguous()
+    dim %= max(x.dim(), 1)
+    shape = list(x.shape) or [1]
+    outer = 1
+    for s_ in shape[:dim]:
+        outer *= s_
+    inner = 1
+    for s_ in shape[dim + 1:]:
+        inner *= s_
+    out_shape = shape[:dim] + shape[dim + 1:]
+    out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    mean = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    code = capi.torch_dtype_code(x.dtype)
+    need = capi.reduce_ext_scratch_bytes(code, outer, shape[dim], inner, True)
+    scratch = torch.empty(max(need, 1), dtype=torch.uint8, device=x.device)
+    capi.moments(x, code, outer, shape[dim], inner, correction, take_sqrt, out, mean, scratch if need else None, need, _stream(x))
+    return out, mean
 
 
 def log_softmax(x, dim=-1, out_dtype=None):
