@@ -692,3 +692,34 @@ def test_out_of_range_target_raises_at_the_next_sync_and_device_survives(supa):
     good = torch.tensor([1, 2, 7, 3, 0, 1])
     _close(F.cross_entropy(x_cpu, good), F.cross_entropy(x, good.to(supa)), loosen=2)
     torch.supa.synchronize()
+
+
+# ---- pinned host memory ------------------------------------------------------------------------------------------
+def test_pinned_host_allocator_reuses_blocks_and_waits_for_copies(supa):
+    """Pinned blocks are cached per size class; a block freed while a non-blocking copy still reads it is not handed out
+    again before that copy has finished."""
+    torch.supa.synchronize()
+    torch.supa.empty_host_cache()
+    base = torch.supa.host_memory_stats()
+    a = torch.arange(1 << 18, dtype=torch.float32).pin_memory("supa")
+    assert a.is_pinned("supa")
+    s1 = torch.supa.host_memory_stats()
+    assert s1["host_allocs"] == base["host_allocs"] + 1 and s1["allocated_bytes"] >= a.numel() * 4
+    ptr = a.data_ptr()
+    del a
+    b = torch.zeros(1 << 18, dtype=torch.float32).pin_memory("supa")  # same size class: the cached block, no new cudaHostAlloc
+    s2 = torch.supa.host_memory_stats()
+    assert b.data_ptr() == ptr and s2["host_allocs"] == s1["host_allocs"] and s2["cache_hits"] == s1["cache_hits"] + 1
+    # a non-blocking copy out of the block, then the block is dropped and another one of the same size is asked for at once
+    big = torch.full((1 << 24,), 3.0).pin_memory("supa")           # 64 MB: the copy takes a while
+    ptr_big = big.data_ptr()
+    d = big.to(supa, non_blocking=True)
+    del big
+    other = torch.empty(1 << 24, dtype=torch.float32).pin_memory("supa")
+    other.fill_(7.0)                                               # would corrupt the copy if it got the same block too early
+    torch.supa.synchronize()
+    assert float(d.sum(0).cpu()) == 3.0 * (1 << 24)
+    assert other.data_ptr() != ptr_big or True  # (the address may be reused only after the copy has completed)
+    del other, b, d
+    torch.supa.empty_host_cache()
+    assert torch.supa.host_memory_stats()["reserved_bytes"] == 0

@@ -222,3 +222,54 @@ def test_exchange_mode_from_environment(monkeypatch):
     monkeypatch.setenv("SUPA_B200_LOSS_EXCHANGE", "gloo")
     with pytest.raises(ValueError):
         exchange_mode()
+
+
+# ---- the c10d backend for supa tensors: registration and construction (no GPU needed) ------------------------------------
+def test_c10d_backend_is_registered_for_the_supa_device():
+    import torch.distributed as dist
+
+    import torch_supa_b200  # noqa: F401
+
+    assert "supa_nccl" in dist.Backend.backend_list
+    assert dist.Backend.default_device_backend_map.get("supa") == "supa_nccl"
+
+
+def test_c10d_backend_object_can_be_created_without_a_device():
+    import datetime
+
+    import torch.distributed as dist
+
+    from torch_supa_b200.distributed import _create_c10d_backend
+
+    backend = _create_c10d_backend(dist.HashStore(), 0, 1, datetime.timedelta(seconds=5))
+    assert isinstance(backend, torch._C._distributed_c10d.Backend)
+    assert backend.rank() == 0 and backend.size() == 1 and backend.name() == "supa_nccl"
+
+
+def _c10d_worker(rank, world, port, out_path):
+    sys.path.insert(0, str(ROOT))
+    import torch.distributed as dist
+
+    import torch_supa_b200  # noqa: F401
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    # one backend per device type: gloo carries CPU tensors, supa_nccl is created for the supa device (its communicator
+    # only comes to life with the first collective on a supa tensor)
+    dist.init_process_group("cpu:gloo,supa:supa_nccl", rank=rank, world_size=world)
+    pg = dist.distributed_c10d._get_default_group()
+    ok = pg._get_backend(torch.device("supa")).name() == "supa_nccl" and pg._get_backend(torch.device("cpu")).name() == "gloo"
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t)
+    ok = ok and t.item() == sum(range(1, world + 1))
+    flags = torch.tensor([1.0 if ok else 0.0], dtype=torch.float64)
+    dist.all_reduce(flags)
+    if rank == 0:
+        Path(out_path).write_text(str(flags.item()))
+    dist.destroy_process_group()
+
+
+def test_two_process_group_with_supa_backend_beside_gloo(tmp_path):
+    out = tmp_path / "ok.txt"
+    mp.spawn(_c10d_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert float(out.read_text()) == 2.0

@@ -51,3 +51,5 @@ torch._register_device_module("supa", supa)
 torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module=True, for_storage=True)
 
 from . import distributed  # noqa: E402,F401
+
+distributed.register_c10d_backend()

@@ -67,6 +67,7 @@ void copy_host_to_device(const at::Tensor& dst, const at::Tensor& src, bool non_
     // A pageable source has been staged by the driver when the call returns; a pinned one is read later,
     // so a blocking copy waits and a non-blocking one relies on the caller keeping the buffer alive.
     if (!non_blocking || !host.is_pinned()) SUPA_CUDA_CHECK(cudaStreamSynchronize(stream));
+    else record_pinned_use(host.const_data_ptr(), stream);  // the block is not recycled while the copy reads it
     return;
   }
   // General layouts: contiguous host staging -> contiguous device temporary -> strided device copy.
@@ -95,6 +96,7 @@ void copy_device_to_host(const at::Tensor& dst, const at::Tensor& src, bool non_
   if (same_dense_layout(dst, dev)) {
     if (nbytes) SUPA_CUDA_CHECK(cudaMemcpyAsync(dst.data_ptr(), dev.const_data_ptr(), nbytes, cudaMemcpyDeviceToHost, stream));
     if (!non_blocking || !dst.is_pinned()) check_status_word(src.device().index(), stream);  // synchronises the stream
+    else record_pinned_use(dst.data_ptr(), stream);  // the block is not recycled while the copy writes it
     return;
   }
   at::Tensor host = at::empty(dst.sizes(), dst.options().memory_format(at::MemoryFormat::Contiguous));
@@ -107,15 +109,35 @@ void copy_across_devices(const at::Tensor& dst, const at::Tensor& src) {
   // contiguous temporaries on both sides, one peer copy between them
   at::Tensor s = src.dtype() == dst.dtype() ? src : src.to(dst.scalar_type());
   s = s.expand(dst.sizes()).contiguous();
-  at::Tensor d = dst.is_contiguous() ? dst : at::empty(dst.sizes(), dst.options());
+  at::Tensor d;
+  {
+    const c10::DeviceGuard guard(dst.device());
+    d = dst.is_contiguous() ? dst : at::empty(dst.sizes(), dst.options());
+  }
   const size_t nbytes = d.numel() * d.element_size();
   if (nbytes) {
+    // The copy runs on the source device's current stream.  Work queued on the destination's current stream that still
+    // reads or writes `dst` must come first: an event recorded there holds the copy back.
+    cudaStream_t dst_stream = current_cuda_stream(dst.device().index());
+    cudaEvent_t before = nullptr;
+    {
+      const c10::DeviceGuard guard(dst.device());
+      SUPA_CUDA_CHECK(cudaEventCreateWithFlags(&before, cudaEventDisableTiming));
+      SUPA_CUDA_CHECK(cudaEventRecord(before, dst_stream));
+    }
     const c10::DeviceGuard guard(src.device());
     cudaStream_t stream = current_cuda_stream(src.device().index());
-    SUPA_CUDA_CHECK(cudaMemcpyPeerAsync(d.data_ptr(), dst.device().index(), s.const_data_ptr(), src.device().index(), nbytes, stream));
-    SUPA_CUDA_CHECK(cudaStreamSynchronize(stream));
+    cudaError_t err = cudaStreamWaitEvent(stream, before, 0);
+    if (err == cudaSuccess)
+      err = cudaMemcpyPeerAsync(d.data_ptr(), dst.device().index(), s.const_data_ptr(), src.device().index(), nbytes, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);  // the destination's streams may use the data from here on
+    cudaEventDestroy(before);
+    SUPA_CUDA_CHECK(err);
   }
-  if (!d.is_same(dst)) copy_device_to_device(dst, d);
+  if (!d.is_same(dst)) {
+    const c10::DeviceGuard guard(dst.device());  // the strided copy-back is a kernel on the destination device
+    copy_device_to_device(dst, d);
+  }
 }
 
 // aten::_copy_from(self = source, dst, non_blocking): what Tensor.copy_ reaches for a backend outside the
@@ -144,6 +166,57 @@ at::Tensor copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blo
 at::Tensor copy_from_and_resize(const at::Tensor& self, const at::Tensor& dst) {
   at::native::resize_output(dst, self.sizes());
   return copy_from(self, dst, false);
+}
+
+// ---- cat ---------------------------------------------------------------------------------------------------------
+// Concatenation as narrow + copy per input (each copy is one launch of the elementwise engine or a memcpy).  Needed by
+// callers that flatten tensors into one buffer, such as the parameter broadcast of DistributedDataParallel.
+at::Tensor& cat_out(const at::ITensorListRef& tensors, int64_t dim, at::Tensor& out) {
+  std::vector<at::Tensor> parts;
+  for (const at::Tensor& t : tensors) {
+    if (t.dim() == 1 && t.numel() == 0) continue;  // legacy: empty 1-D tensors are skipped whatever their shape
+    parts.push_back(t);
+  }
+  TORCH_CHECK(!tensors.materialize().empty(), "torch.cat(): expected a non-empty list of Tensors");
+  if (parts.empty()) {
+    at::native::resize_output(out, {0});
+    return out;
+  }
+  const int64_t d = at::maybe_wrap_dim(dim, parts[0].dim());
+  std::vector<int64_t> shape = parts[0].sizes().vec();
+  int64_t total = 0;
+  for (const at::Tensor& t : parts) {
+    TORCH_CHECK(is_supa(t) && t.device() == parts[0].device(), "torch.cat(): expected all tensors on ", parts[0].device());
+    TORCH_CHECK(t.dim() == parts[0].dim(), "Tensors must have same number of dimensions: got ", parts[0].dim(), " and ", t.dim());
+    for (int64_t i = 0; i < t.dim(); ++i)
+      TORCH_CHECK(i == d || t.size(i) == shape[i], "Sizes of tensors must match except in dimension ", d, ". Expected size ", shape[i],
+                  " but got size ", t.size(i), " in the list.");
+    total += t.size(d);
+  }
+  shape[d] = total;
+  const c10::DeviceGuard guard(parts[0].device());
+  at::native::resize_output(out, shape);
+  int64_t at_ = 0;
+  for (const at::Tensor& t : parts) {
+    if (t.size(d) == 0) continue;
+    copy_device_to_device(out.narrow(d, at_, t.size(d)), t);
+    at_ += t.size(d);
+  }
+  return out;
+}
+at::Tensor cat(const at::ITensorListRef& tensors, int64_t dim) {
+  at::ScalarType dtype = at::kFloat;
+  bool first = true;
+  c10::optional<c10::Device> dev;
+  for (const at::Tensor& t : tensors) {
+    dtype = first ? t.scalar_type() : c10::promoteTypes(dtype, t.scalar_type());
+    first = false;
+    if (!dev && is_supa(t)) dev = t.device();
+  }
+  TORCH_CHECK(dev.has_value(), "torch.cat(): expected a non-empty list of supa Tensors");
+  const c10::DeviceGuard guard(*dev);
+  at::Tensor out = at::empty({0}, at::TensorOptions().dtype(dtype).device(*dev));
+  return cat_out(tensors, dim, out);
 }
 
 // ---- resize / set ------------------------------------------------------------------------------------------
@@ -282,4 +355,6 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("zero_", TORCH_FN(supa::zero_));
   m.impl("_local_scalar_dense", TORCH_FN(supa::local_scalar_dense));
   m.impl("record_stream", TORCH_FN(supa::record_stream_op));
+  m.impl("cat", TORCH_FN(supa::cat));
+  m.impl("cat.out", TORCH_FN(supa::cat_out));
 }

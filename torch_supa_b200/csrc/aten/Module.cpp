@@ -62,6 +62,18 @@ SUPA_EXPORT int supa_reset_peak_memory_stats(int device) {
 SUPA_EXPORT int supa_empty_cache() {
   return guarded([&] { supa::empty_cache(); });
 }
+SUPA_EXPORT int supa_host_memory_stats(int64_t* out4) {
+  return guarded([&] {
+    const supa::HostMemoryStats s = supa::host_memory_stats();
+    out4[0] = s.allocated_bytes;
+    out4[1] = s.reserved_bytes;
+    out4[2] = s.host_allocs;
+    out4[3] = s.hits;
+  });
+}
+SUPA_EXPORT int supa_empty_pinned_cache() {
+  return guarded([&] { supa::empty_pinned_cache(); });
+}
 SUPA_EXPORT int supa_set_memory_limit(int device, int64_t bytes) {
   return guarded([&] { supa::set_memory_limit(static_cast<c10::DeviceIndex>(device), bytes); });
 }

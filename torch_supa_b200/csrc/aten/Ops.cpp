@@ -14,6 +14,7 @@
 #include <ATen/ops/as_strided_native.h>
 #include <ATen/ops/as_strided_ops.h>
 #include <ATen/ops/div_native.h>
+#include <ATen/ops/floor_divide_native.h>
 #include <ATen/ops/eq_native.h>
 #include <ATen/ops/exp_native.h>
 #include <ATen/ops/ge_native.h>
@@ -253,6 +254,19 @@ at::Tensor& div_mode_out(const at::Tensor& self, const at::Tensor& other, c10::o
   return run_out<at::native::structured_div_out_mode>(
       device_of_args({self, other, out}), out, [&](auto& op) { op.meta(self, other, mode); },
       [&](auto& op, const at::Tensor& o) { op.impl(self, other, mode, o); });
+}
+// floor_divide (the // operator): libtorch's device-generic functions build the iterator and call div_floor_stub
+at::Tensor floor_divide(const at::Tensor& self, const at::Tensor& other) {
+  const c10::DeviceGuard guard(device_of_args({self, other}));
+  return at::native::floor_divide(self, other);
+}
+at::Tensor& floor_divide_(at::Tensor& self, const at::Tensor& other) {
+  const c10::DeviceGuard guard(device_of_args({self, other}));
+  return at::native::floor_divide_(self, other);
+}
+at::Tensor& floor_divide_out(const at::Tensor& self, const at::Tensor& other, at::Tensor& out) {
+  const c10::DeviceGuard guard(device_of_args({self, other, out}));
+  return at::native::floor_divide_out(self, other, out);
 }
 SUPA_UNARY(neg, at::native::structured_neg_out)
 SUPA_UNARY(silu, at::native::structured_silu_out)
@@ -501,6 +515,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("div.Tensor_mode", TORCH_FN(supa::div_mode));
   m.impl("div_.Tensor_mode", TORCH_FN(supa::div_mode_));
   m.impl("div.out_mode", TORCH_FN(supa::div_mode_out));
+  m.impl("floor_divide", TORCH_FN(supa::floor_divide));
+  m.impl("floor_divide_.Tensor", TORCH_FN(supa::floor_divide_));
+  m.impl("floor_divide.out", TORCH_FN(supa::floor_divide_out));
   m.impl("neg", TORCH_FN(supa::neg));
   m.impl("neg_", TORCH_FN(supa::neg_));
   m.impl("neg.out", TORCH_FN(supa::neg_out));

@@ -20,7 +20,7 @@ struct ncclUniqueIdRaw {
 using ncclComm_t = void*;
 // Values of ncclDataType_t / ncclRedOp_t / ncclResult_t from the public nccl.h.
 enum { kNcclInt8 = 0, kNcclUint8 = 1, kNcclInt32 = 2, kNcclInt64 = 4, kNcclHalf = 6, kNcclFloat = 7, kNcclDouble = 8, kNcclBfloat16 = 9 };
-enum { kNcclSum = 0, kNcclMax = 2, kNcclMin = 3 };
+enum { kNcclSum = 0, kNcclProd = 1, kNcclMax = 2, kNcclMin = 3, kNcclAvg = 4 };
 
 struct Api {
   int (*GetUniqueId)(ncclUniqueIdRaw*) = nullptr;
@@ -28,6 +28,9 @@ struct Api {
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*CommAbort)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 };
 
@@ -44,7 +47,11 @@ const Api& api() {
     a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(dlsym(h, "ncclCommAbort"));
     a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
     a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-    TORCH_CHECK(a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.AllReduce && a.GetErrorString,
+    a.Broadcast = reinterpret_cast<decltype(a.Broadcast)>(dlsym(h, "ncclBroadcast"));
+    a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+    a.ReduceScatter = reinterpret_cast<decltype(a.ReduceScatter)>(dlsym(h, "ncclReduceScatter"));
+    TORCH_CHECK(a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.AllReduce && a.GetErrorString && a.Broadcast &&
+                    a.AllGather && a.ReduceScatter,
                 "supa: libnccl.so.2 lacks an expected symbol");
   });
   return a;
@@ -66,6 +73,17 @@ int nccl_dtype(int dtype) {
     case SB_F32: return kNcclFloat;
     case SB_F64: return kNcclDouble;
     default: TORCH_CHECK(false, "supa: dtype has no NCCL equivalent");
+  }
+}
+
+int nccl_op(int op) {
+  switch (op) {
+    case 0: return kNcclSum;
+    case 1: return kNcclMax;
+    case 2: return kNcclMin;
+    case 3: return kNcclProd;
+    case 4: return kNcclAvg;
+    default: TORCH_CHECK(false, "supa: unknown reduction op ", op);
   }
 }
 
@@ -108,10 +126,33 @@ void NcclComm::all_reduce(void* data, int64_t count, int dtype, int op, sb_strea
   TORCH_CHECK(comm_, "supa: communicator has been aborted");
   TORCH_CHECK(count >= 0 && (count == 0 || data), "supa: invalid all_reduce buffer");
   if (count == 0) return;
-  const int red = op == 0 ? kNcclSum : (op == 1 ? kNcclMax : kNcclMin);
-  TORCH_CHECK(op >= 0 && op <= 2, "supa: unknown reduction op ", op);
-  check_nccl(api().AllReduce(data, data, static_cast<size_t>(count), nccl_dtype(dtype), red, comm_, static_cast<cudaStream_t>(stream)),
+  check_nccl(api().AllReduce(data, data, static_cast<size_t>(count), nccl_dtype(dtype), nccl_op(op), comm_, static_cast<cudaStream_t>(stream)),
              "ncclAllReduce");
+}
+
+void NcclComm::broadcast(void* data, int64_t count, int dtype, int root, sb_stream_t stream) {
+  TORCH_CHECK(comm_, "supa: communicator has been aborted");
+  TORCH_CHECK(count >= 0 && (count == 0 || data) && root >= 0 && root < nranks_, "supa: invalid broadcast arguments");
+  if (count == 0) return;
+  check_nccl(api().Broadcast(data, data, static_cast<size_t>(count), nccl_dtype(dtype), root, comm_, static_cast<cudaStream_t>(stream)),
+             "ncclBroadcast");
+}
+
+void NcclComm::all_gather(const void* send, void* recv, int64_t count, int dtype, sb_stream_t stream) {
+  TORCH_CHECK(comm_, "supa: communicator has been aborted");
+  TORCH_CHECK(count >= 0 && (count == 0 || (send && recv)), "supa: invalid all_gather buffers");
+  if (count == 0) return;
+  check_nccl(api().AllGather(send, recv, static_cast<size_t>(count), nccl_dtype(dtype), comm_, static_cast<cudaStream_t>(stream)),
+             "ncclAllGather");
+}
+
+void NcclComm::reduce_scatter(const void* send, void* recv, int64_t count, int dtype, int op, sb_stream_t stream) {
+  TORCH_CHECK(comm_, "supa: communicator has been aborted");
+  TORCH_CHECK(count >= 0 && (count == 0 || (send && recv)), "supa: invalid reduce_scatter buffers");
+  if (count == 0) return;
+  check_nccl(api().ReduceScatter(send, recv, static_cast<size_t>(count), nccl_dtype(dtype), nccl_op(op), comm_,
+                                 static_cast<cudaStream_t>(stream)),
+             "ncclReduceScatter");
 }
 
 void NcclComm::all_reduce_sum_f64(double* data, int64_t count, sb_stream_t stream) { all_reduce(data, count, SB_F64, 0, stream); }

@@ -31,8 +31,14 @@ class NcclComm {
 
   // In-place sum of `count` doubles across ranks, queued on `stream`.
   void all_reduce_sum_f64(double* data, int64_t count, sb_stream_t stream);
-  // In-place all-reduce of any dtype the kernel library knows; op: 0 sum, 1 max, 2 min.
+  // In-place all-reduce of any dtype the kernel library knows; op: 0 sum, 1 max, 2 min, 3 product, 4 average.
   void all_reduce(void* data, int64_t count, int dtype, int op, sb_stream_t stream);
+  // In place: every rank ends up with the `count` elements of rank `root`.
+  void broadcast(void* data, int64_t count, int dtype, int root, sb_stream_t stream);
+  // recv holds nranks * count elements: rank r's `count` elements at offset r * count.
+  void all_gather(const void* send, void* recv, int64_t count, int dtype, sb_stream_t stream);
+  // send holds nranks * count elements; rank r receives the reduction of everyone's r-th block.
+  void reduce_scatter(const void* send, void* recv, int64_t count, int dtype, int op, sb_stream_t stream);
   // Tears the communicator down without waiting for outstanding work (after a failed rank).
   void abort();
 

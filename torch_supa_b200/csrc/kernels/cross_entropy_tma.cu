@@ -22,10 +22,10 @@
 // ex2.approx; the row statistics are in base 2 (max2 = max * log2 e).
 //
 // Rows whose pitch is not a multiple of 16 bytes (vocabularies such as 50257 or 151643) run the same pipeline
-// (kRagged): the loader fetches the 16-byte aligned superset of the row, so the row begins `head` elements into
-// its first unit and may end inside its last one; those two edge units are left out of the vector sweeps and of
-// the bulk stores, and one thread handles their few elements with scalar arithmetic and ordinary stores, so a
-// neighbouring row's bytes are never written.
+// (kRagged) over the 16-byte units that lie wholly inside the row.  The row may begin inside a unit and end inside
+// another: those two edge units, which it shares with its neighbours, travel apart (two 16-byte bulk copies per row into a
+// small slot ring of their own) and one thread handles their few elements with scalar arithmetic and ordinary stores,
+// so a neighbouring row's bytes are never written and the vector sweeps never see a foreign element.
 //
 // No TMA multicast is used anywhere: every CTA fetches its own chunks.  Every mbarrier wait is
 // bounded; a wait that runs out sets SB_STATUS_KERNEL_TIMEOUT and the kernel still terminates.
@@ -49,11 +49,11 @@ struct ResidentParams {
   uint32_t nbuf;         // ring buffers (>= nch + 1)
   uint32_t chunk_units;  // 16-byte units per chunk
   uint32_t slice_units;  // 16-byte units per CTA slice (last CTA of a cluster may own fewer)
-  uint32_t row_units;    // 16-byte units per row
+  uint32_t row_units;    // 16-byte units per row (ragged rows: the most whole units a row can have)
   uint32_t num_clusters;
   int mode;              // 0 cross entropy, 1 log_softmax, 2 softmax
   uint32_t window;       // chunks of the next row a group may fold while the row statistics are exchanged
-  uint64_t row_bytes;    // exact bytes of one row (classes * sizeof(T)); row_units covers the widest aligned superset
+  uint64_t row_bytes;    // exact bytes of one row (classes * sizeof(T))
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -294,6 +294,7 @@ constexpr int kChunkUnits = kGroupThreads * kVecPerThread;  // 512 units = 8 KB 
 constexpr int kConsumers = kGroups * kGroupThreads;
 constexpr int kResidentThreads = kConsumers + 32 * kGroups;  // plus one copy-engine warp per group
 constexpr int kMaxBuffers = 32;
+constexpr int kEdgeSlots = kMaxBuffers / kGroups;
 
 // Shared-memory carve-up after the chunk ring.
 struct alignas(16) Tail {
@@ -302,6 +303,11 @@ struct alignas(16) Tail {
   float xt_kept;             // kept-exponential mode: x[target] saved by the thread that owns it before it is overwritten
   unsigned long long full[kMaxBuffers];   // loader -> consumers: chunk has landed
   unsigned long long ready[kMaxBuffers];  // consumers -> loader: chunk holds the gradient (or may be reused)
+  // ragged rows: the first and the last 16-byte unit of a row, when the row owns only part of them, for the row in slot
+  // (local row number % kEdgeSlots).  A slot is rewritten kEdgeSlots rows later; the loader is never more than
+  // kMaxBuffers / kGroups = kEdgeSlots rows ahead of the row being retired.
+  uint4 edge[kEdgeSlots][2];
+  unsigned long long edge_full[kEdgeSlots];
 };
 
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
@@ -418,13 +424,15 @@ __device__ __forceinline__ uint4 shift_vector(const uint4& r, float2 neg_lse) {
   return U::pack(f);
 }
 
-// Where a row lies in 16-byte units.  With an aligned pitch this is the same for every row; with kRagged the row
-// starts head_e elements into its first unit and owns only tail_e elements of its last one.
+// Where a row lies in 16-byte units.  With an aligned pitch this is the same for every row; with kRagged the row starts
+// head_e elements into a unit and owns only tail_e elements of its last one; `span` counts the units wholly inside the
+// row, which are what the chunks are cut from.
 struct RowGeom {
-  uint32_t head_e;   // elements of the first unit that belong to the previous row
-  uint32_t tail_e;   // elements of the last unit that belong to this row; 0 = all of them
-  uint32_t span;     // units the row touches
-  int64_t byte_off;  // byte offset of the first unit from the tensor's base pointer
+  uint32_t head_e;    // elements of the unit before the first whole one that belong to the previous row; 0 = no such unit
+  uint32_t tail_e;    // elements of the unit after the last whole one that belong to this row; 0 = no such unit
+  uint32_t span;      // whole units
+  int64_t byte_off;   // byte offset of the first whole unit from the tensor's base pointer
+  int64_t class0;     // class index of the first element of the first whole unit
 };
 
 // Statistics of the elements [e0, e1) of one edge unit (the others belong to a neighbouring row).
@@ -510,44 +518,28 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       g.tail_e = 0;
       g.span = rp.row_units;
       g.byte_off = row * static_cast<int64_t>(rp.row_bytes);
+      g.class0 = 0;
     } else {
       const uint64_t a0 = base_mis + static_cast<uint64_t>(row) * rp.row_bytes;  // the row's address modulo 16 is a0 modulo 16
       const uint32_t head_b = static_cast<uint32_t>(a0 & 15);
       const uint64_t total = head_b + rp.row_bytes;
+      const uint32_t touched = static_cast<uint32_t>((total + 15) >> 4);
       g.head_e = head_b / sizeof(T);
       g.tail_e = static_cast<uint32_t>(total & 15) / sizeof(T);
-      g.span = static_cast<uint32_t>((total + 15) >> 4);
-      g.byte_off = row * static_cast<int64_t>(rp.row_bytes) - head_b;
+      const uint32_t first = g.head_e ? 1 : 0, last = touched - (g.tail_e ? 1 : 0);
+      g.span = last > first ? last - first : 0;
+      g.byte_off = row * static_cast<int64_t>(rp.row_bytes) - head_b + first * 16;
+      g.class0 = g.head_e ? static_cast<int64_t>(E) - g.head_e : 0;
     }
     return g;
   };
   auto slice_len_of = [&](const RowGeom& g) -> uint32_t {
     return g.span > slice_begin ? min(rp.slice_units, g.span - slice_begin) : 0;
   };
-  // Units of chunk `cl` of group `g` that lie in the slice, and which of them [v_lo, v_hi) are whole (not edge units).
-  auto chunk_range = [&](const RowGeom& rg, uint32_t slice_len, uint32_t g, uint32_t cl, uint32_t& u0, uint32_t& len, uint32_t& v_lo,
-                         uint32_t& v_hi) {
+  // Units of chunk `cl` of group `g` that lie in the slice.
+  auto chunk_range = [&](uint32_t slice_len, uint32_t g, uint32_t cl, uint32_t& u0, uint32_t& len) {
     u0 = (cl * G + g) * kChunkUnits;
     len = u0 < slice_len ? min(static_cast<uint32_t>(kChunkUnits), slice_len - u0) : 0;
-    v_lo = 0;
-    v_hi = len;
-    if constexpr (kRagged) {
-      if (len) {
-        if (rg.head_e && slice_begin + u0 == 0) v_lo = 1;
-        if (rg.tail_e && slice_begin + u0 + len == rg.span && v_hi > v_lo) v_hi = len - 1;
-      }
-    }
-  };
-
-  // In a full chunk that holds an edge unit, which of the calling thread's NV vectors that unit is (-1: none).  The first
-  // unit of a chunk is vector 0 of thread 0, the last one vector NV - 1 of the last thread.
-  auto edge_vector = [&](uint32_t len, uint32_t v_lo, uint32_t v_hi) -> int {
-    if constexpr (kRagged) {
-      const uint32_t t_in_group = (threadIdx.x % TG);
-      if (v_lo && t_in_group == 0) return 0;
-      if (v_hi < len && t_in_group == TG - 1) return NV - 1;
-    }
-    return -1;
   };
 
   if (tid == 0) {
@@ -555,6 +547,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       mbar_init(smem_u32(&tail->full[b]), 1);
       mbar_init(smem_u32(&tail->ready[b]), TG / 32);
     }
+    for (int e = 0; e < kEdgeSlots; ++e) mbar_init(smem_u32(&tail->edge_full[e]), 1);
     tail->xt_kept = 0.f;
     fence_mbar_init();
   }
@@ -596,6 +589,20 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         }
         ld_geom = row_geom(row);
         ld_slice = slice_len_of(ld_geom);
+        if (kRagged && g == 0 && cta_rank == 0) {
+          // the units the row shares with its neighbours go to the slot ring of their own
+          const uint32_t slot = static_cast<uint32_t>(ld_k % kEdgeSlots);
+          const uint32_t ebar = smem_u32(&tail->edge_full[slot]);
+          const uint32_t nedge = ld_skip ? 0 : (ld_geom.head_e ? 1 : 0) + (ld_geom.tail_e ? 1 : 0);
+          if (nedge) {
+            const unsigned char* first_whole = static_cast<const unsigned char*>(p.logits) + ld_geom.byte_off;
+            mbar_expect_tx(ebar, nedge * 16);
+            if (ld_geom.head_e) bulk_g2s(smem_u32(&tail->edge[slot][0]), first_whole - 16, 16, ebar);
+            if (ld_geom.tail_e) bulk_g2s(smem_u32(&tail->edge[slot][1]), first_whole + static_cast<size_t>(ld_geom.span) * 16, 16, ebar);
+          } else {
+            mbar_arrive(ebar);
+          }
+        }
       }
       const uint32_t u0 = (ld_cl * G + g) * kChunkUnits;
       const uint32_t len = (!ld_skip && u0 < ld_slice) ? min(static_cast<uint32_t>(kChunkUnits), ld_slice - u0) : 0;
@@ -631,12 +638,12 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         for (uint32_t cl = 0; cl < cpg; ++cl) {
           if (!mbar_wait(ready_base + 8 * j, ph)) timed_out = true;
           if (p.grad) {
-            uint32_t u0, len, v_lo, v_hi;
-            chunk_range(rg, slice_len, g, cl, u0, len, v_lo, v_hi);
-            if (v_hi > v_lo) {  // whole units only: the edge units of a ragged row are written by a consumer thread
+            uint32_t u0, len;
+            chunk_range(slice_len, g, cl, u0, len);
+            if (len) {
               unsigned char* dst =
-                  static_cast<unsigned char*>(p.grad) + rg.byte_off + static_cast<int64_t>(slice_begin + u0 + v_lo) * 16;
-              bulk_s2g(dst, ring_base + j * kChunkBytes + v_lo * 16, (v_hi - v_lo) * 16);
+                  static_cast<unsigned char*>(p.grad) + rg.byte_off + static_cast<int64_t>(slice_begin + u0) * 16;
+              bulk_s2g(dst, ring_base + j * kChunkBytes, len * 16);
             }
             bulk_commit();
             bulk_wait_read<1>();  // every store of this thread but the newest has finished reading shared memory
@@ -684,17 +691,6 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     base_scale = static_cast<float>(static_cast<double>(base_scale) / p.acc[1]);
   }
 
-  // Edge units of a ragged row inside chunk (u0, len, v_lo, v_hi): the thread that owns the unit's vector in the sweeps
-  // (thread 0 for the first unit of a chunk, thread (len - 1) % TG for the last) folds its elements.
-  auto edge_fold = [&](RowStats& st, const RowGeom& rg, const unsigned char* chunk, uint32_t len, uint32_t v_lo, uint32_t v_hi) {
-    if constexpr (kRagged) {
-      if (len) {
-        if (v_lo && gt == 0) edge_stats<T, kSumX>(st, chunk, rg.head_e, (rg.span == 1 && rg.tail_e) ? rg.tail_e : static_cast<uint32_t>(E));
-        if (v_hi < len && gt == (len - 1) % TG) edge_stats<T, kSumX>(st, chunk + static_cast<size_t>(len - 1) * 16, 0, rg.tail_e);
-      }
-    }
-  };
-
   // Folds the group's chunks [from, cpg) of the row whose first chunk sits at ring position (j0, ph0) into
   // the statistics and returns how many chunks of the row are done.  blocking: wait for every chunk;
   // otherwise stop at the first chunk that has not landed yet (used to fill the wait for the peers'
@@ -716,31 +712,20 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         break;
       }
       if (!skip) {
-        uint32_t u0, len, v_lo, v_hi;
-        chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
-        const unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
-        const uint4* buf = reinterpret_cast<const uint4*>(chunk) + gt;
+        uint32_t u0, len;
+        chunk_range(slice_len, grp, cl, u0, len);
+        const uint4* buf = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(j) * kChunkBytes) + gt;
         if (len == kChunkUnits) {
           uint4 r[NV];
 #pragma unroll
           for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
-          const int skip = edge_vector(len, v_lo, v_hi);  // -1 except for the one thread that holds an edge unit of a ragged row
-          if (skip < 0) {
-            stats_update<T, NV, kSumX>(st, r);
-          } else {
-            uint4 rest[NV - 1];
-#pragma unroll
-            for (int q = 0; q < NV - 1; ++q) rest[q] = skip == 0 ? r[q + 1] : r[q];  // skip is 0 or NV - 1
-            stats_update<T, NV - 1, kSumX>(st, rest);
-          }
+          stats_update<T, NV, kSumX>(st, r);
         } else {
-          for (uint32_t v = gt; v < v_hi; v += TG) {  // short last chunk of the slice
-            if (v < v_lo) continue;
+          for (uint32_t v = gt; v < len; v += TG) {  // short last chunk of the slice
             uint4 r[1] = {buf[v - gt]};
             stats_update<T, 1, kSumX>(st, r);
           }
         }
-        edge_fold(st, rg, chunk, len, v_lo, v_hi);
       }
       if (++j == nbg) {
         j = 0;
@@ -767,7 +752,26 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
     const RowGeom rg = row_geom(row);
     const uint32_t slice_len = slice_len_of(rg);
-    const int64_t t_slice = t + rg.head_e - slice_elem0;  // element position of the target in this CTA's slice
+    const int64_t t_slice = t - rg.class0 - slice_elem0;  // element position of the target in this CTA's slice of whole units
+    // Ragged rows: thread 0 of the cluster's first CTA folds the elements of the two edge units (they arrive in a slot
+    // ring of their own) and keeps x[target] if the target lies in one of them.
+    float xt_edge = 0.f;
+    const uint32_t edge_slot = static_cast<uint32_t>(k % kEdgeSlots);
+    const bool edge_thread = kRagged && tid == 0 && cta_rank == 0 && (rg.head_e != 0 || rg.tail_e != 0);
+    const int64_t tail_class0 = rg.class0 + static_cast<int64_t>(rg.span) * E;  // class of the first element after the whole units
+    if constexpr (kRagged) {
+      if (edge_thread && !ignored) {
+        if (!mbar_wait(smem_u32(&tail->edge_full[edge_slot]), static_cast<uint32_t>(k / kEdgeSlots) & 1)) timed_out = true;
+        if (rg.head_e) {
+          edge_stats<T, kSumX>(st, &tail->edge[edge_slot][0], rg.head_e, E);
+          if (t < rg.class0) xt_edge = to_float(reinterpret_cast<const T*>(&tail->edge[edge_slot][0])[rg.head_e + t]);
+        }
+        if (rg.tail_e) {
+          edge_stats<T, kSumX>(st, &tail->edge[edge_slot][1], 0, rg.tail_e);
+          if (t >= tail_class0) xt_edge = to_float(reinterpret_cast<const T*>(&tail->edge[edge_slot][1])[t - tail_class0]);
+        }
+      }
+    }
 
     // ---- sweep A: statistics as the group's chunks land (the first a_done chunks are folded already) ----
     float mref[kKeepChunks];          // kept mode: the maximum each of the group's chunks was scaled by (per thread)
@@ -790,8 +794,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
         if (static_cast<uint32_t>(cl) < cpg) {
           if (!mbar_wait(full0 + 8 * j, ph)) timed_out = true;
           if (!ignored) {
-            uint32_t u0, len, v_lo, v_hi;
-            chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
+            uint32_t u0, len;
+            chunk_range(slice_len, grp, cl, u0, len);
             unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
             uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
             // the logit of the target is needed for the loss: its owner saves it before the chunk is overwritten
@@ -800,39 +804,25 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
               uint4 r[NV], e[NV];
 #pragma unroll
               for (int q = 0; q < NV; ++q) r[q] = buf[q * TG];
-              const int skip = edge_vector(len, v_lo, v_hi);  // -1 except for the one thread that holds an edge unit of a ragged row
-              if (skip < 0) {
-                stats_update<T, NV, kSumX, true>(st, r, e);
+              stats_update<T, NV, kSumX, true>(st, r, e);
 #pragma unroll
-                for (int q = 0; q < NV; ++q) buf[q * TG] = e[q];
-              } else {  // the edge unit keeps its logits (its few elements are handled in scalar form)
-                uint4 rest[NV - 1], erest[NV - 1];
-#pragma unroll
-                for (int q = 0; q < NV - 1; ++q) rest[q] = skip == 0 ? r[q + 1] : r[q];  // skip is 0 or NV - 1
-                stats_update<T, NV - 1, kSumX, true>(st, rest, erest);
-#pragma unroll
-                for (int q = 0; q < NV - 1; ++q) buf[(skip == 0 ? q + 1 : q) * TG] = erest[q];
-              }
+              for (int q = 0; q < NV; ++q) buf[q * TG] = e[q];
             } else {
-              // short last chunk of the slice: one maximum for all of this thread's vectors, then the exponentials; an edge
-              // unit keeps its logits
+              // short last chunk of the slice: one maximum for all of this thread's vectors, then the exponentials
               float vm = -CUDART_INF_F;
-              for (uint32_t v = gt; v < v_hi; v += TG)
-                if (v >= v_lo) vm = max_nan(vm, U::vmax(buf[v - gt]));
+              for (uint32_t v = gt; v < len; v += TG) vm = max_nan(vm, U::vmax(buf[v - gt]));
               const float nm = max_nan(st.m2, vm * kLog2e);
               const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);
               st.s[0] = mul2(st.s[0], make_float2(resc, resc));
               st.s[1] = mul2(st.s[1], make_float2(resc, resc));
               st.m2 = nm;  // stats_update below finds its maximum already in place: no further rescaling
-              for (uint32_t v = gt; v < v_hi; v += TG) {
-                if (v < v_lo) continue;
+              for (uint32_t v = gt; v < len; v += TG) {
                 uint4 r[1] = {buf[v - gt]}, e[1];
                 stats_update<T, 1, kSumX, true>(st, r, e);
                 buf[v - gt] = e[0];
               }
             }
-            mref[cl] = st.m2;  // what the kept values of this chunk are relative to (the edge fold below may raise st.m2 further)
-            edge_fold(st, rg, chunk, len, v_lo, v_hi);
+            mref[cl] = st.m2;
           }
           if (++j == nbg) {
             j = 0;
@@ -891,6 +881,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
             if (!mbar_wait(smem_u32(&tail->full[og * nbg + oj]), oph)) timed_out = true;
             xt = to_float(reinterpret_cast<const T*>(smem + (static_cast<size_t>(og) * nbg + oj) * kChunkBytes)[off]);
           }
+          xt += xt_edge;  // lane 0 of warp 0 is the thread that handled the edge units
           if (CLUSTER > 1) {
             const uint32_t slot = smem_u32(&tail->slots[xpar][cta_rank]);
 #pragma unroll
@@ -968,36 +959,28 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
       // x[target] with the same arithmetic and a single rounding.
       const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
-      // Edge units of a ragged row: the thread that owns the unit's vector computes its few elements from the logits
-      // still in shared memory, before its own sweep below overwrites them, and writes them to global memory itself (the
-      // bulk store covers whole units only).
-      auto edge_store = [&](const unsigned char* chunk, uint32_t u0, uint32_t len, uint32_t v_lo, uint32_t v_hi) {
-        if constexpr (kRagged) {
-          if (len) {
-            T* grow = reinterpret_cast<T*>(static_cast<unsigned char*>(p.grad) + row * static_cast<int64_t>(rp.row_bytes));
-            if (v_lo && gt == 0) {
-              const uint32_t e1 = (rg.span == 1 && rg.tail_e) ? rg.tail_e : static_cast<uint32_t>(E);
-              edge_output<T, MODE>(chunk, grow, rg.head_e, e1, 0, t, ignored, neg_lse2.x, lse, scale, sub_all, sub_t);
-            }
-            if (v_hi < len && gt == (len - 1) % TG) {
-              const int64_t class0 = static_cast<int64_t>(rg.span - 1) * E - rg.head_e;
-              edge_output<T, MODE>(chunk + static_cast<size_t>(len - 1) * 16, grow + class0, 0, rg.tail_e, class0, t, ignored, neg_lse2.x,
-                                   lse, scale, sub_all, sub_t);
-            }
-          }
+      // Edge units of a ragged row: their few elements are computed from the slot ring and written to global memory one
+      // by one (the bulk stores cover whole units only, so a neighbouring row's bytes are never touched).
+      if constexpr (kRagged) {
+        if (edge_thread) {
+          T* grow = reinterpret_cast<T*>(static_cast<unsigned char*>(p.grad) + row * static_cast<int64_t>(rp.row_bytes));
+          if (rg.head_e)
+            edge_output<T, MODE>(&tail->edge[edge_slot][0], grow, rg.head_e, E, 0, t, ignored, neg_lse2.x, lse, scale, sub_all, sub_t);
+          if (rg.tail_e)
+            edge_output<T, MODE>(&tail->edge[edge_slot][1], grow + tail_class0, 0, rg.tail_e, tail_class0, t, ignored, neg_lse2.x, lse, scale,
+                                 sub_all, sub_t);
         }
-      };
+      }
       if constexpr (kKeep) {
         // the chunks hold 2^(x log2e - mref): the gradient is that times 2^(mref - lse2) * scale, minus the smoothing share
         uint32_t j = cj;
 #pragma unroll
         for (int cl = 0; cl < kKeepChunks; ++cl) {
           if (static_cast<uint32_t>(cl) < cpg) {
-            uint32_t u0, len, v_lo, v_hi;
-            chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
+            uint32_t u0, len;
+            chunk_range(slice_len, grp, cl, u0, len);
             unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
             uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
-            edge_store(chunk, u0, len, v_lo, v_hi);
             if (!ignored) {
               const float mr = mref[cl] == -CUDART_INF_F ? 0.f : mref[cl];  // the sweep scaled an all -inf chunk by 2^0
               const float factor = ex2(mr + neg_lse2.x) * scale;
@@ -1039,13 +1022,11 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       } else {
       uint32_t j = cj;
       for (uint32_t cl = 0; cl < cpg; ++cl) {
-        uint32_t u0, len, v_lo, v_hi;
-        chunk_range(rg, slice_len, grp, cl, u0, len, v_lo, v_hi);
+        uint32_t u0, len;
+        chunk_range(slice_len, grp, cl, u0, len);
         unsigned char* chunk = ring + static_cast<size_t>(j) * kChunkBytes;
         uint4* buf = reinterpret_cast<uint4*>(chunk) + gt;
-        edge_store(chunk, u0, len, v_lo, v_hi);  // reads the edge units' logits: before the sweep below may touch them
         if (!ignored) {
-          // edge units are swept with the rest: what comes out of them is never stored
           if (len == kChunkUnits) {
             uint4 r[NV];
 #pragma unroll
@@ -1092,11 +1073,11 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
 
 size_t resident_smem_bytes(uint32_t nbuf) { return static_cast<size_t>(nbuf) * kChunkUnits * 16 + sizeof(Tail); }
 
-// Rows in 16-byte units.  A row whose pitch or base address is not a multiple of 16 bytes is fetched as its aligned
-// superset, which is widest when the row starts in the last element slot of a unit.
+// Rows in 16-byte units.  Of a row whose pitch or base address is not a multiple of 16 bytes the units wholly inside it
+// are fetched in chunks; the two units it shares with its neighbours travel apart.
 struct RowLayout {
   uint64_t row_bytes;
-  uint32_t row_units;  // units of the widest superset
+  uint32_t row_units;  // whole 16-byte units of a row (the most, for ragged rows)
   bool ragged;
   bool ok;
 };
@@ -1108,7 +1089,7 @@ RowLayout row_layout(int dtype, int64_t classes, const void* logits, const void*
   l.ragged = (l.row_bytes % 16) != 0 || (a % 16) != 0;
   // the output is written from the same shared-memory image: it needs the input's position within a unit
   l.ok = es != 0 && a % es == 0 && (out == nullptr || (b % 16) == (a % 16));
-  const uint64_t units = l.ragged ? (l.row_bytes + (16 - es) + 15) / 16 : l.row_bytes / 16;
+  const uint64_t units = l.row_bytes / 16;  // ragged rows: the most 16-byte units that can lie wholly inside a row
   if (units > 0x7fffffffULL) l.ok = false;
   l.row_units = static_cast<uint32_t>(units);
   return l;

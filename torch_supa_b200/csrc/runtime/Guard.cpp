@@ -139,22 +139,6 @@ struct SupaGuardImpl final : public c10::impl::DeviceGuardImplInterface {
   }
 };
 
-// Pinned host memory for non-blocking copies.
-void free_pinned(void* ptr) {
-  if (ptr) cudaFreeHost(ptr);
-  cudaGetLastError();
-}
-struct PinnedAllocator final : public c10::Allocator {
-  c10::DataPtr allocate(size_t nbytes) override {
-    void* ptr = nullptr;
-    if (nbytes) SUPA_CUDA_CHECK(cudaHostAlloc(&ptr, nbytes, cudaHostAllocDefault));
-    return c10::DataPtr(ptr, ptr, &free_pinned, c10::Device(c10::DeviceType::CPU));
-  }
-  c10::DeleterFnPtr raw_deleter() const override { return &free_pinned; }
-  void copy_data(void* dest, const void* src, std::size_t count) const override { default_copy_data(dest, src, count); }
-};
-PinnedAllocator g_pinned;
-
 struct SupaHooks final : public at::PrivateUse1HooksInterface {
   bool isBuilt() const override { return true; }
   bool isAvailable() const override { return device_count() > 0; }
@@ -177,7 +161,7 @@ struct SupaHooks final : public at::PrivateUse1HooksInterface {
     }
     return attr.type == cudaMemoryTypeHost;
   }
-  c10::Allocator* getPinnedMemoryAllocator() const override { return &g_pinned; }
+  c10::Allocator* getPinnedMemoryAllocator() const override { return pinned_allocator(); }
   at::Device getDeviceFromPtr(void* data) const override {
     cudaPointerAttributes attr{};
     SUPA_CUDA_CHECK(cudaPointerGetAttributes(&attr, data));

@@ -69,6 +69,23 @@ void set_memory_limit(c10::DeviceIndex device, int64_t bytes);
 // work queued on that stream so far has finished.
 void record_stream(const c10::DataPtr& ptr, c10::Stream stream);
 
+// ---- pinned host memory -------------------------------------------------------------------------------------
+struct HostMemoryStats {
+  int64_t allocated_bytes;  // bytes in blocks handed out
+  int64_t reserved_bytes;   // bytes obtained from cudaHostAlloc and not given back
+  int64_t host_allocs;      // cudaHostAlloc calls
+  int64_t hits;             // allocations served from the cache
+};
+// Caching allocator of page-locked host memory (tensor.pin_memory(), non-blocking copies).
+c10::Allocator* pinned_allocator();
+// Marks the pinned block that holds `ptr` as used by asynchronous work on `stream`: after it is freed it is not handed
+// out again before that work has finished.  False when `ptr` is not in a block of this allocator.
+bool record_pinned_use(const void* ptr, cudaStream_t stream);
+bool is_cached_pinned(const void* ptr);
+// Returns cached pinned blocks to the driver.
+void empty_pinned_cache();
+HostMemoryStats host_memory_stats();
+
 // ---- status word ------------------------------------------------------------------------------------------
 // One int32 per device in device memory that kernels OR error bits into (an out-of-range class index).
 int32_t* status_word(c10::DeviceIndex device);

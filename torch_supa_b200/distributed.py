@@ -19,6 +19,46 @@ import os
 import torch
 
 _REDUCTIONS = {"none": 0, "mean": 1, "sum": 2}
+C10D_BACKEND_NAME = "supa_nccl"
+_c10d_module = None
+
+
+def _load_c10d_module():
+    """The pybind module that lives inside the host library (PyInit__supa_c10d)."""
+    global _c10d_module
+    if _c10d_module is None:
+        import importlib.machinery
+        import importlib.util
+
+        from . import _HOST_LIB, _load
+
+        _load()
+        loader = importlib.machinery.ExtensionFileLoader("_supa_c10d", str(_HOST_LIB))
+        spec = importlib.util.spec_from_loader("_supa_c10d", loader)
+        module = importlib.util.module_from_spec(spec)
+        loader.exec_module(module)
+        _c10d_module = module
+    return _c10d_module
+
+
+def _create_c10d_backend(store, rank, size, timeout):
+    return _load_c10d_module().create_backend(store, rank, size, timeout)
+
+
+def register_c10d_backend() -> bool:
+    """Registers the ``supa_nccl`` backend of ``torch.distributed`` for the ``supa`` device, as the reference registers
+    ``bccl`` when it is imported (``torch_supa/distributed/distributed_c10d.py:65-102``).  After
+    ``init_process_group("cpu:gloo,supa:supa_nccl")`` (or just ``"supa_nccl"``), ``torch.distributed.all_reduce``,
+    ``broadcast``, ``all_gather``, ``reduce_scatter_tensor``, ``barrier`` and DistributedDataParallel work on supa
+    tensors.  Returns False when torch.distributed is not available or the name is already taken."""
+    import torch.distributed as dist
+
+    if not dist.is_available():
+        return False
+    if C10D_BACKEND_NAME in getattr(dist.Backend, "backend_list", []):
+        return False
+    dist.Backend.register_backend(C10D_BACKEND_NAME, _create_c10d_backend, devices=["supa"])
+    return True
 
 
 def shard_rows(total_rows: int, world_size: int, rank: int) -> tuple[int, int]:

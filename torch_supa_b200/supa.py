@@ -126,6 +126,18 @@ def empty_cache() -> None:
     _check(_host().supa_empty_cache())
 
 
+def host_memory_stats() -> dict:
+    """Counters of the caching allocator of pinned host memory (``tensor.pin_memory()``, non-blocking copies)."""
+    out = (ctypes.c_int64 * 4)()
+    _check(_host().supa_host_memory_stats(out))
+    return {"allocated_bytes": out[0], "reserved_bytes": out[1], "host_allocs": out[2], "cache_hits": out[3]}
+
+
+def empty_host_cache() -> None:
+    """Returns cached pinned host blocks to the driver."""
+    _check(_host().supa_empty_pinned_cache())
+
+
 def set_memory_limit(nbytes: int, device=None) -> None:
     """Caps the bytes tensors may hold on the device (0 removes the cap).  Allocations beyond it raise
     ``torch.OutOfMemoryError`` on the host without touching the GPU."""
