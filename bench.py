@@ -157,6 +157,35 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Runs this rank on the CPUs next to its GPU (NVML's affinity mask, a read-only query), so that the pinned staging
+    buffers of the end-to-end leg are first touched, and therefore placed, on the GPU's own NUMA node: with every rank on
+    node 0 the host-to-device copies of eight ranks shared one root complex.  Returns the number of CPUs bound to, or None
+    when nothing was changed (no NVML, or the mask does not intersect the CPUs this process may use)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = gpu_index
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                index = int(ids[gpu_index])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        near = {c for c in range(ncpu) if (int(words[c // 64]) >> (c % 64)) & 1}
+        allowed = os.sched_getaffinity(0) & near
+        pynvml.nvmlShutdown()
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return len(allowed)
+    except Exception:
+        return None
+
+
 def algorithmic_bytes(rows, classes, elem_size):
     """Read logits + write gradient + read targets, each once."""
     return 2 * rows * classes * elem_size + rows * 8
@@ -241,6 +270,7 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.supa.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    cpus_bound = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     torch.supa.set_device(local_rank)
     torch.cuda.set_device(local_rank)  # only for the synthetic-data generator
     device = torch.device("supa", local_rank)
@@ -453,7 +483,8 @@ def run_ours(args):
             "notes": {"rows_per_gpu": rows, "timed_after": "warm-up" if args.quick else "warm-up + 160 steps of continuous load (power-capped clocks)",
                       "api": "F.cross_entropy on the supa device + backward" if world == 1 else "sharded_cross_entropy + backward",
                       "exchange": None if comm is None else ("peer memory inside the count and loss kernels" if comm.peer_handle else "ncclAllReduce x2"),
-                      "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs smaller than 2x L2"},
+                      "l2": "inputs larger than L2 (no flush)" if nbytes > (256 << 20) else "inputs smaller than 2x L2",
+                      "cpus_bound_near_gpu": cpus_bound},
             "loss": loss_value, "status_word": status_word, "kernel_variant": variant,
             "burst": {"ms_per_step": burst_ms, "value": rows_total / (burst_ms * 1e-3), "unit": "rows/s",
                       "note": f"{args.steps} steps right after the warm-up, before the power cap lowers the clock"},

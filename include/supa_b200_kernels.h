@@ -486,6 +486,38 @@ typedef struct sb_ce_prob_args {
 } sb_ce_prob_args;
 SB_API int sb_ce_prob_forward_backward(const sb_ce_prob_args* args, sb_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Random fills and dropout from a (seed, offset) pair.
+ *
+ * The pair is what the device generator hands out (philox_engine_inputs,
+ * torch_supa/csrc/aten/SUPAGeneratorImpl.cpp:450-455; the reference feeds it to its vendor library's Philox4_32_10).  The
+ * stream is a function of the element index alone: group g = elements [g*E, (g+1)*E) with E = 4 for element types of up
+ * to 4 bytes and 2 for 8-byte types; words = philox4x32_10(counter {lo(offset/4), hi(offset/4), lo(g), hi(g)},
+ * key {lo(seed), hi(seed)}); element k uses word k (E = 4) or words 2k, 2k+1 (E = 2).  A fill consumes one 128-bit block
+ * per group: advance the offset by 4 per call.  offset must be a multiple of 4.
+ *   SB_RNG_UNIFORM    a + u (b - a), u = (word >> 8) 2^-24 (53 bits for doubles); a value that rounds to b becomes a
+ *   SB_RNG_NORMAL     a + b z; Box-Muller on (word 2j, word 2j+1): u1 = ((w >> 8) + 1) 2^-24, u2 = (w >> 8) 2^-24,
+ *                     z = sqrt(-2 ln u1) (cos, sin)(2 pi u2)
+ *   SB_RNG_INTEGER    low + r mod range (range = 0 means 2^64, 8-byte types only; r is one word when range <= 2^32)
+ *   SB_RNG_BERNOULLI  1 where u < a
+ * sb_dropout: keep_i = (u_i >= p), out = x * keep / (1 - p), mask = keep (one byte per element).
+ * ------------------------------------------------------------------------------------------ */
+typedef enum sb_rng_kind { SB_RNG_UNIFORM = 0, SB_RNG_NORMAL = 1, SB_RNG_INTEGER = 2, SB_RNG_BERNOULLI = 3 } sb_rng_kind;
+typedef struct sb_rng_args {
+  void* dst;       /* contiguous, numel elements of dtype */
+  int32_t dtype;   /* uniform / normal: SB_F32, SB_F64, SB_BF16, SB_F16; integer / bernoulli: any */
+  int32_t kind;    /* sb_rng_kind */
+  int64_t numel;
+  double a, b;
+  int64_t low;
+  uint64_t range;
+  uint64_t seed;
+  uint64_t offset;
+} sb_rng_args;
+SB_API int sb_rng_fill(const sb_rng_args* args, sb_stream_t stream);
+SB_API int sb_dropout(const void* x, void* out, void* mask, int32_t dtype, int64_t numel, double p, uint64_t seed,
+                      uint64_t offset, sb_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -301,6 +301,7 @@ struct alignas(16) Tail {
   float4 slots[2][4];        // cluster exchange: [row parity][source CTA] = {max2, sum, sum x, x[target]}
   float red[3][32];          // per-warp partials
   float xt_kept;             // kept-exponential mode: x[target] saved by the thread that owns it before it is overwritten
+  float xt_edge;             // ragged rows: x[target] when the target lies in an edge unit, saved by the lane that holds it
   unsigned long long full[kMaxBuffers];   // loader -> consumers: chunk has landed
   unsigned long long ready[kMaxBuffers];  // consumers -> loader: chunk holds the gradient (or may be reused)
   // ragged rows: the first and the last 16-byte unit of a row, when the row owns only part of them, for the row in slot
@@ -435,50 +436,6 @@ struct RowGeom {
   int64_t class0;     // class index of the first element of the first whole unit
 };
 
-// Statistics of the elements [e0, e1) of one edge unit (the others belong to a neighbouring row).
-template <typename T, bool kSumX>
-__device__ __forceinline__ void edge_stats(RowStats& st, const void* unit, uint32_t e0, uint32_t e1) {
-  constexpr int E = 16 / sizeof(T);
-  const T* x = static_cast<const T*>(unit);
-  uint4 r[1];
-  T* re = reinterpret_cast<T*>(&r[0]);
-  float sx = 0.f;
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    const bool mine = static_cast<uint32_t>(e) >= e0 && static_cast<uint32_t>(e) < e1;
-    const T v = x[e];
-    re[e] = mine ? v : from_float<T>(-CUDART_INF_F);
-    if (mine) sx += to_float(v);
-  }
-  stats_update<T, 1, false>(st, r);
-  if (kSumX) st.sx[0].x += sx;
-}
-
-// Output of the elements [e0, e1) of one edge unit, written to global memory one element at a time.  `out` points at
-// the class of element e0.
-template <typename T, int MODE>
-__device__ __forceinline__ void edge_output(const void* unit, T* out, uint32_t e0, uint32_t e1, int64_t class0, int64_t target,
-                                            bool ignored, float neg_lse2, float lse, float scale, float sub_all, float sub_t) {
-  constexpr int E = 16 / sizeof(T);
-  const T* x = static_cast<const T*>(unit);
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    if (static_cast<uint32_t>(e) >= e0 && static_cast<uint32_t>(e) < e1) {
-      float g = 0.f;
-      if (!ignored) {
-        const float xv = to_float(x[e]);
-        if (MODE == 1) {
-          g = xv - lse;
-        } else {
-          g = fmaf(ex2(fmaf(xv, kLog2e, neg_lse2)), scale, -sub_all);
-          if (MODE == 0 && class0 + (e - static_cast<int>(e0)) == target) g -= sub_t;
-        }
-      }
-      out[e - static_cast<int>(e0)] = from_float<T>(g);
-    }
-  }
-}
-
 // kKeep (cross entropy on 16-bit logits, at most kKeepChunks chunks per group and row): the statistics sweep overwrites
 // each chunk with its exponentials 2^(x log2e - m), m being the thread's running maximum at that chunk, and the gradient
 // sweep only rescales them: one ex2 per logit instead of two and a third fewer instructions, which is what limits this
@@ -549,6 +506,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     }
     for (int e = 0; e < kEdgeSlots; ++e) mbar_init(smem_u32(&tail->edge_full[e]), 1);
     tail->xt_kept = 0.f;
+    tail->xt_edge = 0.f;
     fence_mbar_init();
   }
   __syncthreads();
@@ -753,22 +711,33 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
     const RowGeom rg = row_geom(row);
     const uint32_t slice_len = slice_len_of(rg);
     const int64_t t_slice = t - rg.class0 - slice_elem0;  // element position of the target in this CTA's slice of whole units
-    // Ragged rows: thread 0 of the cluster's first CTA folds the elements of the two edge units (they arrive in a slot
-    // ring of their own) and keeps x[target] if the target lies in one of them.
-    float xt_edge = 0.f;
+    // Ragged rows: the elements of the two edge units (they arrive in a slot ring of their own) are spread over the lanes of
+    // warp 0 of the cluster's first CTA, one element per lane: lane l holds element l % E of the head unit (l < E) or of
+    // the tail unit.  Each lane folds its element into its own statistics, which the warp reduction below merges anyway.
     const uint32_t edge_slot = static_cast<uint32_t>(k % kEdgeSlots);
-    const bool edge_thread = kRagged && tid == 0 && cta_rank == 0 && (rg.head_e != 0 || rg.tail_e != 0);
     const int64_t tail_class0 = rg.class0 + static_cast<int64_t>(rg.span) * E;  // class of the first element after the whole units
+    bool edge_lane = false;      // this thread holds an element of an edge unit that belongs to the row
+    const T* edge_elem = nullptr;
+    int64_t edge_class = 0;
     if constexpr (kRagged) {
-      if (edge_thread && !ignored) {
+      if (tid < 2 * E && cta_rank == 0) {
+        const uint32_t which = tid / E, e = tid % E;
+        edge_lane = which == 0 ? (rg.head_e != 0 && e >= rg.head_e) : (e < rg.tail_e);
+        edge_elem = reinterpret_cast<const T*>(&tail->edge[edge_slot][which]) + e;
+        edge_class = which == 0 ? static_cast<int64_t>(e) - rg.head_e : tail_class0 + e;
+      }
+      if (warp == 0 && cta_rank == 0 && !ignored && (rg.head_e != 0 || rg.tail_e != 0)) {
         if (!mbar_wait(smem_u32(&tail->edge_full[edge_slot]), static_cast<uint32_t>(k / kEdgeSlots) & 1)) timed_out = true;
-        if (rg.head_e) {
-          edge_stats<T, kSumX>(st, &tail->edge[edge_slot][0], rg.head_e, E);
-          if (t < rg.class0) xt_edge = to_float(reinterpret_cast<const T*>(&tail->edge[edge_slot][0])[rg.head_e + t]);
-        }
-        if (rg.tail_e) {
-          edge_stats<T, kSumX>(st, &tail->edge[edge_slot][1], 0, rg.tail_e);
-          if (t >= tail_class0) xt_edge = to_float(reinterpret_cast<const T*>(&tail->edge[edge_slot][1])[t - tail_class0]);
+        if (edge_lane) {
+          const float x = to_float(*edge_elem);
+          const float nm = max_nan(st.m2, x * kLog2e);
+          const float resc = ex2(nm == -CUDART_INF_F ? 0.f : st.m2 - nm);
+          st.s[0] = mul2(st.s[0], make_float2(resc, resc));
+          st.s[1] = mul2(st.s[1], make_float2(resc, resc));
+          st.m2 = nm;
+          st.s[0].x += ex2(fmaf(x, kLog2e, nm == -CUDART_INF_F ? 0.f : -nm));
+          if (kSumX) st.sx[0].x += x;
+          if (edge_class == t) tail->xt_edge = x;
         }
       }
     }
@@ -881,7 +850,10 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
             if (!mbar_wait(smem_u32(&tail->full[og * nbg + oj]), oph)) timed_out = true;
             xt = to_float(reinterpret_cast<const T*>(smem + (static_cast<size_t>(og) * nbg + oj) * kChunkBytes)[off]);
           }
-          xt += xt_edge;  // lane 0 of warp 0 is the thread that handled the edge units
+          if (kRagged) {  // written by a lane of this warp before the barrier above
+            xt += tail->xt_edge;
+            tail->xt_edge = 0.f;
+          }
           if (CLUSTER > 1) {
             const uint32_t slot = smem_u32(&tail->slots[xpar][cta_rank]);
 #pragma unroll
@@ -959,16 +931,21 @@ __global__ void __launch_bounds__(kResidentThreads, 1) ce_resident_kernel(Reside
       // The class of the target gets (1 - eps) * scale subtracted: its owner recomputes that one element from
       // x[target] with the same arithmetic and a single rounding.
       const float g_target = fmaf(ex2(fmaf(xt_all, kLog2e, neg_lse2.x)), scale, -sub_all) - sub_t;
-      // Edge units of a ragged row: their few elements are computed from the slot ring and written to global memory one
-      // by one (the bulk stores cover whole units only, so a neighbouring row's bytes are never touched).
+      // Edge units of a ragged row: each of their elements is computed by the lane that holds it and written to global
+      // memory on its own (the bulk stores cover whole units only, so a neighbouring row's bytes are never touched).
       if constexpr (kRagged) {
-        if (edge_thread) {
-          T* grow = reinterpret_cast<T*>(static_cast<unsigned char*>(p.grad) + row * static_cast<int64_t>(rp.row_bytes));
-          if (rg.head_e)
-            edge_output<T, MODE>(&tail->edge[edge_slot][0], grow, rg.head_e, E, 0, t, ignored, neg_lse2.x, lse, scale, sub_all, sub_t);
-          if (rg.tail_e)
-            edge_output<T, MODE>(&tail->edge[edge_slot][1], grow + tail_class0, 0, rg.tail_e, tail_class0, t, ignored, neg_lse2.x, lse, scale,
-                                 sub_all, sub_t);
+        if (edge_lane) {
+          float gv = 0.f;
+          if (!ignored) {
+            const float x = to_float(*edge_elem);
+            if (MODE == 1) {
+              gv = x - lse;
+            } else {
+              gv = fmaf(ex2(fmaf(x, kLog2e, neg_lse2.x)), scale, -sub_all);
+              if (MODE == 0 && edge_class == t) gv -= sub_t;
+            }
+          }
+          reinterpret_cast<T*>(static_cast<unsigned char*>(p.grad) + row * static_cast<int64_t>(rp.row_bytes))[edge_class] = from_float<T>(gv);
         }
       }
       if constexpr (kKeep) {
