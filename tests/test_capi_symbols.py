@@ -60,6 +60,17 @@ def test_argument_validation_needs_no_gpu(kernel_lib):
     rdesc = capi.ReduceDesc()
     rdesc.op, rdesc.ndim = 0, 0
     assert kernel_lib.sb_reduce(ctypes.byref(rdesc), None) == -1
+    rng = capi.RngArgs()
+    rng.dst, rng.dtype, rng.kind, rng.numel, rng.a, rng.b, rng.offset = 0x1000, 8, capi.SB_RNG_UNIFORM, 16, 0.0, 1.0, 2
+    assert kernel_lib.sb_rng_fill(ctypes.byref(rng), None) == -1          # an offset that is not a whole Philox block
+    rng.offset, rng.a, rng.b = 4, 1.0, 0.0
+    assert kernel_lib.sb_rng_fill(ctypes.byref(rng), None) == -1          # from > to
+    rng.a, rng.b, rng.dtype = 0.0, 1.0, 4
+    assert kernel_lib.sb_rng_fill(ctypes.byref(rng), None) < 0            # uniform into int32
+    rng.numel = 0
+    assert kernel_lib.sb_rng_fill(ctypes.byref(rng), None) == 0           # nothing to do
+    assert kernel_lib.sb_dropout(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x2000), ctypes.c_void_p(0x3000), 8, ctypes.c_int64(16),
+                                 ctypes.c_double(1.5), ctypes.c_uint64(1), ctypes.c_uint64(0), None) == -1
 
 
 def test_path_classifier_runs_on_host(kernel_lib):

@@ -61,6 +61,24 @@ def test_operators_fail_loudly_without_a_device():
         torch.empty(4, device="supa")
 
 
+def test_seeding_without_a_device_is_ignored():
+    """torch.manual_seed reaches the device module on every machine; with no device there is nothing to seed."""
+    import torch_supa_b200  # noqa: F401
+
+    if torch.supa.device_count() > 0:
+        pytest.skip("a device is present")
+    torch.manual_seed(3)
+    torch.supa.manual_seed(3)
+    torch.supa.manual_seed_all(3)
+    torch.supa.seed()
+    torch.supa.seed_all()
+    assert torch.supa.get_rng_state_all() == []
+    with pytest.raises(RuntimeError):
+        torch.supa.get_rng_state()
+    with pytest.raises(RuntimeError):
+        torch.Generator(device="supa")
+
+
 def test_shard_rows_partitions_exactly():
     from torch_supa_b200.distributed import shard_rows
 

@@ -195,3 +195,44 @@ def test_div_rounding_modes(golden):
         assert np.array_equal(np.signbit(got), np.signbit(want)), key + ": sign of zero"
     assert np.array_equal(oracle.c_div_int(golden["div/ia"], golden["div/ib"], False), golden["div/itrunc"])
     assert np.array_equal(oracle.c_div_int(golden["div/ia"], golden["div/ib"], True), golden["div/ifloor"])
+
+
+# ---- the Philox stream behind the device generator ------------------------------------------------------------------------
+# Known answers published with the algorithm (Random123's kat_vectors, philox4x32 with 10 rounds): counter, key, output.
+PHILOX_KAT = [
+    ((0x00000000,) * 4, (0x00000000,) * 2, (0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8)),
+    ((0xFFFFFFFF,) * 4, (0xFFFFFFFF,) * 2, (0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD)),
+    ((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0), (0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1)),
+]
+
+
+@pytest.mark.parametrize("counter,key,want", PHILOX_KAT)
+def test_philox_known_answers(counter, key, want):
+    got = oracle.philox4x32_10(np.array([counter], np.uint32), key)[0]
+    assert tuple(int(v) for v in got) == want
+
+
+def test_stream_layout_and_offsets():
+    seed = (0x299F31D0 << 32) | 0xA4093822
+    # group g of the stream at offset 4 * b is the block with counter {lo(b), hi(b), lo(g), hi(g)}
+    block = (0x85A308D3 << 32) | 0x243F6A88
+    ctr = np.array([[0x243F6A88, 0x85A308D3, 5, 0]], np.uint32)
+    assert np.array_equal(oracle.rng_words(24, seed, 4 * block)[5], oracle.philox4x32_10(ctr, (0xA4093822, 0x299F31D0))[0])
+    # consecutive fills (offset += 4) do not share a block; 8-byte element types take two words per element
+    a, b = oracle.rng_words(64, 7, 0), oracle.rng_words(64, 7, 4)
+    assert not np.intersect1d(a.reshape(-1), b.reshape(-1)).size
+    assert oracle.rng_words(10, 7, 0, per_group=2).shape == (5, 4)
+
+
+def test_distributions_of_the_stream():
+    n = 1 << 18
+    u = oracle.rng_uniform(n, 11, 0)
+    assert u.dtype == np.float32 and u.min() >= 0 and u.max() < 1 and abs(u.mean() - 0.5) < 4e-3
+    z = oracle.rng_normal(n, 11, 4)
+    assert np.isfinite(z).all() and abs(z.mean()) < 1e-2 and abs(z.std() - 1) < 1e-2
+    r = oracle.rng_integer(n, 11, 8, -3, 10)
+    assert r.min() == -3 and r.max() == 6 and np.all(np.bincount(r + 3) > n / 10 * 0.9)
+    assert abs(oracle.rng_bernoulli(n, 11, 12, 0.3).mean() - 0.3) < 5e-3
+    assert np.array_equal(oracle.rng_dropout_keep(n, 11, 12, 0.3), ~oracle.rng_bernoulli(n, 11, 12, 0.3))
+    w = oracle.rng_integer(1000, 11, 16, -(1 << 63), 0, wide=True)
+    assert w.dtype == np.int64 and (w < 0).any() and (w > 0).any()

@@ -61,6 +61,17 @@ class CEProbArgs(C.Structure):
     ]
 
 
+class RngArgs(C.Structure):
+    """sb_rng_args: a random fill from a (seed, offset) pair."""
+    _fields_ = [
+        ("dst", C.c_void_p), ("dtype", C.c_int32), ("kind", C.c_int32), ("numel", C.c_int64), ("a", C.c_double), ("b", C.c_double),
+        ("low", C.c_int64), ("range", C.c_uint64), ("seed", C.c_uint64), ("offset", C.c_uint64),
+    ]
+
+
+SB_RNG_UNIFORM, SB_RNG_NORMAL, SB_RNG_INTEGER, SB_RNG_BERNOULLI = 0, 1, 2, 3
+
+
 class NLLArgs(C.Structure):
     _fields_ = [
         ("log_probs", C.c_void_p), ("dtype", C.c_int32), ("target_dtype", C.c_int32), ("target", C.c_void_p),
@@ -223,6 +234,15 @@ def moments(inp, dtype, outer, length, inner, correction, take_sqrt, out, mean_o
     check("sb_moments", lib().sb_moments(_p(inp), C.c_int32(dtype), C.c_int64(outer), C.c_int64(length), C.c_int64(inner),
                                          C.c_double(correction), C.c_int32(1 if take_sqrt else 0), _p(out), _p(mean_out), _p(scratch),
                                          C.c_size_t(scratch_bytes), C.c_void_p(stream)))
+
+
+def rng_fill(args: RngArgs, stream=0):
+    check("sb_rng_fill", lib().sb_rng_fill(C.byref(args), C.c_void_p(stream)))
+
+
+def dropout(x, out, mask, dtype, numel, p, seed, offset, stream=0):
+    check("sb_dropout", lib().sb_dropout(_p(x), _p(out), _p(mask), C.c_int32(dtype), C.c_int64(numel), C.c_double(p),
+                                         C.c_uint64(seed), C.c_uint64(offset), C.c_void_p(stream)))
 
 
 def ce_kernel_variant(dtype, rows, classes) -> int:

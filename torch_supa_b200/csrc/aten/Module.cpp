@@ -9,6 +9,7 @@
 #include "Common.h"
 #include "dist/NcclComm.h"
 #include "dist/PeerExchange.h"
+#include "runtime/Generator.h"
 
 namespace {
 
@@ -73,6 +74,40 @@ SUPA_EXPORT int supa_host_memory_stats(int64_t* out4) {
 }
 SUPA_EXPORT int supa_empty_pinned_cache() {
   return guarded([&] { supa::empty_pinned_cache(); });
+}
+// The default generator of `device` (-1: the current device).  op 0: manual_seed(value); 1: seed() -> *out; 2: initial_seed
+// -> *out; 3: offset -> *out; 4: set offset(value).
+SUPA_EXPORT int supa_generator_control(int device, int op, uint64_t value, uint64_t* out) {
+  return guarded([&] {
+    auto* gen = supa::generator_or_default(c10::nullopt, static_cast<c10::DeviceIndex>(device));
+    std::lock_guard<std::mutex> lock(gen->mutex_);
+    switch (op) {
+      case 0: gen->set_current_seed(value); break;
+      case 1: *out = gen->seed(); break;
+      case 2: *out = gen->current_seed(); break;
+      case 3: *out = gen->get_offset(); break;
+      case 4: gen->set_offset(value); break;
+      default: TORCH_CHECK(false, "supa_generator_control: unknown op ", op);
+    }
+  });
+}
+// The 16-byte state (seed, offset) of the default generator of `device`.
+SUPA_EXPORT int supa_get_rng_state(int device, uint8_t* out16) {
+  return guarded([&] {
+    auto* gen = supa::generator_or_default(c10::nullopt, static_cast<c10::DeviceIndex>(device));
+    std::lock_guard<std::mutex> lock(gen->mutex_);
+    const auto state = gen->get_state();
+    std::memcpy(out16, state->data(), 16);
+  });
+}
+SUPA_EXPORT int supa_set_rng_state(int device, const uint8_t* state, int64_t nbytes) {
+  return guarded([&] {
+    auto* gen = supa::generator_or_default(c10::nullopt, static_cast<c10::DeviceIndex>(device));
+    at::Tensor t = at::empty({nbytes}, at::TensorOptions().dtype(at::kByte).device(at::kCPU));
+    std::memcpy(t.data_ptr(), state, static_cast<size_t>(nbytes));
+    std::lock_guard<std::mutex> lock(gen->mutex_);
+    gen->set_state(*t.unsafeGetTensorImpl());
+  });
 }
 SUPA_EXPORT int supa_set_memory_limit(int device, int64_t bytes) {
   return guarded([&] { supa::set_memory_limit(static_cast<c10::DeviceIndex>(device), bytes); });

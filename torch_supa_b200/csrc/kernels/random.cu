@@ -19,9 +19,11 @@ constexpr uint32_t kPhiloxW0 = 0x9E3779B9u, kPhiloxW1 = 0xBB67AE85u;
 __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1) {
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(kPhiloxM0, c.x), lo0 = kPhiloxM0 * c.x;
-    const uint32_t hi1 = __umulhi(kPhiloxM1, c.z), lo1 = kPhiloxM1 * c.z;
-    c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
+    // one 32x32 -> 64 multiply per product (both halves are used)
+    const uint64_t p0 = static_cast<uint64_t>(kPhiloxM0) * c.x;
+    const uint64_t p1 = static_cast<uint64_t>(kPhiloxM1) * c.z;
+    c = make_uint4(static_cast<uint32_t>(p1 >> 32) ^ c.y ^ k0, static_cast<uint32_t>(p1), static_cast<uint32_t>(p0 >> 32) ^ c.w ^ k1,
+                   static_cast<uint32_t>(p0));
     k0 += kPhiloxW0;
     k1 += kPhiloxW1;
   }
@@ -95,9 +97,9 @@ struct Dist<T, SB_RNG_NORMAL> {
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const float u1 = static_cast<float>((ws[2 * k] >> 8) + 1u) * 0x1p-24f;
-      const float r = sqrtf(-2.f * __logf(u1)) * sd;
+      const float r = sqrtf(-2.f * logf(u1)) * sd;  // the accurate logarithm: an approximate one can turn positive next to u1 = 1
       float s, c;
-      __sincosf(6.283185307179586f * u24(ws[2 * k + 1]), &s, &c);
+      sincospif(2.f * u24(ws[2 * k + 1]), &s, &c);
       out[2 * k] = cast_real<T>(fmaf(r, c, mean));
       out[2 * k + 1] = cast_real<T>(fmaf(r, s, mean));
     }

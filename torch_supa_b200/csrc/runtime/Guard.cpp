@@ -8,6 +8,7 @@
 #include <c10/core/impl/DeviceGuardImplInterface.h>
 #include <c10/core/impl/alloc_cpu.h>
 
+#include "Generator.h"
 #include "Runtime.h"
 
 namespace supa {
@@ -162,6 +163,8 @@ struct SupaHooks final : public at::PrivateUse1HooksInterface {
     return attr.type == cudaMemoryTypeHost;
   }
   c10::Allocator* getPinnedMemoryAllocator() const override { return pinned_allocator(); }
+  const at::Generator& getDefaultGenerator(c10::DeviceIndex device_index) const override { return default_generator(device_index); }
+  at::Generator getNewGenerator(c10::DeviceIndex device_index = -1) const override { return new_generator(device_index); }
   at::Device getDeviceFromPtr(void* data) const override {
     cudaPointerAttributes attr{};
     SUPA_CUDA_CHECK(cudaPointerGetAttributes(&attr, data));

@@ -161,6 +161,38 @@ def moments(x, dim, correction=1.0, take_sqrt=False):
     return out, mean
 
 
+_RNG_KINDS = {"uniform": capi.SB_RNG_UNIFORM, "normal": capi.SB_RNG_NORMAL, "integer": capi.SB_RNG_INTEGER,
+              "bernoulli": capi.SB_RNG_BERNOULLI}
+
+
+def rng_fill(out, kind, seed, offset, a=0.0, b=1.0, low=0, range_=0):
+    """Fills the contiguous tensor ``out`` from the Philox stream of (seed, offset): ``kind`` is "uniform" ([a, b)),
+    "normal" (mean a, std b), "integer" (low + r mod range_) or "bernoulli" (probability a).  The caller advances the
+    offset by 4 per fill."""
+    assert out.is_contiguous()
+    args = capi.RngArgs()
+    args.dst = out.data_ptr()
+    args.dtype = capi.torch_dtype_code(out.dtype)
+    args.kind = _RNG_KINDS[kind]
+    args.numel = out.numel()
+    args.a, args.b = float(a), float(b)
+    args.low = int(low)
+    args.range = int(range_)
+    args.seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    args.offset = int(offset)
+    capi.rng_fill(args, _stream(out))
+    return out
+
+
+def dropout(x, p, seed, offset):
+    """(x * keep / (1 - p), keep) with keep drawn from the Philox stream of (seed, offset)."""
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    mask = torch.empty(x.shape, dtype=torch.bool, device=x.device)
+    capi.dropout(x, out, mask, capi.torch_dtype_code(x.dtype), x.numel(), p, int(seed) & 0xFFFFFFFFFFFFFFFF, int(offset), _stream(x))
+    return out, mask
+
+
 def log_softmax(x, dim=-1, out_dtype=None):
     x = x.contiguous()
     dim %= max(x.dim(), 1)

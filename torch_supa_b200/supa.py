@@ -155,12 +155,74 @@ def _is_in_bad_fork() -> bool:
     return False
 
 
-def manual_seed_all(seed: int) -> None:
-    """The operator path has no random kernels; seeding is accepted and ignored."""
+# ---- random number generator (counterpart of torch_supa/supa/random.py:26-200) ---------------------------------------------
+def _generator_control(device, op: int, value: int = 0) -> int:
+    out = ctypes.c_uint64(0)
+    _check(_host().supa_generator_control(_index(device), op, ctypes.c_uint64(value & 0xFFFFFFFFFFFFFFFF), ctypes.byref(out)))
+    return out.value
 
 
 def manual_seed(seed: int) -> None:
-    manual_seed_all(seed)
+    """Seeds the default generator of the current device (and rewinds its offset).  Ignored when no device is present,
+    so that ``torch.manual_seed`` keeps working on a machine without one."""
+    if device_count() > 0:
+        _generator_control(None, 0, int(seed))
+
+
+def manual_seed_all(seed: int) -> None:
+    for i in range(device_count()):
+        _generator_control(i, 0, int(seed))
+
+
+def seed() -> None:
+    """Seeds the current device's default generator from a non-deterministic source."""
+    if device_count() > 0:
+        _generator_control(None, 1)
+
+
+def seed_all() -> None:
+    """One non-deterministic seed, applied to every device."""
+    if device_count() > 0:
+        value = _generator_control(0, 1)
+        for i in range(1, device_count()):
+            _generator_control(i, 0, value)
+
+
+def initial_seed() -> int:
+    return _generator_control(None, 2)
+
+
+def get_rng_state(device="supa") -> torch.Tensor:
+    """The default generator's state as a CPU byte tensor: 8 bytes of seed, 8 bytes of Philox offset."""
+    out = (ctypes.c_uint8 * 16)()
+    _check(_host().supa_get_rng_state(_index(device), out))
+    return torch.tensor(list(out), dtype=torch.uint8)
+
+
+def set_rng_state(new_state: torch.Tensor, device="supa") -> None:
+    state = new_state.detach().to("cpu", torch.uint8).contiguous()
+    buf = (ctypes.c_uint8 * state.numel()).from_buffer_copy(bytes(state.tolist()))
+    _check(_host().supa_set_rng_state(_index(device), buf, ctypes.c_int64(state.numel())))
+
+
+def get_rng_state_all() -> list:
+    return [get_rng_state(i) for i in range(device_count())]
+
+
+def set_rng_state_all(new_states) -> None:
+    for i, state in enumerate(new_states):
+        set_rng_state(state, i)
+
+
+# The runtime initialises on first use; torch.utils.checkpoint reads this attribute to decide whether the device
+# generator's state belongs to the state it preserves.
+_initialized = True
+
+
+def get_amp_supported_dtype() -> list:
+    """The dtypes torch.amp.autocast accepts for this device (torch.utils.checkpoint builds a disabled autocast context for
+    the device it replays on and asks for this list).  No autocast policy table is registered for supa operators."""
+    return [torch.bfloat16, torch.float16]
 
 
 def is_initialized() -> bool:
