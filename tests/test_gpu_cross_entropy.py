@@ -228,7 +228,13 @@ def test_linearity_property_full_vocab(cuda_device):
     (64, 151643, torch.bfloat16, 2),
     (37, 300007, torch.float16, 4),
     (150, 50257, torch.float32, 2),     # 201028 B: ragged rows over a 2-CTA cluster
-    (4096, 2048, torch.float32, 8),     # short rows: held in registers
+    (4096, 2048, torch.float32, 16),    # short aligned rows: one warp per row on the shared-memory slot ring
+    (2000, 1000, torch.bfloat16, 16),   # 2000 B rows
+    (700, 512, torch.bfloat16, 16),     # 1 KB: the shortest rows the ring takes (64 slots)
+    (500, 4088, torch.float16, 16),     # 8176 B: 511 units
+    (300, 4092, torch.float32, 16),     # 16368 B: the longest (13 slots, 6 consumer warps)
+    (20, 2048, torch.float32, 16),      # fewer rows than SMs
+    (4097, 1024, torch.float32, 16),    # a row count that leaves CTAs with unequal shares
     (1000, 4093, torch.bfloat16, 8),    # short ragged rows, one 128-thread group each
     (3000, 100, torch.float32, 8),      # one warp per row
     (777, 1023, torch.float16, 8),
@@ -262,6 +268,36 @@ def test_resident_variants(cuda_device, rows, classes, dtype, variant):
     eloss_n, _, _ = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, 0.0, "none", want_grad=False)
     assert none is None
     assert_close(loss_n, eloss_n, 2e-6, 2e-6, "row losses")
+
+
+@pytest.mark.parametrize("rows,classes,dtype", [(4096, 2048, torch.float32), (3000, 1000, torch.bfloat16), (900, 4088, torch.float16)])
+def test_short_rows_in_registers_when_forced(cuda_device, rows, classes, dtype):
+    """The register kernel still serves the shapes the slot ring has taken over (tuning key 1 = 8), and both kernels agree
+    with the oracle; between themselves the fp32 results differ only by summation order."""
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(rows + classes)
+    logits = (torch.randn(rows, classes, generator=g) * 2).to(dtype)
+    target = torch.randint(0, classes, (rows,), generator=g)
+    target[::7] = -100
+    code = capi.torch_dtype_code(dtype)
+    assert capi.ce_kernel_variant(code, rows, classes) == 16
+    loss_ring, grad_ring = _run(cuda_device, logits, target, label_smoothing=0.1, reduction="mean")
+    capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, 8))
+    try:
+        assert capi.ce_kernel_variant(code, rows, classes) == 8
+        loss_reg, grad_reg = _run(cuda_device, logits, target, label_smoothing=0.1, reduction="mean")
+    finally:
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(1, -1))
+    eloss, egrad, _ = oracle.c_cross_entropy(logits.float().numpy(), target.numpy(), -100, 0.1, "mean")
+    scale = float((target != -100).sum())
+    for loss, grad in ((loss_ring, grad_ring), (loss_reg, grad_reg)):
+        assert rel_err(loss, eloss[0]) <= (2e-6 if dtype == torch.float32 else 1e-2)
+        if dtype == torch.float32:
+            assert_close(grad * scale, egrad * scale, 1e-5, 3e-7, "grad")
+        else:
+            assert_close(grad * scale, egrad * scale, 1.6e-2 if dtype == torch.bfloat16 else 2e-3,
+                         1e-4 if dtype == torch.bfloat16 else max(2e-5, 2.0 ** -24 * scale), "grad")
 
 
 @pytest.mark.parametrize("rows,classes,dtype", [(40, 50257, torch.bfloat16), (40, 32001, torch.float32), (300, 1001, torch.bfloat16),
