@@ -31,6 +31,8 @@ WORKLOADS = {
     # name: (rows of the whole job, classes, dtype, ignore fraction, label smoothing)
     "ce_bf16_32768x128256": (32768, 128256, "bfloat16", 0.05, 0.1),   # the headline configuration
     "ce_fp32_4096x32000": (4096, 32000, "float32", 0.0, 0.0),          # the reference's own CPU-runnable case
+    "ce_bf16_8192x50257": (8192, 50257, "bfloat16", 0.05, 0.1),        # a vocabulary whose row pitch is not a multiple of 16 bytes
+    "ce_fp32_32768x2048": (32768, 2048, "float32", 0.0, 0.0),          # rows of 8 KB: the shared-memory slot ring
 }
 DEFAULT_WORKLOAD = "ce_bf16_32768x128256"
 
@@ -206,7 +208,8 @@ NCU_TRAFFIC_PER_ROW = {
     "ce_bf16_32768x128256": (998.447616e6 + 995.276288e6) / 4096,
 }
 KERNEL_NAMES = {0: "ce_rows_cta_kernel (two sweeps)", 1: "ce_resident_kernel (1 CTA per row)", 2: "ce_resident_kernel (2-CTA cluster per row)",
-                4: "ce_resident_kernel (4-CTA cluster per row)", 8: "ce_rows_reg_kernel (row in registers)"}
+                4: "ce_resident_kernel (4-CTA cluster per row)", 8: "ce_rows_reg_kernel (row in registers)",
+                16: "ce_ring_rows_kernel (groups of rows on a shared-memory slot ring, one warp per row)"}
 
 
 def workload_config(args, world):

@@ -128,7 +128,7 @@ def run_extras(device, peak_gbs, profile=False):
     x = device_randn((32768, 2048), torch.float32, device, 42, 2.0).requires_grad_(True)
     t = device_randn((32768,), torch.int64, device, 43, low=0, high=2047)
     x2 = device_randn((32768, 2048), torch.float32, device, 44, 2.0).requires_grad_(True)
-    entry("cross_entropy fwd+bwd fp32 [32768,2048] (rows held in registers)", 2 * 32768 * 2048 * 4 + 32768 * 8, [ce_call(x, t), ce_call(x2, t)])
+    entry("cross_entropy fwd+bwd fp32 [32768,2048] (8 KB rows: slot ring, one warp per row)", 2 * 32768 * 2048 * 4 + 32768 * 8, [ce_call(x, t), ce_call(x2, t)])
     del x, t, x2
     torch.supa.empty_cache()
 

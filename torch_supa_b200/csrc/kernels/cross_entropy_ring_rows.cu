@@ -50,7 +50,35 @@ struct alignas(16) RingTail {
   unsigned long long full[kRingMaxSlots];   // loader -> consumers: the group has landed
   unsigned long long done[kRingMaxSlots];   // consumers -> storer: R arrivals, the group holds its gradients
   unsigned long long empty[kRingMaxSlots];  // storer -> loader: the group's store has finished reading the slot
+  // Lap of the ring whose load has been issued into the slot, written by the loader.  A consumer waits on `full` by phase
+  // parity, and different warps take different laps of a slot: a warp that came a whole lap early would see the parity of
+  // the lap before last and walk through.  It therefore first waits until the slot's lap number is its own; from then on
+  // the barrier is in that lap's phase or just past it, and the parity is unambiguous.
+  volatile uint32_t lapno[kRingMaxSlots];
+  volatile uint32_t abort;  // set by the first wait that runs out: every other wait of the CTA gives up too
 };
+
+constexpr uint32_t kRingMaxPolls = 1u << 20;  // try_wait attempts before a wait gives up (a legitimate wait lasts microseconds)
+
+// Bounded wait on an mbarrier phase that also ends when another warp of the CTA has given up.
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort) {
+  for (uint32_t i = 0; i < kRingMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u && *abort) return false;
+  }
+  return false;
+}
+// Bounded wait until the slot's lap number is `lap`.
+__device__ __forceinline__ bool ring_wait_lap(volatile uint32_t* lapno, uint32_t lap, volatile uint32_t* abort) {
+  for (uint32_t i = 0; i < (kRingMaxPolls << 4); ++i) {
+    if (*lapno == lap) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort) return false;
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
 
 // NaN-propagating maximum over the warp in one instruction (redux.sync on f32: sm_100a).
 __device__ __forceinline__ float warp_max_nan(float v) {
@@ -84,11 +112,17 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
       mbar_init(smem_u32(&tail->full[s]), 1);
       mbar_init(smem_u32(&tail->done[s]), R);
       mbar_init(smem_u32(&tail->empty[s]), 1);
+      tail->lapno[s] = 0;
     }
+    tail->abort = 0;
     fence_mbar_init();
   }
   __syncthreads();
 
+  auto give_up = [&]() {
+    tail->abort = 1;
+    if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+  };
   auto rows_in_group = [&](int64_t group) {
     const int64_t left = p.rows - group * R;
     return static_cast<uint32_t>(left < static_cast<int64_t>(R) ? left : R);
@@ -99,14 +133,15 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     const char* logits = static_cast<const char*>(p.logits);
     uint32_t slot = 0, lap = 0;
     for (int64_t k = 0; k < n_local; ++k) {
-      if (lap > 0 && !mbar_wait(smem_u32(&tail->empty[slot]), (lap - 1) & 1)) {
-        if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+      if (lap > 0 && !ring_wait(smem_u32(&tail->empty[slot]), (lap - 1) & 1, &tail->abort)) {
+        give_up();
         break;
       }
       if (lane == 0) {
         const int64_t group = first + k * stride;
         const uint32_t bytes = rows_in_group(group) * row_bytes;
         const uint32_t bar = smem_u32(&tail->full[slot]);
+        tail->lapno[slot] = lap;  // the previous lap of this slot is over (its store has been read): consumers of this lap may wait
         mbar_expect_tx(bar, bytes);
         bulk_g2s(smem_u32(smem + static_cast<size_t>(slot) * slot_bytes), logits + group * static_cast<int64_t>(slot_bytes), bytes, bar);
       }
@@ -124,8 +159,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     uint32_t slot = 0, lap = 0;
     int held[2] = {-1, -1};  // slots of the two most recent stores, oldest first
     for (int64_t k = 0; k < n_local; ++k) {
-      if (!mbar_wait(smem_u32(&tail->done[slot]), lap & 1)) {
-        if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+      if (!ring_wait(smem_u32(&tail->done[slot]), lap & 1, &tail->abort)) {
+        give_up();
         break;
       }
       if (lane == 0) {
@@ -193,8 +228,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     }
     t_next = load_target(nk, nj);
 
-    if (!mbar_wait(smem_u32(&tail->full[slot]), lap & 1)) {
-      if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+    if ((lap > 0 && !ring_wait_lap(&tail->lapno[slot], lap, &tail->abort)) || !ring_wait(smem_u32(&tail->full[slot]), lap & 1, &tail->abort)) {
+      give_up();
       break;
     }
     if (row < p.rows) {  // the last group may have fewer than R rows: the missing ones only arrive
@@ -232,7 +267,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           const float2 negm = make_float2(-mm, -mm);
           float2 s2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
           float2 sx2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-          float2 e[NIT][P];  // fp32: the exponentials stay unpacked; 16-bit: repacked into r[n] below
 #pragma unroll
           for (int n = 0; n < NIT; ++n) {
             if (lane + 32 * n < units) {
@@ -244,10 +278,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
                 const float2 ex = make_float2(ex2(y.x), ex2(y.y));
                 s2[q & 1] = add2(s2[q & 1], ex);
                 if (kSumX) sx2[q & 1] = add2(sx2[q & 1], f[q]);
-                if (sizeof(T) == 4) e[n][q] = ex;
-                else f[q] = ex;
+                f[q] = ex;
               }
-              if (sizeof(T) == 2) r[n] = U::pack(f);
+              r[n] = U::pack(f);  // the exponentials replace the logits (fp32: the same registers)
             }
           }
           float s = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
@@ -270,7 +303,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
             const float sub_all = eps_c * scale;
             const float sub_t = (1.f - eps) * scale;
             const float g_t = fmaf(ex2(fmaf(xt, kLog2e, -lse2)), scale, -sub_all) - sub_t;
-            const uint32_t t_vec = static_cast<uint32_t>(t) / E, t_el = static_cast<uint32_t>(t) % E;
+            const uint32_t t_vec = static_cast<uint32_t>(t) / E;
             const float factor = scale / s;  // kept value * factor = softmax * scale
             const float2 f2 = make_float2(factor, factor), n2 = make_float2(-sub_all, -sub_all);
 #pragma unroll
@@ -280,23 +313,14 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
                 uint4 o;
                 if constexpr (std::is_same<T, __nv_bfloat16>::value) {
                   o = grad_from_kept_bf16(r[n], __float2bfloat162_rn(factor), __float2bfloat162_rn(-sub_all));
-                } else if constexpr (sizeof(T) == 2) {
-                  o = grad_from_kept<T>(r[n], f2, n2);
                 } else {
-                  float2 g[P];
-#pragma unroll
-                  for (int q = 0; q < P; ++q) g[q] = fma2(e[n][q], f2, n2);
-                  o = U::pack(g);
-                }
-                if (v == t_vec) {
-                  T* oe = reinterpret_cast<T*>(&o);
-#pragma unroll
-                  for (int q = 0; q < E; ++q)
-                    if (static_cast<uint32_t>(q) == t_el) oe[q] = from_float<T>(g_t);
+                  o = grad_from_kept<T>(r[n], f2, n2);
                 }
                 buf[v] = o;
               }
             }
+            // the target's class, by the lane that has just stored its unit
+            if (static_cast<uint32_t>(lane) == (t_vec & 31u)) reinterpret_cast<T*>(buf)[t] = from_float<T>(g_t);
           }
         } else {
           // pass 0: the row maximum
@@ -450,6 +474,7 @@ int launch_ring_t(const RingParams& rp, size_t smem, int grid, cudaStream_t st, 
   if (per_lane <= 2) return sx ? launch_ring_cfg<T, true, 2>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 2>(rp, smem, grid, st, pdl);
   if (per_lane <= 4) return sx ? launch_ring_cfg<T, true, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4>(rp, smem, grid, st, pdl);
   if (per_lane <= 8) return sx ? launch_ring_cfg<T, true, 8>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 8>(rp, smem, grid, st, pdl);
+  if (per_lane <= 16) return sx ? launch_ring_cfg<T, true, 16>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 16>(rp, smem, grid, st, pdl);
   return sx ? launch_ring_cfg<T, true, 0>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0>(rp, smem, grid, st, pdl);
 }
 
@@ -484,9 +509,15 @@ int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl) {
   if (nslots > kRingMaxSlots) nslots = kRingMaxSlots;
   if (nslots < 3) return SB_ERR_UNSUPPORTED;
   rp.nslots = nslots;
-  // Consumers leave at least six slots' worth of rows to the loads and stores in flight.
-  uint32_t nwarps = nslots * group_rows > 7 ? nslots * group_rows - 6 : 1;
+  // Consumer warps: the arithmetic per byte is fixed per dtype, so the warps needed to keep up with HBM do not depend on the
+  // row length (measured: about 6 for fp32, 12 for 16-bit logits; more warps than that only take slots away from the loads
+  // and stores in flight: fp32 rows of 8 KB run at 0.89 of the copy peak with 6 warps, 0.83 with 16).  Rows under 4 KB add a
+  // fixed cost per row and take all 16.  At least four slots' worth of rows stay with the copy engine.
+  uint32_t nwarps = rp.row_bytes < 4096 ? kRingWarps : (dtype_size(p.dtype) == 2 ? 12 : 7);
+  const uint32_t held_max = nslots * group_rows > 4 * group_rows + 2 ? nslots * group_rows - 4 * group_rows : 2;
+  if (nwarps > held_max) nwarps = held_max;
   if (nwarps > static_cast<uint32_t>(kRingWarps)) nwarps = kRingWarps;
+  if (nwarps < 2) nwarps = 2;
   if (g_ring_warps > 0 && g_ring_warps <= kRingWarps) nwarps = g_ring_warps;
   rp.nwarps = nwarps;
   const size_t smem = static_cast<size_t>(nslots) * slot_bytes + sizeof(RingTail);
