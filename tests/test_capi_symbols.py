@@ -100,3 +100,46 @@ def test_path_classifier_runs_on_host(kernel_lib):
     assert kernel_lib.sb_elementwise_path(ctypes.byref(transposed)) == 2
     odd = desc(capi.EW_MUL, [5, 7, 3], [[3, 15, 1], [1, 5, 35], [1, 5, 35]], [F32] * 3, F32)
     assert kernel_lib.sb_elementwise_path(ctypes.byref(odd)) == 3
+
+
+def test_ctypes_structures_match_the_header(tmp_path):
+    """Every descriptor the Python binding passes by pointer has the size and the field offsets the C compiler gives the
+    header's struct: a field added to the header but not to the binding makes the library read past the Python buffer."""
+    import subprocess
+
+    from torch_supa_b200 import capi
+
+    pairs = {"sb_ce_args": capi.CEArgs, "sb_xchg": capi.Xchg, "sb_ce_prob_args": capi.CEProbArgs, "sb_rng_args": capi.RngArgs,
+             "sb_nll_args": capi.NLLArgs, "sb_nll_nd_args": capi.NLLNdArgs, "sb_ew_desc": capi.EWDesc, "sb_reduce_desc": capi.ReduceDesc}
+    header = (ROOT / "include" / "supa_b200_kernels.h").read_text()
+    assert set(re.findall(r"typedef struct (sb_\w+) \{", header)) == set(pairs), "a struct of the header has no ctypes mirror (or the reverse)"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "supa_b200_kernels.h"', "int main(void) {"]
+    for name, cls in pairs.items():
+        lines.append(f'  printf("{name} size %zu\\n", sizeof({name}));')
+        body = header[header.index(f"typedef struct {name} {{"):header.index(f"}} {name};")]
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        c_fields = []
+        for statement in body.split("{", 1)[1].split(";"):
+            for declarator in statement.split(","):
+                m = re.search(r"(\w+)\s*(?:\[[^\]]*\])*\s*$", declarator.strip())
+                if m:
+                    c_fields.append(m.group(1))
+        py_fields = [f[0] for f in cls._fields_]
+        assert len(c_fields) == len(py_fields), f"{name}: {c_fields} vs {py_fields}"
+        for c_name in c_fields:
+            lines.append(f'  printf("{name} {c_name} %zu\\n", offsetof({name}, {c_name}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    got = {}
+    for line in out:
+        if line:
+            name, field, value = line.split()
+            got.setdefault(name, []).append((field, int(value)))
+    for name, cls in pairs.items():
+        assert got[name][0] == ("size", ctypes.sizeof(cls)), name
+        offsets = [v for _, v in got[name][1:]]
+        assert offsets == [getattr(cls, f[0]).offset for f in cls._fields_], f"{name}: field offsets differ"
