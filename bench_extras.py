@@ -130,6 +130,12 @@ def run_extras(device, peak_gbs, profile=False):
     x2 = device_randn((32768, 2048), torch.float32, device, 44, 2.0).requires_grad_(True)
     entry("cross_entropy fwd+bwd fp32 [32768,2048] (8 KB rows: slot ring, one warp per row)", 2 * 32768 * 2048 * 4 + 32768 * 8, [ce_call(x, t), ce_call(x2, t)])
     del x, t, x2
+    x = device_randn((131072, 1000), torch.bfloat16, device, 45, 2.0).requires_grad_(True)
+    t = device_randn((131072,), torch.int64, device, 46, low=0, high=999)
+    x2 = device_randn((131072, 1000), torch.bfloat16, device, 47, 2.0).requires_grad_(True)
+    entry("cross_entropy fwd+bwd bf16 [131072,1000] (2000 B rows: slot ring, four rows per bulk copy)", 2 * 131072 * 1000 * 2 + 131072 * 8,
+          [ce_call(x, t, label_smoothing=0.1), ce_call(x2, t, label_smoothing=0.1)])
+    del x, t, x2
     torch.supa.empty_cache()
 
     # ---- SwiGLU chain bf16 ----
@@ -242,5 +248,15 @@ def run_extras(device, peak_gbs, profile=False):
 
     entry("binary_cross_entropy_with_logits mean fwd+bwd fp32 [8192,8192] (2 reads + 2 reads, 1 write)", 5 * nb2, bce_step)
     del bx, bt
+    torch.supa.empty_cache()
+
+    # ---- random fills and dropout from the device generator (Philox4x32-10: bound by the integer multiplier, not by HBM) ----
+    r32 = torch.empty((16384, 16384), dtype=torch.float32, device=device)
+    entry("uniform_ fp32 [16384,16384] (write only; Philox-bound)", 16384 * 16384 * 4, lambda: r32.uniform_())
+    entry("normal_ fp32 [16384,16384] (write only; Box-Muller with logf / sincospif)", 16384 * 16384 * 4, lambda: r32.normal_())
+    del r32
+    dx = device_randn((16384, 11008), torch.bfloat16, device, 18)
+    entry("dropout(p=0.1) bf16 [16384,11008] (read, write + 1-byte mask)", 16384 * 11008 * 5, lambda: F.dropout(dx, 0.1, training=True))
+    del dx
     torch.supa.empty_cache()
     return out

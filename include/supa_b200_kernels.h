@@ -218,7 +218,7 @@ SB_API int sb_ce_loss_static_scratch(const sb_ce_args* args, void* loss_out, sb_
 
 /* Which kernel family sb_ce_forward_backward will use for this shape: 0 = generic two-sweep rows,
  * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
- * of 2/4 CTAs, 16 = aligned rows of 1 KB to 16 KB on the shared-memory slot ring (one warp per row), 8 = other rows
+ * of 2/4 CTAs, 16 = aligned rows of 256 B to 16 KB on the shared-memory slot ring (a warp or part of one per row), 8 = other rows
  * shorter than 16 KB held in registers.  For diagnostics and benchmarks. */
 SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
 

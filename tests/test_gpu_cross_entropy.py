@@ -230,13 +230,19 @@ def test_linearity_property_full_vocab(cuda_device):
     (150, 50257, torch.float32, 2),     # 201028 B: ragged rows over a 2-CTA cluster
     (4096, 2048, torch.float32, 16),    # short aligned rows: one warp per row on the shared-memory slot ring
     (2000, 1000, torch.bfloat16, 16),   # 2000 B rows
-    (700, 512, torch.bfloat16, 16),     # 1 KB: the shortest rows the ring takes (64 slots)
+    (701, 512, torch.bfloat16, 16),     # 1 KB: the shortest rows the ring takes; two rows per warp, an odd row count
+    (900, 256, torch.float32, 16),      # 1 KB of fp32
+    (3001, 128, torch.float32, 16),     # 512 B: four rows per warp
+    (3001, 64, torch.float32, 16),      # 256 B: eight rows per warp, the shortest rows the ring takes
+    (1500, 136, torch.bfloat16, 16),    # 272 B = 17 units: eight lanes per row, most lanes' third unit is missing
+    (333, 500, torch.float32, 16),      # 2000 B of fp32: 125 units, the last lanes' fourth unit is missing
     (500, 4088, torch.float16, 16),     # 8176 B: 511 units
     (300, 4092, torch.float32, 16),     # 16368 B: the longest (13 slots, 6 consumer warps)
     (20, 2048, torch.float32, 16),      # fewer rows than SMs
     (4097, 1024, torch.float32, 16),    # a row count that leaves CTAs with unequal shares
     (1000, 4093, torch.bfloat16, 8),    # short ragged rows, one 128-thread group each
-    (3000, 100, torch.float32, 8),      # one warp per row
+    (3000, 100, torch.float32, 16),     # 400 B = 25 units over eight lanes
+    (3000, 50, torch.float32, 8),       # 200 B: under the ring's 256 B, rows in registers (part of a warp each)
     (777, 1023, torch.float16, 8),
 ])
 def test_resident_variants(cuda_device, rows, classes, dtype, variant):

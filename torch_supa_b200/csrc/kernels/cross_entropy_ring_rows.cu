@@ -1,5 +1,5 @@
-// Cross entropy for rows of 1 KB to 16 KB with a 16-byte aligned pitch: groups of whole rows travel through a ring of
-// shared-memory slots, one warp per row.
+// Cross entropy for rows of 256 B to 16 KB with a 16-byte aligned pitch: groups of whole rows travel through a ring of
+// shared-memory slots, one warp (or 16, 8 or 4 lanes of one) per row.
 //
 // A persistent CTA (one per SM) owns every gridDim.x-th group of R consecutive rows (R rows = about 8 KB: bulk copies of
 // a kilobyte or two each cost the copy engine about as much as one of 8 KB, and a row-sized copy per row held these
@@ -31,7 +31,7 @@ namespace {
 constexpr int kRingWarps = 16;                         // consumer warps in the CTA (the launch may use fewer: RingParams::nwarps)
 constexpr int kRingThreads = (kRingWarps + 2) * 32;    // plus the loader warp and the storer warp
 constexpr int kRingMaxSlots = 32;
-constexpr uint32_t kRingMinRowBytes = 1024;
+constexpr uint32_t kRingMinRowBytes = 256;
 constexpr uint32_t kRingMaxRowBytes = 16384;
 constexpr uint32_t kRingGroupBytes = 8192;             // rows are grouped up to about this size per bulk copy
 int g_ring_warps = 0;  // tuning: consumer warps per CTA (0 = automatic)
@@ -90,8 +90,13 @@ __device__ __forceinline__ float warp_max_nan(float v) {
 // NIT > 0: a lane holds its NIT units of the row in registers between the passes (rows of up to 32 * NIT units): one
 // shared-memory read and one write per unit, exponentials kept for every dtype.  NIT = 0: longer rows, three passes over
 // shared memory.
-template <typename T, bool kSumX, int NIT>
+// LPR: lanes per row.  32 = one row per warp; 16 / 8 / 4 = two / four / eight rows per warp side by side (rows of up to
+// 1 KB / 512 B / 256 B, where the fixed cost per row, about 250 instructions, outweighs the arithmetic on the logits): each
+// group of LPR lanes is a consumer of its own with its own place in the CTA's row sequence, and every warp-level primitive
+// is confined to the group.
+template <typename T, bool kSumX, int NIT, int LPR>
 __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParams rp) {
+  static_assert(LPR == 32 || ((LPR == 16 || LPR == 8 || LPR == 4) && NIT > 0), "rows that share a warp stay in registers");
   using U = Unit<T>;
   constexpr int P = U::kPairs;
   constexpr int E = 16 / static_cast<int>(sizeof(T));
@@ -121,7 +126,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
 
   auto give_up = [&]() {
     tail->abort = 1;
-    if (lane == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
+    if ((lane & (LPR - 1)) == 0 && p.status) atomicOr(p.status, SB_STATUS_KERNEL_TIMEOUT);
   };
   auto rows_in_group = [&](int64_t group) {
     const int64_t left = p.rows - group * R;
@@ -194,6 +199,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
 
   // ---- consumers -------------------------------------------------------------------------------------------------------
   if (static_cast<uint32_t>(warp) >= nwarps) return;
+  constexpr uint32_t kSubs = 32 / LPR;                        // consumers per warp
+  const uint32_t sub = static_cast<uint32_t>(lane) / LPR;     // which of them this lane belongs to
+  const uint32_t sl = static_cast<uint32_t>(lane) % LPR;      // lane within the consumer
+  const uint32_t gmask = LPR == 32 ? 0xffffffffu : (((1u << (LPR & 31)) - 1u) << (LPR * sub));
+  const uint32_t me = static_cast<uint32_t>(warp) * kSubs + sub, consumers = nwarps * kSubs;
   auto valid_target = [&](int64_t t) { return t != p.ignore_index && t >= 0 && t < p.classes; };
   const float eps = p.label_smoothing;
   const float eps_c = eps / static_cast<float>(p.classes);
@@ -203,10 +213,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     base_scale = static_cast<float>(static_cast<double>(p.grad_scale) / p.acc[1]);
   }
   const float2 l2e2 = make_float2(kLog2e, kLog2e);
-  // Sequence number i = k * R + j: row j of the CTA's k-th group.  (k, j) advance by nwarps per step without a division.
-  uint32_t j = static_cast<uint32_t>(warp) % R;
-  int64_t k = static_cast<uint32_t>(warp) / R;
-  const uint32_t step_j = nwarps % R, step_k = nwarps / R;
+  // Sequence number i = k * R + j: row j of the CTA's k-th group.  (k, j) advance by the number of consumers per step without
+  // a division.
+  uint32_t j = me % R;
+  int64_t k = me / R;
+  const uint32_t step_j = consumers % R, step_k = consumers / R;
   uint32_t slot = static_cast<uint32_t>(k) % nslots, lap = static_cast<uint32_t>(k) / nslots;
   auto row_of = [&](int64_t kk, uint32_t jj) { return (first + kk * stride) * R + jj; };
   auto load_target = [&](int64_t kk, uint32_t jj) {
@@ -234,17 +245,17 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     }
     if (row < p.rows) {  // the last group may have fewer than R rows: the missing ones only arrive
       const bool ignored = !valid_target(t);
-      if (ignored && t != p.ignore_index && lane == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+      if (ignored && t != p.ignore_index && sl == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
       float wt = 1.f;
       if (p.class_weight && !ignored) wt = p.class_weight[t];
       uint4* buf = reinterpret_cast<uint4*>(smem + static_cast<size_t>(slot) * slot_bytes + static_cast<size_t>(j) * row_bytes);
       if (ignored) {
-        if (lane == 0) {
+        if (sl == 0) {
           p.row_loss[row] = 0.f;
           if (p.row_lse) p.row_lse[row] = 0.f;
         }
         if (p.grad) {
-          for (uint32_t v = lane; v < units; v += 32) buf[v] = make_uint4(0u, 0u, 0u, 0u);
+          for (uint32_t v = sl; v < units; v += LPR) buf[v] = make_uint4(0u, 0u, 0u, 0u);
         }
       } else {
         if constexpr (NIT > 0) {
@@ -253,7 +264,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           float vm = -CUDART_INF_F;
 #pragma unroll
           for (int n = 0; n < NIT; ++n) {
-            const uint32_t v = lane + 32 * n;
+            const uint32_t v = sl + LPR * n;
             if (v < units) {
               r[n] = buf[v];
               vm = max_nan(vm, U::vmax(r[n]));
@@ -261,7 +272,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           }
           const float xt = to_float(reinterpret_cast<const T*>(buf)[t]);  // read before any lane stores a gradient (the
                                                                            // warp-wide reductions below lie in between)
-          vm = warp_max_nan(vm);
+          if constexpr (LPR == 32) {
+            vm = warp_max_nan(vm);
+          } else {
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) vm = max_nan(vm, __shfl_xor_sync(gmask, vm, o));
+          }
           const float m2 = vm * kLog2e;
           const float mm = (m2 == -CUDART_INF_F) ? 0.f : m2;
           const float2 negm = make_float2(-mm, -mm);
@@ -269,7 +285,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           float2 sx2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
           for (int n = 0; n < NIT; ++n) {
-            if (lane + 32 * n < units) {
+            if (sl + LPR * n < units) {
               float2 f[P];
               U::unpack(r[n], f);
 #pragma unroll
@@ -286,13 +302,13 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           float s = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
           float sx = (sx2[0].x + sx2[0].y) + (sx2[1].x + sx2[1].y);
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (kSumX) sx += __shfl_xor_sync(0xffffffffu, sx, o);
+          for (int o = LPR / 2; o > 0; o >>= 1) {
+            s += __shfl_xor_sync(gmask, s, o);
+            if (kSumX) sx += __shfl_xor_sync(gmask, sx, o);
           }
           const float lse2 = m2 + log2f(s);
           const float lse = lse2 * kLn2;
-          if (lane == 0) {
+          if (sl == 0) {
             p.row_loss[row] = ce_row_loss(lse, xt, sx, eps, eps_c) * wt;
             if (p.row_lse) p.row_lse[row] = lse;
           }
@@ -308,7 +324,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
             const float2 f2 = make_float2(factor, factor), n2 = make_float2(-sub_all, -sub_all);
 #pragma unroll
             for (int n = 0; n < NIT; ++n) {
-              const uint32_t v = lane + 32 * n;
+              const uint32_t v = sl + LPR * n;
               if (v < units) {
                 uint4 o;
                 if constexpr (std::is_same<T, __nv_bfloat16>::value) {
@@ -320,12 +336,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               }
             }
             // the target's class, by the lane that has just stored its unit
-            if (static_cast<uint32_t>(lane) == (t_vec & 31u)) reinterpret_cast<T*>(buf)[t] = from_float<T>(g_t);
+            if (sl == t_vec % LPR) reinterpret_cast<T*>(buf)[t] = from_float<T>(g_t);
           }
         } else {
           // pass 0: the row maximum
           float vm = -CUDART_INF_F;
-  #pragma unroll 4
+#pragma unroll 4
           for (uint32_t v = lane; v < units; v += 32) vm = max_nan(vm, U::vmax(buf[v]));
           vm = warp_max_nan(vm);
           const float m2 = vm * kLog2e;
@@ -336,11 +352,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           const float2 negm = make_float2(-mm, -mm);
           float2 s2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
           float2 sx2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-  #pragma unroll 4
+#pragma unroll 4
           for (uint32_t v = lane; v < units; v += 32) {
             float2 f[P];
             U::unpack(buf[v], f);
-  #pragma unroll
+#pragma unroll
             for (int q = 0; q < P; ++q) {
               const float2 y = fma2(f[q], l2e2, negm);
               const float2 e = make_float2(ex2(y.x), ex2(y.y));
@@ -352,7 +368,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           }
           float s = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
           float sx = (sx2[0].x + sx2[0].y) + (sx2[1].x + sx2[1].y);
-  #pragma unroll
+#pragma unroll
           for (int o = 16; o > 0; o >>= 1) {
             s += __shfl_xor_sync(0xffffffffu, s, o);
             if (kSumX) sx += __shfl_xor_sync(0xffffffffu, sx, o);
@@ -374,7 +390,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
             const uint32_t t_vec = static_cast<uint32_t>(t) / E, t_el = static_cast<uint32_t>(t) % E;
             auto patch = [&](uint4 o) {
               T* oe = reinterpret_cast<T*>(&o);
-  #pragma unroll
+#pragma unroll
               for (int q = 0; q < E; ++q)
                 if (static_cast<uint32_t>(q) == t_el) oe[q] = from_float<T>(g_t);
               return o;
@@ -383,7 +399,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               const float factor = scale / s;  // kept value * factor = softmax * scale
               if constexpr (std::is_same<T, __nv_bfloat16>::value) {
                 const __nv_bfloat162 f2 = __float2bfloat162_rn(factor), n2 = __float2bfloat162_rn(-sub_all);
-  #pragma unroll 4
+#pragma unroll 4
                 for (uint32_t v = lane; v < units; v += 32) {
                   uint4 o = grad_from_kept_bf16(buf[v], f2, n2);
                   if (v == t_vec) o = patch(o);
@@ -391,7 +407,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
                 }
               } else {
                 const float2 f2 = make_float2(factor, factor), n2 = make_float2(-sub_all, -sub_all);
-  #pragma unroll 4
+#pragma unroll 4
                 for (uint32_t v = lane; v < units; v += 32) {
                   uint4 o = grad_from_kept<T>(buf[v], f2, n2);
                   if (v == t_vec) o = patch(o);
@@ -400,7 +416,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               }
             } else {
               const float2 nl2 = make_float2(-lse2, -lse2), sc2 = make_float2(scale, scale), n2 = make_float2(-sub_all, -sub_all);
-  #pragma unroll 4
+#pragma unroll 4
               for (uint32_t v = lane; v < units; v += 32) {
                 uint4 o = grad_vector<T>(buf[v], nl2, sc2, n2);
                 if (v == t_vec) o = patch(o);
@@ -412,8 +428,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
       }
       if (p.grad) fence_proxy_async();  // this lane's writes to the slot, before the bulk store reads them
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&tail->done[slot]));
+    __syncwarp(gmask);
+    if (sl == 0) mbar_arrive(smem_u32(&tail->done[slot]));
     slot += static_cast<uint32_t>(nk - k);
     while (slot >= nslots) {
       slot -= nslots;
@@ -435,9 +451,9 @@ size_t ring_smem_limit() {
   return limit;
 }
 
-template <typename T, bool SUMX, int NIT>
+template <typename T, bool SUMX, int NIT, int LPR>
 int launch_ring_cfg(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
-  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT>;
+  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT, LPR>;
   static bool configured = false;  // per instantiation; the attribute is per device, set again after a device change is harmless
   static int configured_dev = -1;
   int dev = 0;
@@ -469,13 +485,17 @@ int launch_ring_cfg(const RingParams& rp, size_t smem, int grid, cudaStream_t st
 
 template <typename T>
 int launch_ring_t(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
-  const uint32_t per_lane = (rp.units + 31) / 32;
   const bool sx = rp.p.label_smoothing != 0.f;
-  if (per_lane <= 2) return sx ? launch_ring_cfg<T, true, 2>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 2>(rp, smem, grid, st, pdl);
-  if (per_lane <= 4) return sx ? launch_ring_cfg<T, true, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4>(rp, smem, grid, st, pdl);
-  if (per_lane <= 8) return sx ? launch_ring_cfg<T, true, 8>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 8>(rp, smem, grid, st, pdl);
-  if (per_lane <= 16) return sx ? launch_ring_cfg<T, true, 16>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 16>(rp, smem, grid, st, pdl);
-  return sx ? launch_ring_cfg<T, true, 0>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0>(rp, smem, grid, st, pdl);
+  const uint32_t u = rp.units;
+  // Rows of 1 KB: two rows per warp (bf16 [131072,512]: 0.71 of the copy peak against 0.54 with a warp per row; for rows of
+  // 2 KB the same split measured slower, 0.75 against 0.82).  Longer ones: one row per warp, in registers up to 8 KB.
+  if (u <= 16) return sx ? launch_ring_cfg<T, true, 4, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 4>(rp, smem, grid, st, pdl);
+  if (u <= 32) return sx ? launch_ring_cfg<T, true, 4, 8>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 8>(rp, smem, grid, st, pdl);
+  if (u <= 64) return sx ? launch_ring_cfg<T, true, 4, 16>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 16>(rp, smem, grid, st, pdl);
+  if (u <= 128) return sx ? launch_ring_cfg<T, true, 4, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 32>(rp, smem, grid, st, pdl);
+  if (u <= 256) return sx ? launch_ring_cfg<T, true, 8, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 8, 32>(rp, smem, grid, st, pdl);
+  if (u <= 512) return sx ? launch_ring_cfg<T, true, 16, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 16, 32>(rp, smem, grid, st, pdl);
+  return sx ? launch_ring_cfg<T, true, 0, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32>(rp, smem, grid, st, pdl);
 }
 
 }  // namespace
