@@ -171,11 +171,38 @@ __global__ void __launch_bounds__(256) lsm_fwd_strided_kernel(const Tin* __restr
 }
 
 // ---- backward: log_softmax: grad_in = g - exp(y) * sum(g);  softmax: grad_in = y * (g - sum(g * y)) -------
+// The row of g is read twice (for the sum, then for the result).  The first read asks L2 to keep the lines (evict_last),
+// the second one and the single read of y release them (evict_first): with several hundred rows of 100 KB and more in flight
+// next to the streams of y and of the result, the second read of g otherwise misses L2 for part of the row.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+template <typename A, typename T, int VEC>
+__device__ __forceinline__ void load_hinted(const T* p, A (&out)[VEC], uint64_t policy) {
+  if constexpr (sizeof(T) * VEC == 16) {
+    uint4 raw;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                 : "l"(p), "l"(policy));
+    load_as<A, T, VEC>(&raw, out);
+  } else {
+    load_as<A, T, VEC>(p, out);
+  }
+}
+
 template <typename T, typename Tgi, typename A, int VEC, int THREADS, bool LOG>
 __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
                                                               Tgi* __restrict__ gin, int64_t rows, int64_t C) {
   __shared__ A sm[32];
   const int64_t nvec = C / VEC;
+  const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* g = gout + row * C;
     const T* y = yout + row * C;
@@ -183,13 +210,13 @@ __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restric
     A acc = 0;
     for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
       A f[VEC];
-      load_as<A, T, VEC>(g + i * VEC, f);
+      load_hinted<A, T, VEC>(g + i * VEC, f, keep);
       if (LOG) {
 #pragma unroll
         for (int k = 0; k < VEC; ++k) acc += f[k];
       } else {
         A yy[VEC];
-        load_as<A, T, VEC>(y + i * VEC, yy);
+        load_hinted<A, T, VEC>(y + i * VEC, yy, keep);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) acc += f[k] * yy[k];
       }
@@ -197,10 +224,14 @@ __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restric
     const A sum = block_sum<A, THREADS>(acc, sm);
     for (int64_t i = threadIdx.x; i < nvec; i += THREADS) {
       A f[VEC], yy[VEC];
-      load_as<A, T, VEC>(g + i * VEC, f);
-      load_as<A, T, VEC>(y + i * VEC, yy);
+      load_hinted<A, T, VEC>(g + i * VEC, f, stream);
+      load_hinted<A, T, VEC>(y + i * VEC, yy, stream);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) f[k] = LOG ? f[k] - acc_exp<A>(yy[k]) * sum : yy[k] * (f[k] - sum);
+      for (int k = 0; k < VEC; ++k) {
+        // 16-bit results: the approximate exponential (2 ulp of fp32) is far inside the rounding of the result
+        if constexpr (LOG && sizeof(Tgi) == 2 && std::is_same<A, float>::value) f[k] = f[k] - exp_fast(yy[k]) * sum;
+        else f[k] = LOG ? f[k] - acc_exp<A>(yy[k]) * sum : yy[k] * (f[k] - sum);
+      }
       store_as<A, Tgi, VEC>(o + i * VEC, f);
     }
   }
@@ -284,11 +315,18 @@ int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int
   const int sms = sm_count();
   if (inner == 1 && D > 1024) {
     constexpr int kVec = 16 / sizeof(T);
-    constexpr int kThreads = 512;
-    const int grid = static_cast<int>(outer < 4LL * sms ? outer : 4LL * sms);
     const size_t gi_align = sizeof(Tgi) * kVec >= 16 ? 16 : sizeof(Tgi) * kVec;
     const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(gout) % 16 == 0 &&
                          reinterpret_cast<uintptr_t>(yout) % 16 == 0 && reinterpret_cast<uintptr_t>(gin) % gi_align == 0;
+    // Rows of 64 KB and more: fewer, larger CTAs, so that the rows being re-read (two per SM) stay a fraction of L2.
+    if (aligned && static_cast<size_t>(D) * sizeof(T) >= 65536) {
+      constexpr int kBig = 1024;
+      const int grid = static_cast<int>(outer < 2LL * sms ? outer : 2LL * sms);
+      lsm_bwd_cta_kernel<T, Tgi, A, kVec, kBig, LOG><<<grid, kBig, 0, st>>>(g, y, o, outer, D);
+      return launch_status();
+    }
+    constexpr int kThreads = 512;
+    const int grid = static_cast<int>(outer < 4LL * sms ? outer : 4LL * sms);
     if (aligned) lsm_bwd_cta_kernel<T, Tgi, A, kVec, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
     else lsm_bwd_cta_kernel<T, Tgi, A, 1, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
     return launch_status();
