@@ -120,6 +120,14 @@ def run_extras(device, peak_gbs, profile=False):
     del sets, cx, ct
     torch.supa.empty_cache()
 
+    # ---- cross entropy with class-probability targets (logits and targets read, gradient written) ----
+    x = device_randn((4096, 32000), torch.float32, device, 48, 2.0).requires_grad_(True)
+    q = torch.softmax(device_randn((4096, 32000), torch.float32, device, 49, 2.0), -1)
+    entry("cross_entropy fwd+bwd fp32 [4096,32000], probability targets (2 reads + 1 write; two sweeps, second from L2)", 3 * 4096 * 32000 * 4,
+          ce_call(x, q))
+    del x, q
+    torch.supa.empty_cache()
+
     # ---- cross entropy on row shapes outside the benchmark's: a vocabulary whose pitch is not a multiple of 16 bytes, short rows ----
     x = device_randn((8192, 50257), torch.bfloat16, device, 40, 2.0).requires_grad_(True)
     t = device_randn((8192,), torch.int64, device, 41, low=0, high=50256)

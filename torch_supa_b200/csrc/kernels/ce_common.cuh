@@ -52,6 +52,37 @@ __device__ __forceinline__ void ce_store_loss(double loss_sum, double count, int
   }
 }
 
+// ---- L2 residency hints for rows that are read twice --------------------------------------------------------------------
+// A two-sweep kernel reads a row, reduces it and reads it again.  The first read asks L2 to keep the lines (evict_last); the
+// second one, and everything read once, releases them (evict_first).
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ld_hint_u4(const void* p, uint64_t policy) {
+  uint4 r;
+  asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p), "l"(policy));
+  return r;
+}
+// 16-byte vector load with a policy; other widths load plainly.
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_vec_hint(const T* p, uint64_t policy) {
+  if constexpr (sizeof(T) * N == 16) {
+    const uint4 raw = ld_hint_u4(p, policy);
+    return *reinterpret_cast<const Vec<T, N>*>(&raw);
+  } else {
+    return load_vec<T, N>(p);
+  }
+}
+
 // Kernel families (defined in cross_entropy.cu, cross_entropy_rows.cu and cross_entropy_tma.cu).
 int ce_launch_generic(const CEParams& p, cudaStream_t st);
 int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant, bool pdl);

@@ -6,8 +6,8 @@
 //   loss_i  = sum_c w_c q_ic (lse_i - x_ic) = A_i lse_i - B_i,   A_i = sum_c w_c q_ic,  B_i = sum_c w_c q_ic x_ic
 //   grad_ic = (exp(x_ic - lse_i) A_i - w_c q_ic) * scale_i
 // One CTA per row, grid-stride over rows: the first sweep streams the logits and the target row together (online
-// max / sum of exponentials, A, B), the second forms the gradient; the second read of both rows is served by L1 / L2
-// because the CTA has just streamed them.  16-byte accesses when the row pitch allows it.
+// max / sum of exponentials, A, B), the second forms the gradient; the second read of both rows is served by L2 (the first
+// read asks it to keep the lines, the second releases them).  16-byte accesses when the row pitch allows it.
 #include "ce_common.cuh"
 
 namespace sb {
@@ -36,13 +36,15 @@ __global__ void __launch_bounds__(THREADS) ce_prob_rows_kernel(ProbParams p) {
   const float keep = 1.f - p.eps;
   const float eps_c = p.eps / static_cast<float>(C);
 
+  const uint64_t l2_keep = l2_policy_keep(), l2_stream = l2_policy_stream();
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const T* x = static_cast<const T*>(p.logits) + row * C;
     const T* tq = static_cast<const T*>(p.target) + row * C;
     float m = -CUDART_INF_F, s = 0.f, a = 0.f, b = 0.f;
     for (int64_t i = tid; i < nvec; i += THREADS) {
-      const Vec<T, VEC> v = load_vec<T, VEC>(x + i * VEC);
-      const Vec<T, VEC> tv = load_vec<T, VEC>(tq + i * VEC);
+      // the gradient sweep reads both rows again: ask L2 to keep them (without a gradient they are read once)
+      const Vec<T, VEC> v = load_vec_hint<T, VEC>(x + i * VEC, p.grad ? l2_keep : l2_stream);
+      const Vec<T, VEC> tv = load_vec_hint<T, VEC>(tq + i * VEC, p.grad ? l2_keep : l2_stream);
       float f[VEC];
       float vmax = -CUDART_INF_F;
 #pragma unroll
@@ -96,8 +98,8 @@ __global__ void __launch_bounds__(THREADS) ce_prob_rows_kernel(ProbParams p) {
       const float pa = s_out[1] * scale;  // what the softmax is multiplied by
       T* g = static_cast<T*>(p.grad) + row * C;
       for (int64_t i = tid; i < nvec; i += THREADS) {
-        const Vec<T, VEC> v = load_vec<T, VEC>(x + i * VEC);
-        const Vec<T, VEC> tv = load_vec<T, VEC>(tq + i * VEC);
+        const Vec<T, VEC> v = load_vec_hint<T, VEC>(x + i * VEC, l2_stream);
+        const Vec<T, VEC> tv = load_vec_hint<T, VEC>(tq + i * VEC, l2_stream);
         Vec<T, VEC> o;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {

@@ -174,23 +174,10 @@ __global__ void __launch_bounds__(256) lsm_fwd_strided_kernel(const Tin* __restr
 // The row of g is read twice (for the sum, then for the result).  The first read asks L2 to keep the lines (evict_last),
 // the second one and the single read of y release them (evict_first): with several hundred rows of 100 KB and more in flight
 // next to the streams of y and of the result, the second read of g otherwise misses L2 for part of the row.
-__device__ __forceinline__ uint64_t l2_policy_keep() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_stream() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
 template <typename A, typename T, int VEC>
 __device__ __forceinline__ void load_hinted(const T* p, A (&out)[VEC], uint64_t policy) {
   if constexpr (sizeof(T) * VEC == 16) {
-    uint4 raw;
-    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                 : "l"(p), "l"(policy));
+    const uint4 raw = ld_hint_u4(p, policy);
     load_as<A, T, VEC>(&raw, out);
   } else {
     load_as<A, T, VEC>(p, out);
