@@ -143,6 +143,31 @@ def test_outer_broadcast_binary_ops(cuda_device, shape, dtype):
                 _cmp(out, ref, dtype, "div")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_outer_broadcast_16_bit_on_every_bit_pattern(cuda_device, dtype):
+    """add / sub / mul of the outer-broadcast form run on packed 16-bit pairs without widening.  Operands drawn from all
+    65536 bit patterns (subnormals, infinities, NaNs, exponents 30 binades apart, sums that fall on rounding ties) must give
+    the bits of the widen-operate-round route that PyTorch's CPU kernels take; with alpha != 1 the fp32 route is used."""
+    from torch_supa_b200 import capi
+
+    g = torch.Generator().manual_seed(11)
+    a = torch.randint(-32768, 32768, (24, 1, 4096), generator=g, dtype=torch.int32).to(torch.int16).view(dtype)
+    b = torch.randint(-32768, 32768, (1, 20, 4096), generator=g, dtype=torch.int32).to(torch.int16).view(dtype)
+    # neighbours in magnitude as well: the same patterns with a few low bits changed
+    b[0, :10] = (a[:10, 0].view(torch.int16) ^ torch.randint(0, 8, (10, 4096), generator=g, dtype=torch.int32).to(torch.int16)).view(dtype)
+    for op, fn in ((capi.EW_ADD, torch.add), (capi.EW_SUB, torch.sub), (capi.EW_MUL, torch.mul)):
+        for x, y in ((a, b), (b, a)):
+            out = _ew(cuda_device, op, (24, 20, 4096), dtype, x, y)
+            ref = fn(x, y)
+            nan = torch.isnan(ref)
+            assert torch.equal(torch.isnan(out), nan), (op, "NaN positions")
+            assert torch.equal(out.view(torch.int16)[~nan], ref.view(torch.int16)[~nan]), (op, x is a)
+    out = _ew(cuda_device, capi.EW_ADD, (24, 20, 4096), dtype, a, b, alpha=0.5)
+    ref = torch.add(a, b, alpha=0.5)
+    ok = torch.isfinite(ref)
+    assert torch.equal(out[ok], ref[ok])
+
+
 def test_transposed_operand_mul_both_orders(cuda_device):
     from torch_supa_b200 import capi, functional as F2
 

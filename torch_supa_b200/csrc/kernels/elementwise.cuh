@@ -582,6 +582,69 @@ __global__ void __launch_bounds__(kEwThreads) ew_outer_kernel(EwParams p, uint32
   }
 }
 
+// The outer-broadcast form for add / sub (alpha = 1) / mul with all three operands of one 16-bit floating type, on packed
+// pairs without widening.  The result is bit for bit the one of the fp32 route (widen, operate, round): the product of two
+// such values is exact in fp32, and so is their sum whenever the exponents are close enough for the smaller operand to
+// reach the rounding position of the result (more than 13 binades apart for fp16, 16 for bf16, the smaller one cannot
+// change the rounded result either way), so the fp32 route rounds once as well.  Four packed instructions per 16-byte result
+// instead of eight conversions, eight fp32 operations and four packs.
+template <typename S, int OPK>
+__device__ __forceinline__ uint32_t native16_pair(uint32_t a, uint32_t b) {
+  if constexpr (std::is_same<S, __half>::value) {
+    const __half2 x = *reinterpret_cast<const __half2*>(&a), y = *reinterpret_cast<const __half2*>(&b);
+    const __half2 r = OPK == 0 ? __hadd2(x, y) : (OPK == 1 ? __hmul2(x, y) : __hsub2(x, y));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&a), y = *reinterpret_cast<const __nv_bfloat162*>(&b);
+    const __nv_bfloat162 r = OPK == 0 ? __hadd2(x, y) : (OPK == 1 ? __hmul2(x, y) : __hsub2(x, y));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+// OPK: 0 add, 1 mul, 2 sub (first operand minus second).  KX as in ew_outer_kernel.
+template <typename S, int OPK, int R1, int R2, int KX>
+__global__ void __launch_bounds__(kEwThreads) ew_outer_native16_kernel(EwParams p, uint32_t tiles1, uint32_t tiles2) {
+  static_assert(sizeof(S) == 2 && kEwVec == 8, "one 16-byte vector of eight 16-bit values");
+  constexpr int KY = 1 - KX;
+  const uint32_t nv = p.sizes[0] / kEwVec;
+  const uint64_t item = static_cast<uint64_t>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const uint32_t v = static_cast<uint32_t>(item % nv);
+  uint64_t t = item / nv;
+  const uint32_t t1 = static_cast<uint32_t>(t % tiles1);
+  t /= tiles1;
+  const uint32_t t2 = static_cast<uint32_t>(t % tiles2);
+  const uint64_t i3 = t / tiles2;
+  if (i3 >= p.sizes[3]) return;
+  const uint32_t i1 = t1 * R1, i2 = t2 * R2;
+  const int64_t col = static_cast<int64_t>(v) * kEwVec;
+  const S* xs = static_cast<const S*>(p.data[KX + 1]) + col + i3 * p.strides[KX + 1][3];
+  const S* ys = static_cast<const S*>(p.data[KY + 1]) + col + i3 * p.strides[KY + 1][3];
+  S* os = static_cast<S*>(p.data[0]) + col + i3 * p.strides[0][3];
+  uint4 x[R2], y[R1];
+#pragma unroll
+  for (int r = 0; r < R2; ++r)
+    if (i2 + r < p.sizes[2]) x[r] = *reinterpret_cast<const uint4*>(xs + (i2 + r) * p.strides[KX + 1][2]);
+#pragma unroll
+  for (int r = 0; r < R1; ++r)
+    if (i1 + r < p.sizes[1]) y[r] = *reinterpret_cast<const uint4*>(ys + (i1 + r) * p.strides[KY + 1][1]);
+#pragma unroll
+  for (int r2 = 0; r2 < R2; ++r2) {
+#pragma unroll
+    for (int r1 = 0; r1 < R1; ++r1) {
+      if (i2 + r2 < p.sizes[2] && i1 + r1 < p.sizes[1]) {
+        // operand order: input 0 op input 1
+        const uint4& a = KX == 0 ? x[r2] : y[r1];
+        const uint4& b = KX == 0 ? y[r1] : x[r2];
+        uint4 o;
+        o.x = native16_pair<S, OPK>(a.x, b.x);
+        o.y = native16_pair<S, OPK>(a.y, b.y);
+        o.z = native16_pair<S, OPK>(a.z, b.z);
+        o.w = native16_pair<S, OPK>(a.w, b.w);
+        st_stream_u4(os + (i2 + r2) * p.strides[0][2] + (i1 + r1) * p.strides[0][1], o);
+      }
+    }
+  }
+}
+
 // ---- path 2: tiled transpose ------------------------------------------------------------------------------
 // 32 x 32 tile over (dim0, dim1); dims 2.. are walked by blockIdx.z (flattened).  Operands whose unit
 // stride lies along dim1 are read with threads along dim1 and turned through shared memory.
@@ -806,6 +869,17 @@ int ew_launch_vector(const sb_ew_desc* d, const EwPlan& plan, cudaStream_t st) {
       const uint64_t items = static_cast<uint64_t>(p.sizes[0] / kEwVec) * tiles1 * tiles2 * p.sizes[3];
       const uint64_t blocks = (items + kEwThreads - 1) / kEwThreads;
       if (blocks > 0x7fffffffULL) return SB_ERR_TOO_LARGE;
+      if constexpr (!IO::kDynamic && std::is_same<CT, float>::value && (OP == SB_EW_ADD || OP == SB_EW_SUB || OP == SB_EW_MUL)) {
+        using S = typename IO::storage;
+        if constexpr (std::is_same<S, __half>::value || std::is_same<S, __nv_bfloat16>::value) {
+          if (OP == SB_EW_MUL || p.alpha == 1.0) {  // the packed route has no alpha
+            constexpr int kOpk = OP == SB_EW_ADD ? 0 : (OP == SB_EW_MUL ? 1 : 2);
+            if (plan.outer == 1) ew_outer_native16_kernel<S, kOpk, R1, R2, 0><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
+            else ew_outer_native16_kernel<S, kOpk, R1, R2, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
+            return launch_status();
+          }
+        }
+      }
       if (plan.outer == 1) ew_outer_kernel<Op, CT, IO, R1, R2, 0><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
       else ew_outer_kernel<Op, CT, IO, R1, R2, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, st>>>(p, tiles1, tiles2);
       return launch_status();
