@@ -218,7 +218,7 @@ SB_API int sb_ce_loss_static_scratch(const sb_ce_args* args, void* loss_out, sb_
 
 /* Which kernel family sb_ce_forward_backward will use for this shape: 0 = generic two-sweep rows,
  * 1 = row resident in shared memory of one CTA (TMA bulk ring), 2/4 = resident across a cluster
- * of 2/4 CTAs, 16 = aligned rows of 256 B to 16 KB on the shared-memory slot ring (a warp or part of one per row), 8 = other rows
+ * of 2/4 CTAs, 16 = aligned rows of 256 B to 32 KB on the shared-memory slot ring (part of a warp, a warp or four warps per row), 8 = other rows
  * shorter than 16 KB held in registers.  For diagnostics and benchmarks. */
 SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
 
@@ -231,7 +231,8 @@ SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
  * key 3 = how the resident kernel forms bf16 gradients: 1 (default) rescales the exponentials kept from the statistics
  * sweep (one ex2 per logit, one more bf16 rounding), 0 recomputes them (two ex2 per logit);
  * key 5 = limit, in milliseconds, of the waits of sb_ce_count_exchange / sb_ce_loss_exchange (1..60000, default 10000);
- * key 6 = consumer warps per CTA of the slot-ring kernel (0 automatic, 1..16). */
+ * key 6 = consumer warps per CTA of the slot-ring kernel (0 automatic, 1..16);
+ * key 7 = longest row, in bytes, the slot-ring kernel takes (16384..65536, default 32768). */
 SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------

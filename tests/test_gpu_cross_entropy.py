@@ -212,7 +212,11 @@ def test_linearity_property_full_vocab(cuda_device):
 
 
 @pytest.mark.parametrize("rows,classes,dtype,variant", [
-    (300, 4100, torch.float32, 1),      # 16400 B: two chunks, the second one unit shorter
+    (300, 4100, torch.float32, 16),     # 16400 B: the shortest rows a team of four warps sweeps (1025 units)
+    (200, 8192, torch.float32, 16),     # 32 KB: the longest rows of the slot ring (6 slots, three teams)
+    (200, 16384, torch.bfloat16, 16),   # 32 KB of bf16
+    (300, 12000, torch.float16, 16),    # 24000 B
+    (100, 8196, torch.float32, 1),      # 32784 B: just past the ring, resident in one CTA (five chunks, the last one short)
     (300, 32000, torch.float32, 1),     # the fp32 benchmark row
     (200, 45000, torch.float32, 1),     # 180000 B: about the largest single-CTA rows
     (200, 50000, torch.float32, 2),     # 200000 B: leaves no spare buffers in one CTA, goes to a 2-CTA cluster

@@ -89,10 +89,11 @@ int ce_launch_resident(const CEParams& p, cudaStream_t st, int variant, bool pdl
 // Rows of less than 16 KB held in registers (one warp or one 128-thread group per row): one read and one write
 // per logit.  rows_reg_applies says whether the shape and the pointers qualify.
 bool rows_reg_applies(int dtype, int64_t classes, const void* logits, const void* grad);
-// Rows of 256 B to 16 KB with a 16-byte aligned pitch, a warp (or part of one) per row on a ring of shared-memory slots fed by
+// Rows of 256 B to 32 KB with a 16-byte aligned pitch, a warp (part of one, or four) per row on a ring of shared-memory slots fed by
 // bulk copies.
 bool ring_rows_applies(int dtype, int64_t classes, const void* logits, const void* grad);
 int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl);
+int ring_set_max_bytes(int n);  // tuning: longest row the slot-ring kernel takes (16384..65536)
 int ring_set_warps(int n);  // tuning: consumer warps per CTA of the slot-ring kernel (0 = automatic)
 int ce_launch_rows_reg(const CEParams& p, cudaStream_t st);
 // Chooses the resident family for a shape: 0 none, 1/2/4 = resident in shared memory of a 1/2/4-CTA cluster.

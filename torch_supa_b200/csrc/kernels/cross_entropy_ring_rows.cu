@@ -1,5 +1,5 @@
-// Cross entropy for rows of 256 B to 16 KB with a 16-byte aligned pitch: groups of whole rows travel through a ring of
-// shared-memory slots, one warp (or 16, 8 or 4 lanes of one) per row.
+// Cross entropy for rows of 256 B to 32 KB with a 16-byte aligned pitch: groups of whole rows travel through a ring of
+// shared-memory slots, one warp (or 16, 8 or 4 lanes of one, or a team of four warps) per row.
 //
 // A persistent CTA (one per SM) owns every gridDim.x-th group of R consecutive rows (R rows = about 8 KB: bulk copies of
 // a kilobyte or two each cost the copy engine about as much as one of 8 KB, and a row-sized copy per row held these
@@ -32,9 +32,10 @@ constexpr int kRingWarps = 16;                         // consumer warps in the 
 constexpr int kRingThreads = (kRingWarps + 2) * 32;    // plus the loader warp and the storer warp
 constexpr int kRingMaxSlots = 32;
 constexpr uint32_t kRingMinRowBytes = 256;
-constexpr uint32_t kRingMaxRowBytes = 16384;
+constexpr uint32_t kRingMaxRowBytes = 32768;            // up to and including
 constexpr uint32_t kRingGroupBytes = 8192;             // rows are grouped up to about this size per bulk copy
 int g_ring_warps = 0;  // tuning: consumer warps per CTA (0 = automatic)
+int g_ring_max_bytes = static_cast<int>(kRingMaxRowBytes);  // tuning: longest row the ring takes
 
 struct RingParams {
   CEParams p;
@@ -56,6 +57,8 @@ struct alignas(16) RingTail {
   // the barrier is in that lap's phase or just past it, and the parity is unambiguous.
   volatile uint32_t lapno[kRingMaxSlots];
   volatile uint32_t abort;  // set by the first wait that runs out: every other wait of the CTA gives up too
+  float team[kRingWarps][3][4];  // [team][maximum, sum of exponentials, sum of logits][warp of the team]
+  volatile uint32_t team_failed[kRingWarps];
 };
 
 constexpr uint32_t kRingMaxPolls = 1u << 20;  // try_wait attempts before a wait gives up (a legitimate wait lasts microseconds)
@@ -94,9 +97,13 @@ __device__ __forceinline__ float warp_max_nan(float v) {
 // 1 KB / 512 B / 256 B, where the fixed cost per row, about 250 instructions, outweighs the arithmetic on the logits): each
 // group of LPR lanes is a consumer of its own with its own place in the CTA's row sequence, and every warp-level primitive
 // is confined to the group.
-template <typename T, bool kSumX, int NIT, int LPR>
+// TW: warps per row.  Rows of more than 16 KB are swept by a team of TW warps (three passes over shared memory, the two
+// reductions finished through a few floats of shared memory and a named barrier per team): a single warp would hold a slot
+// for too long, and rows of this length leave only a handful of slots.
+template <typename T, bool kSumX, int NIT, int LPR, int TW>
 __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParams rp) {
   static_assert(LPR == 32 || ((LPR == 16 || LPR == 8 || LPR == 4) && NIT > 0), "rows that share a warp stay in registers");
+  static_assert(TW == 1 || (NIT == 0 && LPR == 32 && kRingWarps % TW == 0), "teams of warps sweep shared memory");
   using U = Unit<T>;
   constexpr int P = U::kPairs;
   constexpr int E = 16 / static_cast<int>(sizeof(T));
@@ -115,11 +122,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < nslots; ++s) {
       mbar_init(smem_u32(&tail->full[s]), 1);
-      mbar_init(smem_u32(&tail->done[s]), R);
+      mbar_init(smem_u32(&tail->done[s]), R * TW);  // one arrival per warp that worked on a row of the group
       mbar_init(smem_u32(&tail->empty[s]), 1);
       tail->lapno[s] = 0;
     }
     tail->abort = 0;
+    for (int w = 0; w < kRingWarps; ++w) tail->team_failed[w] = 0;
     fence_mbar_init();
   }
   __syncthreads();
@@ -203,7 +211,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
   const uint32_t sub = static_cast<uint32_t>(lane) / LPR;     // which of them this lane belongs to
   const uint32_t sl = static_cast<uint32_t>(lane) % LPR;      // lane within the consumer
   const uint32_t gmask = LPR == 32 ? 0xffffffffu : (((1u << (LPR & 31)) - 1u) << (LPR * sub));
-  const uint32_t me = static_cast<uint32_t>(warp) * kSubs + sub, consumers = nwarps * kSubs;
+  const uint32_t team = static_cast<uint32_t>(warp) / TW, tw_rank = static_cast<uint32_t>(warp) % TW;
+  const uint32_t me = team * kSubs + sub, consumers = (nwarps / TW) * kSubs;
+  // position and stride of this lane in the sweeps over a row in shared memory
+  const uint32_t lane_pos = TW > 1 ? tw_rank * 32 + static_cast<uint32_t>(lane) : sl;
+  const uint32_t lane_step = TW > 1 ? 32 * TW : LPR;
+  const bool leader = sl == 0 && tw_rank == 0;  // writes the row's loss
   auto valid_target = [&](int64_t t) { return t != p.ignore_index && t >= 0 && t < p.classes; };
   const float eps = p.label_smoothing;
   const float eps_c = eps / static_cast<float>(p.classes);
@@ -239,23 +252,30 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
     }
     t_next = load_target(nk, nj);
 
-    if ((lap > 0 && !ring_wait_lap(&tail->lapno[slot], lap, &tail->abort)) || !ring_wait(smem_u32(&tail->full[slot]), lap & 1, &tail->abort)) {
+    bool landed = (lap == 0 || ring_wait_lap(&tail->lapno[slot], lap, &tail->abort)) && ring_wait(smem_u32(&tail->full[slot]), lap & 1, &tail->abort);
+    if constexpr (TW > 1) {
+      // the warps of a team meet at named barriers while they work on a row: they go on, or give up, together
+      if (!landed) tail->team_failed[team] = 1;
+      named_barrier(1 + team, 32 * TW);
+      landed = tail->team_failed[team] == 0;
+    }
+    if (!landed) {
       give_up();
       break;
     }
     if (row < p.rows) {  // the last group may have fewer than R rows: the missing ones only arrive
       const bool ignored = !valid_target(t);
-      if (ignored && t != p.ignore_index && sl == 0 && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+      if (ignored && t != p.ignore_index && leader && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
       float wt = 1.f;
       if (p.class_weight && !ignored) wt = p.class_weight[t];
       uint4* buf = reinterpret_cast<uint4*>(smem + static_cast<size_t>(slot) * slot_bytes + static_cast<size_t>(j) * row_bytes);
       if (ignored) {
-        if (sl == 0) {
+        if (leader) {
           p.row_loss[row] = 0.f;
           if (p.row_lse) p.row_lse[row] = 0.f;
         }
         if (p.grad) {
-          for (uint32_t v = sl; v < units; v += LPR) buf[v] = make_uint4(0u, 0u, 0u, 0u);
+          for (uint32_t v = lane_pos; v < units; v += lane_step) buf[v] = make_uint4(0u, 0u, 0u, 0u);
         }
       } else {
         if constexpr (NIT > 0) {
@@ -342,18 +362,26 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           // pass 0: the row maximum
           float vm = -CUDART_INF_F;
 #pragma unroll 4
-          for (uint32_t v = lane; v < units; v += 32) vm = max_nan(vm, U::vmax(buf[v]));
+          for (uint32_t v = lane_pos; v < units; v += lane_step) vm = max_nan(vm, U::vmax(buf[v]));
+          const float xt = to_float(reinterpret_cast<const T*>(buf)[t]);  // before the reduction: its synchronisation orders
+                                                                           // this read before the owner's write in pass 1
           vm = warp_max_nan(vm);
+          if constexpr (TW > 1) {
+            if (lane == 0) tail->team[team][0][tw_rank] = vm;
+            named_barrier(1 + team, 32 * TW);
+            vm = tail->team[team][0][0];
+#pragma unroll
+            for (int w = 1; w < TW; ++w) vm = max_nan(vm, tail->team[team][0][w]);
+          }
           const float m2 = vm * kLog2e;
           const float mm = (m2 == -CUDART_INF_F) ? 0.f : m2;  // a row of -inf: keep (-inf) - (-inf) out of the arithmetic
-          const float xt = to_float(reinterpret_cast<const T*>(buf)[t]);
           if (kKeep) __syncwarp();  // every lane has read x[target] before its owner overwrites it
           // pass 1: sum of exponentials relative to the row maximum, sum of logits
           const float2 negm = make_float2(-mm, -mm);
           float2 s2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
           float2 sx2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll 4
-          for (uint32_t v = lane; v < units; v += 32) {
+          for (uint32_t v = lane_pos; v < units; v += lane_step) {
             float2 f[P];
             U::unpack(buf[v], f);
 #pragma unroll
@@ -373,9 +401,23 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
             s += __shfl_xor_sync(0xffffffffu, s, o);
             if (kSumX) sx += __shfl_xor_sync(0xffffffffu, sx, o);
           }
+          if constexpr (TW > 1) {
+            if (lane == 0) {
+              tail->team[team][1][tw_rank] = s;
+              tail->team[team][2][tw_rank] = sx;
+            }
+            named_barrier(1 + team, 32 * TW);
+            s = tail->team[team][1][0];
+            sx = tail->team[team][2][0];
+#pragma unroll
+            for (int w = 1; w < TW; ++w) {  // the same order in every warp: all of them get the same bits
+              s += tail->team[team][1][w];
+              sx += tail->team[team][2][w];
+            }
+          }
           const float lse2 = m2 + log2f(s);
           const float lse = lse2 * kLn2;
-          if (lane == 0) {
+          if (leader) {
             p.row_loss[row] = ce_row_loss(lse, xt, sx, eps, eps_c) * wt;
             if (p.row_lse) p.row_lse[row] = lse;
           }
@@ -400,7 +442,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               if constexpr (std::is_same<T, __nv_bfloat16>::value) {
                 const __nv_bfloat162 f2 = __float2bfloat162_rn(factor), n2 = __float2bfloat162_rn(-sub_all);
 #pragma unroll 4
-                for (uint32_t v = lane; v < units; v += 32) {
+                for (uint32_t v = lane_pos; v < units; v += lane_step) {
                   uint4 o = grad_from_kept_bf16(buf[v], f2, n2);
                   if (v == t_vec) o = patch(o);
                   buf[v] = o;
@@ -408,7 +450,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               } else {
                 const float2 f2 = make_float2(factor, factor), n2 = make_float2(-sub_all, -sub_all);
 #pragma unroll 4
-                for (uint32_t v = lane; v < units; v += 32) {
+                for (uint32_t v = lane_pos; v < units; v += lane_step) {
                   uint4 o = grad_from_kept<T>(buf[v], f2, n2);
                   if (v == t_vec) o = patch(o);
                   buf[v] = o;
@@ -417,7 +459,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
             } else {
               const float2 nl2 = make_float2(-lse2, -lse2), sc2 = make_float2(scale, scale), n2 = make_float2(-sub_all, -sub_all);
 #pragma unroll 4
-              for (uint32_t v = lane; v < units; v += 32) {
+              for (uint32_t v = lane_pos; v < units; v += lane_step) {
                 uint4 o = grad_vector<T>(buf[v], nl2, sc2, n2);
                 if (v == t_vec) o = patch(o);
                 buf[v] = o;
@@ -451,9 +493,9 @@ size_t ring_smem_limit() {
   return limit;
 }
 
-template <typename T, bool SUMX, int NIT, int LPR>
+template <typename T, bool SUMX, int NIT, int LPR, int TW = 1>
 int launch_ring_cfg(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
-  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT, LPR>;
+  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT, LPR, TW>;
   static bool configured = false;  // per instantiation; the attribute is per device, set again after a device change is harmless
   static int configured_dev = -1;
   int dev = 0;
@@ -495,10 +537,17 @@ int launch_ring_t(const RingParams& rp, size_t smem, int grid, cudaStream_t st, 
   if (u <= 128) return sx ? launch_ring_cfg<T, true, 4, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 32>(rp, smem, grid, st, pdl);
   if (u <= 256) return sx ? launch_ring_cfg<T, true, 8, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 8, 32>(rp, smem, grid, st, pdl);
   if (u <= 512) return sx ? launch_ring_cfg<T, true, 16, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 16, 32>(rp, smem, grid, st, pdl);
-  return sx ? launch_ring_cfg<T, true, 0, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32>(rp, smem, grid, st, pdl);
+  if (u <= 1024) return sx ? launch_ring_cfg<T, true, 0, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32>(rp, smem, grid, st, pdl);
+  return sx ? launch_ring_cfg<T, true, 0, 32, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32, 4>(rp, smem, grid, st, pdl);
 }
 
 }  // namespace
+
+int ring_set_max_bytes(int n) {
+  if (n < 16384 || n > 65536) return SB_ERR_INVALID_ARGUMENT;
+  g_ring_max_bytes = n;
+  return SB_OK;
+}
 
 int ring_set_warps(int n) {
   if (n < 0 || n > kRingWarps) return SB_ERR_INVALID_ARGUMENT;
@@ -509,7 +558,7 @@ int ring_set_warps(int n) {
 bool ring_rows_applies(int dtype, int64_t classes, const void* logits, const void* grad) {
   if (dtype != SB_F32 && dtype != SB_BF16 && dtype != SB_F16) return false;
   const uint64_t row_bytes = static_cast<uint64_t>(classes) * dtype_size(dtype);
-  if (row_bytes < kRingMinRowBytes || row_bytes >= kRingMaxRowBytes || row_bytes % 16) return false;
+  if (row_bytes < kRingMinRowBytes || row_bytes > static_cast<uint64_t>(g_ring_max_bytes) || row_bytes % 16) return false;
   return reinterpret_cast<uintptr_t>(logits) % 16 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0;
 }
 
@@ -538,7 +587,13 @@ int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl) {
   if (nwarps > held_max) nwarps = held_max;
   if (nwarps > static_cast<uint32_t>(kRingWarps)) nwarps = kRingWarps;
   if (nwarps < 2) nwarps = 2;
-  if (g_ring_warps > 0 && g_ring_warps <= kRingWarps) nwarps = g_ring_warps;
+  if (rp.units > 1024) {
+    // rows of more than 16 KB: teams of four warps, one slot each; three slots stay with the copy engine
+    uint32_t teams = nslots > 4 ? nslots - 3 : 1;
+    if (teams > 4) teams = 4;
+    nwarps = teams * 4;
+  }
+  if (g_ring_warps > 0 && g_ring_warps <= kRingWarps && (rp.units <= 1024 || g_ring_warps % 4 == 0)) nwarps = g_ring_warps;
   rp.nwarps = nwarps;
   const size_t smem = static_cast<size_t>(nslots) * slot_bytes + sizeof(RingTail);
   const int64_t sms = sm_count();

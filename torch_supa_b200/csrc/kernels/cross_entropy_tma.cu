@@ -902,8 +902,12 @@ int ce_choose_family(const CEParams& p) {
   // class weights together with label smoothing weight every class of the row: only the two-sweep kernel reads them
   if (p.class_weight && p.label_smoothing != 0.f) return 0;
   if (g_ce_force_variant == 0) return 0;
+  const bool forced_resident = g_ce_force_variant >= 1 && g_ce_force_variant <= 4;
+  // Aligned rows of up to 32 KB go to the slot ring: below 64 KB the resident kernel has too few chunks per row for its four
+  // groups (fp32 rows of 18 / 24 / 32 KB: 0.47 / 0.60 / 0.73 of the copy peak).
+  if (!forced_resident && g_ce_force_variant != 8 && ring_rows_applies(p.dtype, p.classes, p.logits, p.grad)) return 16;
   int variant = ce_choose_variant(p.dtype, p.rows, p.classes, p.logits, p.grad);
-  if (g_ce_force_variant > 0 && g_ce_force_variant <= 4 && variant != 0) variant = g_ce_force_variant;  // falls back if it does not fit
+  if (forced_resident && variant != 0) variant = g_ce_force_variant;  // falls back if it does not fit
   if (variant != 0) return variant;
   if (g_ce_force_variant != 8 && ring_rows_applies(p.dtype, p.classes, p.logits, p.grad)) return 16;
   return rows_reg_applies(p.dtype, p.classes, p.logits, p.grad) ? 8 : 0;
@@ -945,6 +949,7 @@ extern "C" int sb_set_tuning(int32_t key, int32_t value) {
   }
   if (key == 5 && value >= 1 && value <= 60000) return sb::xchg_set_timeout_ms(value);
   if (key == 6) return sb::ring_set_warps(value);
+  if (key == 7) return sb::ring_set_max_bytes(value);
   return SB_ERR_INVALID_ARGUMENT;
 }
 
