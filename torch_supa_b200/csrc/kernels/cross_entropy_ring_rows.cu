@@ -100,14 +100,18 @@ __device__ __forceinline__ float warp_max_nan(float v) {
 // TW: warps per row.  Rows of more than 16 KB are swept by a team of TW warps (three passes over shared memory, the two
 // reductions finished through a few floats of shared memory and a named barrier per team): a single warp would hold a slot
 // for too long, and rows of this length leave only a handful of slots.
-template <typename T, bool kSumX, int NIT, int LPR, int TW>
+// MODE 0: cross entropy (losses and gradient).  MODE 1: log_softmax (x - lse out; no targets, no losses).  MODE 2: softmax
+// (the gradient formula with scale 1, nothing subtracted and no target).  In modes 1 and 2 `grad` is the output.
+template <typename T, bool kSumX, int NIT, int LPR, int TW, int MODE>
 __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParams rp) {
+  static_assert(MODE == 0 || !kSumX, "only the cross entropy needs the sum of the logits");
   static_assert(LPR == 32 || ((LPR == 16 || LPR == 8 || LPR == 4) && NIT > 0), "rows that share a warp stay in registers");
   static_assert(TW == 1 || (NIT == 0 && LPR == 32 && kRingWarps % TW == 0), "teams of warps sweep shared memory");
   using U = Unit<T>;
   constexpr int P = U::kPairs;
   constexpr int E = 16 / static_cast<int>(sizeof(T));
-  constexpr bool kKeep = sizeof(T) == 2;  // 16-bit logits: one ex2 per logit, the gradient pass rescales
+  constexpr bool kKeep = sizeof(T) == 2 && MODE != 1;  // 16-bit logits: one ex2 per logit, the gradient pass rescales
+                                                        // (log_softmax needs the logits themselves in its last pass)
   extern __shared__ __align__(128) unsigned char smem[];
   const CEParams& p = rp.p;
   const uint32_t nslots = rp.nslots, units = rp.units, row_bytes = rp.row_bytes, nwarps = rp.nwarps, R = rp.group_rows;
@@ -233,7 +237,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
   const uint32_t step_j = consumers % R, step_k = consumers / R;
   uint32_t slot = static_cast<uint32_t>(k) % nslots, lap = static_cast<uint32_t>(k) / nslots;
   auto row_of = [&](int64_t kk, uint32_t jj) { return (first + kk * stride) * R + jj; };
-  auto load_target = [&](int64_t kk, uint32_t jj) {
+  auto load_target = [&](int64_t kk, uint32_t jj) -> int64_t {
+    if constexpr (MODE != 0) return 0;
     const int64_t r = row_of(kk, jj);
     return (kk < n_local && r < p.rows) ? p.target[r] : p.ignore_index;
   };
@@ -264,7 +269,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
       break;
     }
     if (row < p.rows) {  // the last group may have fewer than R rows: the missing ones only arrive
-      const bool ignored = !valid_target(t);
+      const bool ignored = MODE == 0 && !valid_target(t);
       if (ignored && t != p.ignore_index && leader && p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
       float wt = 1.f;
       if (p.class_weight && !ignored) wt = p.class_weight[t];
@@ -290,8 +295,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               vm = max_nan(vm, U::vmax(r[n]));
             }
           }
-          const float xt = to_float(reinterpret_cast<const T*>(buf)[t]);  // read before any lane stores a gradient (the
-                                                                           // warp-wide reductions below lie in between)
+          // x[target] is read before any lane stores a gradient (the warp-wide reductions below lie in between)
+          const float xt = MODE == 0 ? to_float(reinterpret_cast<const T*>(buf)[t]) : 0.f;
           if constexpr (LPR == 32) {
             vm = warp_max_nan(vm);
           } else {
@@ -316,7 +321,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
                 if (kSumX) sx2[q & 1] = add2(sx2[q & 1], f[q]);
                 f[q] = ex;
               }
-              r[n] = U::pack(f);  // the exponentials replace the logits (fp32: the same registers)
+              if (MODE != 1) r[n] = U::pack(f);  // the exponentials replace the logits (fp32: the same registers)
             }
           }
           float s = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
@@ -328,15 +333,15 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           }
           const float lse2 = m2 + log2f(s);
           const float lse = lse2 * kLn2;
-          if (sl == 0) {
+          if (MODE == 0 && sl == 0) {
             p.row_loss[row] = ce_row_loss(lse, xt, sx, eps, eps_c) * wt;
             if (p.row_lse) p.row_lse[row] = lse;
           }
           if (p.grad) {
-            float scale = base_scale * wt;
-            if (p.row_grad_out) scale *= p.row_grad_out[row];
+            float scale = MODE == 0 ? base_scale * wt : 1.f;
+            if (MODE == 0 && p.row_grad_out) scale *= p.row_grad_out[row];
             if (lse != lse) scale = lse;  // a NaN row has a NaN gradient
-            const float sub_all = eps_c * scale;
+            const float sub_all = MODE == 0 ? eps_c * scale : 0.f;
             const float sub_t = (1.f - eps) * scale;
             const float g_t = fmaf(ex2(fmaf(xt, kLog2e, -lse2)), scale, -sub_all) - sub_t;
             const uint32_t t_vec = static_cast<uint32_t>(t) / E;
@@ -347,7 +352,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               const uint32_t v = sl + LPR * n;
               if (v < units) {
                 uint4 o;
-                if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                if constexpr (MODE == 1) {
+                  o = shift_vector<T>(r[n], make_float2(-lse, -lse));
+                } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
                   o = grad_from_kept_bf16(r[n], __float2bfloat162_rn(factor), __float2bfloat162_rn(-sub_all));
                 } else {
                   o = grad_from_kept<T>(r[n], f2, n2);
@@ -356,15 +363,15 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
               }
             }
             // the target's class, by the lane that has just stored its unit
-            if (sl == t_vec % LPR) reinterpret_cast<T*>(buf)[t] = from_float<T>(g_t);
+            if (MODE == 0 && sl == t_vec % LPR) reinterpret_cast<T*>(buf)[t] = from_float<T>(g_t);
           }
         } else {
           // pass 0: the row maximum
           float vm = -CUDART_INF_F;
 #pragma unroll 4
           for (uint32_t v = lane_pos; v < units; v += lane_step) vm = max_nan(vm, U::vmax(buf[v]));
-          const float xt = to_float(reinterpret_cast<const T*>(buf)[t]);  // before the reduction: its synchronisation orders
-                                                                           // this read before the owner's write in pass 1
+          // x[target]: before the reduction, whose synchronisation orders this read before the owner's write in pass 1
+          const float xt = MODE == 0 ? to_float(reinterpret_cast<const T*>(buf)[t]) : 0.f;
           vm = warp_max_nan(vm);
           if constexpr (TW > 1) {
             if (lane == 0) tail->team[team][0][tw_rank] = vm;
@@ -417,19 +424,19 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
           }
           const float lse2 = m2 + log2f(s);
           const float lse = lse2 * kLn2;
-          if (leader) {
+          if (MODE == 0 && leader) {
             p.row_loss[row] = ce_row_loss(lse, xt, sx, eps, eps_c) * wt;
             if (p.row_lse) p.row_lse[row] = lse;
           }
           if (p.grad) {
-            float scale = base_scale * wt;
-            if (p.row_grad_out) scale *= p.row_grad_out[row];
+            float scale = MODE == 0 ? base_scale * wt : 1.f;
+            if (MODE == 0 && p.row_grad_out) scale *= p.row_grad_out[row];
             if (lse != lse) scale = lse;  // a NaN row has a NaN gradient
-            const float sub_all = eps_c * scale;
+            const float sub_all = MODE == 0 ? eps_c * scale : 0.f;
             const float sub_t = (1.f - eps) * scale;
             // gradient of the target's class from fp32 arithmetic on the saved logit
             const float g_t = fmaf(ex2(fmaf(xt, kLog2e, -lse2)), scale, -sub_all) - sub_t;
-            const uint32_t t_vec = static_cast<uint32_t>(t) / E, t_el = static_cast<uint32_t>(t) % E;
+            const uint32_t t_vec = MODE == 0 ? static_cast<uint32_t>(t) / E : 0xffffffffu, t_el = static_cast<uint32_t>(t) % E;
             auto patch = [&](uint4 o) {
               T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -437,7 +444,11 @@ __global__ void __launch_bounds__(kRingThreads, 1) ce_ring_rows_kernel(RingParam
                 if (static_cast<uint32_t>(q) == t_el) oe[q] = from_float<T>(g_t);
               return o;
             };
-            if (kKeep) {
+            if constexpr (MODE == 1) {
+              const float2 nl = make_float2(-lse, -lse);
+#pragma unroll 4
+              for (uint32_t v = lane_pos; v < units; v += lane_step) buf[v] = shift_vector<T>(buf[v], nl);
+            } else if (kKeep) {
               const float factor = scale / s;  // kept value * factor = softmax * scale
               if constexpr (std::is_same<T, __nv_bfloat16>::value) {
                 const __nv_bfloat162 f2 = __float2bfloat162_rn(factor), n2 = __float2bfloat162_rn(-sub_all);
@@ -493,9 +504,9 @@ size_t ring_smem_limit() {
   return limit;
 }
 
-template <typename T, bool SUMX, int NIT, int LPR, int TW = 1>
+template <typename T, bool SUMX, int NIT, int LPR, int TW, int MODE>
 int launch_ring_cfg(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
-  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT, LPR, TW>;
+  auto kernel = ce_ring_rows_kernel<T, SUMX, NIT, LPR, TW, MODE>;
   static bool configured = false;  // per instantiation; the attribute is per device, set again after a device change is harmless
   static int configured_dev = -1;
   int dev = 0;
@@ -525,20 +536,28 @@ int launch_ring_cfg(const RingParams& rp, size_t smem, int grid, cudaStream_t st
   return SB_OK;
 }
 
-template <typename T>
-int launch_ring_t(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
-  const bool sx = rp.p.label_smoothing != 0.f;
+// The instantiation for the row length: lanes per row, units per lane in registers, warps per row.
+template <typename T, bool SUMX, int MODE>
+int launch_ring_shape(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl) {
   const uint32_t u = rp.units;
-  // Rows of 1 KB: two rows per warp (bf16 [131072,512]: 0.71 of the copy peak against 0.54 with a warp per row; for rows of
-  // 2 KB the same split measured slower, 0.75 against 0.82).  Longer ones: one row per warp, in registers up to 8 KB.
-  if (u <= 16) return sx ? launch_ring_cfg<T, true, 4, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 4>(rp, smem, grid, st, pdl);
-  if (u <= 32) return sx ? launch_ring_cfg<T, true, 4, 8>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 8>(rp, smem, grid, st, pdl);
-  if (u <= 64) return sx ? launch_ring_cfg<T, true, 4, 16>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 16>(rp, smem, grid, st, pdl);
-  if (u <= 128) return sx ? launch_ring_cfg<T, true, 4, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 4, 32>(rp, smem, grid, st, pdl);
-  if (u <= 256) return sx ? launch_ring_cfg<T, true, 8, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 8, 32>(rp, smem, grid, st, pdl);
-  if (u <= 512) return sx ? launch_ring_cfg<T, true, 16, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 16, 32>(rp, smem, grid, st, pdl);
-  if (u <= 1024) return sx ? launch_ring_cfg<T, true, 0, 32>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32>(rp, smem, grid, st, pdl);
-  return sx ? launch_ring_cfg<T, true, 0, 32, 4>(rp, smem, grid, st, pdl) : launch_ring_cfg<T, false, 0, 32, 4>(rp, smem, grid, st, pdl);
+  // Rows of up to 256 B / 512 B / 1 KB: eight / four / two rows per warp (bf16 [131072,512]: 0.71 of the copy peak against 0.54
+  // with a warp per row; for rows of 2 KB the same split measured slower, 0.75 against 0.82).  Longer ones: one row per warp,
+  // in registers up to 8 KB, in shared memory up to 16 KB; beyond that a team of four warps per row.
+  if (u <= 16) return launch_ring_cfg<T, SUMX, 4, 4, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 32) return launch_ring_cfg<T, SUMX, 4, 8, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 64) return launch_ring_cfg<T, SUMX, 4, 16, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 128) return launch_ring_cfg<T, SUMX, 4, 32, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 256) return launch_ring_cfg<T, SUMX, 8, 32, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 512) return launch_ring_cfg<T, SUMX, 16, 32, 1, MODE>(rp, smem, grid, st, pdl);
+  if (u <= 1024) return launch_ring_cfg<T, SUMX, 0, 32, 1, MODE>(rp, smem, grid, st, pdl);
+  return launch_ring_cfg<T, SUMX, 0, 32, 4, MODE>(rp, smem, grid, st, pdl);
+}
+
+template <typename T>
+int launch_ring_t(const RingParams& rp, size_t smem, int grid, cudaStream_t st, bool pdl, int mode) {
+  if (mode == 1) return launch_ring_shape<T, false, 1>(rp, smem, grid, st, pdl);
+  if (mode == 2) return launch_ring_shape<T, false, 2>(rp, smem, grid, st, pdl);
+  return rp.p.label_smoothing != 0.f ? launch_ring_shape<T, true, 0>(rp, smem, grid, st, pdl) : launch_ring_shape<T, false, 0>(rp, smem, grid, st, pdl);
 }
 
 }  // namespace
@@ -562,7 +581,8 @@ bool ring_rows_applies(int dtype, int64_t classes, const void* logits, const voi
   return reinterpret_cast<uintptr_t>(logits) % 16 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0;
 }
 
-int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl) {
+namespace {
+int launch_ring(const CEParams& p, cudaStream_t st, bool pdl, int mode) {
   RingParams rp;
   rp.p = p;
   rp.row_bytes = static_cast<uint32_t>(p.classes * dtype_size(p.dtype));
@@ -599,10 +619,28 @@ int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl) {
   const int64_t sms = sm_count();
   const int grid = static_cast<int>(rp.ngroups < sms ? rp.ngroups : sms);
   switch (p.dtype) {
-    case SB_F32: return launch_ring_t<float>(rp, smem, grid, st, pdl);
-    case SB_BF16: return launch_ring_t<__nv_bfloat16>(rp, smem, grid, st, pdl);
-    default: return launch_ring_t<__half>(rp, smem, grid, st, pdl);
+    case SB_F32: return launch_ring_t<float>(rp, smem, grid, st, pdl, mode);
+    case SB_BF16: return launch_ring_t<__nv_bfloat16>(rp, smem, grid, st, pdl, mode);
+    default: return launch_ring_t<__half>(rp, smem, grid, st, pdl, mode);
   }
+}
+}  // namespace
+
+int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl) { return launch_ring(p, st, pdl, 0); }
+
+// log_softmax (mode 1) / softmax (mode 2) over the last dimension of a contiguous [rows, dim] array on the same ring.
+// SB_ERR_UNSUPPORTED when the shape does not qualify.
+int lsm_launch_ring(const void* in, void* out, int dtype, int64_t rows, int64_t dim, int mode, cudaStream_t st) {
+  if (rows <= 0 || !ring_rows_applies(dtype, dim, in, out)) return SB_ERR_UNSUPPORTED;
+  CEParams p{};
+  p.logits = in;
+  p.grad = out;
+  p.rows = rows;
+  p.classes = dim;
+  p.dtype = dtype;
+  p.grad_scale = 1.f;
+  p.reduction = SB_REDUCTION_NONE;
+  return launch_ring(p, st, false, mode);
 }
 
 }  // namespace sb

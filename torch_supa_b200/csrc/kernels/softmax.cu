@@ -266,8 +266,11 @@ int launch_fwd(const void* in, void* out, int64_t outer, int64_t D, int64_t inne
   Tout* y = static_cast<Tout*>(out);
   const int sms = sm_count();
   if (inner == 1 && std::is_same<Tin, Tout>::value && sizeof(Tin) <= 4) {
-    // long rows: keep the row in shared memory (one HBM read, one HBM write)
-    const int rc = lsm_launch_resident(in, out, DTypeOf<Tin>::value, outer, D, LOG ? 1 : 2, st);
+    // one HBM read, one HBM write: aligned rows of up to 32 KB on the slot ring (groups of rows, a warp or a team per row),
+    // long rows resident in shared memory chunk by chunk
+    int rc = lsm_launch_ring(in, out, DTypeOf<Tin>::value, outer, D, LOG ? 1 : 2, st);
+    if (rc != SB_ERR_UNSUPPORTED) return rc;
+    rc = lsm_launch_resident(in, out, DTypeOf<Tin>::value, outer, D, LOG ? 1 : 2, st);
     if (rc != SB_ERR_UNSUPPORTED) return rc;
   }
   if (inner == 1) {
