@@ -202,12 +202,12 @@ def moved_bytes(rows, classes, elem_size, ignored_rows):
 # DRAM bytes per row of the dominant kernel: dram__bytes_read.sum + dram__bytes_write.sum of ONE fused-sweep launch, from the
 # ncu captures summarised under profiles/ (each file names its command), divided by the rows of the captured launch.  Traffic
 # is proportional to the rows, so the figure is scaled by the rows of the timed launch.  Captured on the tree of commit
-# 5257ec6; re-capture when cross_entropy_tma.cu or cross_entropy_ring_rows.cu change.
+# 67f1c25; re-capture when cross_entropy_tma.cu or cross_entropy_ring_rows.cu change.
 NCU_TRAFFIC_PER_ROW = {
-    "ce_fp32_4096x32000": (524.463616e6 + 468.479744e6) / 4096,      # profiles/ce_resident_kernel_fp32_4096x32000.md
-    "ce_bf16_32768x128256": (998.445568e6 + 994.540544e6) / 4096,    # profiles/ce_resident_kernel_bf16_4096x128256.md
-    "ce_bf16_8192x50257": (782.571776e6 + 770.006528e6) / 8192,      # profiles/ce_resident_kernel_ragged_bf16_8192x50257.md
-    "ce_fp32_32768x2048": (268.974080e6 + 212.401152e6) / 32768,     # profiles/ce_ring_rows_kernel_fp32_32768x2048.md
+    "ce_fp32_4096x32000": (524.369152e6 + 468.845312e6) / 4096,      # profiles/ce_resident_kernel_fp32_4096x32000.md
+    "ce_bf16_32768x128256": (998.445568e6 + 994.885888e6) / 4096,    # profiles/ce_resident_kernel_bf16_4096x128256.md
+    "ce_bf16_8192x50257": (782.501888e6 + 769.983744e6) / 8192,      # profiles/ce_resident_kernel_ragged_bf16_8192x50257.md
+    "ce_fp32_32768x2048": (268.949760e6 + 213.385216e6) / 32768,     # profiles/ce_ring_rows_kernel_fp32_32768x2048.md
 }
 KERNEL_NAMES = {0: "ce_rows_cta_kernel (two sweeps)", 1: "ce_resident_kernel (1 CTA per row)", 2: "ce_resident_kernel (2-CTA cluster per row)",
                 4: "ce_resident_kernel (4-CTA cluster per row)", 8: "ce_rows_reg_kernel (row in registers)",
