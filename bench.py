@@ -472,7 +472,7 @@ def run_ours(args):
     achieved_moved = moved / (kernel_ms * 1e-3) / 1e9
     variant = capi.ce_kernel_variant(capi.torch_dtype_code(dtype), rows, classes)
     extras = None
-    if rank == 0 and world == 1 and args.extras and not args.quick:
+    if rank == 0 and world == 1 and args.extras and (not args.quick or args.extras == 2):
         extras = bench_extras.run_extras(device, peak, profile=args.extras == 2)
     # my kernels per step: count, fused sweep, loss sum + finish (the two exchanges ride inside the count and the loss kernel),
     # fill of the root gradient (by autograd), rescale; through NCCL the loss sum and its finish are two launches
