@@ -224,6 +224,53 @@ __global__ void __launch_bounds__(THREADS) lsm_bwd_cta_kernel(const T* __restric
   }
 }
 
+// Short rows (up to 1024 elements) with 16-byte aligned pitch: a warp (or 16 / 8 lanes of one, for rows of up to 16 / 8
+// vectors) per row, 16-byte accesses, the row of g held in registers between the sum and the result (one read of g, one of
+// y, one write).
+template <typename T, typename Tgi, typename A, int VEC, int LPR, int NIT, bool LOG>
+__global__ void __launch_bounds__(256) lsm_bwd_warp_vec_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
+                                                               Tgi* __restrict__ gin, int64_t rows, int64_t D) {
+  // LPR lanes per row, up to NIT vectors per lane
+  constexpr int kSubs = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane / LPR, sl = lane % LPR;
+  const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << (LPR & 31)) - 1u) << (LPR * sub));
+  const int nvec = static_cast<int>(D / VEC);
+  const int64_t first = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kSubs + sub;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8 * kSubs;
+  for (int64_t row = first; row < rows; row += stride) {
+    const T* g = gout + row * D;
+    const T* y = yout + row * D;
+    Tgi* o = gin + row * D;
+    A gv[NIT][VEC], yv[NIT][VEC];
+    A acc = 0;
+#pragma unroll
+    for (int n = 0; n < NIT; ++n) {
+      const int v = sl + LPR * n;
+      if (v < nvec) {
+        load_as<A, T, VEC>(g + v * VEC, gv[n]);
+        load_as<A, T, VEC>(y + v * VEC, yv[n]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc += LOG ? gv[n][k] : gv[n][k] * yv[n][k];
+      }
+    }
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
+#pragma unroll
+    for (int n = 0; n < NIT; ++n) {
+      const int v = sl + LPR * n;
+      if (v < nvec) {
+        A r[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          if constexpr (LOG && sizeof(Tgi) == 2 && std::is_same<A, float>::value) r[k] = gv[n][k] - exp_fast(yv[n][k]) * acc;
+          else r[k] = LOG ? gv[n][k] - acc_exp<A>(yv[n][k]) * acc : yv[n][k] * (gv[n][k] - acc);
+        }
+        store_as<A, Tgi, VEC>(o + v * VEC, r);
+      }
+    }
+  }
+}
+
 template <typename T, typename Tgi, typename A, bool LOG>
 __global__ void __launch_bounds__(256) lsm_bwd_strided_kernel(const T* __restrict__ gout, const T* __restrict__ yout,
                                                               Tgi* __restrict__ gin, int64_t outer, int64_t D,
@@ -322,6 +369,31 @@ int launch_bwd(const void* gout, const void* yout, void* gin, int64_t outer, int
     if (aligned) lsm_bwd_cta_kernel<T, Tgi, A, kVec, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
     else lsm_bwd_cta_kernel<T, Tgi, A, 1, kThreads, LOG><<<grid, kThreads, 0, st>>>(g, y, o, outer, D);
     return launch_status();
+  }
+  if (inner == 1 && D <= 1024 && sizeof(T) <= 4) {
+    constexpr int kVec = 16 / sizeof(T);
+    const size_t gi_align = sizeof(Tgi) * kVec >= 16 ? 16 : sizeof(Tgi) * kVec;
+    const bool aligned = D % kVec == 0 && reinterpret_cast<uintptr_t>(gout) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(yout) % 16 == 0 && reinterpret_cast<uintptr_t>(gin) % gi_align == 0;
+    if (aligned) {
+      const int64_t nvec = D / kVec;
+      // rows per warp: as many as leave each lane two to four vectors (more rows in flight hide more latency)
+      int lpr, nit;
+      if (nvec <= 16) lpr = 8, nit = 2;
+      else if (nvec <= 32) lpr = 16, nit = 2;
+      else if (nvec <= 64) lpr = 16, nit = 4;
+      else if (nvec <= 128) lpr = 32, nit = 4;
+      else lpr = 32, nit = 8;
+      const int64_t per_cta = 8 * (32 / lpr);
+      const int64_t ctas = (outer + per_cta - 1) / per_cta;
+      const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
+      if (lpr == 8) lsm_bwd_warp_vec_kernel<T, Tgi, A, kVec, 8, 2, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D);
+      else if (lpr == 16 && nit == 2) lsm_bwd_warp_vec_kernel<T, Tgi, A, kVec, 16, 2, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D);
+      else if (lpr == 16) lsm_bwd_warp_vec_kernel<T, Tgi, A, kVec, 16, 4, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D);
+      else if (nit == 4) lsm_bwd_warp_vec_kernel<T, Tgi, A, kVec, 32, 4, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D);
+      else lsm_bwd_warp_vec_kernel<T, Tgi, A, kVec, 32, 8, LOG><<<grid, 256, 0, st>>>(g, y, o, outer, D);
+      return launch_status();
+    }
   }
   const bool warp_rows = inner == 1;
   const int64_t total = warp_rows ? (outer + 7) / 8 : (outer * inner + 255) / 256;
