@@ -232,7 +232,9 @@ SB_API int sb_ce_kernel_variant(int32_t dtype, int64_t rows, int64_t classes);
  * sweep (one ex2 per logit, one more bf16 rounding), 0 recomputes them (two ex2 per logit);
  * key 5 = limit, in milliseconds, of the waits of sb_ce_count_exchange / sb_ce_loss_exchange (1..60000, default 10000);
  * key 6 = consumer warps per CTA of the slot-ring kernel (0 automatic, 1..16);
- * key 7 = longest row, in bytes, the slot-ring kernel takes (16384..65536, default 32768). */
+ * key 7 = longest row, in bytes, the slot-ring kernel takes (16384..65536, default 32768);
+ * key 8 = longest row, in bytes, that one warp reduces in sb_reduce before a CTA takes each row (0 = the 16-byte
+ * vector row kernels off, 4096..262144, default 8192). */
 SB_API int sb_set_tuning(int32_t key, int32_t value);
 
 /* ------------------------------------------------------------------------------------------

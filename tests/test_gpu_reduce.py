@@ -8,7 +8,7 @@ from tests.helpers import accumulation_tol, assert_close
 
 pytestmark = pytest.mark.gpu
 
-OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3}
+OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "nansum": 5}
 
 
 def _red(dev, op, x, dims, **kw):
@@ -38,7 +38,12 @@ def test_fixtures(golden, cuda_device):
 SHAPES = [((16,), [0]), ((1024, 512), [-1]), ((1023, 511), [-1]), ((1025, 513), [0]), ((128, 2135), [1]),
           ((64, 65536), [-1]), ((3, 200000), [-1]), ((1, 1 << 20), [1]), ((7, 9, 11), [1]), ((7, 9, 11), [0, 2]),
           ((5, 6, 7, 8), [1, 3]), ((300, 40), [0]), ((2, 70000), [0]), ((1,), [0]), ((4, 1, 6), [1]),
-          ((33, 1000), [0, 1])]
+          ((33, 1000), [0, 1]),
+          # column reductions cut into row chunks: tall and narrow, 125 column vectors, an unaligned pitch, a middle dimension
+          ((100000, 64), [0]), ((5000, 1000), [0]), ((4096, 4099), [0]), ((7, 3000, 96), [1]), ((70000, 8), [0]), ((300, 16384), [0]),
+          # rows of whole 16-byte vectors: lanes share a row (4 B - 4 KB), then a warp per row (to 8 KB), then a CTA
+          ((5000, 64), [-1]), ((3001, 256), [-1]), ((777, 1000), [-1]), ((301, 1024), [-1]), ((4099, 8), [-1]),
+          ((203, 4096), [-1]), ((101, 3000), [-1]), ((67, 4), [-1]), ((50, 8192), [-1]), ((9, 40, 72), [2])]
 
 
 @pytest.mark.parametrize("shape,dims", SHAPES)
@@ -65,6 +70,23 @@ def test_against_pytorch_cpu(cuda_device, shape, dims, op, dtype):
         assert_close(out.double().numpy(), ref64.numpy(), rtol, atol * (1 if op == "mean" else max(1.0, n ** 0.5 / 8)), op)
     else:
         assert_close(out.numpy(), ref64.numpy(), 1e-12, 1e-10, op)
+
+
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64, torch.uint8, torch.bool])
+def test_tall_column_sums_of_integers_are_exact(cuda_device, dtype):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randint(0, 2 if dtype == torch.bool else 100, (50000, 48), generator=g).to(dtype)
+    out = _red(cuda_device, "sum", x, [0])
+    assert out.dtype == torch.int64 and torch.equal(out, x.sum(0))
+    assert torch.equal(_red(cuda_device, "amax", x, [0]), x.amax(0)) if dtype != torch.bool else True
+
+
+def test_column_sum_is_bit_reproducible(cuda_device):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(200000, 96, generator=g)
+    a = _red(cuda_device, "sum", x, [0])
+    b = _red(cuda_device, "sum", x, [0])
+    assert torch.equal(a, b)
 
 
 def test_oracle_rows(cuda_device):
@@ -105,6 +127,53 @@ def test_keepdim_and_noncontiguous_input(cuda_device):
     xt = x.to(cuda_device).t()  # [60, 40] with strides (1, 60)
     out = F2.reduce(OPS["sum"], xt, [1]).cpu()
     assert_close(out.numpy(), x.t().sum(1).numpy(), 1e-5, 1e-5, "transposed view")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cols", [64, 1000, 2048])
+def test_rows_of_a_strided_view(cuda_device, dtype, cols):
+    # rows that are slices of longer rows, kept dimensions that do not merge, NaN and minus infinity in the data
+    from torch_supa_b200 import functional as F2
+
+    g = torch.Generator().manual_seed(cols)
+    x = torch.randn(6, 50, 2 * cols, generator=g).to(dtype)
+    x[1, 2, 3] = float("-inf")
+    x[4, 7, cols - 1] = float("nan")
+    xd = x.to(cuda_device)
+    view = xd[:, 1:, cols // 2: cols // 2 + cols]
+    ref = x[:, 1:, cols // 2: cols // 2 + cols]
+    got, want = F2.reduce(OPS["amax"], view, [-1]).cpu(), ref.amax(-1)
+    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.equal(got[~torch.isnan(got)], want[~torch.isnan(want)])
+    s, sw = F2.reduce(OPS["sum"], view, [-1]).cpu().double(), ref.double().sum(-1)
+    fin = torch.isfinite(sw)
+    assert torch.equal(torch.isnan(s), torch.isnan(sw)) and torch.equal(torch.isinf(s), torch.isinf(sw))
+    assert_close(s[fin].numpy(), sw[fin].numpy(), 1e-2 if dtype == torch.bfloat16 else 1e-5, 1e-1 if dtype == torch.bfloat16 else 1e-3,
+                 "sum")
+    ns = F2.reduce(OPS["nansum"], view, [-1]).cpu().double()
+    nsw = torch.nan_to_num(ref.double(), nan=0.0, neginf=float("-inf")).sum(-1)
+    fin = torch.isfinite(nsw)
+    assert not torch.isnan(ns).any()
+    assert_close(ns[fin].numpy(), nsw[fin].numpy(), 1e-2 if dtype == torch.bfloat16 else 1e-5,
+                 1e-1 if dtype == torch.bfloat16 else 1e-3, "nansum")
+
+
+def test_row_kernels_agree_with_the_cta_kernel(cuda_device):
+    # the same rows through the vector row kernels and, with them switched off, through the older ones
+    from torch_supa_b200 import capi, functional as F2
+
+    g = torch.Generator().manual_seed(8)
+    for cols, dtype in ((64, torch.float32), (1000, torch.bfloat16), (2048, torch.float16), (4096, torch.float32)):
+        x = torch.randn(999, cols, generator=g).to(dtype).to(cuda_device)
+        new = {op: F2.reduce(OPS[op], x, [-1]) for op in ("sum", "amax", "amin", "prod")}
+        capi.check("sb_set_tuning", capi.lib().sb_set_tuning(8, 0))
+        try:
+            old = {op: F2.reduce(OPS[op], x, [-1]) for op in new}
+        finally:
+            capi.check("sb_set_tuning", capi.lib().sb_set_tuning(8, 8192))
+        for op in ("amax", "amin"):
+            assert torch.equal(new[op], old[op]), (op, cols)
+        assert_close(new["sum"].double().cpu().numpy(), old["sum"].double().cpu().numpy(), 1e-2 if dtype != torch.float32 else 1e-5,
+                     1e-1 if dtype != torch.float32 else 1e-3, "sum")
 
 
 def test_split_rows_path_is_deterministic(cuda_device):

@@ -94,6 +94,7 @@ bool rows_reg_applies(int dtype, int64_t classes, const void* logits, const void
 bool ring_rows_applies(int dtype, int64_t classes, const void* logits, const void* grad);
 int ce_launch_ring_rows(const CEParams& p, cudaStream_t st, bool pdl);
 int lsm_launch_ring(const void* in, void* out, int dtype, int64_t rows, int64_t dim, int mode, cudaStream_t st);
+int red_set_warp_row_bytes(int n);  // tuning: longest row one warp reduces (0 = vector row kernels off, 4096..262144)
 int ring_set_max_bytes(int n);  // tuning: longest row the slot-ring kernel takes (16384..65536)
 int ring_set_warps(int n);  // tuning: consumer warps per CTA of the slot-ring kernel (0 = automatic)
 int ce_launch_rows_reg(const CEParams& p, cudaStream_t st);

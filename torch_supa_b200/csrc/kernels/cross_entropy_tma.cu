@@ -950,6 +950,7 @@ extern "C" int sb_set_tuning(int32_t key, int32_t value) {
   if (key == 5 && value >= 1 && value <= 60000) return sb::xchg_set_timeout_ms(value);
   if (key == 6) return sb::ring_set_warps(value);
   if (key == 7) return sb::ring_set_max_bytes(value);
+  if (key == 8) return sb::red_set_warp_row_bytes(value);
   return SB_ERR_INVALID_ARGUMENT;
 }
 

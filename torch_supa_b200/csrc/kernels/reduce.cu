@@ -35,6 +35,8 @@ struct RedParams {
   int splits;                // path 1
   int64_t seg;               // path 1: elements per segment (multiple of the vector width)
   void* scratch;
+  int vpr;                   // path 2: column vectors one warp covers per row (a power of two up to 32)
+  int col_vec;               // path 2: 1 = 16-byte column vectors
 };
 
 struct RedGenericParams {
@@ -290,6 +292,126 @@ __global__ void __launch_bounds__(THREADS) red_rows_warp_kernel(RedParams p) {
   }
 }
 
+// Offsets of output row `o` when only kept dimension 0 has more than one element (no divisions).
+__device__ __forceinline__ void row_offsets(const RedParams& p, bool flat, int64_t o, int64_t& in_off, int64_t& out_off) {
+  if (flat) {
+    in_off = o * p.keep_in_strides[0];
+    out_off = o * p.keep_out_strides[0];
+  } else {
+    keep_offsets(p, o, in_off, out_off);
+  }
+}
+
+// Rows of up to 256 vectors of 16 bytes, every row on a 16-byte boundary.  `lpr` lanes (a power of two) share a row
+// and a lane keeps eight vectors in flight: 8 / nv consecutive rows with nv vectors of each (nv a power of two), so
+// that a row of 256 bytes costs a lane one load and a row of 4 KB eight.
+template <class IO, class F, typename A, int VEC>
+__global__ void __launch_bounds__(256) red_rows_sub_kernel(RedParams p, int lpr, int nv) {
+  using S = typename IO::storage;
+  static_assert(sizeof(S) * VEC == 16, "one 16-byte vector per load");
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (lpr - 1);
+  const int nv_shift = __ffs(nv) - 1;
+  const int ru = 8 >> nv_shift;  // rows per lane group and step
+  const int nvec = static_cast<int>(p.L / VEC);
+  const int groups_per_warp = 32 / lpr;
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t rows_per_warp = static_cast<int64_t>(groups_per_warp) * ru;
+  const bool flat = p.keep_sizes[1] == 1 && p.keep_sizes[2] == 1;
+  // the trip count is the same for the whole warp: the shuffles below name every lane
+  for (int64_t wbase = gwarp * rows_per_warp; wbase < p.noutputs; wbase += nwarps * rows_per_warp) {
+    const int64_t base = wbase + static_cast<int64_t>(lane / lpr) * ru;
+    // Every slot loads: a slot past the last row or the last vector reads the nearest valid one instead and is left out
+    // when the values are folded (a load under a condition would make the loads wait for one another).
+    uint4 raw[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      int64_t row = base + (k >> nv_shift);
+      row = row < p.noutputs ? row : p.noutputs - 1;
+      int v = sub + (k & (nv - 1)) * lpr;
+      v = v < nvec ? v : nvec - 1;
+      int64_t in_off, out_off;
+      row_offsets(p, flat, row, in_off, out_off);
+      raw[k] = *reinterpret_cast<const uint4*>(static_cast<const S*>(p.in) + in_off + static_cast<int64_t>(v) * VEC);
+    }
+    A s[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const bool live = base + (k >> nv_shift) < p.noutputs && sub + (k & (nv - 1)) * lpr < nvec;
+      A x[VEC];
+      load_as<A, S, VEC>(&raw[k], x);
+      s[k] = live ? F::pre(x[0]) : F::identity();
+#pragma unroll
+      for (int e = 1; e < VEC; ++e) s[k] = F::combine(s[k], live ? F::pre(x[e]) : F::identity());
+    }
+    if (nv > 1) {
+#pragma unroll
+      for (int k = 0; k < 8; k += 2) s[k] = F::combine(s[k], s[k + 1]);
+    }
+    if (nv > 2) {
+      s[0] = F::combine(s[0], s[2]);
+      s[4] = F::combine(s[4], s[6]);
+    }
+    if (nv > 4) s[0] = F::combine(s[0], s[4]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if ((k & (nv - 1)) == 0) {  // the same for every lane
+        A v = s[k];
+        for (int off = 1; off < lpr; off <<= 1) v = F::combine(v, __shfl_xor_sync(0xffffffffu, v, off));
+        const int64_t row = base + (k >> nv_shift);
+        if (sub == 0 && row < p.noutputs) {
+          int64_t in_off, out_off;
+          row_offsets(p, flat, row, in_off, out_off);
+          A r[1] = {apply_scale<A>(v, p.scale)};
+          DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+        }
+      }
+    }
+  }
+}
+
+// Rows of more than 256 vectors, up to 8 KB unless tuned otherwise: a warp per row, eight vectors in flight per lane, one
+// accumulator per vector element.  No shared memory and no CTA barrier, which is what a CTA per row pays for at this
+// length.
+template <class IO, class F, typename A, int VEC>
+__global__ void __launch_bounds__(256) red_rows_warp_vec_kernel(RedParams p) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = static_cast<int>(p.L / VEC);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  const bool flat = p.keep_sizes[1] == 1 && p.keep_sizes[2] == 1;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < p.noutputs; row += nwarps) {
+    int64_t in_off, out_off;
+    row_offsets(p, flat, row, in_off, out_off);
+    A acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = F::identity();
+    int v = lane;
+    for (; v + 7 * 32 < nvec; v += 8 * 32) {
+      A x[8][VEC];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) IO::template load<A, VEC>(p.in, in_off + static_cast<int64_t>(v + k * 32) * VEC, p.in_dtype, x[k]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = F::combine(acc[e], F::pre(x[k][e]));
+    }
+    for (; v < nvec; v += 32) {
+      A x[VEC];
+      IO::template load<A, VEC>(p.in, in_off + static_cast<int64_t>(v) * VEC, p.in_dtype, x);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = F::combine(acc[e], F::pre(x[e]));
+    }
+#pragma unroll
+    for (int e = 1; e < VEC; ++e) acc[0] = F::combine(acc[0], acc[e]);
+    const A r0 = warp_reduce<F, A>(acc[0]);
+    if (lane == 0) {
+      A r[1] = {apply_scale<A>(r0, p.scale)};
+      DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+    }
+  }
+}
+
 // ---- path 1 ------------------------------------------------------------------------------------------------
 template <class IO, class F, typename A, int VEC, int THREADS>
 __global__ void __launch_bounds__(THREADS) red_split_partial_kernel(RedParams p) {
@@ -325,35 +447,94 @@ __global__ void __launch_bounds__(256) red_split_final_kernel(RedParams p) {
   }
 }
 
+// Elements per 16-byte column vector of the statically typed inputs (fp32, bf16, fp16); the dynamically typed ones (double
+// and integer accumulation) go element by element.
+template <class IO> struct ColumnVector { static constexpr int value = 1; };
+template <typename S> struct ColumnVector<StaticIO<S>> { static constexpr int value = 16 / static_cast<int>(sizeof(S)); };
+
 // ---- path 2 ------------------------------------------------------------------------------------------------
-// keep_sizes[0] = kept dimension 0 (unit strides), keep_sizes[1..2] = outer kept dims; L rows of stride
-// red_stride are reduced.  Block = 32 columns x 8 row lanes.
-template <class IO, class F, typename A>
+// keep_sizes[0] = kept dimension 0 (unit strides), keep_sizes[1..2] = outer kept dims; L rows of stride red_stride are
+// reduced (the shape of `x.sum(0)`).  The L rows are cut into `splits` chunks of `seg` rows so that tall, narrow inputs
+// still fill the GPU; a CTA takes one chunk of one tile of columns.  A warp covers `vpr` column vectors (16 bytes each when
+// the pitch allows it) of 32 / vpr rows at a time, its 8 warps further rows; the partial results of the chunks are added
+// in chunk order by a second kernel (fixed order: bit-reproducible), or written directly when there is one chunk.
+template <class IO, class F, typename A, int VEC>
 __global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
-  __shared__ A sm[8][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const uint32_t col = blockIdx.x * 32 + tx;
-  uint64_t r = blockIdx.y;
+  __shared__ A sm[8][32 * VEC];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vpr = p.vpr, rows_per_warp = 32 / vpr;
+  const int cvl = lane % vpr, rsub = lane / vpr;
+  const int64_t nvec = p.keep_sizes[0] / VEC;
+  const int64_t cv = static_cast<int64_t>(blockIdx.x) * vpr + cvl;
+  const uint64_t r = blockIdx.z;
   const uint64_t i1 = r % p.keep_sizes[1];
   const uint64_t i2 = r / p.keep_sizes[1];
   const int64_t in_base = static_cast<int64_t>(i1) * p.keep_in_strides[1] + static_cast<int64_t>(i2) * p.keep_in_strides[2];
-  const int64_t out_base = static_cast<int64_t>(i1) * p.keep_out_strides[1] + static_cast<int64_t>(i2) * p.keep_out_strides[2];
-  A v = F::identity();
-  if (col < p.keep_sizes[0]) {
-    for (int64_t j = ty; j < p.L; j += 8) {
-      A one[1];
-      IO::template load<A, 1>(p.in, in_base + col * p.keep_in_strides[0] + j * p.red_stride, p.in_dtype, one);
-      v = F::combine(v, F::pre(one[0]));
+  const int64_t chunk = blockIdx.y;
+  const int64_t begin = chunk * p.seg;
+  const int64_t end = begin + p.seg < p.L ? begin + p.seg : p.L;
+  A acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = F::identity();
+  if (cv < nvec) {
+    const int64_t col0 = in_base + cv * VEC;
+    const int64_t step = 8 * rows_per_warp;
+    int64_t j = begin + warp * rows_per_warp + rsub;
+    // four rows in flight per thread
+    for (; j + 3 * step < end; j += 4 * step) {
+      A v[4][VEC];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) IO::template load<A, VEC>(p.in, col0 + (j + u * step) * p.red_stride, p.in_dtype, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], F::pre(v[u][k]));
+    }
+    for (; j < end; j += step) {
+      A v[VEC];
+      IO::template load<A, VEC>(p.in, col0 + j * p.red_stride, p.in_dtype, v);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], F::pre(v[k]));
     }
   }
-  sm[ty][tx] = v;
-  __syncthreads();
-  if (ty == 0 && col < p.keep_sizes[0]) {
-    A a = sm[0][tx];
+  // rows that share the warp, then the 8 warps
+  for (int off = vpr; off < 32; off <<= 1)
 #pragma unroll
-    for (int k = 1; k < 8; ++k) a = F::combine(a, sm[k][tx]);
-    A o[1] = {apply_scale<A>(a, p.scale)};
-    DynamicIO::store<A, 1>(p.out, out_base + col * p.keep_out_strides[0], p.out_dtype, o);
+    for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], __shfl_xor_sync(0xffffffffu, acc[k], off));
+  if (rsub == 0)
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) sm[warp][cvl * VEC + k] = acc[k];
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < vpr * VEC) {
+    const int64_t col = (static_cast<int64_t>(blockIdx.x) * vpr) * VEC + t;
+    if (col < static_cast<int64_t>(p.keep_sizes[0])) {
+      A a = sm[0][t];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) a = F::combine(a, sm[w][t]);
+      if (p.splits > 1) {
+        const int64_t o = static_cast<int64_t>(r) * p.keep_sizes[0] + col;
+        static_cast<A*>(p.scratch)[o * p.splits + chunk] = a;
+      } else {
+        const int64_t out_base = static_cast<int64_t>(i1) * p.keep_out_strides[1] + static_cast<int64_t>(i2) * p.keep_out_strides[2];
+        A o1[1] = {apply_scale<A>(a, p.scale)};
+        DynamicIO::store<A, 1>(p.out, out_base + col * p.keep_out_strides[0], p.out_dtype, o1);
+      }
+    }
+  }
+}
+
+// The chunks' partial results of one output, added in chunk order.
+template <class F, typename A>
+__global__ void __launch_bounds__(256) red_cols_final_kernel(RedParams p) {
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; o < p.noutputs; o += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t in_off, out_off;
+    keep_offsets(p, o, in_off, out_off);
+    const A* part = static_cast<const A*>(p.scratch) + o * p.splits;
+    A v = part[0];
+    for (int s2 = 1; s2 < p.splits; ++s2) v = F::combine(v, part[s2]);
+    A r[1] = {apply_scale<A>(v, p.scale)};
+    DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
   }
 }
 
@@ -546,17 +727,66 @@ int make_plan(const sb_reduce_desc* d, Plan* plan) {
     p.red_stride = g.red_in_strides[0];
     if (outer <= 65535) {
       plan->path = 2;
+      // 16-byte column vectors when every row segment starts on a 16-byte boundary
+      const int vec = static_cast<int>(16 / es);
+      bool col_vec = acc_of(d->in_dtype) == 0 && g.keep_sizes[0] % vec == 0 && reinterpret_cast<uintptr_t>(d->in) % 16 == 0 &&
+                     (static_cast<uint64_t>(p.red_stride < 0 ? -p.red_stride : p.red_stride) * es) % 16 == 0;
+      for (int k = 1; k < nkeep; ++k) {
+        const uint64_t st = static_cast<uint64_t>(g.keep_in_strides[k] < 0 ? -g.keep_in_strides[k] : g.keep_in_strides[k]);
+        col_vec = col_vec && (st * es) % 16 == 0;
+      }
+      p.col_vec = col_vec ? 1 : 0;
+      const int64_t nvec = col_vec ? g.keep_sizes[0] / vec : g.keep_sizes[0];
+      int vpr = 1;
+      while (vpr < 32 && vpr < nvec) vpr <<= 1;
+      p.vpr = vpr;
+      // chunks of rows: enough CTAs for eight per SM, at least 256 rows each, at most 1024 chunks
+      const int64_t tiles = (nvec + vpr - 1) / vpr * static_cast<int64_t>(outer);
+      int64_t want = (8LL * sm_count() + tiles - 1) / tiles;
+      const int64_t max_by_len = (p.L + 255) / 256;
+      if (want > max_by_len) want = max_by_len;
+      if (want > 1024) want = 1024;
+      if (want < 1) want = 1;
+      p.seg = (p.L + want - 1) / want;
+      p.splits = static_cast<int>((p.L + p.seg - 1) / p.seg);
+      if (p.splits > 1) plan->scratch_bytes = static_cast<size_t>(noutputs) * p.splits * 8;
       return SB_OK;
     }
   }
   return SB_OK;
 }
 
+// Longest row (bytes) that a single warp reduces; longer rows take a CTA each.  0 switches the vector row kernels off.
+int64_t g_warp_row_bytes = 8192;
+
 template <class IO, class F, typename A>
 int launch_paths(const Plan& plan, cudaStream_t st) {
   const RedParams& p = plan.p;
   const int sms = sm_count();
   if (plan.path == 0) {
+    constexpr int kVec = ColumnVector<IO>::value;
+    if constexpr (kVec > 1) {
+      // rows of whole 16-byte vectors on 16-byte boundaries
+      const int64_t nvec = p.L / kVec;
+      if (plan.vec_ok && p.L % kVec == 0 && nvec >= 1 && g_warp_row_bytes > 0) {
+        if (nvec <= 256) {
+          int lpr = 1, nv = 1;
+          while (lpr < 32 && lpr < nvec) lpr <<= 1;
+          while (static_cast<int64_t>(lpr) * nv < nvec) nv <<= 1;
+          const int64_t rows_per_cta = 8LL * (32 / lpr) * (8 / nv);
+          int64_t ctas = (p.noutputs + rows_per_cta - 1) / rows_per_cta;
+          if (ctas > 8LL * sms) ctas = 8LL * sms;
+          red_rows_sub_kernel<IO, F, A, kVec><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr, nv);
+          return launch_status();
+        }
+        if (nvec * 16 <= g_warp_row_bytes) {
+          int64_t ctas = (p.noutputs + 7) / 8;
+          if (ctas > 8LL * sms) ctas = 8LL * sms;
+          red_rows_warp_vec_kernel<IO, F, A, kVec><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p);
+          return launch_status();
+        }
+      }
+    }
     if (p.L <= 1024) {
       const int64_t ctas = (p.noutputs + 7) / 8;
       const int grid = static_cast<int>(ctas < 16LL * sms ? ctas : 16LL * sms);
@@ -581,9 +811,17 @@ int launch_paths(const Plan& plan, cudaStream_t st) {
     return launch_status();
   }
   if (plan.path == 2) {
-    uint64_t outer = static_cast<uint64_t>(p.keep_sizes[1]) * p.keep_sizes[2];
-    dim3 grid((p.keep_sizes[0] + 31) / 32, static_cast<unsigned>(outer));
-    red_cols_kernel<IO, F, A><<<grid, 256, 0, st>>>(p);
+    const uint64_t outer = static_cast<uint64_t>(p.keep_sizes[1]) * p.keep_sizes[2];
+    constexpr int kVec = ColumnVector<IO>::value;
+    const int64_t nvec = p.col_vec ? p.keep_sizes[0] / kVec : p.keep_sizes[0];
+    dim3 grid(static_cast<unsigned>((nvec + p.vpr - 1) / p.vpr), static_cast<unsigned>(p.splits), static_cast<unsigned>(outer));
+    if (p.col_vec) red_cols_kernel<IO, F, A, kVec><<<grid, 256, 0, st>>>(p);
+    else red_cols_kernel<IO, F, A, 1><<<grid, 256, 0, st>>>(p);
+    int rc = launch_status();
+    if (rc != SB_OK || p.splits == 1) return rc;
+    int64_t ctas = (p.noutputs + 255) / 256;
+    if (ctas > 8LL * sms) ctas = 8LL * sms;
+    red_cols_final_kernel<F, A><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p);
     return launch_status();
   }
   int64_t ctas = (plan.g.noutputs + 255) / 256;
@@ -605,6 +843,12 @@ int launch_op(int op, const Plan& plan, cudaStream_t st) {
 }
 
 }  // namespace
+
+int red_set_warp_row_bytes(int n) {
+  if (n != 0 && (n < 4096 || n > 262144)) return SB_ERR_INVALID_ARGUMENT;
+  g_warp_row_bytes = n;
+  return SB_OK;
+}
 }  // namespace sb
 
 using namespace sb;
@@ -629,7 +873,7 @@ int sb_reduce(const sb_reduce_desc* d, sb_stream_t stream) {
   if (rc != SB_OK) return rc;
   if (plan.g.noutputs == 0) return SB_OK;
   if (plan.g.nreduce == 0) return SB_ERR_INVALID_ARGUMENT;  // the caller fills identities for empty reductions
-  if (plan.path == 1) {
+  if (plan.scratch_bytes > 0) {
     if (!d->scratch || d->scratch_bytes < plan.scratch_bytes) return SB_ERR_INVALID_ARGUMENT;
     if (reinterpret_cast<uintptr_t>(d->scratch) % 8) return SB_ERR_MISALIGNED;
   }
