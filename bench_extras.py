@@ -211,6 +211,20 @@ def run_extras(device, peak_gbs, profile=False):
           lambda: cr.sum(-1, dtype=torch.float32), 0.125, what)
     del r, cr
     torch.supa.empty_cache()
+    # short rows (lane groups share a row) and column sums (rows cut into chunks over the grid)
+    tall = device_randn((4194304, 64), torch.float32, device, 21)
+    nb = 4194304 * 64 * 4
+    entry("sum(-1) fp32 [4194304,64]", nb + 4194304 * 4, lambda: tall.sum(-1))
+    entry("amax(-1) fp32 [4194304,64]", nb + 4194304 * 4, lambda: tall.amax(-1))
+    entry("sum(0) fp32 [4194304,64]", nb, lambda: tall.sum(0))
+    del tall
+    torch.supa.empty_cache()
+    mid = device_randn((524288, 1024), torch.bfloat16, device, 22)
+    nb = 524288 * 1024 * 2
+    entry("sum(-1) bf16 [524288,1024]", nb + 524288 * 2, lambda: mid.sum(-1))
+    entry("sum(0) bf16 [524288,1024]", nb, lambda: mid.sum(0))
+    del mid
+    torch.supa.empty_cache()
     ls_rows = 16384 if profile else 65536
     sm = device_randn((ls_rows, 32000), torch.float32, device, 12, 3.0)
     csm = cpu_like(sm, 2048)

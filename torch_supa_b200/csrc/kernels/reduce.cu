@@ -371,6 +371,75 @@ __global__ void __launch_bounds__(256) red_rows_sub_kernel(RedParams p, int lpr,
   }
 }
 
+// The same split of the work for rows of exactly lpr * NV vectors (a power of two of them) whose kept dimensions collapse
+// to one row pitch: no slot needs clamping, the addresses are a row pointer plus constants, and the lane groups add
+// their R = 8 / NV row sums crosswise - each exchange hands half of a lane's sums to its partner, so after log2 R
+// exchanges lane `sub` holds row `sub` alone - which takes R - 1 + log2(lpr / R) shuffles and one store for R rows
+// where the kernel above spends R log2 lpr shuffles and R stores.  Needs lpr >= R.
+template <class IO, class F, typename A, int VEC, int NV>
+__global__ void __launch_bounds__(256) red_rows_pow2_kernel(RedParams p, int lpr) {
+  using S = typename IO::storage;
+  static_assert(sizeof(S) * VEC == 16, "one 16-byte vector per load");
+  constexpr int R = 8 / NV;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (lpr - 1);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t rows_per_warp = static_cast<int64_t>(32 / lpr) * R;
+  const int64_t pitch = p.keep_in_strides[0];
+  const int64_t opitch = p.keep_out_strides[0];
+  const S* in = static_cast<const S*>(p.in) + sub * VEC;
+  const int64_t kstep = static_cast<int64_t>(lpr) * VEC;
+  for (int64_t wbase = gwarp * rows_per_warp; wbase < p.noutputs; wbase += nwarps * rows_per_warp) {
+    const int64_t base = wbase + static_cast<int64_t>(lane / lpr) * R;
+    const bool whole = wbase + rows_per_warp <= p.noutputs;  // the same for the warp
+    uint4 raw[8];
+    if (whole) {
+      const S* src = in + base * pitch;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) raw[k] = *reinterpret_cast<const uint4*>(src + (k / NV) * pitch + (k % NV) * kstep);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        int64_t row = base + k / NV;
+        row = row < p.noutputs ? row : p.noutputs - 1;
+        raw[k] = *reinterpret_cast<const uint4*>(in + row * pitch + (k % NV) * kstep);
+      }
+    }
+    A t[R];
+#pragma unroll
+    for (int u = 0; u < R; ++u) {
+#pragma unroll
+      for (int kk = 0; kk < NV; ++kk) {
+        A x[VEC];
+        load_as<A, S, VEC>(&raw[u * NV + kk], x);
+        if (kk == 0) t[u] = F::pre(x[0]);
+        else t[u] = F::combine(t[u], F::pre(x[0]));
+#pragma unroll
+        for (int e = 1; e < VEC; ++e) t[u] = F::combine(t[u], F::pre(x[e]));
+      }
+    }
+    // crosswise: after the exchange at distance d a lane keeps the rows whose index has the lane's bit d
+#pragma unroll
+    for (int d = 1, held = R; d < R; d <<= 1, held >>= 1) {
+      const bool upper = (sub & d) != 0;
+#pragma unroll
+      for (int j = 0; j < held / 2; ++j) {
+        const A keep = upper ? t[2 * j + 1] : t[2 * j];
+        const A send = upper ? t[2 * j] : t[2 * j + 1];
+        t[j] = F::combine(keep, __shfl_xor_sync(0xffffffffu, send, d));
+      }
+    }
+    A v = t[0];
+    for (int d = R; d < lpr; d <<= 1) v = F::combine(v, __shfl_xor_sync(0xffffffffu, v, d));
+    const int64_t row = base + sub;
+    if (sub < R && row < p.noutputs) {
+      A r[1] = {apply_scale<A>(v, p.scale)};
+      DynamicIO::store<A, 1>(p.out, row * opitch, p.out_dtype, r);
+    }
+  }
+}
+
 // Rows of more than 256 vectors, up to 8 KB unless tuned otherwise: a warp per row, eight vectors in flight per lane, one
 // accumulator per vector element.  No shared memory and no CTA barrier, which is what a CTA per row pays for at this
 // length.
@@ -447,6 +516,14 @@ __global__ void __launch_bounds__(256) red_split_final_kernel(RedParams p) {
   }
 }
 
+// A 16-byte load that stays where it is written: eight of them in a row are eight loads in flight (left to itself the
+// compiler moves each load down to its use to save registers).
+__device__ __forceinline__ uint4 load_u4_in_order(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+
 // Elements per 16-byte column vector of the statically typed inputs (fp32, bf16, fp16); the dynamically typed ones (double
 // and integer accumulation) go element by element.
 template <class IO> struct ColumnVector { static constexpr int value = 1; };
@@ -457,7 +534,7 @@ template <typename S> struct ColumnVector<StaticIO<S>> { static constexpr int va
 // reduced (the shape of `x.sum(0)`).  The L rows are cut into `splits` chunks of `seg` rows so that tall, narrow inputs
 // still fill the GPU; a CTA takes one chunk of one tile of columns.  A warp covers `vpr` column vectors (16 bytes each when
 // the pitch allows it) of 32 / vpr rows at a time, its 8 warps further rows; the partial results of the chunks are added
-// in chunk order by a second kernel (fixed order: bit-reproducible), or written directly when there is one chunk.
+// by a second kernel in an order that the plan alone fixes (bit-reproducible), or written directly when there is one chunk.
 template <class IO, class F, typename A, int VEC>
 __global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
   __shared__ A sm[8][32 * VEC];
@@ -480,6 +557,28 @@ __global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
     const int64_t col0 = in_base + cv * VEC;
     const int64_t step = 8 * rows_per_warp;
     int64_t j = begin + warp * rows_per_warp + rsub;
+    if constexpr (VEC > 1) {
+      // Full-width tiles: eight rows in flight per thread, kept as loaded and widened only when they are added.
+      // Narrower tiles measured faster with the four rows of the loop below.
+      using S = typename IO::storage;
+      static_assert(sizeof(S) * VEC == 16, "one 16-byte vector per load");
+      if (vpr == 32) {
+        const S* src = static_cast<const S*>(p.in) + col0;
+        const int64_t rs = p.red_stride;
+        for (; j + 7 * step < end; j += 8 * step) {
+          uint4 raw[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) raw[u] = load_u4_in_order(src + (j + u * step) * rs);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            A x[VEC];
+            load_as<A, S, VEC>(&raw[u], x);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] = F::combine(acc[k], F::pre(x[k]));
+          }
+        }
+      }
+    }
     // four rows in flight per thread
     for (; j + 3 * step < end; j += 4 * step) {
       A v[4][VEC];
@@ -524,17 +623,36 @@ __global__ void __launch_bounds__(256) red_cols_kernel(RedParams p) {
   }
 }
 
-// The chunks' partial results of one output, added in chunk order.
+// The chunks' partial results of one output, added by `lanes` lanes (a power of two): lane l adds chunks l, l + lanes,
+// ... in that order and the lanes' sums are added pairwise; the order depends on nothing but the plan, so the result
+// is the same on every run.
 template <class F, typename A>
-__global__ void __launch_bounds__(256) red_cols_final_kernel(RedParams p) {
-  for (int64_t o = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; o < p.noutputs; o += static_cast<int64_t>(gridDim.x) * 256) {
-    int64_t in_off, out_off;
-    keep_offsets(p, o, in_off, out_off);
-    const A* part = static_cast<const A*>(p.scratch) + o * p.splits;
-    A v = part[0];
-    for (int s2 = 1; s2 < p.splits; ++s2) v = F::combine(v, part[s2]);
-    A r[1] = {apply_scale<A>(v, p.scale)};
-    DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+__global__ void __launch_bounds__(256) red_cols_final_kernel(RedParams p, int lanes) {
+  const int lane = threadIdx.x & 31, sub = lane & (lanes - 1);
+  const int per_warp = 32 / lanes;
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  for (int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); w * per_warp < p.noutputs; w += nwarps) {
+    const int64_t o = w * per_warp + lane / lanes;
+    A v = F::identity();
+    if (o < p.noutputs) {
+      const A* part = static_cast<const A*>(p.scratch) + o * p.splits;
+      int s2 = sub;
+      for (; s2 + 7 * lanes < p.splits; s2 += 8 * lanes) {  // eight loads in flight
+        A a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) a[u] = part[s2 + u * lanes];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v = F::combine(v, a[u]);
+      }
+      for (; s2 < p.splits; s2 += lanes) v = F::combine(v, part[s2]);
+    }
+    for (int d = 1; d < lanes; d <<= 1) v = F::combine(v, __shfl_xor_sync(0xffffffffu, v, d));
+    if (sub == 0 && o < p.noutputs) {
+      int64_t in_off, out_off;
+      keep_offsets(p, o, in_off, out_off);
+      A r[1] = {apply_scale<A>(v, p.scale)};
+      DynamicIO::store<A, 1>(p.out, out_off, p.out_dtype, r);
+    }
   }
 }
 
@@ -776,6 +894,16 @@ int launch_paths(const Plan& plan, cudaStream_t st) {
           const int64_t rows_per_cta = 8LL * (32 / lpr) * (8 / nv);
           int64_t ctas = (p.noutputs + rows_per_cta - 1) / rows_per_cta;
           if (ctas > 8LL * sms) ctas = 8LL * sms;
+          if (static_cast<int64_t>(lpr) * nv == nvec && lpr >= 8 / nv && p.keep_sizes[1] == 1 && p.keep_sizes[2] == 1) {
+            const unsigned grid = static_cast<unsigned>(ctas);
+            switch (nv) {
+              case 1: red_rows_pow2_kernel<IO, F, A, kVec, 1><<<grid, 256, 0, st>>>(p, lpr); break;
+              case 2: red_rows_pow2_kernel<IO, F, A, kVec, 2><<<grid, 256, 0, st>>>(p, lpr); break;
+              case 4: red_rows_pow2_kernel<IO, F, A, kVec, 4><<<grid, 256, 0, st>>>(p, lpr); break;
+              default: red_rows_pow2_kernel<IO, F, A, kVec, 8><<<grid, 256, 0, st>>>(p, lpr); break;
+            }
+            return launch_status();
+          }
           red_rows_sub_kernel<IO, F, A, kVec><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr, nv);
           return launch_status();
         }
@@ -819,9 +947,11 @@ int launch_paths(const Plan& plan, cudaStream_t st) {
     else red_cols_kernel<IO, F, A, 1><<<grid, 256, 0, st>>>(p);
     int rc = launch_status();
     if (rc != SB_OK || p.splits == 1) return rc;
-    int64_t ctas = (p.noutputs + 255) / 256;
+    int lanes = 1;
+    while (lanes < 32 && lanes < p.splits) lanes <<= 1;
+    int64_t ctas = (p.noutputs + 8 * (32 / lanes) - 1) / (8 * (32 / lanes));
     if (ctas > 8LL * sms) ctas = 8LL * sms;
-    red_cols_final_kernel<F, A><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p);
+    red_cols_final_kernel<F, A><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lanes);
     return launch_status();
   }
   int64_t ctas = (plan.g.noutputs + 255) / 256;
