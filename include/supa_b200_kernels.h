@@ -410,7 +410,8 @@ SB_API int sb_elementwise_path(const sb_ew_desc* desc);
  * Replaces gpu_reduce_kernel / ReduceOp / setReduceConfig
  * (torch_supa/csrc/aten/ops/kernels/reduce/Reduce.cuh:220-224,400-476,1040-1333) for sum_kernel_cuda
  * (ReduceSumKernel.cu:80-113), mean_kernel_cuda (ReduceMomentKernel.cu:16-55) and the amax stub of the
- * external native-op library.  Dimensions fastest first; a reduced dimension has out_stride 0.
+ * external native-op library.  Dimensions in any order (the planner orders them by input stride itself: a TensorIterator lists
+ * the reduced dimensions first); a reduced dimension has out_stride 0.
  * Accumulation is fp32 for fp16/bf16/fp32 inputs, fp64 for fp64, int64 for integers; amax is exact and
  * propagates NaN.
  * ------------------------------------------------------------------------------------------ */

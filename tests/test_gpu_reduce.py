@@ -1,5 +1,6 @@
 """Reductions through the C ABI against fixtures, oracle and PyTorch CPU (needs a GPU)."""
 import numpy as np
+
 import pytest
 import torch
 
@@ -174,6 +175,36 @@ def test_row_kernels_agree_with_the_cta_kernel(cuda_device):
             assert torch.equal(new[op], old[op]), (op, cols)
         assert_close(new["sum"].double().cpu().numpy(), old["sum"].double().cpu().numpy(), 1e-2 if dtype != torch.float32 else 1e-5,
                      1e-1 if dtype != torch.float32 else 1e-3, "sum")
+
+
+def test_dimension_order_of_the_descriptor_does_not_choose_the_path(cuda_device):
+    # a TensorIterator lists the reduced dimensions first: x.sum(0) arrives as [rows (reduced, stride cols), cols (kept, stride 1)]
+    from torch_supa_b200 import capi
+
+    x = torch.randn(5000, 96, device=cuda_device)
+    out = torch.empty(96, device=cuda_device)
+    d = capi.make_reduce_desc(OPS["sum"], x, out, [0])
+    assert d.ndim == 2 and capi.reduce_path(d) == 2
+    for field in (d.sizes, d.in_strides, d.out_strides):
+        field[0], field[1] = field[1], field[0]
+    assert d.in_strides[0] == 96 and d.out_strides[0] == 0
+    assert capi.reduce_path(d) == 2
+    scratch = torch.empty(max(capi.reduce_scratch_bytes(d), 8), dtype=torch.uint8, device=cuda_device)
+    d.scratch, d.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    capi.reduce(d)
+    torch.cuda.synchronize()
+    assert_close(out.cpu().numpy(), x.cpu().double().sum(0).numpy(), 1e-5, 1e-3, "sum(0), reduced dimension listed first")
+    # through the operator: the same plan, so the same bits as the C ABI call in stride order
+    import torch_supa_b200  # noqa: F401  (registers the supa device)
+
+    xs = x.cpu().to("supa")
+    assert torch.equal(xs.sum(0).cpu(), capi_sum0(x))
+
+
+def capi_sum0(x):
+    from torch_supa_b200 import functional as F2
+
+    return F2.reduce(OPS["sum"], x, [0]).cpu()
 
 
 def test_split_rows_path_is_deterministic(cuda_device):

@@ -722,9 +722,10 @@ int make_plan(const sb_reduce_desc* d, Plan* plan) {
   if (d->op == SB_RED_MEAN && plan->acc == 2) return SB_ERR_UNSUPPORTED;  // mean is defined on floating types
   if ((d->op == SB_RED_AMAX || d->op == SB_RED_AMIN) && d->in_dtype == SB_BOOL) plan->acc = 2;
 
-  // split, drop size-1 dims, coalesce
-  Dim dims[SB_MAX_DIMS];
-  int n = 0;
+  // Drop size-1 dims, order the rest by input stride (callers list them in any order: a TensorIterator puts the
+  // reduced dimensions first, whatever their strides), then merge neighbours that walk memory as one dimension.
+  Dim raw[SB_MAX_DIMS];
+  int nraw = 0;
   int64_t noutputs = 1, nreduce = 1;
   for (int i = 0; i < d->ndim; ++i) {
     if (d->sizes[i] < 0) return SB_ERR_INVALID_ARGUMENT;
@@ -733,7 +734,20 @@ int make_plan(const sb_reduce_desc* d, Plan* plan) {
     if (red) nreduce *= d->sizes[i];
     else noutputs *= d->sizes[i];
     if (d->sizes[i] == 1) continue;
-    Dim cur{d->sizes[i], d->in_strides[i], d->out_strides[i], red};
+    raw[nraw++] = Dim{d->sizes[i], d->in_strides[i], d->out_strides[i], red};
+  }
+  // a stride of zero (an expanded input) names no position in memory: such dimensions go last
+  auto mag = [](int64_t v) { return v == 0 ? INT64_MAX : (v < 0 ? -v : v); };
+  for (int i = 1; i < nraw; ++i) {  // insertion sort: stable, at most SB_MAX_DIMS entries
+    const Dim cur = raw[i];
+    int j = i;
+    for (; j > 0 && mag(raw[j - 1].in_stride) > mag(cur.in_stride); --j) raw[j] = raw[j - 1];
+    raw[j] = cur;
+  }
+  Dim dims[SB_MAX_DIMS];
+  int n = 0;
+  for (int i = 0; i < nraw; ++i) {
+    const Dim& cur = raw[i];
     if (n > 0) {
       Dim& prev = dims[n - 1];
       if (prev.reduced == cur.reduced && cur.in_stride == prev.in_stride * prev.size &&
