@@ -103,7 +103,10 @@ def test_indexed_extrema_golden(golden, cuda_device, dim, is_max):
 
 
 @pytest.mark.parametrize("shape,dim", [((7, 100000), 1), ((3, 5000000), 1), ((2000, 300), 1), ((64, 257, 33), 1), ((1, 3000000), 1),
-                                       ((100000, 8), 0), ((70000, 3), 1)])
+                                       ((100000, 8), 0), ((70000, 3), 1),
+                                       # lane groups per row (1 - 32 lanes, vector and scalar loads), columns in chunks
+                                       ((70001, 64), 1), ((5000, 1000), 1), ((3000, 1001), 1), ((9000, 8), 1), ((4000, 2048), 1),
+                                       ((300000, 64), 0), ((40000, 33), 0), ((3, 20000, 70), 1), ((50, 4100), 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32, torch.int64, torch.float64])
 def test_indexed_extrema_bit_exact_against_cpu(cuda_device, shape, dim, dtype):
     """Every path of the kernel (rows in one CTA, rows cut into segments, columns), every accumulation type; few distinct
@@ -162,7 +165,9 @@ def test_moments_golden(golden, cuda_device, dim):
         assert_close(mean.cpu().numpy(), golden["mom/mean1"], 2e-6, 1e-6, "mean")
 
 
-@pytest.mark.parametrize("shape,dim", [((5, 200000), 1), ((3000, 700), 1), ((40, 1000, 9), 1), ((2, 4000000), 1)])
+@pytest.mark.parametrize("shape,dim", [((5, 200000), 1), ((3000, 700), 1), ((40, 1000, 9), 1), ((2, 4000000), 1),
+                                       ((70001, 64), 1), ((3000, 1001), 1), ((9000, 8), 1), ((2000, 2048), 1), ((300000, 64), 0),
+                                       ((40000, 33), 0), ((3, 20000, 70), 1), ((50, 4100), 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
 def test_moments_against_oracle(cuda_device, shape, dim, dtype):
     from torch_supa_b200 import functional as F2
