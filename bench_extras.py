@@ -217,6 +217,8 @@ def run_extras(device, peak_gbs, profile=False):
     entry("sum(-1) fp32 [4194304,64]", nb + 4194304 * 4, lambda: tall.sum(-1))
     entry("amax(-1) fp32 [4194304,64]", nb + 4194304 * 4, lambda: tall.amax(-1))
     entry("sum(0) fp32 [4194304,64]", nb, lambda: tall.sum(0))
+    entry("argmax(-1) fp32 [4194304,64] (value and index state per lane group)", nb + 4194304 * 8, lambda: tall.argmax(-1))
+    entry("var(0) fp32 [4194304,64] (fp64 state, columns in chunks)", nb, lambda: tall.var(0))
     del tall
     torch.supa.empty_cache()
     mid = device_randn((524288, 1024), torch.bfloat16, device, 22)
@@ -224,6 +226,12 @@ def run_extras(device, peak_gbs, profile=False):
     entry("sum(-1) bf16 [524288,1024]", nb + 524288 * 2, lambda: mid.sum(-1))
     entry("sum(0) bf16 [524288,1024]", nb, lambda: mid.sum(0))
     del mid
+    torch.supa.empty_cache()
+    wide = device_randn((8192, 32000), torch.float32, device, 23)
+    nb = 8192 * 32000 * 4
+    entry("argmax(-1) fp32 [8192,32000]", nb + 8192 * 8, lambda: wide.argmax(-1))
+    entry("var(-1) fp32 [8192,32000]", nb + 8192 * 4, lambda: wide.var(-1))
+    del wide
     torch.supa.empty_cache()
     ls_rows = 16384 if profile else 65536
     sm = device_randn((ls_rows, 32000), torch.float32, device, 12, 3.0)

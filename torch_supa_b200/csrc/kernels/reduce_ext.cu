@@ -67,6 +67,36 @@ template <typename A, bool IS_MAX> struct ArgOp {
       s.i = idx;
     }
   }
+  // VEC elements at rising indices idx0 .. idx0 + VEC - 1.  For fp32 states the extremum of the vector is formed first
+  // (NaN-propagating, one instruction per element) and only a vector that beats the running state is searched for the
+  // position of its extremum: on unsorted data that happens about ln(n) times per thread.
+  template <int VEC> __device__ static __forceinline__ void fold_vec(State& s, const A (&x)[VEC], int64_t idx0) {
+    if constexpr (std::is_same<A, float>::value && VEC > 1) {
+      float m = x[0];
+#pragma unroll
+      for (int k = 1; k < VEC; ++k) {
+        if constexpr (IS_MAX) asm("max.NaN.f32 %0, %1, %2;" : "=f"(m) : "f"(m), "f"(x[k]));
+        else asm("min.NaN.f32 %0, %1, %2;" : "=f"(m) : "f"(m), "f"(x[k]));
+      }
+      const bool sn = is_nan(s.v), mn = is_nan(m);
+      const bool take = s.i < 0 || (mn ? !sn : (!sn && (IS_MAX ? m > s.v : m < s.v)));
+      if (take) {
+        int k0 = VEC - 1;
+#pragma unroll
+        for (int k = VEC - 2; k >= 0; --k)
+          if (mn ? is_nan(x[k]) : x[k] == m) k0 = k;  // the first of equal extrema, the first NaN
+        float v = x[VEC - 1];
+#pragma unroll
+        for (int k = VEC - 2; k >= 0; --k)
+          if (k0 == k) v = x[k];
+        s.v = v;
+        s.i = idx0 + k0;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
+    }
+  }
   __device__ static __forceinline__ void merge(State& s, const State& o) {
     if (wins(o.v, o.i, s.v, s.i)) s = o;
   }
@@ -107,6 +137,10 @@ struct MomentOp {
     const double d = x - s.shift;
     s.s1 += d;
     s.s2 = fma(d, d, s.s2);
+  }
+  template <int VEC> __device__ static __forceinline__ void fold_vec(State& s, const double (&x)[VEC], int64_t idx0) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
   }
   __device__ static __forceinline__ void merge(State& s, const State& o) {  // every partial of a row uses the same shift
     s.s1 += o.s1;
@@ -163,15 +197,12 @@ __global__ void __launch_bounds__(THREADS) ext_rows_kernel(ExtParams p) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) DynamicIO::load<A, VEC>(p.in, base + e + u * kStep, p.in_dtype, x[u]);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) Op::fold(s, x[u][k], e + u * kStep + k);
+    for (int u = 0; u < kUnroll; ++u) Op::template fold_vec<VEC>(s, x[u], e + u * kStep);
   }
   for (; e < end; e += kStep) {
     A x[VEC];
     DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x);
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) Op::fold(s, x[k], e + k);
+    Op::template fold_vec<VEC>(s, x, e);
   }
   s = warp_fold<Op>(s);
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
@@ -226,15 +257,12 @@ __global__ void __launch_bounds__(256) ext_rows_group_kernel(ExtParams p, int lp
       DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x[0]);
       DynamicIO::load<A, VEC>(p.in, base + e + step, p.in_dtype, x[1]);
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) Op::fold(s, x[u][k], e + u * step + k);
+      for (int u = 0; u < 2; ++u) Op::template fold_vec<VEC>(s, x[u], e + u * step);
     }
     if (e < p.L) {
       A x[VEC];
       DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) Op::fold(s, x[k], e + k);
+      Op::template fold_vec<VEC>(s, x, e);
     }
     for (int o = lpr >> 1; o > 0; o >>= 1) {
       const State other = Op::shfl(s, o);
@@ -372,7 +400,8 @@ int launch_ext(ExtParams p, cudaStream_t st) {
   if (p.inner == 1 && p.L * static_cast<int64_t>(dtype_size(p.in_dtype)) <= kGroupRowBytes) {
     const int64_t es = static_cast<int64_t>(dtype_size(p.in_dtype));
     const bool vec = p.L % 4 == 0 && reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es * 4 < 16 ? es * 4 : 16) == 0;
-    const int64_t units = vec ? p.L / 4 : p.L;  // loads per row
+    const bool vec8 = es == 2 && p.L % 8 == 0 && reinterpret_cast<uintptr_t>(p.in) % 16 == 0;  // 16-byte loads of 16-bit elements
+    const int64_t units = vec8 ? p.L / 8 : (vec ? p.L / 4 : p.L);  // loads per row
     int lpr = 1;
     while (lpr < 32 && lpr * 2 <= units) lpr <<= 1;  // at least one load per lane, two where the row has them
     if (lpr > 1 && lpr * 2 > units) lpr >>= 1;
@@ -380,7 +409,8 @@ int launch_ext(ExtParams p, cudaStream_t st) {
     int64_t ctas = (p.outer + rows_per_cta - 1) / rows_per_cta;
     const int64_t cap = 8LL * sm_count();
     if (ctas > cap) ctas = cap;
-    if (vec) ext_rows_group_kernel<Op, 4><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr);
+    if (vec8) ext_rows_group_kernel<Op, 8><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr);
+    else if (vec) ext_rows_group_kernel<Op, 4><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr);
     else ext_rows_group_kernel<Op, 1><<<static_cast<unsigned>(ctas), 256, 0, st>>>(p, lpr);
     return launch_status();
   }
@@ -390,6 +420,7 @@ int launch_ext(ExtParams p, cudaStream_t st) {
     // (not for the moments: with their fp64 state the vector form measured slower, 0.51 against 0.78 on fp32 rows of 32000)
     const bool vec4 = !std::is_same<Op, MomentOp>::value && p.L % 4 == 0 && p.seg % 4 == 0 &&
                       reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es4 < 16 ? es4 : 16) == 0;
+    const bool vec8 = vec4 && dtype_size(p.in_dtype) == 2 && p.L % 8 == 0 && p.seg % 8 == 0 && reinterpret_cast<uintptr_t>(p.in) % 16 == 0;
     if (p.outer > 65535) {  // gridDim.y limit: treat the rows as columns of an [1, L, outer]-like walk is wrong; fold in slabs
       for (int64_t r0 = 0; r0 < p.outer; r0 += 65535) {
         ExtParams q = p;
@@ -400,13 +431,15 @@ int launch_ext(ExtParams p, cudaStream_t st) {
         if (p.out1) q.out1 = static_cast<char*>(p.out1) + r0 * (std::is_same<Op, MomentOp>::value ? dtype_size(p.out_dtype) : 8);
         q.nseg = 1;
         q.seg = q.L;
-        if (vec4) ext_rows_kernel<Op, 256, 4><<<dim3(1, static_cast<unsigned>(n)), 256, 0, st>>>(q);
+        if (vec8) ext_rows_kernel<Op, 256, 8><<<dim3(1, static_cast<unsigned>(n)), 256, 0, st>>>(q);
+        else if (vec4) ext_rows_kernel<Op, 256, 4><<<dim3(1, static_cast<unsigned>(n)), 256, 0, st>>>(q);
         else ext_rows_kernel<Op, 256, 1><<<dim3(1, static_cast<unsigned>(n)), 256, 0, st>>>(q);
         if (launch_status() != SB_OK) return SB_ERR_CUDA;
       }
       return SB_OK;
     }
-    if (vec4) ext_rows_kernel<Op, 256, 4><<<dim3(p.nseg, static_cast<unsigned>(p.outer)), 256, 0, st>>>(p);
+    if (vec8) ext_rows_kernel<Op, 256, 8><<<dim3(p.nseg, static_cast<unsigned>(p.outer)), 256, 0, st>>>(p);
+    else if (vec4) ext_rows_kernel<Op, 256, 4><<<dim3(p.nseg, static_cast<unsigned>(p.outer)), 256, 0, st>>>(p);
     else ext_rows_kernel<Op, 256, 1><<<dim3(p.nseg, static_cast<unsigned>(p.outer)), 256, 0, st>>>(p);
     if (launch_status() != SB_OK) return SB_ERR_CUDA;
     if (p.nseg > 1) {
