@@ -274,13 +274,16 @@ __global__ void __launch_bounds__(256) ext_rows_group_kernel(ExtParams p, int lp
 
 // ---- columns in chunks: grid (column tiles of 32, chunks of rows, outer) -------------------------------------------
 template <class Op, int CV>
-__global__ void __launch_bounds__(256) ext_cols_chunk_kernel(ExtParams p) {
+__global__ void __launch_bounds__(256) ext_cols_chunk_kernel(ExtParams p, int cpr) {
   using A = typename Op::Acc;
   using State = typename Op::State;
   extern __shared__ __align__(16) unsigned char ext_smem[];
-  State* sm = reinterpret_cast<State*>(ext_smem);  // [8 warps][32 lanes][CV]
+  State* sm = reinterpret_cast<State*>(ext_smem);  // [8 warps][cpr lanes][CV]
+  // `cpr` lanes (a power of two) cover a row of the tile, CV neighbouring columns each; the warp's other lanes take
+  // the next rows, so that a narrow tensor still gives every lane a column
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t col = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * CV;  // CV neighbouring columns per thread
+  const int csub = lane & (cpr - 1), rsub = lane / cpr, rpw = 32 / cpr;
+  const int64_t col = (static_cast<int64_t>(blockIdx.x) * cpr + csub) * CV;
   const int64_t o = blockIdx.z;
   const int64_t chunk = blockIdx.y;
   const int64_t begin = chunk * p.seg;
@@ -293,32 +296,43 @@ __global__ void __launch_bounds__(256) ext_cols_chunk_kernel(ExtParams p) {
 #pragma unroll
   for (int c = 0; c < CV; ++c) s[c] = Op::init(first[c]);
   if (live) {
-    int64_t e = begin + warp;
-    for (; e + 24 < end; e += 32) {
+    const int64_t step = 8 * rpw;
+    int64_t e = begin + warp * rpw + rsub;
+    for (; e + 3 * step < end; e += 4 * step) {
       A x[4][CV];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) DynamicIO::load<A, CV>(p.in, base + (e + 8 * u) * p.inner, p.in_dtype, x[u]);
+      for (int u = 0; u < 4; ++u) DynamicIO::load<A, CV>(p.in, base + (e + u * step) * p.inner, p.in_dtype, x[u]);
 #pragma unroll
       for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int c = 0; c < CV; ++c) Op::fold(s[c], x[u][c], e + 8 * u);
+        for (int c = 0; c < CV; ++c) Op::fold(s[c], x[u][c], e + u * step);
     }
-    for (; e < end; e += 8) {
+    for (; e < end; e += step) {
       A x[CV];
       DynamicIO::load<A, CV>(p.in, base + e * p.inner, p.in_dtype, x);
 #pragma unroll
       for (int c = 0; c < CV; ++c) Op::fold(s[c], x[c], e);
     }
   }
-#pragma unroll
-  for (int c = 0; c < CV; ++c) sm[(warp * 32 + lane) * CV + c] = s[c];
-  __syncthreads();
-  if (warp == 0 && live) {
+  // lanes cpr apart hold the same columns (and, for the moments, the same shift)
+  for (int d = 16; d >= cpr; d >>= 1) {
 #pragma unroll
     for (int c = 0; c < CV; ++c) {
-      State t = sm[lane * CV + c];
+      const State other = Op::shfl(s[c], d);
+      Op::merge(s[c], other);
+    }
+  }
+  if (rsub == 0) {
 #pragma unroll
-      for (int w = 1; w < 8; ++w) Op::merge(t, sm[(w * 32 + lane) * CV + c]);
+    for (int c = 0; c < CV; ++c) sm[(warp * cpr + csub) * CV + c] = s[c];
+  }
+  __syncthreads();
+  if (warp == 0 && rsub == 0 && live) {
+#pragma unroll
+    for (int c = 0; c < CV; ++c) {
+      State t = sm[csub * CV + c];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) Op::merge(t, sm[(w * cpr + csub) * CV + c]);
       const int64_t out_index = o * p.inner + col + c;
       if (p.nseg == 1) Op::finish(p, t, out_index);
       else static_cast<State*>(p.scratch)[out_index * p.nseg + chunk] = t;
@@ -381,7 +395,12 @@ int plan_segments(int64_t outer, int64_t L, int64_t* seg) {
 
 // Chunks of rows for the column kernel: enough CTAs for eight per SM, at least 256 rows each, at most 1024 chunks.
 int plan_chunks(int64_t outer, int64_t L, int64_t inner, int64_t* seg) {
-  const int64_t tile_cols = (inner % 4 == 0 && inner >= 128) ? 128 : 32;  // the launch takes four columns per thread then
+  // the launch takes four columns per thread when inner allows it (tiles of up to 128 columns), else tiles of 32
+  int64_t tile_cols = 32;
+  if (inner % 4 == 0) {
+    tile_cols = 4;
+    while (tile_cols < 128 && tile_cols < inner) tile_cols <<= 1;
+  }
   const int64_t tiles = (inner + tile_cols - 1) / tile_cols * outer;
   int64_t want = (8LL * sm_count() + tiles - 1) / tiles;
   const int64_t by_len = (L + 255) / 256;
@@ -452,12 +471,15 @@ int launch_ext(ExtParams p, cudaStream_t st) {
   if (p.outer <= 65535 && p.L >= 64) {
     // four neighbouring columns per thread when every row of columns starts on the boundary such a load needs
     const int64_t es4 = static_cast<int64_t>(dtype_size(p.in_dtype)) * 4;
-    const bool cv4 = p.inner % 4 == 0 && p.inner >= 128 && reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es4 < 16 ? es4 : 16) == 0;
+    const bool cv4 = p.inner % 4 == 0 && reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es4 < 16 ? es4 : 16) == 0;
     const int cv = cv4 ? 4 : 1;
-    dim3 grid(static_cast<unsigned>((p.inner + 32 * cv - 1) / (32 * cv)), static_cast<unsigned>(p.nseg), static_cast<unsigned>(p.outer));
-    const size_t smem = sizeof(typename Op::State) * 256 * cv;
-    if (cv4) ext_cols_chunk_kernel<Op, 4><<<grid, 256, smem, st>>>(p);
-    else ext_cols_chunk_kernel<Op, 1><<<grid, 256, smem, st>>>(p);
+    const int64_t units = p.inner / cv;  // column groups per row
+    int cpr = 1;
+    while (cpr < 32 && cpr < units) cpr <<= 1;
+    dim3 grid(static_cast<unsigned>((units + cpr - 1) / cpr), static_cast<unsigned>(p.nseg), static_cast<unsigned>(p.outer));
+    const size_t smem = sizeof(typename Op::State) * 8 * cpr * cv;
+    if (cv4) ext_cols_chunk_kernel<Op, 4><<<grid, 256, smem, st>>>(p, cpr);
+    else ext_cols_chunk_kernel<Op, 1><<<grid, 256, smem, st>>>(p, cpr);
     if (launch_status() != SB_OK) return SB_ERR_CUDA;
     if (p.nseg > 1) {
       int64_t ctas = (total + 7) / 8;
