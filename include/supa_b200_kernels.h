@@ -439,7 +439,8 @@ typedef struct sb_reduce_desc {
   size_t scratch_bytes;
 } sb_reduce_desc;
 
-/* Scratch the launch needs (only when one output is split over several CTAs); 0 for most shapes. */
+/* Scratch the launch needs (when one output is split over several CTAs: few long rows, or column sums whose rows are
+ * cut into chunks); 0 for most shapes. */
 SB_API size_t sb_reduce_scratch_bytes(const sb_reduce_desc* desc);
 SB_API int sb_reduce(const sb_reduce_desc* desc, sb_stream_t stream);
 /* 0 = inner-contiguous rows, 1 = rows split over several CTAs (two stage), 2 = outer (column) reduce,
@@ -457,8 +458,8 @@ SB_API int sb_reduce_path(const sb_reduce_desc* desc);
  * sb_moments: variance or standard deviation with the given correction (M2 / max(0, L - correction)), and optionally
  * the mean, in `dtype` (torch_supa/csrc/aten/ops/StdVar.cpp:34-63).  Accumulated in fp64.
  *
- * scratch: sb_reduce_ext_scratch_bytes(...) bytes, 8-byte aligned, needed only when few long rows are cut into
- * segments (the call returns 0 otherwise).
+ * scratch: sb_reduce_ext_scratch_bytes(...) bytes, 8-byte aligned, needed when few long rows are cut into segments
+ * or the rows of a column reduction (inner > 1) into chunks (the call returns 0 otherwise).
  * ------------------------------------------------------------------------------------------ */
 SB_API size_t sb_reduce_ext_scratch_bytes(int32_t dtype, int64_t outer, int64_t L, int64_t inner, int32_t moments);
 SB_API int sb_arg_reduce(const void* in, int32_t dtype, int64_t outer, int64_t L, int64_t inner, int32_t is_max, void* values,
