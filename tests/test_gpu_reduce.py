@@ -207,6 +207,73 @@ def capi_sum0(x):
     return F2.reduce(OPS["sum"], x, [0]).cpu()
 
 
+@pytest.fixture(scope="module")
+def supa():
+    import torch_supa_b200  # noqa: F401  (registers the supa device)
+
+    if not torch.supa.is_available():
+        pytest.skip("no supa device")
+    return torch.device("supa", 0)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_seeded_random_shapes_views_and_dims(supa, seed):
+    """Random shapes (sizes drawn around the kernels' switch points), dimension sets, dtypes and views (slices, permutations,
+    expanded dimensions) through the operator, against PyTorch CPU: sum, amax, mean, argmax and var."""
+    import random
+
+    rnd = random.Random(1000 + seed)
+    g = torch.Generator().manual_seed(seed)
+    sizes = [1, 2, 3, 4, 7, 8, 16, 31, 32, 33, 64, 100, 128, 255, 256, 257, 1000, 1024, 2048, 2052, 4096, 5000]
+    for _ in range(40):
+        nd = rnd.choice([1, 2, 2, 2, 3, 3, 4])
+        shape, numel = [], 1
+        for _d in range(nd):
+            cand = [v for v in sizes if numel * v <= 3_000_000] or [1]
+            shape.append(rnd.choice(cand))
+            numel *= shape[-1]
+        dtype = rnd.choice([torch.float32, torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int32, torch.int64])
+        if dtype.is_floating_point:
+            x = torch.randn(shape, generator=g).to(dtype)
+        else:
+            x = torch.randint(-50, 50, shape, generator=g).to(dtype)
+        view = rnd.choice(["plain", "plain", "slice", "permute", "expand"])
+        d = x.to(supa)
+        if view == "slice" and shape[-1] >= 8:
+            lo = rnd.choice([0, 1, 4])
+            hi = shape[-1] - rnd.choice([0, 1, 4])
+            x, d = x[..., lo:hi], d[..., lo:hi]
+        elif view == "permute" and nd >= 2:
+            perm = list(range(nd))
+            rnd.shuffle(perm)
+            x, d = x.permute(perm), d.permute(perm)
+        elif view == "expand":
+            x, d = x.unsqueeze(0).expand(3, *x.shape), d.unsqueeze(0).expand(3, *d.shape)
+        k = rnd.randint(1, x.dim())
+        dims = sorted(rnd.sample(range(x.dim()), k))
+        what = f"{tuple(x.shape)} strides {tuple(x.stride())} {dtype} dims {dims}"
+        n = 1
+        for dd in dims:
+            n *= x.shape[dd]
+        ref = x.double().sum(dims) if dtype.is_floating_point else x.sum(dims)
+        got = d.sum(dims).cpu()
+        if dtype.is_floating_point:
+            tol = {torch.float32: 2e-5, torch.float64: 1e-11, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
+            scale = float(x.double().abs().sum(dims).max()) if x.numel() else 1.0
+            assert torch.allclose(got.double(), ref, rtol=tol, atol=tol * max(scale, 1.0)), "sum " + what
+            assert torch.equal(d.amax(dims).cpu(), x.amax(dims)), "amax " + what
+            m = d.mean(dims).cpu().double()
+            assert torch.allclose(m, x.double().mean(dims), rtol=tol, atol=tol * max(scale / max(n, 1), 1.0)), "mean " + what
+        else:
+            assert torch.equal(got, ref), "sum " + what
+            assert torch.equal(d.amax(dims).cpu(), x.amax(dims)), "amax " + what
+        one = rnd.choice(range(x.dim()))
+        assert torch.equal(d.argmax(one).cpu(), x.argmax(one)), f"argmax({one}) " + what
+        if dtype in (torch.float32, torch.float64) and x.shape[one] > 1:
+            v, rv = d.var(one).cpu().double(), x.double().var(one)
+            assert torch.allclose(v, rv, rtol=1e-4 if dtype == torch.float32 else 1e-10, atol=1e-6), f"var({one}) " + what
+
+
 def test_split_rows_path_is_deterministic(cuda_device):
     from torch_supa_b200 import capi, functional as F2
 
