@@ -114,7 +114,7 @@ def test_nll_fixtures(golden, cuda_device, name):
     assert_close(gi.cpu().numpy(), golden[name + "/grad_in"], 2e-6, 1e-7, name + " backward")
 
 
-@pytest.mark.parametrize("rows,classes", [(16, 10), (1000, 2000), (20000, 100), (100, 20000)])
+@pytest.mark.parametrize("rows,classes", [(16, 10), (1000, 2000), (20000, 100), (100, 20000), (70001, 33)])
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
 def test_nll_against_oracle(cuda_device, rows, classes, reduction, dtype):
@@ -135,6 +135,34 @@ def test_nll_against_oracle(cuda_device, rows, classes, reduction, dtype):
     egi = oracle.c_nll_loss_backward(go.double().numpy(), t.numpy(), classes, None, -100, reduction, float(tw))
     assert_close(gi.double().cpu().numpy(), egi, rtol, 0, "backward")
     assert int((gi != 0).sum()) <= rows
+
+
+def test_nll_many_rows_weights_and_targets_out_of_range(cuda_device):
+    """The reduction over a cluster of CTAs (16384 rows and more): class weights, ignored rows, and targets outside
+    [0, classes), which are reported in the status word and left out."""
+    from torch_supa_b200 import capi, functional as F2
+
+    g = torch.Generator().manual_seed(9)
+    rows, classes = 50001, 37
+    logp = F.log_softmax(torch.randn(rows, classes, generator=g), 1)
+    w = torch.rand(classes, generator=g) + 0.5
+    t = torch.randint(0, classes, (rows,), generator=g)
+    t[::5] = -100
+    bad = torch.tensor([3, 20000, 49999])
+    t_bad = t.clone()
+    t_bad[bad] = torch.tensor([-5, classes, 1000])
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    for red in ("mean", "sum"):
+        out, tw = F2.nll_loss_forward(logp.to(cuda_device), t_bad.to(cuda_device), w.to(cuda_device), -100, red, status)
+        t_ref = t_bad.clone()
+        t_ref[bad] = -100  # an index out of range is skipped like an ignored one
+        ref = F.nll_loss(logp.double(), t_ref, w.double(), ignore_index=-100, reduction=red)
+        assert_close(np.atleast_1d(out.double().cpu().numpy()), np.atleast_1d(ref.numpy()), 2e-6, 2e-6, red)
+        keep = t_ref != -100
+        assert abs(float(tw) - float(w[t_ref[keep]].double().sum())) <= 1e-6 * float(tw)
+        a = F2.nll_loss_forward(logp.to(cuda_device), t_bad.to(cuda_device), w.to(cuda_device), -100, red, status)[0]
+        assert torch.equal(a, out), "the same bits on every run"
+    assert int(status.item()) & capi.STATUS_TARGET_OUT_OF_RANGE
 
 
 def test_nll_uint8_targets(cuda_device):

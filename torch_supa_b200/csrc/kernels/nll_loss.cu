@@ -1,12 +1,16 @@
 // nll_loss forward / backward for [rows, classes] log-probabilities and class-index targets.
 //
 // forward:  out_i = -w[t_i] * x[i, t_i] (0 when t_i == ignore_index); `none` stores out_i, `sum` and
-//           `mean` reduce it in a fixed order (one CTA, per-thread strided partial sums then a tree, so
-//           the result is bit-reproducible); total_weight = sum of w[t_i] over rows that count.
+//           `mean` reduce it in a fixed order (one CTA, or a cluster of eight for 16384 rows and more: per-thread
+//           strided partial sums with four gathers in flight, a tree per CTA, the CTAs' sums added in rank order
+//           through distributed shared memory, so the result is bit-reproducible); total_weight = sum of w[t_i]
+//           over rows that count.
 // backward: grad_input is zero except [i, t_i] = -w[t_i] * g, with g = grad_output_i for `none`,
 //           grad_output for `sum`, grad_output / total_weight for `mean`.
 // An index outside [0, classes) that is not ignore_index sets SB_STATUS_TARGET_OUT_OF_RANGE and the row
 // is skipped; nothing traps.
+#include <cooperative_groups.h>
+
 #include "io.cuh"
 
 namespace sb {
@@ -55,14 +59,57 @@ __global__ void __launch_bounds__(256) nll_fwd_none_kernel(NllParams p, T* __res
   }
 }
 
+// Whether a target counts (an index outside [0, classes) that is not ignore_index is reported and skipped).
+__device__ __forceinline__ bool target_counts(const NllParams& p, int64_t t) {
+  if (t == p.ignore_index) return false;
+  if (t < 0 || t >= p.classes) {
+    if (p.status) atomicOr(p.status, SB_STATUS_TARGET_OUT_OF_RANGE);
+    return false;
+  }
+  return true;
+}
+
+constexpr int kNllClusterMax = 8;
+
 template <typename T, typename A>
 __global__ void __launch_bounds__(1024) nll_fwd_reduce_kernel(NllParams p, T* __restrict__ out, T* __restrict__ total_weight) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned nranks = cluster.num_blocks(), rank = cluster.block_rank();
   __shared__ double s_v[32];
   __shared__ double s_w[32];
+  __shared__ double c_v[kNllClusterMax];  // the copy of rank 0 collects the CTAs' sums
+  __shared__ double c_w[kNllClusterMax];
   const T* x = static_cast<const T*>(p.x);
   const T* w = static_cast<const T*>(p.weight);
   double av = 0.0, aw = 0.0;
-  for (int64_t i = threadIdx.x; i < p.rows; i += 1024) {
+  const int64_t stride = static_cast<int64_t>(nranks) * 1024;
+  int64_t i = static_cast<int64_t>(rank) * 1024 + threadIdx.x;
+  // four rows per thread at a time: the four targets, then the four elements they name, are in flight together
+  // (a row that does not count reads class 0 instead and is left out of the sums; rows exist, so classes > 0 here
+  // whenever a target can count)
+  for (; i + 3 * stride < p.rows; i += 4 * stride) {
+    int64_t t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = load_target(p, i + u * stride);
+    bool ok[4];
+    A xv[4], wt[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      ok[u] = target_counts(p, t[u]);
+      const int64_t tt = ok[u] ? t[u] : 0;
+      xv[u] = p.classes > 0 ? convert<A, T>(x[(i + u * stride) * p.classes + tt]) : A(0);
+      wt[u] = (w && p.classes > 0) ? convert<A, T>(w[tt]) : A(1);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (ok[u]) {
+        av -= static_cast<double>(wt[u]) * static_cast<double>(xv[u]);
+        aw += static_cast<double>(wt[u]);
+      }
+    }
+  }
+  for (; i < p.rows; i += stride) {
     int64_t t;
     if (row_counts(p, i, t)) {
       const double wt = w ? static_cast<double>(convert<A, T>(w[t])) : 1.0;
@@ -81,11 +128,21 @@ __global__ void __launch_bounds__(1024) nll_fwd_reduce_kernel(NllParams p, T* __
     av = warp_sum(s_v[threadIdx.x]);
     aw = warp_sum(s_w[threadIdx.x]);
     if (threadIdx.x == 0) {
-      double r = av;
-      if (p.reduction == SB_REDUCTION_MEAN) r = av / aw;  // 0/0 = NaN when every row is ignored
-      *out = convert<T, A>(static_cast<A>(r));
-      *total_weight = convert<T, A>(static_cast<A>(aw));
+      cluster.map_shared_rank(c_v, 0)[rank] = av;
+      cluster.map_shared_rank(c_w, 0)[rank] = aw;
     }
+  }
+  cluster.sync();  // every CTA's pair is in rank 0's shared memory; no CTA leaves before
+  if (rank == 0 && threadIdx.x == 0) {
+    double tv = c_v[0], tw = c_w[0];
+    for (unsigned r = 1; r < nranks; ++r) {
+      tv += c_v[r];
+      tw += c_w[r];
+    }
+    double r = tv;
+    if (p.reduction == SB_REDUCTION_MEAN) r = tv / tw;  // 0/0 = NaN when every row is ignored
+    *out = convert<T, A>(static_cast<A>(r));
+    *total_weight = convert<T, A>(static_cast<A>(tw));
   }
 }
 
@@ -137,7 +194,23 @@ int launch_fwd(const sb_nll_args* a, void* output, void* total_weight, cudaStrea
     nll_fwd_none_kernel<T, A><<<grid, 256, 0, st>>>(p, static_cast<T*>(output));
     return launch_status();
   }
-  nll_fwd_reduce_kernel<T, A><<<1, 1024, 0, st>>>(p, static_cast<T*>(output), static_cast<T*>(total_weight));
+  cudaLaunchConfig_t cfg{};
+  const unsigned ranks = a->rows >= 16384 ? kNllClusterMax : 1;
+  cfg.gridDim = dim3(ranks);
+  cfg.blockDim = dim3(1024);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ranks;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, nll_fwd_reduce_kernel<T, A>, p, static_cast<T*>(output), static_cast<T*>(total_weight)) != cudaSuccess) {
+    cudaGetLastError();
+    return SB_ERR_CUDA;
+  }
   return launch_status();
 }
 
