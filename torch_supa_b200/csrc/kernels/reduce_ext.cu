@@ -68,8 +68,8 @@ template <typename A, bool IS_MAX> struct ArgOp {
     }
   }
   // VEC elements at rising indices idx0 .. idx0 + VEC - 1.  For fp32 states the extremum of the vector is formed first
-  // (NaN-propagating, one instruction per element) and only a vector that beats the running state is searched for the
-  // position of its extremum: on unsorted data that happens about ln(n) times per thread.
+  // (NaN-propagating, one instruction per element) and a vector that beats the running state leaves only its extremum
+  // and its first index behind, without a branch; resolve() finds the position inside that one vector afterwards.
   template <int VEC> __device__ static __forceinline__ void fold_vec(State& s, const A (&x)[VEC], int64_t idx0) {
     if constexpr (std::is_same<A, float>::value && VEC > 1) {
       float m = x[0];
@@ -80,21 +80,33 @@ template <typename A, bool IS_MAX> struct ArgOp {
       }
       const bool sn = is_nan(s.v), mn = is_nan(m);
       const bool take = s.i < 0 || (mn ? !sn : (!sn && (IS_MAX ? m > s.v : m < s.v)));
-      if (take) {
+      s.v = take ? m : s.v;
+      s.i = take ? idx0 : s.i;
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
+    }
+  }
+  // After a thread's last fold_vec and before its state meets another thread's: s.i is the first index of the vector
+  // that holds the extremum s.v; read that vector again and take the first element equal to it (the first NaN when
+  // it is NaN), value and index.  `base` is the element offset of index 0.
+  template <int VEC> __device__ static __forceinline__ void resolve(State& s, const void* in, int64_t base, int dtype) {
+    if constexpr (std::is_same<A, float>::value && VEC > 1) {
+      if (s.i >= 0) {
+        float x[VEC];
+        DynamicIO::load<float, VEC>(in, base + s.i, dtype, x);
+        const bool mn = is_nan(s.v);
         int k0 = VEC - 1;
 #pragma unroll
         for (int k = VEC - 2; k >= 0; --k)
-          if (mn ? is_nan(x[k]) : x[k] == m) k0 = k;  // the first of equal extrema, the first NaN
+          if (mn ? is_nan(x[k]) : x[k] == s.v) k0 = k;
         float v = x[VEC - 1];
 #pragma unroll
         for (int k = VEC - 2; k >= 0; --k)
           if (k0 == k) v = x[k];
         s.v = v;
-        s.i = idx0 + k0;
+        s.i += k0;
       }
-    } else {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
     }
   }
   __device__ static __forceinline__ void merge(State& s, const State& o) {
@@ -142,6 +154,7 @@ struct MomentOp {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
   }
+  template <int VEC> __device__ static __forceinline__ void resolve(State&, const void*, int64_t, int) {}
   __device__ static __forceinline__ void merge(State& s, const State& o) {  // every partial of a row uses the same shift
     s.s1 += o.s1;
     s.s2 += o.s2;
@@ -204,6 +217,7 @@ __global__ void __launch_bounds__(THREADS) ext_rows_kernel(ExtParams p) {
     DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x);
     Op::template fold_vec<VEC>(s, x, e);
   }
+  Op::template resolve<VEC>(s, p.in, base, p.in_dtype);
   s = warp_fold<Op>(s);
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
   __syncthreads();
@@ -264,6 +278,7 @@ __global__ void __launch_bounds__(256) ext_rows_group_kernel(ExtParams p, int lp
       DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x);
       Op::template fold_vec<VEC>(s, x, e);
     }
+    Op::template resolve<VEC>(s, p.in, base, p.in_dtype);
     for (int o = lpr >> 1; o > 0; o >>= 1) {
       const State other = Op::shfl(s, o);
       Op::merge(s, other);
