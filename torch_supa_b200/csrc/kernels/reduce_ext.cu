@@ -2,9 +2,9 @@
 // max.dim, min.dim) and variance / standard deviation (with the mean).  The tensor is seen as [outer, L, inner],
 // contiguous, reduced over L, the view the softmax kernels use too.
 //
-//   inner == 1   rows: up to 8 KB a group of lanes (a power of two, up to a warp) per row, four elements per load where
-//                the rows allow it; longer rows a CTA each (or, with few rows, several CTAs per row, each on a
-//                segment, folded by a second kernel in a fixed order);
+//   inner == 1   rows: up to 8 KB (32 KB for the extrema of fp32 / bf16 / fp16 rows) a group of lanes (a power of two,
+//                up to a warp) per row, 16-byte loads where the rows allow it; longer rows a CTA each (or, with few
+//                rows, several CTAs per row, each on a segment, folded by a second kernel in a fixed order);
 //   inner  > 1   columns: a CTA takes 32 neighbouring columns of one chunk of the L rows (its 8 warps take rows in
 //                turn, four loads in flight), so that a tall narrow input still fills the GPU; the chunks' states go to
 //                scratch and a second kernel merges them, a warp per output.
@@ -205,6 +205,27 @@ __global__ void __launch_bounds__(THREADS) ext_rows_kernel(ExtParams p) {
   constexpr int kUnroll = 4;
   constexpr int64_t kStep = static_cast<int64_t>(THREADS) * VEC;
   int64_t e = begin + static_cast<int64_t>(threadIdx.x) * VEC;
+  if constexpr (std::is_same<A, float>::value && VEC > 1) {
+    // fp32 states over 16-byte vectors (4 fp32 or 8 16-bit elements): eight loads in flight, kept as loaded and widened
+    // only when they are folded
+    const int64_t es = p.in_dtype == SB_F32 ? 4 : 2;
+    if (VEC * es == 16 && (p.in_dtype == SB_F32 || p.in_dtype == SB_BF16 || p.in_dtype == SB_F16)) {
+      const char* src = static_cast<const char*>(p.in) + base * es;
+      for (; e + 7 * kStep < end; e += 8 * kStep) {
+        uint4 raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(src + (e + u * kStep) * es);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          A x[VEC];
+          if (p.in_dtype == SB_F32) load_as<float, float, VEC>(&raw[u], x);
+          else if (p.in_dtype == SB_BF16) load_as<float, __nv_bfloat16, VEC>(&raw[u], x);
+          else load_as<float, __half, VEC>(&raw[u], x);
+          Op::template fold_vec<VEC>(s, x, e + u * kStep);
+        }
+      }
+    }
+  }
   for (; e + (kUnroll - 1) * kStep < end; e += kUnroll * kStep) {
     A x[kUnroll][VEC];
 #pragma unroll
@@ -266,6 +287,27 @@ __global__ void __launch_bounds__(256) ext_rows_group_kernel(ExtParams p, int lp
     DynamicIO::load<A, 1>(p.in, base, p.in_dtype, first);
     State s = Op::init(first[0]);
     int64_t e = static_cast<int64_t>(sub) * VEC;
+    if constexpr (std::is_same<A, float>::value && VEC > 1) {
+      // fp32 states over 16-byte vectors: eight loads in flight per lane, widened only when they are folded (the launch
+      // picks lpr so that a lane has about eight vectors of its row)
+      const int64_t es = p.in_dtype == SB_F32 ? 4 : 2;
+      if (VEC * es == 16 && (p.in_dtype == SB_F32 || p.in_dtype == SB_BF16 || p.in_dtype == SB_F16)) {
+        const char* src = static_cast<const char*>(p.in) + base * es;
+        for (; e + 7 * step < p.L; e += 8 * step) {
+          uint4 raw[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(src + (e + u * step) * es);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            A x[VEC];
+            if (p.in_dtype == SB_F32) load_as<float, float, VEC>(&raw[u], x);
+            else if (p.in_dtype == SB_BF16) load_as<float, __nv_bfloat16, VEC>(&raw[u], x);
+            else load_as<float, __half, VEC>(&raw[u], x);
+            Op::template fold_vec<VEC>(s, x, e + u * step);
+          }
+        }
+      }
+    }
     for (; e + step < p.L; e += 2 * step) {
       A x[2][VEC];
       DynamicIO::load<A, VEC>(p.in, base + e, p.in_dtype, x[0]);
@@ -426,12 +468,15 @@ int plan_chunks(int64_t outer, int64_t L, int64_t inner, int64_t* seg) {
   return static_cast<int>((L + *seg - 1) / *seg);
 }
 
-// Longest row (bytes) that a group of lanes takes; longer rows get a CTA each.
-constexpr int64_t kGroupRowBytes = 8192;
+// Longest row (bytes) that a group of lanes takes; longer rows get a CTA each.  Extrema of the floating types keep
+// eight 16-byte loads per lane in flight, which a warp sustains up to 32 KB; a CTA needs 64 KB rows for the same.
+__host__ __device__ constexpr int64_t group_row_bytes(int dtype, bool moments) {
+  return (!moments && (dtype == SB_F32 || dtype == SB_BF16 || dtype == SB_F16)) ? 32768 : 8192;
+}
 
 template <class Op>
 int launch_ext(ExtParams p, cudaStream_t st) {
-  if (p.inner == 1 && p.L * static_cast<int64_t>(dtype_size(p.in_dtype)) <= kGroupRowBytes) {
+  if (p.inner == 1 && p.L * static_cast<int64_t>(dtype_size(p.in_dtype)) <= group_row_bytes(p.in_dtype, std::is_same<Op, MomentOp>::value)) {
     const int64_t es = static_cast<int64_t>(dtype_size(p.in_dtype));
     const bool vec = p.L % 4 == 0 && reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es * 4 < 16 ? es * 4 : 16) == 0;
     const bool vec8 = es == 2 && p.L % 8 == 0 && reinterpret_cast<uintptr_t>(p.in) % 16 == 0;  // 16-byte loads of 16-bit elements
@@ -439,6 +484,12 @@ int launch_ext(ExtParams p, cudaStream_t st) {
     int lpr = 1;
     while (lpr < 32 && lpr * 2 <= units) lpr <<= 1;  // at least one load per lane, two where the row has them
     if (lpr > 1 && lpr * 2 > units) lpr >>= 1;
+    const bool deep = !std::is_same<Op, MomentOp>::value && (vec8 || (vec && es == 4)) &&
+                      (p.in_dtype == SB_F32 || p.in_dtype == SB_BF16 || p.in_dtype == SB_F16);
+    if (deep) {  // 16-byte vectors and an fp32 state: eight vectors of the row per lane
+      lpr = 1;
+      while (lpr < 32 && lpr * 8 < units) lpr <<= 1;
+    }
     const int64_t rows_per_cta = 8LL * (32 / lpr);
     int64_t ctas = (p.outer + rows_per_cta - 1) / rows_per_cta;
     const int64_t cap = 8LL * sm_count();
@@ -541,7 +592,7 @@ int fill_params(ExtParams* p, const void* in, int dtype, int64_t outer, int64_t 
   p->nseg = 1;
   p->seg = L;
   p->scratch = nullptr;
-  const bool group_rows = inner == 1 && L * static_cast<int64_t>(dtype_size(dtype)) <= kGroupRowBytes;
+  const bool group_rows = inner == 1 && L * static_cast<int64_t>(dtype_size(dtype)) <= group_row_bytes(dtype, moments);
   if (!group_rows && outer > 0 && outer <= 65535 && L > 0 && (inner == 1 || L >= 64)) {
     p->nseg = inner == 1 ? plan_segments(outer, L, &p->seg) : plan_chunks(outer, L, inner, &p->seg);
     if (p->nseg > 1) {
@@ -565,7 +616,7 @@ size_t sb_reduce_ext_scratch_bytes(int32_t dtype, int64_t outer, int64_t L, int6
   if (inner <= 0 || outer <= 0 || outer > 65535 || L <= 0) return 0;
   const int kind = acc_kind(dtype);
   if (kind < 0) return 0;
-  if (inner == 1 && L * static_cast<int64_t>(dtype_size(dtype)) <= kGroupRowBytes) return 0;
+  if (inner == 1 && L * static_cast<int64_t>(dtype_size(dtype)) <= group_row_bytes(dtype, moments != 0)) return 0;
   if (inner > 1 && L < 64) return 0;
   int64_t seg = 0;
   const int nseg = inner == 1 ? plan_segments(outer, L, &seg) : plan_chunks(outer, L, inner, &seg);
