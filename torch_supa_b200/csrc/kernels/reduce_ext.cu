@@ -2,7 +2,7 @@
 // max.dim, min.dim) and variance / standard deviation (with the mean).  The tensor is seen as [outer, L, inner],
 // contiguous, reduced over L, the view the softmax kernels use too.
 //
-//   inner == 1   rows: up to 8 KB (32 KB for the extrema of fp32 / bf16 / fp16 rows) a group of lanes (a power of two,
+//   inner == 1   rows: up to 8 KB (32 KB for fp32 / bf16 / fp16 rows) a group of lanes (a power of two,
 //                up to a warp) per row, 16-byte loads where the rows allow it; longer rows a CTA each (or, with few
 //                rows, several CTAs per row, each on a segment, folded by a second kernel in a fixed order);
 //   inner  > 1   columns: a CTA takes 32 neighbouring columns of one chunk of the L rows (its 8 warps take rows in
@@ -11,7 +11,8 @@
 //
 // Index rules are those of PyTorch's CPU kernels, which the reference's tests take as golden: of equal extrema the
 // lowest index wins; NaN beats every number for max AND for min, and of several NaN the first.  Variance follows
-// var(correction): M2 / max(0, n - correction), accumulated in fp64 as shifted sums (shift = the row's first element).
+// var(correction): M2 / max(0, n - correction), accumulated in fp64 as shifted sums (shift = the row's first element;
+// over rows of fp32 / bf16 / fp16 values the sums of up to eight neighbouring terms are formed in fp32 first).
 #include <type_traits>
 
 #include "io.cuh"
@@ -42,6 +43,7 @@ template <typename A> struct ArgState {
 template <typename A, bool IS_MAX> struct ArgOp {
   using State = ArgState<A>;
   using Acc = A;
+  static constexpr bool kMoments = false;
   __device__ static __forceinline__ bool is_nan(A x) {
     if constexpr (std::is_floating_point<A>::value) return x != x;
     else return false;
@@ -140,19 +142,38 @@ struct MomentState {
   double s1, s2;  // sums of (x - shift) and of its square
   double shift;
 };
-struct MomentOp {
+// A = float for fp32 / bf16 / fp16 inputs, double for fp64 inputs.  The state is fp64 either way.
+template <typename A> struct MomentOpT {
   using State = MomentState;
-  using Acc = double;
-  __device__ static __forceinline__ State init(double first) { return State{0.0, 0.0, first}; }
+  using Acc = A;
+  static constexpr bool kMoments = true;
+  __device__ static __forceinline__ State init(A first) { return State{0.0, 0.0, static_cast<double>(first)}; }
   __device__ static __forceinline__ State neutral_like(const State& s) { return State{0.0, 0.0, s.shift}; }
-  __device__ static __forceinline__ void fold(State& s, double x, int64_t) {
-    const double d = x - s.shift;
+  __device__ static __forceinline__ void fold(State& s, A x, int64_t) {
+    const double d = static_cast<double>(x) - s.shift;
     s.s1 += d;
     s.s2 = fma(d, d, s.s2);
   }
-  template <int VEC> __device__ static __forceinline__ void fold_vec(State& s, const double (&x)[VEC], int64_t idx0) {
+  // A vector of fp32 values: the differences from the shift (itself an fp32 value: the row's first element), their sum
+  // and the sum of their squares are formed in fp32 (at most eight terms, a relative error of a few 2^-24 of the
+  // vector's own terms) and only the two sums go through the fp64 pipe, which otherwise bounds the kernel at three fp64
+  // operations and a conversion per element.
+  template <int VEC> __device__ static __forceinline__ void fold_vec(State& s, const A (&x)[VEC], int64_t idx0) {
+    if constexpr (std::is_same<A, float>::value && VEC > 1) {
+      const float shift = static_cast<float>(s.shift);
+      float b1 = 0.f, b2 = 0.f;
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
+      for (int k = 0; k < VEC; ++k) {
+        const float d = x[k] - shift;
+        b1 += d;
+        b2 = fmaf(d, d, b2);
+      }
+      s.s1 += static_cast<double>(b1);
+      s.s2 += static_cast<double>(b2);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) fold(s, x[k], idx0 + k);
+    }
   }
   template <int VEC> __device__ static __forceinline__ void resolve(State&, const void*, int64_t, int) {}
   __device__ static __forceinline__ void merge(State& s, const State& o) {  // every partial of a row uses the same shift
@@ -468,15 +489,16 @@ int plan_chunks(int64_t outer, int64_t L, int64_t inner, int64_t* seg) {
   return static_cast<int>((L + *seg - 1) / *seg);
 }
 
-// Longest row (bytes) that a group of lanes takes; longer rows get a CTA each.  Extrema of the floating types keep
-// eight 16-byte loads per lane in flight, which a warp sustains up to 32 KB; a CTA needs 64 KB rows for the same.
+// Longest row (bytes) that a group of lanes takes; longer rows get a CTA each.  fp32 / bf16 / fp16 rows keep eight 16-byte
+// loads per lane in flight, which a warp sustains up to 32 KB; a CTA needs 64 KB rows for the same.
 __host__ __device__ constexpr int64_t group_row_bytes(int dtype, bool moments) {
-  return (!moments && (dtype == SB_F32 || dtype == SB_BF16 || dtype == SB_F16)) ? 32768 : 8192;
+  (void)moments;
+  return (dtype == SB_F32 || dtype == SB_BF16 || dtype == SB_F16) ? 32768 : 8192;
 }
 
 template <class Op>
 int launch_ext(ExtParams p, cudaStream_t st) {
-  if (p.inner == 1 && p.L * static_cast<int64_t>(dtype_size(p.in_dtype)) <= group_row_bytes(p.in_dtype, std::is_same<Op, MomentOp>::value)) {
+  if (p.inner == 1 && p.L * static_cast<int64_t>(dtype_size(p.in_dtype)) <= group_row_bytes(p.in_dtype, Op::kMoments)) {
     const int64_t es = static_cast<int64_t>(dtype_size(p.in_dtype));
     const bool vec = p.L % 4 == 0 && reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es * 4 < 16 ? es * 4 : 16) == 0;
     const bool vec8 = es == 2 && p.L % 8 == 0 && reinterpret_cast<uintptr_t>(p.in) % 16 == 0;  // 16-byte loads of 16-bit elements
@@ -484,7 +506,7 @@ int launch_ext(ExtParams p, cudaStream_t st) {
     int lpr = 1;
     while (lpr < 32 && lpr * 2 <= units) lpr <<= 1;  // at least one load per lane, two where the row has them
     if (lpr > 1 && lpr * 2 > units) lpr >>= 1;
-    const bool deep = !std::is_same<Op, MomentOp>::value && (vec8 || (vec && es == 4)) &&
+    const bool deep = std::is_same<typename Op::Acc, float>::value && (vec8 || (vec && es == 4)) &&
                       (p.in_dtype == SB_F32 || p.in_dtype == SB_BF16 || p.in_dtype == SB_F16);
     if (deep) {  // 16-byte vectors and an fp32 state: eight vectors of the row per lane
       lpr = 1;
@@ -502,8 +524,8 @@ int launch_ext(ExtParams p, cudaStream_t st) {
   if (p.inner == 1) {
     // four elements per load when every row and every segment starts on the boundary such a load needs
     const int64_t es4 = static_cast<int64_t>(dtype_size(p.in_dtype)) * 4;
-    // (not for the moments: with their fp64 state the vector form measured slower, 0.51 against 0.78 on fp32 rows of 32000)
-    const bool vec4 = !std::is_same<Op, MomentOp>::value && p.L % 4 == 0 && p.seg % 4 == 0 &&
+    // (not for the moments of fp64 inputs: with an fp64 operation per element the vector form measured slower)
+    const bool vec4 = (!Op::kMoments || std::is_same<typename Op::Acc, float>::value) && p.L % 4 == 0 && p.seg % 4 == 0 &&
                       reinterpret_cast<uintptr_t>(p.in) % static_cast<uintptr_t>(es4 < 16 ? es4 : 16) == 0;
     const bool vec8 = vec4 && dtype_size(p.in_dtype) == 2 && p.L % 8 == 0 && p.seg % 8 == 0 && reinterpret_cast<uintptr_t>(p.in) % 16 == 0;
     if (p.outer > 65535) {  // gridDim.y limit: treat the rows as columns of an [1, L, outer]-like walk is wrong; fold in slabs
@@ -513,7 +535,7 @@ int launch_ext(ExtParams p, cudaStream_t st) {
         q.outer = n;
         q.in = static_cast<const char*>(p.in) + r0 * p.L * dtype_size(p.in_dtype);
         if (p.out0) q.out0 = static_cast<char*>(p.out0) + r0 * dtype_size(p.out_dtype);
-        if (p.out1) q.out1 = static_cast<char*>(p.out1) + r0 * (std::is_same<Op, MomentOp>::value ? dtype_size(p.out_dtype) : 8);
+        if (p.out1) q.out1 = static_cast<char*>(p.out1) + r0 * (Op::kMoments ? dtype_size(p.out_dtype) : 8);
         q.nseg = 1;
         q.seg = q.L;
         if (vec8) ext_rows_kernel<Op, 256, 8><<<dim3(1, static_cast<unsigned>(n)), 256, 0, st>>>(q);
@@ -656,7 +678,8 @@ int sb_moments(const void* in, int32_t dtype, int64_t outer, int64_t L, int64_t 
   p.out_dtype = dtype;
   p.correction = correction;
   p.take_sqrt = take_sqrt;
-  return launch_ext<MomentOp>(p, as_stream(stream));
+  if (dtype == SB_F64) return launch_ext<MomentOpT<double>>(p, as_stream(stream));
+  return launch_ext<MomentOpT<float>>(p, as_stream(stream));
 }
 
 }  // extern "C"
