@@ -456,7 +456,8 @@ SB_API int sb_reduce_path(const sb_reduce_desc* desc);
  * `values` (in `dtype`) and `indices` (int64) have outer * inner elements; either may be NULL.  Bit-exact.
  *
  * sb_moments: variance or standard deviation with the given correction (M2 / max(0, L - correction)), and optionally
- * the mean, in `dtype` (torch_supa/csrc/aten/ops/StdVar.cpp:34-63).  Accumulated in fp64.
+ * the mean, in `dtype` (torch_supa/csrc/aten/ops/StdVar.cpp:34-63).  The running sums are fp64; over rows of fp32 / bf16 /
+ * fp16 values the sums of up to eight neighbouring terms are formed in fp32 first.
  *
  * scratch: sb_reduce_ext_scratch_bytes(...) bytes, 8-byte aligned, needed when few long rows are cut into segments
  * or the rows of a column reduction (inner > 1) into chunks (the call returns 0 otherwise).
