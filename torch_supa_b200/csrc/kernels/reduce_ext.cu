@@ -13,6 +13,7 @@
 // lowest index wins; NaN beats every number for max AND for min, and of several NaN the first.  Variance follows
 // var(correction): M2 / max(0, n - correction), accumulated in fp64 as shifted sums (shift = the row's first element;
 // over rows of fp32 / bf16 / fp16 values the sums of up to eight neighbouring terms are formed in fp32 first).
+#include <limits>
 #include <type_traits>
 
 #include "io.cuh"
@@ -31,6 +32,7 @@ struct ExtParams {
   int nseg;
   void* scratch;   // rows path with nseg > 1: nseg partial states per row
   double correction;
+  double inv_n, inv_denom;  // moments: 1 / L and 1 / max(0, L - correction) (inf when that is zero), formed on the host
   int take_sqrt;
 };
 
@@ -184,16 +186,16 @@ template <typename A> struct MomentOpT {
     return State{__shfl_down_sync(0xffffffffu, s.s1, o), __shfl_down_sync(0xffffffffu, s.s2, o), s.shift};
   }
   __device__ static __forceinline__ void finish(const ExtParams& p, const State& s, int64_t out_index) {
-    const double n = static_cast<double>(p.L);
-    double m2 = s.s2 - s.s1 * s.s1 / n;
+    // products with the reciprocals instead of three fp64 divisions per output (the last bit of the fp64 value may
+    // differ from the quotient's; it is rounded to the output type afterwards)
+    double m2 = s.s2 - s.s1 * s.s1 * p.inv_n;
     if (m2 < 0.0) m2 = 0.0;  // rounding of a constant row
-    const double denom = fmax(0.0, n - p.correction);
-    double v = m2 / denom;   // n <= correction: inf or NaN, as on the CPU
+    double v = m2 * p.inv_denom;   // L <= correction: the reciprocal is inf, so inf or NaN, as on the CPU
     if (p.take_sqrt) v = sqrt(v);
     double o[1] = {v};
     DynamicIO::store<double, 1>(p.out0, out_index, p.out_dtype, o);
     if (p.out1) {
-      double mean[1] = {s.shift + s.s1 / n};
+      double mean[1] = {s.shift + s.s1 * p.inv_n};
       DynamicIO::store<double, 1>(p.out1, out_index, p.out_dtype, mean);
     }
   }
@@ -677,6 +679,11 @@ int sb_moments(const void* in, int32_t dtype, int64_t outer, int64_t L, int64_t 
   p.out1 = mean_out;
   p.out_dtype = dtype;
   p.correction = correction;
+  p.inv_n = 1.0 / static_cast<double>(L);
+  {
+    const double denom = static_cast<double>(L) - correction;
+    p.inv_denom = denom > 0.0 ? 1.0 / denom : std::numeric_limits<double>::infinity();
+  }
   p.take_sqrt = take_sqrt;
   if (dtype == SB_F64) return launch_ext<MomentOpT<double>>(p, as_stream(stream));
   return launch_ext<MomentOpT<float>>(p, as_stream(stream));
