@@ -291,3 +291,52 @@ def test_two_process_group_with_supa_backend_beside_gloo(tmp_path):
     out = tmp_path / "ok.txt"
     mp.spawn(_c10d_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     assert float(out.read_text()) == 2.0
+
+
+# ---- reduction planning (host side of sb_reduce / sb_arg_reduce / sb_moments; no kernel is launched) -----------------
+def _reduce_desc(sizes, in_strides, out_strides, dtype):
+    from torch_supa_b200 import capi
+
+    d = capi.ReduceDesc()
+    d.op = capi.RED_SUM
+    d.ndim = len(sizes)
+    for i, (n, si, so) in enumerate(zip(sizes, in_strides, out_strides)):
+        d.sizes[i], d.in_strides[i], d.out_strides[i] = n, si, so
+    d.in_dtype = d.out_dtype = dtype
+    d.in_, d.out = 0x7F0000000000, 0x7F0100000000  # never dereferenced by the planner
+    return d
+
+
+def test_reduce_plan_does_not_depend_on_the_order_of_the_dimensions():
+    from torch_supa_b200 import capi
+
+    # x[5000, 96].sum(0): in stride order (columns first) and as a TensorIterator lists it (the reduced dimension first)
+    a = _reduce_desc([96, 5000], [1, 96], [1, 0], capi.F32)
+    b = _reduce_desc([5000, 96], [96, 1], [0, 1], capi.F32)
+    assert capi.reduce_path(a) == capi.reduce_path(b) == 2
+    assert capi.reduce_scratch_bytes(a) == capi.reduce_scratch_bytes(b) > 0
+    # x[5000, 96].sum(1): rows
+    c = _reduce_desc([96, 5000], [1, 96], [0, 1], capi.F32)
+    e = _reduce_desc([5000, 96], [96, 1], [1, 0], capi.F32)
+    assert capi.reduce_path(c) == capi.reduce_path(e) == 0
+    assert capi.reduce_scratch_bytes(c) == capi.reduce_scratch_bytes(e) == 0
+    # a middle dimension of [7, 3000, 96], listed in three orders
+    orders = [([96, 3000, 7], [1, 96, 288000], [1, 0, 96]), ([3000, 96, 7], [96, 1, 288000], [0, 1, 96]),
+              ([7, 3000, 96], [288000, 96, 1], [96, 0, 1])]
+    plans = {(capi.reduce_path(_reduce_desc(*o, capi.BF16)), capi.reduce_scratch_bytes(_reduce_desc(*o, capi.BF16))) for o in orders}
+    assert len(plans) == 1 and next(iter(plans))[0] == 2
+    # an expanded (stride 0) kept dimension does not take the row path away from x.sum(-1)
+    f = _reduce_desc([3, 64, 1000], [0, 1, 64], [1000, 0, 1], capi.F32)
+    assert capi.reduce_path(f) == 0
+
+
+def test_few_long_rows_and_tall_columns_ask_for_scratch():
+    from torch_supa_b200 import capi
+
+    few_long = _reduce_desc([1 << 21, 4], [1, 1 << 21], [0, 1], capi.F32)
+    assert capi.reduce_path(few_long) == 1 and capi.reduce_scratch_bytes(few_long) > 0
+    assert capi.reduce_ext_scratch_bytes(capi.F32, 4, 1 << 21, 1, False) > 0       # argmax of four long rows: segments
+    assert capi.reduce_ext_scratch_bytes(capi.F32, 100000, 64, 1, False) == 0      # short rows: a lane group each
+    assert capi.reduce_ext_scratch_bytes(capi.F32, 1, 100000, 64, True) > 0        # var(0) of a tall matrix: row chunks
+    assert capi.reduce_ext_scratch_bytes(capi.F32, 1, 32, 64, True) == 0           # too few rows to cut
+    assert capi.reduce_ext_scratch_bytes(capi.F32, 70000, 100000, 3, False) == 0   # more outer slices than grid.z takes
