@@ -1,13 +1,21 @@
 // Reductions sum / mean / amax / amin / prod / nansum over any set of dimensions.
 //
-// Path 0  rows       the reduced run is contiguous (unit input stride on dimension 0) and every other
-//                    dimension is kept: one CTA (long rows) or one warp (short rows) per output,
-//                    16-byte loads, 8 independent accumulators per thread, shuffle + shared-memory tree.
+// The dimensions of the descriptor may come in any order; they are sorted by input stride, then neighbours that walk
+// memory as one dimension are merged.
+//
+// Path 0  rows       the reduced run is contiguous (unit input stride) and every other dimension is kept.  Rows of
+//                    whole 16-byte vectors of fp32 / bf16 / fp16: up to 4 KB a group of lanes per row, eight
+//                    vectors in flight per lane (several rows where a row has fewer), the groups' sums added
+//                    crosswise when the row is a power of two of vectors; up to 8 KB a warp per row; longer rows
+//                    and all other types: one CTA (long rows) or one warp (short rows) per output, 16-byte
+//                    loads where the pitch allows, shuffle + shared-memory tree.
 // Path 1  split rows same layout but too few outputs to fill the GPU: each row is cut into segments,
 //                    one CTA per segment writes a partial into caller-provided scratch, a second
 //                    kernel folds the partials in a fixed order (no atomics: bit-reproducible).
-// Path 2  columns    dimension 0 is kept with unit strides and dimension 1 is reduced: threads run along
-//                    the kept dimension so that loads stay coalesced.
+// Path 2  columns    the fastest dimension is kept with unit strides and one dimension is reduced: lanes run along
+//                    the kept dimension (16-byte column vectors where the pitch allows), the reduced rows are cut
+//                    into chunks over the grid so that a tall narrow input fills the GPU, the chunks' partial
+//                    results go to scratch and a second kernel adds them, a warp per output.
 // Path 3  generic    one thread per output walking the reduced index space.
 //
 // Accumulation type: fp32 for fp32/bf16/fp16, fp64 for fp64, int64 for integer and bool inputs.
